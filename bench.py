@@ -1,0 +1,367 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 decode GEMV path (BASELINE.json metric: achieved HBM GB/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (BASELINE configs[1] at M=1): the four decode GEMV shapes
+(K,N) in {(4096,6144),(4096,4096),(4096,28672),(14336,4096)}, x bf16 ~ N(0,1), weights bf16 ~ N(0,0.02)
+quantized to NVFP4 (global 448*6/amax).  One step = one pass over `copies` distinct weight sets of
+all four shapes, so a step streams ~1 GB of weights (far larger than the 126 MB L2: every launch
+reads cold weights).  value = algorithmic bytes of the step / device time, where
+bytes(M,N,K) = N*K/2 + N*K/16 + 2*M*K + 2*M*N + 4.
+
+At N > 1 the same matrices are sharded tensor-parallel over the ranks (strong scaling): the three
+K=4096 shapes column-parallel (rows split, all-gather of y), the K=14336 shape row-parallel (K
+split, all-reduce of the partial y), one process per GPU over NCCL.
+
+`--impl reference` times the reference's CPU path for the same linears (weights dequantized to
+bf16 once, then bf16 x bf16 -> f32 -> bf16, all host cores) through the CPU oracle.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+SHAPES_KN = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]  # (K, N)
+ROW_PARALLEL = {(14336, 4096)}  # split along K at N > 1; the others split along N
+COPIES = 8
+METRIC = "nvfp4_decode_gemv_hbm_gbs"
+
+
+def algo_bytes(m: int, n: int, k: int) -> int:
+    return n * k // 2 + n * k // 16 + 2 * m * k + 2 * m * n + 4
+
+
+def step_bytes(copies: int) -> int:
+    return copies * sum(algo_bytes(1, n, k) for k, n in SHAPES_KN)
+
+
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_b200(args) -> dict:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import speaches_plus_b200 as sp
+    from speaches_plus_b200 import tp as tpmod
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sp.ffi.lib()
+
+    # ---- synthetic weights: seeded, identical on every rank, then sharded ----
+    copies = COPIES
+    layers = []  # (K, N, [TpLinear per copy])
+    for si, (k, n) in enumerate(SHAPES_KN):
+        mode = "row" if (k, n) in ROW_PARALLEL else "column"
+        per_copy = []
+        for c in range(copies):
+            gen = torch.Generator(device=dev).manual_seed(1000 * si + c)
+            w = (torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            per_copy.append(tpmod.TpNvfp4Linear.from_bf16(w, mode, rank, world))
+            del w
+        layers.append((k, n, per_copy))
+    gen = torch.Generator(device=dev).manual_seed(7)
+    xs = {k: torch.randn((1, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+          for k in {k for k, _ in SHAPES_KN}}
+    torch.cuda.synchronize()
+
+    def one_step():
+        for k, n, per_copy in layers:
+            x = xs[k]
+            for lin in per_copy:
+                lin.forward(x)
+
+    launches_per_step = copies * len(SHAPES_KN)
+
+    # ---- device-resident timing: the step captured once as a CUDA graph ----
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            one_step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_step()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+        ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    total_bytes = step_bytes(copies)
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-shape breakdown (each shape's copies timed as their own region) ----
+    per_shape = {}
+    with torch.cuda.stream(stream):
+        for k, n, per_copy in layers:
+            reps = 20
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            # interleave with the other shapes' weights between repetitions to keep L2 cold
+            times = []
+            for _ in range(reps):
+                for kk, nn, pc in layers:
+                    if (kk, nn) != (k, n):
+                        pc[0].forward(xs[kk])
+                a.record(stream)
+                for lin in per_copy:
+                    lin.forward(xs[k])
+                b.record(stream)
+                stream.synchronize()
+                times.append(a.elapsed_time(b) / len(per_copy))
+            us = statistics.median(times) * 1e3
+            per_shape[f"K{k}_N{n}"] = {"us_per_launch_eager": round(us, 3),
+                                        "gbs": round(algo_bytes(1, n, k) / (us * 1e-6) / 1e9, 1)}
+
+    # ---- end to end through the public API with host buffers ----
+    pin_x = {k: torch.randn((1, k), dtype=torch.float32).to(torch.bfloat16).pin_memory() for k in xs}
+    pin_y = {(k, n): torch.empty((1, n), dtype=torch.bfloat16).pin_memory() for k, n in SHAPES_KN}
+    dx = {k: torch.empty((1, k), dtype=torch.bfloat16, device=dev) for k in xs}
+    h2d = launches_per_step and sum(2 * k for k, n in SHAPES_KN) * copies
+    d2h = sum(2 * n for k, n in SHAPES_KN) * copies
+
+    def e2e_step():
+        for k, n, per_copy in layers:
+            for lin in per_copy:
+                dx[k].copy_(pin_x[k], non_blocking=True)
+                y = lin.forward(dx[k])
+                pin_y[(k, n)].copy_(y, non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            e2e_step()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_steps = max(3, min(args.steps, 20))
+        a.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record(stream)
+        stream.synchronize()
+        e2e_ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = total_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
+
+    out = None
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        peak, peak_src = 6650.0, "fallback"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+            peak, peak_src = float(peaks["hbm_gbs"]), "measured"
+        per_gpu_gbs = value / world
+        out = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "e2m1*ue4m3 x bf16 -> f32",
+            "data": "synthetic",
+            "config": {"workload": "configs[1] NVFP4 GEMV shape sweep, M=1", "shapes_KN": SHAPES_KN,
+                       "weight_copies_per_shape": copies, "launches_per_step": launches_per_step,
+                       "parallelism": f"tp{world}" if world > 1 else "single",
+                       "l2": f"inputs larger than L2: {total_bytes / 1e6:.0f} MB of cold weights per step",
+                       "timing": "CUDA events around K replays of a CUDA graph of one step"},
+            "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "path": "Nvfp4Linear.forward per GEMV: pinned x -> device, launch, y -> pinned host"},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu_gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(per_gpu_gbs / peak, 4), "peak_source": peak_src,
+                         "frac_of_nominal_8TBs": round(per_gpu_gbs / 8000.0, 4), "traffic": None,
+                         "kernel": "w4a16_mma_kernel", "bytes_per_launch_avg": total_bytes // launches_per_step,
+                         "us_per_launch_avg": round(ms_per_step * 1e3 / launches_per_step, 3)},
+            "per_shape": per_shape,
+            "clocks": clocks,
+        }
+        if args.cpu_baseline:
+            out["cpu_baseline"] = cpu_reference_leg(passes=3, warm=1)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+_CPU_CACHE = {}
+
+
+def _cpu_weights():
+    """bf16 weights of the four shapes as the reference's Cpu backend holds them: quantized to NVFP4,
+    then dequantized to bf16 (done once, not timed)."""
+    import numpy as np
+
+    from oracle import ref
+    if "w" not in _CPU_CACHE:
+        ws = []
+        for si, (k, n) in enumerate(SHAPES_KN):
+            rng = np.random.default_rng(1000 * si)
+            w = ref.f32_to_bf16((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)))
+            packed, sw, alpha = ref.quantize_weight_bf16(w)
+            ws.append((k, n, ref.dequantize_to_bf16(packed, sw, n, k, alpha)))
+        rng = np.random.default_rng(7)
+        xs = {k: ref.f32_to_bf16(rng.standard_normal((1, k), dtype=np.float32)) for k, _ in SHAPES_KN}
+        _CPU_CACHE["w"] = (ws, xs)
+    return _CPU_CACHE["w"]
+
+
+def cpu_pass() -> float:
+    """One pass over the four shapes on the host cores; returns seconds."""
+    from oracle import ref
+    ws, xs = _cpu_weights()
+    t0 = time.perf_counter()
+    for k, n, w in ws:
+        ref.linear_cpu_backend(w, xs[k], threads=0)
+    return time.perf_counter() - t0
+
+
+def cpu_reference_leg(passes: int, warm: int) -> dict:
+    from oracle import ref
+    for _ in range(warm):
+        cpu_pass()
+    ts = [cpu_pass() for _ in range(passes)]
+    t = statistics.median(ts)
+    b = sum(algo_bytes(1, n, k) for k, n in SHAPES_KN)
+    return {"value": round(b / t / 1e9, 3), "unit": "GB/s", "cores": ref.num_threads(), "kind": "port",
+            "sample": f"one weight set of each of the 4 shapes (M=1), median of {passes} passes; weights "
+                      "dequantized to bf16 beforehand (untimed), as the reference's Cpu backend holds them",
+            "ms_per_pass": round(t * 1e3, 2)}
+
+
+def run_reference(args) -> dict | None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle import ref
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
+        cpu_pass()
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_pass()
+    dt = (time.perf_counter() - t0) / steps
+    b = sum(algo_bytes(1, n, k) for k, n in SHAPES_KN)
+    v = round(b / dt / 1e9, 3)
+    sample = ("each step = one weight set of each of the 4 shapes at M=1 (1/%d of the B200 arm's step), CPU oracle "
+              "port of the reference's Cpu-backend linear, all host threads" % COPIES)
+    return {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": warm, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16 x bf16 -> f32",
+            "data": "synthetic",
+            "config": {"workload": "configs[1] NVFP4 GEMV shape sweep, M=1", "shapes_KN": SHAPES_KN,
+                       "weight_copies_per_shape": 1, "parallelism": "host cores"},
+            "cpu_baseline": {"value": v, "unit": "GB/s", "cores": ref.num_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        out = run_reference(args)
+    else:
+        if args.gpus > 1:
+            args.cpu_baseline = False
+        out = run_b200(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

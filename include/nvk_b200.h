@@ -1,0 +1,197 @@
+/*
+ * libnvk_b200 -- C ABI of the B200 (sm_100a) NVFP4 linear path.
+ *
+ * Drop-in boundary: every `nv_kernels_*` symbol below has the name, argument order, argument
+ * meaning and return convention of the declaration it replaces in the reference project's
+ * hand-written kernel header (rust/crates/nv-kernels/include/nv_kernels.h, cited per symbol),
+ * which the reference binds with bindgen and re-exports 1:1 as `nv_kernels::cuda::<name>`.
+ * `nvk_b200_*` symbols are additions with no counterpart there.
+ *
+ * Conventions (as in the reference):
+ *   - `stream` is a cudaStream_t / CUstream passed as void*; every call only enqueues work on it,
+ *     never synchronises and never allocates device memory.
+ *   - bf16 tensors are uint16_t*, packed e2m1 (two values per byte, even k in the low nibble)
+ *     and ue4m3 block scales are uint8_t*; all pointers are device pointers owned by the caller.
+ *   - Weight matrices are row-major [N, K/2] bytes; their block scales use the 128x4 swizzled
+ *     layout, ceil(N/128)*128 * ceil(K/64)*4 bytes: scale of (row n, block kb) sits at
+ *       ((n/128 * ceil(K/64) + kb/4) * 32 + n%32) * 16 + ((n/32)%4) * 4 + kb%4.
+ *   - Return value: 0 = enqueued (or an empty problem); -1 = shape/route refused, nothing
+ *     launched; -2 = bad argument or alignment; -3 = resource limit; -9 = grid axis too large;
+ *     a positive value is a cudaError_t.
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* replaces rust/crates/nv-kernels/include/nv_kernels.h:11 */
+int nv_kernels_capability(int* sm_major, int* sm_minor);
+
+/* ---- W4A16 linear: y = bf16(alpha * x W^T), fp32 accumulate ---------------------------------- */
+
+/* M = 1.  Refuses K % 16 != 0 with -1; N <= 0 or K <= 0 is a no-op returning 0.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:534-543
+ * (kernel: rust/crates/nv-kernels/cuda/gemv_nvfp4.cu:224-312) */
+int nv_kernels_nvfp4_gemv_bf16act(void* stream, const uint8_t* W_packed, const uint8_t* W_scales,
+                                  const uint16_t* x_bf16, uint16_t* y, float alpha, int N, int K);
+
+/* M = 1, two weight matrices sharing one x (gate + up); wq_b == sc_b == y_b == NULL runs one arm.
+ * Refuses K % 32 != 0, N <= 0, K <= 0 or a half-null second arm with -1.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:584-597
+ * (rust/crates/nv-kernels/cuda/gemv_nvfp4_w4a16_decode.cu:111-150,186-220) */
+int nv_kernels_gemv_nvfp4_w4a16_dual_m1(void* stream, const uint8_t* wq_a, const uint8_t* sc_a,
+                                        const uint8_t* wq_b, const uint8_t* sc_b, const uint16_t* x,
+                                        uint16_t* y_a, uint16_t* y_b, float alpha_a, float alpha_b, int N,
+                                        int K);
+
+/* M = 1 down projection whose activation is bf16(SiLU(gate) * up), computed in fp32 and rounded
+ * to bf16 before the contraction.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:615-625
+ * (rust/crates/nv-kernels/cuda/gemv_nvfp4_w4a16_decode.cu:152-182,222-251) */
+int nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1(void* stream, const uint8_t* wq, const uint8_t* sc,
+                                                   const uint16_t* gate, const uint16_t* up, uint16_t* y,
+                                                   float alpha, int N, int K);
+
+/* 1 <= M <= 16, x is [M, K], y is [M, N]; optional second arm.  Refuses M > 16, K % 32 != 0 and
+ * N % 32 != 0 with -1, as the reference does.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:599-613
+ * (rust/crates/nv-kernels/cuda/gemm_nvfp4_w4a16_mk_mma.cu:57-231,290-326) */
+int nv_kernels_gemm_nvfp4_w4a16_mk_dual(void* stream, const uint8_t* wq_a, const uint8_t* sc_a,
+                                        const uint8_t* wq_b, const uint8_t* sc_b, const uint16_t* x,
+                                        uint16_t* y_a, uint16_t* y_b, float alpha_a, float alpha_b, int M, int N,
+                                        int K);
+
+/* No counterpart in the reference: the same contraction for 1 <= M <= 64, any N, K % 16 == 0,
+ * optional second arm, optional SiLU prologue (x = gate, x2 = up; x2 == NULL for a plain x). */
+int nvk_b200_linear_nvfp4_w4a16(void* stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
+                                const uint8_t* sc_b, const uint16_t* x, const uint16_t* x2, uint16_t* y_a,
+                                uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K);
+
+/* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
+ * how many CTAs of a cluster share one row tile's K range. */
+int nvk_b200_set_tuning(int force_ksplit);
+
+/* bf16 weights, M = 1 (lm_head): y[n] = bf16(sum_k W[n,k] x[k]).
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:116-123
+ * (rust/crates/nv-kernels/cuda/gemv_bf16.cu:22-76,467-533) */
+int nv_kernels_gemv_bf16(void* stream, const uint16_t* W, const uint16_t* x, uint16_t* y, int N, int K);
+
+/* ---- bf16 -> NVFP4 quantizers (byte-exact with nv_quant::nvfp4::quantize_block_with_global,
+ *      rust/crates/nv-quant/src/nvfp4.rs:91-129) -------------------------------------------------- */
+
+/* Rows [m_logical, m_padded) quantize zeros.  -2 if m_logical is outside [0, m_padded].
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1370-1379
+ * (rust/crates/nv-kernels/cuda/quantize_nvfp4_bf16.cu:73-120,352-377) */
+int nv_kernels_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16, uint8_t* packed_out,
+                                   uint8_t* scales_out_swizzled, float stored_global, int m_padded,
+                                   int m_logical, int K);
+
+/* replaces rust/crates/nv-kernels/include/nv_kernels.h:1381-1389 (quantize_nvfp4_bf16.cu:327-350) */
+int nv_kernels_quantize_nvfp4_bf16_rows(void* stream, const uint16_t* x_bf16, uint8_t* packed_out,
+                                        uint8_t* scales_out_swizzled, float stored_global, int m_rows, int K);
+
+/* One row, scales written linearly ([K/16]).
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:525-532
+ * (rust/crates/nv-kernels/cuda/gemv_nvfp4.cu:79-120,181-199) */
+int nv_kernels_nvfp4_quantize_row_bf16(void* stream, const uint16_t* x, uint8_t* packed_out, uint8_t* scales_out,
+                                       float stored_global, int K);
+
+/* Stored global of row r is stored_globals[r / m_per_expert] (device array).  The `_strided`
+ * forms touch only row 0 of every m_per_expert-row tile and return -3 unless
+ * m_total % m_per_expert == 0.
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:1348-1368
+ * (rust/crates/nv-kernels/cuda/quantize_nvfp4_bf16.cu:122-170,277-325) */
+int nv_kernels_quantize_nvfp4_bf16_per_expert(void* stream, const uint16_t* x_bf16, uint8_t* packed_out,
+                                              uint8_t* scales_out_swizzled, const float* stored_globals,
+                                              int m_per_expert, int m_total, int K);
+int nv_kernels_quantize_nvfp4_bf16_per_expert_strided(void* stream, const uint16_t* x_bf16, uint8_t* packed_out,
+                                                      uint8_t* scales_out_swizzled, const float* stored_globals,
+                                                      int m_per_expert, int m_total, int K);
+
+/* Quantizes SiLU(gate) * up evaluated in fp32 (no bf16 rounding in between).
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:1324-1346
+ * (rust/crates/nv-kernels/cuda/quantize_nvfp4_bf16.cu:172-275) */
+int nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert(void* stream, const uint16_t* y_gate_bf16,
+                                                       const uint16_t* y_up_bf16, uint8_t* packed_out,
+                                                       uint8_t* scales_out_swizzled, const float* stored_globals,
+                                                       int m_per_expert, int m_total, int K);
+int nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert_strided(void* stream, const uint16_t* y_gate_bf16,
+                                                               const uint16_t* y_up_bf16, uint8_t* packed_out,
+                                                               uint8_t* scales_out_swizzled,
+                                                               const float* stored_globals, int m_per_expert,
+                                                               int m_total, int K);
+
+/* RMSNorm fused in front of the quantizer; the row is staged in shared memory (K * 2 bytes), and
+ * K * 2 > 48 KiB is refused with -3.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1391-1402
+ * (rust/crates/nv-kernels/cuda/rmsnorm_quantize_nvfp4_bf16.cu:92-197) */
+int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16, const uint16_t* weight_bf16,
+                                           uint8_t* packed_out, uint8_t* scales_out_swizzled, float stored_global,
+                                           float eps, int m_padded, int m_logical, int K);
+
+/* ---- MoE decode ------------------------------------------------------------------------------ */
+
+/* mode 0: top-K of the (optionally tanh soft-capped) logits, softmax over the K winners;
+ * mode 1: sigmoid scores, selection on score + bias, optional renormalisation.  Ties go to the
+ * lower expert id; weights are multiplied by routed_scaling.  -2 if E > 4096, K > 32 or K > E.
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:1538-1567
+ * (rust/crates/nv-kernels/cuda/moe_route.cu:75-329) */
+int nv_kernels_moe_route_topk(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
+                              float* topk_weights, int n_tokens, int E, int K, int mode, float softcap,
+                              int norm_topk, float routed_scaling);
+int nv_kernels_moe_route_topk_shared_tail(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
+                                          float* topk_weights, int n_tokens, int E, int K, int mode, float softcap,
+                                          int norm_topk, float routed_scaling, int shared_tail_id);
+
+/* out[r, :] = x[src_idx[r], :], a zero row when src_idx[r] is outside [0, n_tokens).  The strided
+ * form touches rows 0, row_stride, 2*row_stride, ...
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:1433-1452 (cuda/gather_rows_bf16.cu) */
+int nv_kernels_gather_rows_bf16(void* stream, const uint16_t* x_bf16, const int32_t* src_idx, uint16_t* out_bf16,
+                                int m_total_padded, int hidden, int n_tokens);
+int nv_kernels_gather_rows_bf16_strided(void* stream, const uint16_t* x_bf16, const int32_t* src_idx,
+                                        uint16_t* out_bf16, int m_total_padded, int hidden, int n_tokens,
+                                        int row_stride);
+
+/* dst[i] = ids[i] >= 0 ? src[ids[i]] : 0.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1593-1599 (cuda/moe_route.cu:536-561) */
+int nv_kernels_gather_f32_by_ids(void* stream, const float* src, const int32_t* ids, float* dst, int n);
+
+/* y_acc[n,h] = sum_s w[n,s] * y_sorted[inv_perm[n,s], h] in fp32, s ascending.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1526-1536 (cuda/moe_unpermute_scatter.cu:6-32) */
+int nv_kernels_moe_unpermute_scatter(void* stream, const uint16_t* y_sorted_bf16, const float* topk_weights,
+                                     const int32_t* inv_perm, float* y_acc_f32, int n_tokens, int k, int hidden,
+                                     int y_sorted_row_stride);
+
+/* out = bf16(resid + bf16(combine + shared)).
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1454-1466 (cuda/moe_unpermute_scatter.cu:34-64) */
+int nv_kernels_moe_unpermute_scatter_tail(void* stream, const uint16_t* y_sorted_bf16, const float* topk_weights,
+                                          const int32_t* inv_perm, const float* shared_f32,
+                                          const uint16_t* resid_bf16, uint16_t* out_bf16, int n_tokens, int k,
+                                          int hidden, int y_sorted_row_stride);
+
+/* Sort the n_tokens*k routed slots by expert: expert_offsets[E+1], permuted_token_idx[pos] = token,
+ * inv_perm[slot] = pos.  Slots of one expert keep their original order (the reference leaves that
+ * order to atomics).  scratch_counts is E int32 of caller scratch.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1601-1611 (cuda/moe_permute.cu) */
+int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permuted_token_idx,
+                           int32_t* expert_offsets, int32_t* inv_perm, int32_t* scratch_counts, int n_tokens, int k,
+                           int num_experts);
+
+/* Grouped M=1 expert GEMV with NVFP4 weights AND NVFP4 activations: group g multiplies row 0 of its
+ * a_tile_stride_rows-row activation tile by expert group_expert_ids[g]; an id outside
+ * [0, num_experts_total) writes zeros.  -1 on bad shapes, -2 unless a_packed/b_packed are 8-byte
+ * aligned, -9 if num_groups > 65535.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1020-1035
+ * (rust/crates/nv-kernels/cuda/moe_grouped_fp4_gemv.cu:77-180) */
+int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packed, const uint8_t* a_scales,
+                                            const uint8_t* b_packed, const uint8_t* b_scales, const float* alphas,
+                                            uint16_t* d_bf16, const int32_t* group_expert_ids, int num_groups,
+                                            int num_experts_total, int n, int k, int a_tile_stride_rows,
+                                            long long d_group_stride_elems);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,92 @@
+"""ctypes binding of libnvk_b200.so: one Python function per C symbol of include/nvk_b200.h.
+
+Pointers are passed as integers (`tensor.data_ptr()`), the stream as the integer value of a
+cudaStream_t.  Nothing here computes: a missing library or symbol raises at import/first use.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+
+_HERE = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libnvk_b200.so"
+
+_vp, _i, _f, _ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
+
+# name -> argument types (every function returns int)
+SIGNATURES = {
+    "nv_kernels_capability": [_vp, _vp],
+    "nv_kernels_nvfp4_gemv_bf16act": [_vp, _vp, _vp, _vp, _vp, _f, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a16_dual_m1": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1": [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i],
+    "nv_kernels_gemm_nvfp4_w4a16_mk_dual": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
+    "nvk_b200_linear_nvfp4_w4a16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
+    "nvk_b200_set_tuning": [_i],
+    "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
+    "nv_kernels_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _f, _i, _i, _i],
+    "nv_kernels_quantize_nvfp4_bf16_rows": [_vp, _vp, _vp, _vp, _f, _i, _i],
+    "nv_kernels_nvfp4_quantize_row_bf16": [_vp, _vp, _vp, _vp, _f, _i],
+    "nv_kernels_quantize_nvfp4_bf16_per_expert": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_quantize_nvfp4_bf16_per_expert_strided": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert_strided": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_rmsnorm_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
+    "nv_kernels_moe_route_topk": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _f],
+    "nv_kernels_moe_route_topk_shared_tail": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _f, _i],
+    "nv_kernels_gather_rows_bf16": [_vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_gather_rows_bf16_strided": [_vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "nv_kernels_gather_f32_by_ids": [_vp, _vp, _vp, _vp, _i],
+    "nv_kernels_moe_unpermute_scatter": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "nv_kernels_moe_unpermute_scatter_tail": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "nv_kernels_moe_permute": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_moe_grouped_fp4_gemv_m1_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll],
+}
+
+_lib = None
+
+
+class NvkError(RuntimeError):
+    """A launcher returned a non-zero status."""
+
+    def __init__(self, name: str, rc: int):
+        self.name, self.rc = name, rc
+        kind = {-1: "shape/route refused", -2: "bad argument or alignment", -3: "resource limit",
+                -9: "grid axis too large"}.get(rc, "cudaError_t" if rc > 0 else "error")
+        super().__init__(f"{name} returned {rc} ({kind})")
+
+
+def lib() -> C.CDLL:
+    """Load the CUDA library.  There is no fallback: a missing build is an error."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python speaches-plus_b200/build.py` "
+                "(this package has no CPU or PyTorch fallback)")
+        L = C.CDLL(str(LIB_PATH))
+        for name, args in SIGNATURES.items():
+            fn = getattr(L, name)  # AttributeError if a declared symbol is not exported
+            fn.argtypes = args
+            fn.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def call(name: str, *args) -> int:
+    """Call a launcher and return its raw status."""
+    return int(getattr(lib(), name)(*args))
+
+
+def check(name: str, *args) -> None:
+    """Call a launcher; raise NvkError on a non-zero status."""
+    rc = call(name, *args)
+    if rc != 0:
+        raise NvkError(name, rc)
+
+
+def capability() -> tuple[int, int]:
+    a, b = C.c_int(0), C.c_int(0)
+    rc = int(lib().nv_kernels_capability(C.addressof(a), C.addressof(b)))
+    if rc != 0:
+        raise NvkError("nv_kernels_capability", rc)
+    return a.value, b.value

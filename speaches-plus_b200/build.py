@@ -1,0 +1,56 @@
+"""Compile the CUDA sources under csrc/ into libnvk_b200.so (sm_100a only), in-tree.
+
+    python speaches-plus_b200/build.py [--force] [--verbose]
+
+The library is a plain C-ABI shared object (see include/nvk_b200.h); it links the CUDA
+runtime statically so that it loads next to any other CUDA user in the process.
+"""
+from __future__ import annotations
+
+import pathlib
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = pathlib.Path(__file__).resolve().parent
+CSRC = HERE / "csrc"
+OBJ = HERE / "build"
+LIB = HERE / "libnvk_b200.so"
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC"]
+
+
+def sources():
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _newest_dep() -> float:
+    return max(f.stat().st_mtime for f in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")))
+
+
+def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
+    if not force and LIB.exists() and LIB.stat().st_mtime >= _newest_dep():
+        return LIB
+    OBJ.mkdir(exist_ok=True)
+    extra = ["-Xptxas", "-v"] if verbose else []
+
+    def compile_one(src: pathlib.Path) -> pathlib.Path:
+        obj = OBJ / (src.stem + ".o")
+        cmd = ["nvcc", *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src.name}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(compile_one, sources()))
+    cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs),
+           "-cudart", "static"]
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,123 @@
+// Shared device/host helpers for the NVFP4 linear path (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+// Return codes follow the reference launchers: 0 = enqueued, -1 = shape/route refused
+// without launching, -2 = bad argument/alignment, -3 = resource limit, -9 = grid axis too
+// large; a positive value is a cudaError_t.
+#define NVK_OK 0
+#define NVK_ERR_SHAPE (-1)
+#define NVK_ERR_ARG (-2)
+#define NVK_ERR_RESOURCE (-3)
+#define NVK_ERR_GRID_AXIS (-9)
+
+namespace nvk {
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Byte offset of the ue4m3 scale of (row m, 16-block kb) in the 128x4 swizzled layout
+// (the tcgen05 block-scale atom): 512-byte tiles of 128 rows x 4 blocks, tile-major by
+// (row tile, k tile); inside a tile byte = (m%32)*16 + ((m/32)%4)*4 + kb%4.
+__host__ __device__ __forceinline__ size_t swz_offset(int m, int kb, int k_blocks) {
+    size_t k_tiles = (size_t)((k_blocks + 3) >> 2);
+    return (((size_t)(m >> 7) * k_tiles + (size_t)(kb >> 2)) * 32 + (size_t)(m & 31)) * 16 +
+           (size_t)((m >> 5) & 3) * 4 + (size_t)(kb & 3);
+}
+
+// ue4m3 byte -> f32.  Bits 6..3 exponent (bias 7), 2..0 mantissa, exponent 0 = m * 2^-9.
+// Placing the 7 payload bits at f32 bits 26..20 yields value * 2^-120 with f32 subnormals
+// covering the exponent-0 case, so one multiply by 2^120 decodes every byte exactly
+// (bit 7 is ignored, 0x7F decodes to 480 like the formula does).
+__device__ __forceinline__ float ue4m3_to_f32(uint32_t b) {
+    return __uint_as_float((b & 0x7Fu) << 20) * 1.329227995784916e36f;  // 2^120
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) { return __uint_as_float(b16 << 16); }
+
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+// Four packed e2m1 bytes (8 values, even element in the low nibble) -> four f16x2.
+__device__ __forceinline__ void e2m1x8_to_f16x2x4(uint32_t w, uint32_t& h0, uint32_t& h1, uint32_t& h2,
+                                                  uint32_t& h3) {
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
+        : "r"(w));
+}
+
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// e2m1 nearest-code search, first minimum wins (ties go to the lower code).
+__device__ __forceinline__ uint32_t encode_e2m1(float x) {
+    const float a = fabsf(x);
+    // Midpoints of the codebook {0,.5,1,1.5,2,3,4,6}; "greater than" keeps ties low.
+    uint32_t c = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+    return c | (signbit(x) ? 8u : 0u);
+}
+
+// ue4m3 encoder: clamp to 448, subnormal grid below 2^-6, round-half-away mantissa with
+// carry, never emits 0x7F.  Exponent from the f32 bit field (exact floor(log2)).
+__device__ __forceinline__ uint32_t encode_ue4m3(float s) {
+    if (!(s > 0.f) || !isfinite(s)) return 0u;
+    const float c = fminf(s, 448.f);
+    if (c < 0.015625f) {
+        int m = (int)roundf(c / 0.001953125f);
+        return m <= 0 ? 0u : (m <= 7 ? (uint32_t)m : 8u);
+    }
+    int e2;
+    (void)frexpf(c, &e2);
+    int ex = e2 - 1;
+    float mf = ldexpf(c, -ex) - 1.f;
+    int mant = (int)roundf(mf * 8.f);
+    if (mant < 0) mant = 0;
+    if (mant > 7) {
+        mant = 0;
+        ex += 1;
+    }
+    int biased = ex + 7;
+    biased = biased < 1 ? 1 : (biased > 15 ? 15 : biased);
+    uint32_t byte = ((uint32_t)biased << 3) | (uint32_t)mant;
+    return byte == 0x7Fu ? 0x7Eu : byte;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Raise the dynamic shared memory limit of a kernel once, never lower it.
+struct SmemOptin {
+    size_t raised = 48 * 1024;
+    int ensure(const void* func, size_t bytes) {
+        if (bytes <= raised) return 0;
+        cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return (int)e;
+        raised = bytes;
+        return 0;
+    }
+};
+
+}  // namespace nvk

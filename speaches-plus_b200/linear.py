@@ -1,0 +1,184 @@
+"""Host-side mirror of the reference's NVFP4 `Linear` (rust/crates/nv-layers/src/linear.rs) and of
+its dense W4A16 MLP pair (rust/crates/nv-models/src/qwen3_5_moe.rs:661-792), over libnvk_b200.
+
+torch is used for device memory and streams only; every operator is one or more launches of the
+CUDA library on the current stream.  There is one route per M class and no fallback.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _ffi
+
+BLOCK_SIZE = 16   # rust/crates/nv-quant/src/nvfp4.rs:1
+MIN_TILE = 128    # rust/crates/nv-quant/src/nvfp4.rs:2 ; linear.rs:1565-1579 refuses smaller dims
+MAX_DECODE_M = 64  # rows one launch of the decode-sized route takes
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def swizzled_scale_bytes(rows: int, cols: int) -> int:
+    """Size of the swizzled block-scale buffer (rust/crates/nv-layers/src/linear.rs:2178-2180)."""
+    return -(-rows // 128) * 128 * -(-(cols // 16) // 4) * 4
+
+
+def stored_global_from_amax(amax: float) -> float:
+    """448*6/amax in f32 (rust/crates/nv-layers/src/linear.rs:2161-2175); 1.0 for an all-zero tensor."""
+    a = np.float32(amax)
+    if a == 0 or not np.isfinite(a):
+        return 1.0
+    return float(np.float32(np.float32(448.0) * np.float32(6.0)) / a)
+
+
+def quantize_nvfp4_bf16(x: torch.Tensor, stored_global: float, m_padded: int | None = None):
+    """bf16 [m, K] -> (packed [m_padded, K/2] u8, swizzled scales u8) via nv_kernels_quantize_nvfp4_bf16."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    m, k = x.shape
+    mp = m if m_padded is None else m_padded
+    packed = torch.empty((mp, k // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(swizzled_scale_bytes(mp, k), dtype=torch.uint8, device=x.device)
+    _ffi.check("nv_kernels_quantize_nvfp4_bf16", _stream(), x.data_ptr(), packed.data_ptr(), scales.data_ptr(),
+               float(stored_global), mp, m, k)
+    return packed, scales
+
+
+def quantize_weight_nvfp4(w: torch.Tensor):
+    """bf16 weight [N, K] on the GPU -> (packed, scales_swizzled, weight_alpha, stored_global).
+
+    Follows Linear::from_bf16_quantized_nvfp4_dev (rust/crates/nv-layers/src/linear.rs:2124-2226):
+    stored_global = 448*6/max|W|, weight_alpha = 1/stored_global, activation global 1.0."""
+    assert w.dim() == 2
+    w = w.contiguous()
+    amax = float(w.abs().max().float().item())
+    g = stored_global_from_amax(amax)
+    packed, scales = quantize_nvfp4_bf16(w, g)
+    return packed, scales, float(np.float32(1.0) / np.float32(g)), g
+
+
+class Nvfp4Linear:
+    """NVFP4 weight-only linear: y = x W^T (+ bias), bf16 in/out, fp32 accumulate.
+
+    Storage mirrors `Nvfp4Storage` (rust/crates/nv-layers/src/linear.rs:308-318): packed weights
+    [out, in/2], swizzled block scales, `weight_alpha` = 1/stored weight global (times the
+    reciprocal of a stored input global when a checkpoint carries one)."""
+
+    def __init__(self, weight_u8: torch.Tensor, weight_scales: torch.Tensor, weight_alpha: float,
+                 in_features: int, out_features: int, bias: torch.Tensor | None = None,
+                 input_stored_global: float = 1.0):
+        if in_features % BLOCK_SIZE != 0:
+            raise ValueError(f"nvfp4 linear: in_features {in_features} is not a multiple of {BLOCK_SIZE}")
+        if in_features < MIN_TILE or out_features < MIN_TILE:
+            raise ValueError(f"nvfp4 linear: dims ({out_features},{in_features}) below MIN_TILE={MIN_TILE}")
+        if weight_u8.numel() != out_features * in_features // 2:
+            raise ValueError("nvfp4 linear: packed weight has the wrong number of bytes")
+        if weight_scales.numel() < swizzled_scale_bytes(out_features, in_features):
+            raise ValueError("nvfp4 linear: swizzled scale buffer too small")
+        self.weight_u8 = weight_u8.contiguous()
+        self.weight_scales = weight_scales.contiguous()
+        self.weight_alpha = float(weight_alpha)
+        self.input_stored_global = float(input_stored_global)
+        self.in_features, self.out_features = in_features, out_features
+        self.bias = bias
+
+    # -- constructors (names follow the reference) --
+    @classmethod
+    def new_nvfp4(cls, weight_u8, weight_scales_swizzled, weight_alpha, in_features, out_features, bias=None):
+        return cls(weight_u8, weight_scales_swizzled, weight_alpha, in_features, out_features, bias)
+
+    @classmethod
+    def from_bf16_quantized_nvfp4_dev(cls, weight: torch.Tensor, bias: torch.Tensor | None = None):
+        n, k = weight.shape
+        packed, scales, alpha, _ = quantize_weight_nvfp4(weight)
+        return cls(packed, scales, alpha, k, n, bias)
+
+    def nvfp4_parts(self):
+        """(packed weights, swizzled scales, weight_alpha) -- linear.rs:411-451."""
+        return self.weight_u8, self.weight_scales, self.weight_alpha
+
+    # -- forward --
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.in_features:
+            raise ValueError(f"nvfp4 linear: input last dim {x.shape[-1]} != {self.in_features}")
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        y = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+        self.forward_into(x2, y)
+        if self.bias is not None:
+            y += self.bias
+        return y.reshape(*lead, self.out_features)
+
+    __call__ = forward
+
+    def forward_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
+        """x2 [M, in] bf16 contiguous -> y [M, out]; rows are independent, so M > 64 runs as row
+        chunks (results are bit-identical under any row chunking)."""
+        assert x2.is_cuda and x2.dtype == torch.bfloat16 and x2.is_contiguous() and y.is_contiguous()
+        m = x2.shape[0]
+        s = _stream()
+        if m == 1:
+            _ffi.check("nv_kernels_nvfp4_gemv_bf16act", s, self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
+                       x2.data_ptr(), y.data_ptr(), self.weight_alpha, self.out_features, self.in_features)
+            return
+        for r0 in range(0, m, MAX_DECODE_M):
+            mm = min(MAX_DECODE_M, m - r0)
+            _ffi.check("nvk_b200_linear_nvfp4_w4a16", s, self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
+                       None, None, x2[r0:].data_ptr(), None, y[r0:].data_ptr(), None, self.weight_alpha, 0.0, mm,
+                       self.out_features, self.in_features)
+
+
+class Bf16Linear:
+    """bf16 linear used for the lm_head at M=1 (nv_kernels_gemv_bf16); rows loop for M > 1."""
+
+    def __init__(self, weight: torch.Tensor):
+        assert weight.dtype == torch.bfloat16 and weight.dim() == 2
+        self.weight = weight.contiguous()
+        self.out_features, self.in_features = weight.shape
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        y = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+        s = _stream()
+        for r in range(x2.shape[0]):
+            _ffi.check("nv_kernels_gemv_bf16", s, self.weight.data_ptr(), x2[r].data_ptr(), y[r].data_ptr(),
+                       self.out_features, self.in_features)
+        return y.reshape(*x.shape[:-1], self.out_features)
+
+    __call__ = forward
+
+
+class Nvfp4Mlp:
+    """SwiGLU MLP on the W4A16 route: one dual launch for gate+up sharing x, one launch for down
+    with SiLU(gate)*up fused as its prologue (the activation is rounded to bf16 first, as the
+    reference's decode kernel does; rust/crates/nv-kernels/cuda/gemv_nvfp4_w4a16_decode.cu:165-170)."""
+
+    def __init__(self, gate: Nvfp4Linear, up: Nvfp4Linear, down: Nvfp4Linear):
+        assert gate.in_features == up.in_features and gate.out_features == up.out_features
+        assert down.in_features == gate.out_features
+        self.gate, self.up, self.down = gate, up, down
+        self._gu = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, self.gate.in_features).contiguous()
+        m = x2.shape[0]
+        inter, hidden = self.gate.out_features, self.down.out_features
+        if self._gu is None or self._gu.shape[1] != m or self._gu.device != x.device:
+            self._gu = torch.empty((2, m, inter), dtype=torch.bfloat16, device=x.device)
+        g, u = self._gu[0], self._gu[1]
+        y = torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device)
+        s = _stream()
+        for r0 in range(0, m, MAX_DECODE_M):
+            mm = min(MAX_DECODE_M, m - r0)
+            _ffi.check("nvk_b200_linear_nvfp4_w4a16", s, self.gate.weight_u8.data_ptr(),
+                       self.gate.weight_scales.data_ptr(), self.up.weight_u8.data_ptr(),
+                       self.up.weight_scales.data_ptr(), x2[r0:].data_ptr(), None, g[r0:].data_ptr(),
+                       u[r0:].data_ptr(), self.gate.weight_alpha, self.up.weight_alpha, mm, inter,
+                       self.gate.in_features)
+            _ffi.check("nvk_b200_linear_nvfp4_w4a16", s, self.down.weight_u8.data_ptr(),
+                       self.down.weight_scales.data_ptr(), None, None, g[r0:].data_ptr(), u[r0:].data_ptr(),
+                       y[r0:].data_ptr(), None, self.down.weight_alpha, 0.0, mm, hidden, inter)
+        return y.reshape(*x.shape[:-1], hidden)
+
+    __call__ = forward

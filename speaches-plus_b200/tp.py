@@ -1,0 +1,113 @@
+"""Tensor-parallel sharding of NVFP4 linears across the GPUs of one node (one process per GPU,
+torch.distributed / NCCL).  The reference has no multi-GPU code for this path; this is new design.
+
+Column-parallel (QKV, gate/up, lm_head): output rows are split.  A shard is a whole number of
+128-row scale tiles, so the packed rows and the swizzled scale tiles of a shard are both contiguous
+slices.  y shards are all-gathered only where the full vector is needed.
+
+Row-parallel (o_proj, down): K is split at multiples of 64 (one scale k-tile).  Each rank produces a
+partial y over its K slice and the partials are summed with an all-reduce on the same stream.
+
+The weight is quantized once with the global of the WHOLE matrix and then sliced, so a sharded
+linear uses exactly the bytes the unsharded one does.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import linear as L
+
+
+def column_shard_rows(n: int, rank: int, world: int) -> tuple[int, int]:
+    """Row range [r0, r1) of a column-parallel shard: 128-row tiles dealt out as evenly as possible."""
+    tiles = -(-n // 128)
+    base, extra = divmod(tiles, world)
+    t0 = rank * base + min(rank, extra)
+    t1 = t0 + base + (1 if rank < extra else 0)
+    return min(t0 * 128, n), min(t1 * 128, n)
+
+
+def row_shard_cols(k: int, rank: int, world: int) -> tuple[int, int]:
+    """K range [k0, k1) of a row-parallel shard: 64-element scale k-tiles dealt out evenly."""
+    tiles = -(-k // 64)
+    base, extra = divmod(tiles, world)
+    t0 = rank * base + min(rank, extra)
+    t1 = t0 + base + (1 if rank < extra else 0)
+    return min(t0 * 64, k), min(t1 * 64, k)
+
+
+def shard_nvfp4(packed: torch.Tensor, scales_swz: torch.Tensor, n: int, k: int, mode: str, rank: int, world: int):
+    """Slice (packed [n, k/2] u8, swizzled scales) for one rank.  Returns (packed, scales, n_local, k_local,
+    offset) where offset is the first row (column mode) or first K index (row mode) of the shard."""
+    k_tiles = -(-(k // 16) // 4)
+    m_tiles = -(-n // 128)
+    sc = scales_swz[: m_tiles * k_tiles * 512].reshape(m_tiles, k_tiles, 512)
+    if mode == "column":
+        r0, r1 = column_shard_rows(n, rank, world)
+        return (packed[r0:r1].contiguous(), sc[r0 // 128: -(-r1 // 128)].reshape(-1).contiguous(), r1 - r0, k, r0)
+    if mode == "row":
+        k0, k1 = row_shard_cols(k, rank, world)
+        return (packed[:, k0 // 2: k1 // 2].contiguous(), sc[:, k0 // 64: -(-k1 // 64)].reshape(-1).contiguous(), n,
+                k1 - k0, k0)
+    raise ValueError(f"unknown tensor-parallel mode {mode!r}")
+
+
+class TpNvfp4Linear:
+    """One rank's shard of an NVFP4 linear plus the collective that completes it."""
+
+    def __init__(self, local: L.Nvfp4Linear | None, mode: str, rank: int, world: int, n: int, k: int, offset: int,
+                 group=None):
+        self.local, self.mode, self.rank, self.world = local, mode, rank, world
+        self.n, self.k, self.offset, self.group = n, k, offset, group
+        self._bufs = {}
+
+    @classmethod
+    def from_bf16(cls, w: torch.Tensor, mode: str, rank: int, world: int, group=None):
+        n, k = w.shape
+        packed, scales, alpha, _ = L.quantize_weight_nvfp4(w)
+        return cls.from_parts(packed, scales, alpha, n, k, mode, rank, world, group)
+
+    @classmethod
+    def from_parts(cls, packed, scales, alpha, n, k, mode, rank, world, group=None):
+        if world == 1:
+            return cls(L.Nvfp4Linear(packed, scales, alpha, k, n), mode, 0, 1, n, k, 0, group)
+        if mode == "column" and n % (128 * world) != 0:
+            raise ValueError(f"column-parallel needs N={n} to be a multiple of 128*{world}")
+        if mode == "row" and k % (64 * world) != 0:
+            raise ValueError(f"row-parallel needs K={k} to be a multiple of 64*{world}")
+        p, s, nl, kl, off = shard_nvfp4(packed, scales, n, k, mode, rank, world)
+        return cls(L.Nvfp4Linear(p, s, alpha, kl, nl), mode, rank, world, n, k, off, group)
+
+    def _buf(self, name, shape, device):
+        key = (name, tuple(shape))
+        if key not in self._bufs:
+            self._bufs[key] = torch.empty(shape, dtype=torch.bfloat16, device=device)
+        return self._bufs[key]
+
+    def forward(self, x: torch.Tensor, gather: bool = True) -> torch.Tensor:
+        """x [M, K] (full K on every rank) -> y.  Column mode returns the full [M, N] when `gather`
+        (else this rank's [M, N/world] shard); row mode returns the all-reduced [M, N]."""
+        m = x.shape[0]
+        if self.world == 1:
+            y = self._buf("y", (m, self.n), x.device)
+            self.local.forward_into(x, y)
+            return y
+        if self.mode == "column":
+            yl = self._buf("yl", (m, self.local.out_features), x.device)
+            self.local.forward_into(x, yl)
+            if not gather:
+                return yl
+            nl = self.local.out_features
+            full = self._buf("yg", (self.world * m, nl), x.device)  # rank-major: [world, m, nl]
+            dist.all_gather_into_tensor(full, yl, group=self.group)
+            if m == 1:
+                return full.reshape(1, self.n)
+            return full.reshape(self.world, m, nl).permute(1, 0, 2).reshape(m, self.n)
+        xs = x[:, self.offset: self.offset + self.local.in_features]
+        if m > 1:
+            xs = xs.contiguous()
+        y = self._buf("yr", (m, self.n), x.device)
+        self.local.forward_into(xs, y)
+        dist.all_reduce(y, group=self.group)
+        return y

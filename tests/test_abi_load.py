@@ -1,0 +1,51 @@
+"""CPU-side checks of the drop-in boundary: the library loads without a GPU and exports every
+symbol that include/nvk_b200.h declares; the Python binding covers the same set."""
+import ctypes
+import pathlib
+import re
+
+import speaches_plus_b200 as sp
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "nvk_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\bint\s+((?:nv_kernels|nvk_b200)_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_path_entry_points():
+    syms = declared_symbols()
+    for must in ("nv_kernels_nvfp4_gemv_bf16act", "nv_kernels_gemv_nvfp4_w4a16_dual_m1",
+                 "nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1", "nv_kernels_gemm_nvfp4_w4a16_mk_dual",
+                 "nv_kernels_moe_grouped_fp4_gemv_m1_bf16", "nv_kernels_quantize_nvfp4_bf16",
+                 "nv_kernels_moe_route_topk", "nv_kernels_gemv_bf16", "nv_kernels_capability"):
+        assert must in syms
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(str(sp.ffi.LIB_PATH))
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in include/nvk_b200.h but not exported"
+
+
+def test_binding_matches_header():
+    assert sorted(sp.ffi.SIGNATURES) == declared_symbols()
+    sp.ffi.lib()  # resolves every symbol, raises if one is missing
+
+
+def test_header_compiles_as_c(tmp_path):
+    import subprocess
+    src = tmp_path / "t.c"
+    src.write_text('#include "nvk_b200.h"\nint main(void){return 0;}\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", str(ROOT / "include"), "-c", str(src), "-o",
+                    str(tmp_path / "t.o")], check=True)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    import pytest
+    monkeypatch.setattr(sp.ffi, "_lib", None)
+    monkeypatch.setattr(sp.ffi, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        sp.ffi.lib()

@@ -1,0 +1,300 @@
+"""GPU parity of the W4A16 NVFP4 linear against the CPU oracle, through the C ABI.
+
+Tolerances (written here, as the contract asks):
+  * vs the f64 statement of the contraction: |got-want| / max(|want|, rms, 1e-3) < 1e-4 + 1e-2 -- the
+    reference's own GEMV bound (rust/crates/nv-quant/tests/nvfp4_m1_gemv_ab.rs:103-118), i.e.
+    fp32-accumulate noise plus bf16 output rounding; in practice the worst case is ~2^-9.
+  * vs the reference's Cpu-backend linear (weights dequantized to bf16, f32 matmul, bf16 out):
+    max relative error < 1e-2 with the same floored denominator.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+TOL_F64 = 1e-4 + 1e-2
+TOL_CPU_BACKEND = 1e-2
+
+
+def run_gemv(packed, sw, x_bits, alpha, n, k, entry="nv_kernels_nvfp4_gemv_bf16act"):
+    d_w, d_s, d_x = U.dev(packed), U.dev(sw), U.dev(x_bits)
+    y = torch.full((n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")  # canary tail
+    rc = U.ffi.call(entry, U.stream(), d_w.data_ptr(), d_s.data_ptr(), d_x.data_ptr(), y.data_ptr(), float(alpha),
+                    n, k)
+    assert rc == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[n:] == 0x7FC0), "wrote past the end of y"
+    return out[:n]
+
+
+def run_linear(packed, sw, x_bits, alpha, m, n, k, packed_b=None, sw_b=None, alpha_b=0.0, up_bits=None):
+    d = [U.dev(packed), U.dev(sw), U.dev(x_bits)]
+    db = [U.dev(packed_b), U.dev(sw_b)] if packed_b is not None else None
+    du = U.dev(up_bits) if up_bits is not None else None
+    y = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    yb = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda") if db else None
+    rc = U.ffi.call("nvk_b200_linear_nvfp4_w4a16", U.stream(), d[0].data_ptr(), d[1].data_ptr(),
+                    db[0].data_ptr() if db else None, db[1].data_ptr() if db else None, d[2].data_ptr(),
+                    du.data_ptr() if du is not None else None, y.data_ptr(), yb.data_ptr() if db else None,
+                    float(alpha), float(alpha_b), m, n, k)
+    assert rc == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[m * n:] == 0x7FC0)
+    if db:
+        outb = U.host_u16(yb)
+        assert np.all(outb[m * n:] == 0x7FC0)
+        return out[:m * n].reshape(m, n), outb[:m * n].reshape(m, n)
+    return out[:m * n].reshape(m, n)
+
+
+def check_against_oracle(got_bits, packed, sw, x_bits, alpha, n, k, cpu_backend=True):
+    got = ref.bf16_to_f32(got_bits).reshape(-1, n)
+    want = ref.linear_w4a16_f64(packed, sw, x_bits, alpha, n, k)
+    e = U.rel_err_floor(got, want)
+    assert e < TOL_F64, f"vs f64 oracle: {e}"
+    if cpu_backend:
+        w_bf16 = ref.dequantize_to_bf16(packed, sw, n, k, alpha)
+        want2 = ref.bf16_to_f32(ref.linear_cpu_backend(w_bf16, np.asarray(x_bits).reshape(-1, k)))
+        e2 = U.rel_err_floor(got, want2)
+        assert e2 < TOL_CPU_BACKEND, f"vs Cpu-backend linear: {e2}"
+    return e
+
+
+def test_capability_is_sm100():
+    U.require_gpu()
+    assert U.ffi.capability() == (10, 0)
+
+
+def test_config0_single_linear_seed0():
+    """BASELINE configs[0]: x [1,4096] ~ N(0,1), W [4096,4096] ~ N(0,0.02), seed 0."""
+    U.require_gpu()
+    rng = np.random.default_rng(0)
+    x = U.gauss_bf16(rng, (1, 4096))
+    packed, sw, alpha, _ = U.make_weight(rng, 4096, 4096)
+    got = run_gemv(packed, sw, x, alpha, 4096, 4096)
+    e = check_against_oracle(got, packed, sw, x, alpha, 4096, 4096)
+    assert e < 6e-3  # bf16 output rounding (2^-9 ~ 2e-3 of |want|, relative to the floored denominator)
+
+
+def sin_bf16(n, seed, scale):
+    j = np.arange(n, dtype=np.float32)
+    return ref.f32_to_bf16(np.sin(j * np.float32(seed)).astype(np.float32) * np.float32(scale))
+
+
+@pytest.mark.parametrize("n,k,alpha", [(64, 256, 1.0), (129, 1024, 1.0), (640, 5376, 0.5), (5376, 5376, 1.0)])
+def test_m1_gemv_reference_shapes(n, k, alpha):
+    """Shapes, generators and bound of rust/crates/nv-quant/tests/nvfp4_m1_gemv_ab.rs:61-120
+    (sin-wave weights quantized with global 1.0, sin-wave x times 2)."""
+    U.require_gpu()
+    w = sin_bf16(n * k, 0.00071, 1.0).reshape(n, k)
+    packed, lin = ref.quantize_rows_bf16(w, 1.0)
+    sw = ref.swizzle_scales(lin)
+    x = sin_bf16(k, 0.00131, 2.0).reshape(1, k)
+    got = run_gemv(packed, sw, x, alpha, n, k)
+    check_against_oracle(got, packed, sw, x, alpha, n, k, cpu_backend=False)
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 31, 33, 127, 128, 129, 255, 257])
+@pytest.mark.parametrize("k", [16, 32, 48, 64, 128, 144, 256, 272, 1040])
+def test_m1_ragged_shapes(n, k):
+    """Every residue class the launch geometry cares about: N around the 8/32/128 row groupings,
+    K around the 16/32/64/256 groupings (K % 32 != 0 takes the generic route)."""
+    U.require_gpu()
+    rng = np.random.default_rng(1000 * n + k)
+    packed, sw, alpha, _ = U.make_weight(rng, n, k, std=0.5)
+    x = U.gauss_bf16(rng, (1, k))
+    got = run_gemv(packed, sw, x, alpha, n, k)
+    check_against_oracle(got, packed, sw, x, alpha, n, k, cpu_backend=False)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 11, 16, 17, 31, 32, 33, 63, 64])
+@pytest.mark.parametrize("n,k", [(256, 512), (96, 320), (384, 4096)])
+def test_skinny_m_sweep(m, n, k):
+    U.require_gpu()
+    rng = np.random.default_rng(7 * m + n + k)
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    got = run_linear(packed, sw, x, alpha, m, n, k)
+    check_against_oracle(got, packed, sw, x, alpha, n, k)
+
+
+@pytest.mark.parametrize("ks", [1, 2, 4, 8])
+def test_cluster_split_k_is_consistent(ks):
+    """Every cluster size gives the oracle's answer (the partial tiles are summed through
+    distributed shared memory in a fixed order), and each is bit-stable run to run."""
+    U.require_gpu()
+    rng = np.random.default_rng(42)
+    n, k, m = 384, 2048 + 256, 4
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    assert U.ffi.call("nvk_b200_set_tuning", ks) == 0
+    try:
+        a = run_linear(packed, sw, x, alpha, m, n, k)
+        b = run_linear(packed, sw, x, alpha, m, n, k)
+    finally:
+        U.ffi.call("nvk_b200_set_tuning", 0)
+    assert np.array_equal(a, b)
+    check_against_oracle(a, packed, sw, x, alpha, n, k)
+
+
+def test_multi_phase_activation_staging():
+    """K large enough at M=64 that the activations are staged in several phases, with magnitudes
+    that change by 2^40 along K so the per-phase power-of-two rescale is exercised."""
+    U.require_gpu()
+    rng = np.random.default_rng(5)
+    n, k, m = 128, 4096, 64
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    xf = rng.standard_normal((m, k)).astype(np.float32)
+    xf[:, 1024:2048] *= np.float32(2.0 ** 20)
+    xf[:, 3072:] *= np.float32(2.0 ** -20)
+    x = ref.f32_to_bf16(xf)
+    U.ffi.call("nvk_b200_set_tuning", 1)
+    try:
+        got = run_linear(packed, sw, x, alpha, m, n, k)
+    finally:
+        U.ffi.call("nvk_b200_set_tuning", 0)
+    check_against_oracle(got, packed, sw, x, alpha, n, k, cpu_backend=False)
+
+
+def test_wide_dynamic_range_and_special_values():
+    U.require_gpu()
+    rng = np.random.default_rng(9)
+    n, k = 256, 1024
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    xf = rng.standard_normal((1, k)).astype(np.float32) * np.exp2(rng.integers(-30, 10, size=(1, k))).astype(np.float32)
+    x = ref.f32_to_bf16(xf)
+    got = run_gemv(packed, sw, x, alpha, n, k)
+    check_against_oracle(got, packed, sw, x, alpha, n, k, cpu_backend=False)
+    # all-zero activation -> exact zeros
+    z = np.zeros((1, k), np.uint16)
+    assert np.all(ref.bf16_to_f32(run_gemv(packed, sw, z, alpha, n, k)) == 0)
+    # tiny activations (below f16 range before the power-of-two pre-scale)
+    tiny = ref.f32_to_bf16((rng.standard_normal((1, k)) * 1e-30).astype(np.float32))
+    got = ref.bf16_to_f32(run_gemv(packed, sw, tiny, alpha, n, k))
+    want = ref.linear_w4a16_f64(packed, sw, tiny, alpha, n, k)
+    assert np.max(np.abs(got - want)) <= 1e-2 * np.sqrt(np.mean(want ** 2)) + 1e-38
+
+
+def test_every_scale_byte_and_code_decodes_like_the_oracle():
+    """Random nibbles and random scale bytes over the whole 0..0x7E range (plus 0x7F and bytes with
+    bit 7 set, which the reference's decode formula still defines)."""
+    U.require_gpu()
+    rng = np.random.default_rng(11)
+    n, k = 128, 512
+    packed = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    lin = rng.integers(0, 0x7F, size=(n, k // 16), dtype=np.uint8)
+    lin[0, :8] = [0x7F, 0x80, 0xFF, 0x00, 0x01, 0x07, 0x08, 0x7E]
+    sw = ref.swizzle_scales(lin)
+    x = U.gauss_bf16(rng, (1, k))
+    got = run_gemv(packed, sw, x, 2.0 ** -12, n, k)
+    check_against_oracle(got, packed, sw, x, 2.0 ** -12, n, k, cpu_backend=False)
+
+
+def test_dual_and_silu_prologue_m1():
+    """gate+up in one launch, then the down projection with SiLU(gate)*up as its prologue; shapes of
+    rust/crates/nv-kernels/tests/gemv_nvfp4_w4a16_decode_parity.rs (N=256, K=512) and a wider one."""
+    U.require_gpu()
+    for (inter, hidden) in [(256, 512), (1536, 1024)]:
+        rng = np.random.default_rng(inter)
+        pg, sg, ag, _ = U.make_weight(rng, inter, hidden)
+        pu, su, au, _ = U.make_weight(rng, inter, hidden)
+        pd, sd, ad, _ = U.make_weight(rng, hidden, inter)
+        x = U.gauss_bf16(rng, (1, hidden), 4.0)
+        d = [U.dev(a) for a in (pg, sg, pu, su, x)]
+        yg = torch.zeros(inter, dtype=torch.int16, device="cuda")
+        yu = torch.zeros(inter, dtype=torch.int16, device="cuda")
+        assert U.ffi.call("nv_kernels_gemv_nvfp4_w4a16_dual_m1", U.stream(), d[0].data_ptr(), d[1].data_ptr(),
+                          d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(), yg.data_ptr(), yu.data_ptr(), ag, au,
+                          inter, hidden) == 0
+        torch.cuda.synchronize()
+        g_bits, u_bits = U.host_u16(yg), U.host_u16(yu)
+        check_against_oracle(g_bits, pg, sg, x, ag, inter, hidden)
+        check_against_oracle(u_bits, pu, su, x, au, inter, hidden)
+        dd = [U.dev(a) for a in (pd, sd)]
+        yd = torch.zeros(hidden, dtype=torch.int16, device="cuda")
+        assert U.ffi.call("nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1", U.stream(), dd[0].data_ptr(),
+                          dd[1].data_ptr(), yg.data_ptr(), yu.data_ptr(), yd.data_ptr(), ad, hidden, inter) == 0
+        torch.cuda.synchronize()
+        act = ref.f32_to_bf16(ref.silu_mul(g_bits, u_bits, round_bf16=True)).reshape(1, inter)
+        want = ref.linear_w4a16_f64(pd, sd, act, ad, hidden, inter)
+        e = U.rel_err_floor(ref.bf16_to_f32(U.host_u16(yd)).reshape(1, hidden), want)
+        assert e < 2e-2  # reference bound for this pair (gemv_nvfp4_w4a16_decode_parity.rs: 2e-2)
+
+
+@pytest.mark.parametrize("m", [2, 6, 16])
+def test_mk_dual_reference_symbol(m):
+    U.require_gpu()
+    rng = np.random.default_rng(m)
+    n, k = 512, 640
+    pa, sa, aa, _ = U.make_weight(rng, n, k)
+    pb, sb, ab, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    d = [U.dev(a) for a in (pa, sa, pb, sb, x)]
+    ya = torch.zeros(m * n, dtype=torch.int16, device="cuda")
+    yb = torch.zeros(m * n, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_gemm_nvfp4_w4a16_mk_dual", U.stream(), *[t.data_ptr() for t in d], ya.data_ptr(),
+                      yb.data_ptr(), aa, ab, m, n, k) == 0
+    torch.cuda.synchronize()
+    check_against_oracle(U.host_u16(ya), pa, sa, x, aa, n, k)
+    check_against_oracle(U.host_u16(yb), pb, sb, x, ab, n, k)
+    # single arm through the same symbol
+    yc = torch.zeros(m * n, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_gemm_nvfp4_w4a16_mk_dual", U.stream(), d[0].data_ptr(), d[1].data_ptr(), None, None,
+                      d[4].data_ptr(), yc.data_ptr(), None, aa, 0.0, m, n, k) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(U.host_u16(yc), U.host_u16(ya))
+
+
+def test_refusals_match_the_reference():
+    U.require_gpu()
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p, s = t.data_ptr(), U.stream()
+    f = U.ffi.call
+    assert f("nv_kernels_nvfp4_gemv_bf16act", s, p, p, p, p, 1.0, 0, 256) == 0       # empty: no-op
+    assert f("nv_kernels_nvfp4_gemv_bf16act", s, p, p, p, p, 1.0, 64, 250) == -1     # K % 16
+    assert f("nv_kernels_gemv_nvfp4_w4a16_dual_m1", s, p, p, None, None, p, p, None, 1.0, 1.0, 64, 48) == -1  # K % 32
+    assert f("nv_kernels_gemv_nvfp4_w4a16_dual_m1", s, p, p, p, None, p, p, None, 1.0, 1.0, 64, 64) == -1  # half-null arm
+    assert f("nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1", s, p, p, p, p, p, 1.0, 0, 64) == -1
+    assert f("nv_kernels_gemm_nvfp4_w4a16_mk_dual", s, p, p, None, None, p, p, None, 1.0, 1.0, 17, 64, 64) == -1
+    assert f("nv_kernels_gemm_nvfp4_w4a16_mk_dual", s, p, p, None, None, p, p, None, 1.0, 1.0, 0, 64, 64) == -1
+    assert f("nvk_b200_linear_nvfp4_w4a16", s, p, p, None, None, p, None, p, None, 1.0, 0.0, 65, 128, 128) == -1
+    torch.cuda.synchronize()
+
+
+def test_row_chunk_invariance_is_bitwise():
+    """rust/crates/nv-layers/tests/nvfp4_chunk_invariance.rs: a projection is bit-identical under
+    row chunking, and does change when an input changes."""
+    U.require_gpu()
+    rng = np.random.default_rng(77)
+    n, k, m = 1024, 5376, 48
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    full = run_linear(packed, sw, x, alpha, m, n, k)
+    for chunk in (1, 3, 8, 16, 24):
+        parts = [run_linear(packed, sw, x[r:r + chunk], alpha, min(chunk, m - r), n, k) for r in range(0, m, chunk)]
+        assert np.array_equal(np.concatenate(parts, 0), full), f"chunk {chunk}"
+    x2 = x.copy()
+    x2[5, 100] ^= 0x0100
+    assert not np.array_equal(run_linear(packed, sw, x2, alpha, m, n, k)[5], full[5])
+
+
+def test_bf16_lm_head_gemv():
+    U.require_gpu()
+    rng = np.random.default_rng(3)
+    for n, k in [(1000, 5120), (37, 200), (4096, 4104)]:
+        w = U.gauss_bf16(rng, (n, k), 0.02)
+        x = U.gauss_bf16(rng, (1, k))
+        dw, dx = U.dev(w), U.dev(x)
+        y = torch.zeros(n, dtype=torch.int16, device="cuda")
+        assert U.ffi.call("nv_kernels_gemv_bf16", U.stream(), dw.data_ptr(), dx.data_ptr(), y.data_ptr(), n, k) == 0
+        torch.cuda.synchronize()
+        want = ref.bf16_to_f32(x).astype(np.float64) @ ref.bf16_to_f32(w).astype(np.float64).T
+        assert U.rel_err_floor(ref.bf16_to_f32(U.host_u16(y)).reshape(1, n), want) < 1e-2
+        cpu = ref.linear_cpu_backend(w, x)
+        assert U.bf16_ulp_diff(U.host_u16(y), cpu[0]).max() <= 2

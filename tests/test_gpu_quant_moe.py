@@ -1,0 +1,353 @@
+"""GPU parity of the quantizers (byte-exact) and the MoE decode plumbing against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+def gpu_quantize(x_bits, g, m_padded=None):
+    m, k = x_bits.shape
+    mp = m if m_padded is None else m_padded
+    dx = U.dev(x_bits)
+    packed = torch.full((mp * k // 2 + 32,), 0xAB, dtype=torch.uint8, device="cuda")
+    nsw = ref.swizzled_len(mp, k // 16)
+    scales = torch.zeros(nsw + 32, dtype=torch.uint8, device="cuda")
+    scales[nsw:] = 0xCD
+    rc = U.ffi.call("nv_kernels_quantize_nvfp4_bf16", U.stream(), dx.data_ptr(), packed.data_ptr(),
+                    scales.data_ptr(), float(g), mp, m, k)
+    assert rc == 0
+    torch.cuda.synchronize()
+    p, s = packed.cpu().numpy(), scales.cpu().numpy()
+    assert np.all(p[mp * k // 2:] == 0xAB) and np.all(s[nsw:] == 0xCD)
+    return p[:mp * k // 2].reshape(mp, k // 2), s[:nsw]
+
+
+@pytest.mark.parametrize("m,k,g", [(128, 128, 1.0), (130, 272, 1.0), (7, 48, 3.5), (256, 1024, 0.0073),
+                                   (64, 4096, 448.0), (33, 64, 0.0), (512, 5376, 134.4)])
+def test_quantizer_is_byte_exact(m, k, g):
+    """rust/crates/nv-kernels/tests/quantize_nvfp4_bf16.rs: device bytes == host quantizer + swizzle
+    (sin-wave inputs times 2.5), extended with gaussian magnitudes from 1e-4 to 500."""
+    U.require_gpu()
+    j = np.arange(m * k, dtype=np.float32)
+    x1 = ref.f32_to_bf16(np.sin(j * np.float32(0.37)).astype(np.float32) * np.float32(2.5)).reshape(m, k)
+    rng = np.random.default_rng(m * k)
+    mags = np.exp(rng.uniform(np.log(1e-4), np.log(500.0), size=(m, 1))).astype(np.float32)
+    x2 = ref.f32_to_bf16((rng.standard_normal((m, k)).astype(np.float32) * mags))
+    x2[0, :16] = 0  # an all-zero block
+    for x in (x1, x2):
+        p, s = gpu_quantize(x, g)
+        pw, lw = ref.quantize_rows_bf16(x, g)
+        assert np.array_equal(p, pw)
+        assert np.array_equal(s, ref.swizzle_scales(lw))
+
+
+def test_quantizer_ties_and_pad_rows():
+    U.require_gpu()
+    k = 64
+    x = np.zeros((3, k), np.float32)
+    x[0, :8] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0]
+    x[1, :8] = [-0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0]
+    x[2, 16:24] = [6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+    xb = ref.f32_to_bf16(x)
+    p, s = gpu_quantize(xb, 1.0, m_padded=128)
+    pw, lw = ref.quantize_rows_bf16(xb, 1.0, m_padded=128)
+    assert np.array_equal(p, pw) and np.array_equal(s, ref.swizzle_scales(lw))
+    assert np.all(p[3:] == 0)  # pad rows quantize zeros
+    assert U.ffi.call("nv_kernels_quantize_nvfp4_bf16", U.stream(), 0, 0, 0, 1.0, 4, 5, 64) == -2
+    assert U.ffi.call("nv_kernels_quantize_nvfp4_bf16", U.stream(), 0, 0, 0, 1.0, 4, 4, 40) == -1
+    assert U.ffi.call("nv_kernels_quantize_nvfp4_bf16", U.stream(), 0, 0, 0, 1.0, 0, 0, 64) == 0
+
+
+def test_weight_quantizer_matches_oracle_and_feeds_the_gemv():
+    """Linear::from_bf16_quantized_nvfp4_dev rule end to end on the GPU: global 448*6/amax,
+    alpha = 1/global; bytes equal the oracle's, so the GEMV sees identical operands."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(0)
+    w = U.gauss_bf16(rng, (384, 1024), 0.02)
+    wt = U.dev(w).view(torch.bfloat16)
+    lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(wt)
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    assert np.array_equal(lin.weight_u8.cpu().numpy(), packed)
+    assert np.array_equal(lin.weight_scales.cpu().numpy(), sw)
+    assert lin.weight_alpha == alpha
+    x = U.gauss_bf16(rng, (5, 1024))
+    y = lin(U.dev(x).view(torch.bfloat16))
+    want = ref.linear_w4a16_f64(packed, sw, x, alpha, 384, 1024)
+    assert U.rel_err_floor(y.float().cpu().numpy(), want) < 1e-2
+
+
+def test_row_quantizer_linear_scales():
+    U.require_gpu()
+    rng = np.random.default_rng(4)
+    k = 1024
+    x = U.gauss_bf16(rng, (1, k), 3.0)
+    dx = U.dev(x)
+    packed = torch.zeros(k // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(k // 16, dtype=torch.uint8, device="cuda")
+    assert U.ffi.call("nv_kernels_nvfp4_quantize_row_bf16", U.stream(), dx.data_ptr(), packed.data_ptr(),
+                      scales.data_ptr(), 2.0, k) == 0
+    torch.cuda.synchronize()
+    pw, lw = ref.quantize_rows_bf16(x, 2.0)
+    assert np.array_equal(packed.cpu().numpy(), pw[0]) and np.array_equal(scales.cpu().numpy(), lw[0])
+
+
+@pytest.mark.parametrize("strided", [False, True])
+def test_per_expert_quantizers(strided):
+    U.require_gpu()
+    rng = np.random.default_rng(8)
+    mpe, tiles, k = 128, 5, 768
+    m = mpe * tiles
+    x = U.gauss_bf16(rng, (m, k), 2.0)
+    up = U.gauss_bf16(rng, (m, k), 1.0)
+    globals_ = np.array([1.0, 0.5, 37.0, 0.0, 448.0], np.float32)
+    name = "nv_kernels_quantize_nvfp4_bf16_per_expert" + ("_strided" if strided else "")
+    dx, du, dg = U.dev(x), U.dev(up), U.dev(globals_)
+    nsw = ref.swizzled_len(m, k // 16)
+    packed = torch.zeros((m, k // 2), dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(nsw, dtype=torch.uint8, device="cuda")
+    assert U.ffi.call(name, U.stream(), dx.data_ptr(), packed.data_ptr(), scales.data_ptr(), dg.data_ptr(), mpe, m,
+                      k) == 0
+    torch.cuda.synchronize()
+    p, s = packed.cpu().numpy(), ref.unswizzle_scales(scales.cpu().numpy(), m, k // 16)
+    rows = range(0, m, mpe) if strided else range(m)
+    for r in rows:
+        pw, lw = ref.quantize_rows_bf16(x[r:r + 1], float(globals_[r // mpe]))
+        assert np.array_equal(p[r], pw[0]) and np.array_equal(s[r], lw[0]), r
+    if strided:
+        assert np.all(p[1:mpe] == 0)  # untouched rows
+        assert U.ffi.call(name, U.stream(), dx.data_ptr(), packed.data_ptr(), scales.data_ptr(), dg.data_ptr(), mpe,
+                          m - 1, k) == -3
+
+    # fused SiLU(gate)*up -> quantize: device expf may differ from libm by an ulp, so allow a
+    # handful of off-by-one codes and no larger difference (the reference's own test allows 2%).
+    name2 = "nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert" + ("_strided" if strided else "")
+    packed.zero_(); scales.zero_()
+    assert U.ffi.call(name2, U.stream(), dx.data_ptr(), du.data_ptr(), packed.data_ptr(), scales.data_ptr(),
+                      dg.data_ptr(), mpe, m, k) == 0
+    torch.cuda.synchronize()
+    p, s = packed.cpu().numpy(), ref.unswizzle_scales(scales.cpu().numpy(), m, k // 16)
+    act = ref.silu_mul(x, up, round_bf16=False)
+    off_by_one = worse = total = 0
+    for r in rows:
+        g = float(globals_[r // mpe])
+        pw, lw = ref.quantize_rows(act[r:r + 1], g)
+        same_scale = s[r] == lw[0]
+        assert same_scale.mean() > 0.995
+        for shift in (0, 4):
+            a = ((p[r] >> shift) & 0xF).astype(np.int32).reshape(-1, 8)[same_scale].ravel()
+            b = ((pw[0] >> shift) & 0xF).astype(np.int32).reshape(-1, 8)[same_scale].ravel()
+            d = np.abs((a & 7) - (b & 7))
+            sign_ok = ((a >> 3) == (b >> 3)) | (((a & 7) == 0) & ((b & 7) == 0))
+            off_by_one += int(np.sum((d == 1) & sign_ok))
+            worse += int(np.sum((d > 1) | ~sign_ok))
+            total += a.size
+    assert worse == 0 and off_by_one <= total // 1000
+
+
+def test_rmsnorm_quantize():
+    U.require_gpu()
+    rng = np.random.default_rng(12)
+    m, k, eps, g = 5, 2048, 1e-6, 3.0
+    x = U.gauss_bf16(rng, (m, k), 1.5)
+    w = U.gauss_bf16(rng, (k,), 1.0)
+    dx, dw = U.dev(x), U.dev(w)
+    mp = 128
+    nsw = ref.swizzled_len(mp, k // 16)
+    packed = torch.zeros((mp, k // 2), dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(nsw, dtype=torch.uint8, device="cuda")
+    assert U.ffi.call("nv_kernels_rmsnorm_quantize_nvfp4_bf16", U.stream(), dx.data_ptr(), dw.data_ptr(),
+                      packed.data_ptr(), scales.data_ptr(), g, eps, mp, m, k) == 0
+    torch.cuda.synchronize()
+    xf, wf = ref.bf16_to_f32(x), ref.bf16_to_f32(w)
+    rstd = (1.0 / np.sqrt((xf.astype(np.float64) ** 2).mean(1) + eps)).astype(np.float32)
+    normed = ref.f32_to_bf16((xf * rstd[:, None]) * wf[None, :])
+    pw, lw = ref.quantize_rows_bf16(normed, g, m_padded=mp)
+    p, s = packed.cpu().numpy(), ref.unswizzle_scales(scales.cpu().numpy(), mp, k // 16)
+    # rsqrtf and the sum order differ from numpy by an ulp: require near-total byte agreement
+    assert (p == pw).mean() > 0.999 and (s == lw).mean() > 0.999
+    assert np.all(p[m:] == 0)
+    assert U.ffi.call("nv_kernels_rmsnorm_quantize_nvfp4_bf16", U.stream(), dx.data_ptr(), dw.data_ptr(),
+                      packed.data_ptr(), scales.data_ptr(), g, eps, 1, 1, 32768) == -3
+
+
+@pytest.mark.parametrize("E,K,mode", [(128, 8, 0), (256, 8, 0), (16, 4, 0), (512, 6, 0), (128, 8, 1)])
+def test_router(E, K, mode):
+    U.require_gpu()
+    rng = np.random.default_rng(E + K)
+    n = 33
+    lg = rng.standard_normal((n, E)).astype(np.float32)
+    lg[0, 5] = lg[0, 77 % E] = 9.0  # a tie at the top
+    bias = (rng.standard_normal(E) * 0.1).astype(np.float32) if mode == 1 else None
+    dl = U.dev(lg)
+    db = U.dev(bias) if bias is not None else None
+    ids = torch.zeros((n, K), dtype=torch.int32, device="cuda")
+    w = torch.zeros((n, K), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_route_topk", U.stream(), dl.data_ptr(), db.data_ptr() if db is not None else None,
+                      ids.data_ptr(), w.data_ptr(), n, E, K, mode, 0.0, 1, 2.5 if mode == 1 else 1.0) == 0
+    torch.cuda.synchronize()
+    wi, ww = ref.moe_route_topk(lg, K, bias=bias, mode=mode, norm_topk=True, routed_scaling=2.5 if mode == 1 else 1.0)
+    assert np.array_equal(ids.cpu().numpy(), wi)
+    np.testing.assert_allclose(w.cpu().numpy(), ww, rtol=2e-6, atol=1e-7)
+    if mode == 0:
+        np.testing.assert_allclose(w.cpu().numpy().sum(1), 1.0, rtol=1e-5)
+    assert U.ffi.call("nv_kernels_moe_route_topk", U.stream(), 0, 0, 0, 0, 1, 8, 9, 0, 0.0, 1, 1.0) == -2
+
+
+def test_router_shared_tail():
+    U.require_gpu()
+    rng = np.random.default_rng(2)
+    n, E, K = 4, 64, 4
+    lg = rng.standard_normal((n, E)).astype(np.float32)
+    dl = U.dev(lg)
+    ids = torch.zeros((n, K + 1), dtype=torch.int32, device="cuda")
+    w = torch.zeros((n, K + 1), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_route_topk_shared_tail", U.stream(), dl.data_ptr(), None, ids.data_ptr(),
+                      w.data_ptr(), n, E, K, 0, 0.0, 1, 1.0, E) == 0
+    torch.cuda.synchronize()
+    wi, ww = ref.moe_route_topk(lg, K)
+    assert np.array_equal(ids.cpu().numpy()[:, :K], wi) and np.all(ids.cpu().numpy()[:, K] == E)
+    assert np.all(w.cpu().numpy()[:, K] == 1.0)
+
+
+def test_gather_unpermute_permute():
+    U.require_gpu()
+    rng = np.random.default_rng(6)
+    n_tok, H, k, E = 6, 200, 3, 10
+    x = U.gauss_bf16(rng, (n_tok, H))
+    src = np.array([2, -1, 5, 0, 9, 3, 3], np.int32)  # -1 and 9 are out of range -> zero rows
+    dx, ds = U.dev(x), U.dev(src)
+    out = torch.full((len(src), H), 0x1111, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_gather_rows_bf16", U.stream(), dx.data_ptr(), ds.data_ptr(), out.data_ptr(),
+                      len(src), H, n_tok) == 0
+    torch.cuda.synchronize()
+    o = U.host_u16(out)
+    for r, s_ in enumerate(src):
+        assert np.array_equal(o[r], x[s_] if 0 <= s_ < n_tok else np.zeros(H, np.uint16))
+    # strided: only rows 0, 3, 6 are written
+    out.fill_(0x1111)
+    src9 = np.array([1, 0, 0, 4, 0, 0, -1, 0, 0], np.int32)
+    ds9 = U.dev(src9)
+    out9 = torch.full((9, H), 0x1111, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_gather_rows_bf16_strided", U.stream(), dx.data_ptr(), ds9.data_ptr(),
+                      out9.data_ptr(), 9, H, n_tok, 3) == 0
+    torch.cuda.synchronize()
+    o9 = U.host_u16(out9)
+    assert np.array_equal(o9[0], x[1]) and np.array_equal(o9[3], x[4]) and np.all(o9[6] == 0)
+    assert np.all(o9[1] == 0x1111)
+    assert U.ffi.call("nv_kernels_gather_rows_bf16_strided", U.stream(), dx.data_ptr(), ds9.data_ptr(),
+                      out9.data_ptr(), 9, H, n_tok, 4) == -3
+
+    # gather_f32_by_ids
+    srcf = rng.standard_normal(E).astype(np.float32)
+    idsf = np.array([3, -1, 9, 0], np.int32)
+    dsf, dif = U.dev(srcf), U.dev(idsf)
+    dst = torch.zeros(4, dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_gather_f32_by_ids", U.stream(), dsf.data_ptr(), dif.data_ptr(), dst.data_ptr(), 4) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), np.array([srcf[3], 0, srcf[9], srcf[0]], np.float32))
+
+    # permute + unpermute
+    topk = np.stack([rng.permutation(E)[:k] for _ in range(n_tok)]).astype(np.int32)
+    dt = U.dev(topk)
+    perm = torch.zeros(n_tok * k, dtype=torch.int32, device="cuda")
+    offs = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    inv = torch.zeros(n_tok * k, dtype=torch.int32, device="cuda")
+    scr = torch.zeros(E, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_permute", U.stream(), dt.data_ptr(), perm.data_ptr(), offs.data_ptr(),
+                      inv.data_ptr(), scr.data_ptr(), n_tok, k, E) == 0
+    torch.cuda.synchronize()
+    perm_h, offs_h, inv_h = perm.cpu().numpy(), offs.cpu().numpy(), inv.cpu().numpy()
+    counts = np.bincount(topk.ravel(), minlength=E)
+    assert np.array_equal(offs_h, np.concatenate([[0], np.cumsum(counts)]))
+    assert sorted(inv_h) == list(range(n_tok * k))
+    for t in range(n_tok * k):
+        e = topk.ravel()[t]
+        assert offs_h[e] <= inv_h[t] < offs_h[e + 1] and perm_h[inv_h[t]] == t // k
+
+    stride = H + 8
+    ys = U.gauss_bf16(rng, (n_tok * k, stride))
+    wts = rng.random((n_tok, k)).astype(np.float32)
+    dy, dw = U.dev(ys), U.dev(wts)
+    acc = torch.zeros((n_tok, H), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_unpermute_scatter", U.stream(), dy.data_ptr(), dw.data_ptr(), inv.data_ptr(),
+                      acc.data_ptr(), n_tok, k, H, stride) == 0
+    torch.cuda.synchronize()
+    want = ref.moe_unpermute_scatter(ys, wts, inv_h.reshape(n_tok, k), H, stride)
+    np.testing.assert_allclose(acc.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+
+    shared = rng.standard_normal((n_tok, H)).astype(np.float32)
+    resid = U.gauss_bf16(rng, (n_tok, H))
+    dsh, dr = U.dev(shared), U.dev(resid)
+    outb = torch.zeros((n_tok, H), dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_unpermute_scatter_tail", U.stream(), dy.data_ptr(), dw.data_ptr(),
+                      inv.data_ptr(), dsh.data_ptr(), dr.data_ptr(), outb.data_ptr(), n_tok, k, H, stride) == 0
+    torch.cuda.synchronize()
+    fb = ref.bf16_to_f32(ref.f32_to_bf16(acc.cpu().numpy() + shared))
+    want_tail = ref.f32_to_bf16(ref.bf16_to_f32(resid) + fb)
+    assert U.bf16_ulp_diff(U.host_u16(outb), want_tail).max() <= 1
+
+
+@pytest.mark.parametrize("n,k", [(512, 2048), (2048, 512), (768, 2048), (200, 272)])
+def test_grouped_w4a4_expert_gemv(n, k):
+    """rust/crates/nv-kernels/tests/moe_grouped_fp4_gemv_parity.rs shapes: grouped == per-expert
+    oracle within 2 bf16 ulp or 1e-3 abs, out-of-range ids write zeros, bit-stable run to run."""
+    U.require_gpu()
+    rng = np.random.default_rng(n + k)
+    E, groups, tile = 6, 9, 128
+    ids = np.array([0, 5, 2, 2, -1, 3, 6, 1, 4], np.int32)  # -1 and 6 are out of range
+    wf = (rng.standard_normal((E, n, k)) * 0.05).astype(np.float32)
+    bp = np.zeros((E, n, k // 2), np.uint8)
+    n_pad, kb_pad = -(-n // 128) * 128, -(-(k // 16) // 4) * 4
+    bs = np.zeros((E, n_pad * kb_pad), np.uint8)
+    b_lin = []
+    alphas = np.zeros(E, np.float32)
+    for e in range(E):
+        g = ref.weight_global(wf[e])
+        p, lin = ref.quantize_rows(wf[e], g)
+        bp[e], bs[e] = p, ref.swizzle_scales(lin)
+        b_lin.append(lin)
+        alphas[e] = np.float32(1.0) / np.float32(g)
+    xa = (rng.standard_normal((groups, k)) * 2.0).astype(np.float32)
+    ap = np.zeros((groups * tile, k // 2), np.uint8)
+    a_sw = np.zeros((groups, tile * kb_pad), np.uint8)
+    a_lin = []
+    for g_ in range(groups):
+        p, lin = ref.quantize_rows(xa[g_:g_ + 1], 1.0)
+        ap[g_ * tile] = p[0]
+        full = np.zeros((tile, k // 16), np.uint8)
+        full[0] = lin[0]
+        a_sw[g_] = ref.swizzle_scales(full)
+        a_lin.append(lin)
+    d_stride = n + 16
+    dev = [U.dev(a) for a in (ap, a_sw, bp, bs, alphas, ids)]
+    d = torch.full((groups, d_stride), 0x7FC0, dtype=torch.int16, device="cuda")
+
+    def run():
+        rc = U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", U.stream(), dev[0].data_ptr(), dev[1].data_ptr(),
+                        dev[2].data_ptr(), dev[3].data_ptr(), dev[4].data_ptr(), d.data_ptr(), dev[5].data_ptr(),
+                        groups, E, n, k, tile, d_stride)
+        assert rc == 0
+        torch.cuda.synchronize()
+        return U.host_u16(d).copy()
+
+    out = run()
+    assert np.array_equal(out, run())  # bit-stable
+    assert np.all(out[:, n:] == 0x7FC0)
+    for g_ in range(groups):
+        e = ids[g_]
+        if e < 0 or e >= E:
+            assert np.all(out[g_, :n] == 0)
+            continue
+        want = ref.matmul_w4a4(ap[g_ * tile:g_ * tile + 1], a_lin[g_], bp[e], b_lin[e], 1, n, k, float(alphas[e]))
+        ulp = U.bf16_ulp_diff(out[g_, :n], want[0])
+        absd = np.abs(ref.bf16_to_f32(out[g_, :n]) - ref.bf16_to_f32(want[0]))
+        assert np.all((ulp <= 2) | (absd <= 1e-3))
+    s = U.stream()
+    assert U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, 0, 0, 0, 0, 0, 0, 0, 70000, E, n, k, 128, n) == -9
+    assert U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, 0, 0, 0, 0, 0, 0, 0, 4, E, n, k, 100, n) == -1
+    assert U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, 4, 0, 0, 0, 0, 0, 0, 4, E, n, k, 128, n) == -2

@@ -1,0 +1,99 @@
+"""Tensor-parallel host logic on CPU: two gloo ranks shard an NVFP4 linear column- and row-parallel,
+run the local shards through the CPU oracle, complete them with the package's own collectives and
+must reproduce the unsharded oracle (column: bit-exact; row: within the bf16 partial-sum rounding)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import ref
+
+
+class OracleLocal:
+    """Stands in for the CUDA shard: same attributes, the contraction done by the CPU oracle."""
+
+    def __init__(self, packed, scales, alpha, k, n):
+        self.p, self.s, self.alpha = packed.numpy(), scales.numpy(), alpha
+        self.in_features, self.out_features = k, n
+
+    def forward_into(self, x, y):
+        xb = x.contiguous().view(torch.int16).numpy().view(np.uint16)
+        out = ref.linear_w4a16_f64(self.p, self.s, xb, self.alpha, self.out_features, self.in_features)
+        y.copy_(torch.from_numpy(ref.f32_to_bf16(out.astype(np.float32)).view(np.int16)).view(torch.bfloat16))
+
+
+def _worker(rank, world, port, n, k, m, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import speaches_plus_b200 as sp
+        from speaches_plus_b200 import tp
+        rng = np.random.default_rng(0)
+        w = ref.f32_to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        packed, sw, alpha = ref.quantize_weight_bf16(w)
+        x = ref.f32_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+        xt = torch.from_numpy(x.view(np.int16)).view(torch.bfloat16)
+        want = ref.linear_w4a16_f64(packed, sw, x, alpha, n, k)
+        res = {}
+        for mode in ("column", "row"):
+            p, s, nl, kl, off = tp.shard_nvfp4(torch.from_numpy(packed), torch.from_numpy(sw), n, k, mode, rank, world)
+            # the shard must be exactly the oracle's slice
+            if mode == "column":
+                lin = ref.unswizzle_scales(sw, n, k // 16)
+                assert np.array_equal(p.numpy(), packed[off:off + nl])
+                assert np.array_equal(ref.unswizzle_scales(s.numpy(), nl, k // 16), lin[off:off + nl])
+            else:
+                lin = ref.unswizzle_scales(sw, n, k // 16)
+                assert np.array_equal(p.numpy(), packed[:, off // 2:(off + kl) // 2])
+                assert np.array_equal(ref.unswizzle_scales(s.numpy(), n, kl // 16), lin[:, off // 16:(off + kl) // 16])
+            t = tp.TpNvfp4Linear(OracleLocal(p, s, alpha, kl, nl), mode, rank, world, n, k, off)
+            y = t.forward(xt).float().numpy()
+            res[mode] = y
+        if rank == 0:
+            q.put((res, want))
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("m", [1, 3])
+def test_two_rank_column_and_row_parallel(m):
+    n, k, world = 512, 1024, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n, k, m, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res, want = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    col = res["column"]
+    assert np.array_equal(ref.f32_to_bf16(col), ref.f32_to_bf16(want.astype(np.float32)))
+    rms = float(np.sqrt(np.mean(want ** 2)))
+    err = np.max(np.abs(res["row"] - want) / np.maximum(np.abs(want), max(rms, 1e-3)))
+    assert err < 1e-2  # two bf16 partials + bf16 sum: well inside the 1e-2 bound
+
+
+def test_shard_ranges_cover_everything():
+    from speaches_plus_b200 import tp
+    for n, world in [(10240, 8), (51200, 8), (4096, 4), (6144, 2), (28672, 8), (151936, 8), (384, 2)]:
+        edges = [tp.column_shard_rows(n, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == n
+        for a, b in zip(edges, edges[1:]):
+            assert a[1] == b[0] and a[0] % 128 == 0
+    for k, world in [(8192, 8), (25600, 8), (14336, 8), (14336, 4), (4096, 2)]:
+        edges = [tp.row_shard_cols(k, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == k
+        for a, b in zip(edges, edges[1:]):
+            assert a[1] == b[0] and a[0] % 64 == 0
