@@ -430,7 +430,9 @@ int nvo_moe_route_topk(const float* logits, const float* bias, int32_t* ids, flo
 }
 
 /* ---- combine: rust/crates/nv-kernels/cuda/moe_unpermute_scatter.cu:6-32 ----
- * y_acc[n,h] = sum_s w[n,s] * bf16(y_sorted[inv_perm[n,s], h]), f32, s in order. */
+ * y_acc[n,h] = sum_s w[n,s] * bf16(y_sorted[inv_perm[n,s], h]), f32, s in order.  The reference
+ * statement `acc += w * v` is device code, which nvcc contracts to one fused multiply-add; fmaf
+ * states that rounding explicitly. */
 void nvo_moe_unpermute_scatter(const uint16_t* y_sorted, const float* w, const int32_t* inv_perm,
                                float* y_acc, int n_tokens, int k, int H, int row_stride) {
     for (int n = 0; n < n_tokens; ++n)
@@ -438,7 +440,7 @@ void nvo_moe_unpermute_scatter(const uint16_t* y_sorted, const float* w, const i
             float acc = 0.0f;
             for (int s = 0; s < k; ++s) {
                 int row = inv_perm[n * k + s];
-                acc += w[n * k + s] * nvo_bf16_to_f32(y_sorted[(size_t)row * row_stride + h]);
+                acc = fmaf(w[n * k + s], nvo_bf16_to_f32(y_sorted[(size_t)row * row_stride + h]), acc);
             }
             y_acc[(size_t)n * H + h] = acc;
         }

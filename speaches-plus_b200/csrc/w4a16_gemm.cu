@@ -58,11 +58,13 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
     return v;
 }
 
-// ue4m3 byte i of `w` -> f16x2 {s, s} * 2^-8 (payload bits placed in the f16 exponent/mantissa
-// fields; f16 subnormals cover exponent 0).  The 2^8 is restored in the epilogue.
-__device__ __forceinline__ uint32_t scale_f16x2(uint32_t w, int i) {
-    uint32_t b = __byte_perm(w, 0u, 0x4040u | (uint32_t)(i << 4) | (uint32_t)(i << 12));  // {0,b,0,b}
-    return (b >> 1) & 0x3F803F80u;
+// Two ue4m3 scale bytes (the low or high half of `w`, bit 7 of each byte already cleared) -> f16x2.
+// ue4m3 is the non-negative half of e4m3, so the hardware e4m3 convert is exact for 0x00..0x7E;
+// 0x7F (never produced by an NVFP4 encoder, NaN in e4m3) converts to NaN.
+__device__ __forceinline__ __half2 scales2_f16(uint32_t w, int half) {
+    uint32_t d;
+    asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo;}" : "=r"(d) : "r"(half ? (w >> 16) : w));
+    return *reinterpret_cast<__half2*>(&d);
 }
 
 struct WFrag {
@@ -77,10 +79,13 @@ __device__ __forceinline__ void ldg_nc_v8(uint32_t (&d)[8], const void* p) {
                  : "l"(p));
 }
 
-template <int NT, bool DUAL, int PRO, int KW, bool V8>
-__global__ void __launch_bounds__(128 * KW, 1) w4a16_mma_kernel(const GemmParams p) {
-    constexpr int THREADS = 128 * KW;
-    constexpr int MT = 8 * NT;  // token columns
+// NT: 8-token column tiles; HG: 32-row groups per CTA (rows per CTA = 32*HG); KW: warps along K.
+template <int NT, bool DUAL, int PRO, int HG, int KW, bool V8>
+__global__ void __launch_bounds__(32 * HG * KW, NT <= 2 ? 2 : 1) w4a16_mma_kernel(const GemmParams p) {
+    constexpr int THREADS = 32 * HG * KW;
+    constexpr int MT = 8 * NT;       // token columns
+    constexpr int ROWS = 32 * HG;    // weight rows per CTA
+    constexpr int SUB = 4 / HG;      // CTAs per 128-row scale tile
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ uint32_t s_amax[MT];   // slice maximum (bf16 magnitude bits), then f32 bits of 2^-pw
     __shared__ int s_pw[MT];          // power of two currently folded into the accumulators
@@ -88,11 +93,13 @@ __global__ void __launch_bounds__(128 * KW, 1) w4a16_mma_kernel(const GemmParams
 
     cg::cluster_group cluster = cg::this_cluster();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int h = warp & 3, kw = warp >> 2;
+    const int hl = warp % HG, kw = warp / HG;  // local row group, K-warp
     const int gid = lane >> 2, tg = lane & 3;
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
-    const int mt = tile - arm * p.tiles_per_arm;
+    const int sub = tile - arm * p.tiles_per_arm;
+    const int mt = sub / SUB;                 // 128-row scale tile
+    const int h = (sub % SUB) * HG + hl;      // 32-row group inside it: rows 8h+gid + 32*d2
     const int crank = blockIdx.x;
     const int nranks = gridDim.x;
     const int M = p.M, N = p.N, K = p.K;
@@ -141,26 +148,39 @@ __global__ void __launch_bounds__(128 * KW, 1) w4a16_mma_kernel(const GemmParams
         f.sc = v0 ? ldg_nc_v4(sc_thread + (size_t)kt * 512) : z;
     };
 
-    const uint8_t* xs_thread = smem + (size_t)gid * p.x_stride + tg * 16;
+    // B-fragment source rows: token 8n+gid, clamped to the last real token so that no load needs a
+    // predicate (columns past M compute a duplicate that is never written out).
+    const uint8_t* xs_tok[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) xs_tok[n] = smem + (size_t)min(8 * n + gid, M - 1) * p.x_stride + tg * 16;
 
     auto compute = [&](const WFrag& f, int s_local) {
-        const uint8_t* xs = xs_thread + (size_t)s_local * 512;
-        const uint32_t scw[4] = {f.sc.x, f.sc.y, f.sc.z, f.sc.w};
+        const int xoff = s_local * 512;
+        const uint32_t scw[4] = {f.sc.x & 0x7F7F7F7Fu, f.sc.y & 0x7F7F7F7Fu, f.sc.z & 0x7F7F7F7Fu,
+                                 f.sc.w & 0x7F7F7F7Fu};
+        __half2 sp[4][2];  // row d2: {s0,s1}, {s2,s3}
+#pragma unroll
+        for (int d2 = 0; d2 < 4; ++d2) {
+            sp[d2][0] = scales2_f16(scw[d2], 0);
+            sp[d2][1] = scales2_f16(scw[d2], 1);
+        }
 #pragma unroll
         for (int wi = 0; wi < 8; ++wi) {
             uint32_t a[4][4];
 #pragma unroll
             for (int d2 = 0; d2 < 4; ++d2) {
                 nvk::e2m1x8_to_f16x2x4(f.w[d2][wi], a[d2][0], a[d2][1], a[d2][2], a[d2][3]);
-                const uint32_t s = scale_f16x2(scw[d2], wi >> 1);
+                const __half2 pr = sp[d2][wi >> 2];
+                const __half2 s = ((wi >> 1) & 1) ? __high2half2(pr) : __low2half2(pr);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) a[d2][i] = nvk::hmul2_u32(a[d2][i], s);
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a[d2][i]), s);
+                    a[d2][i] = *reinterpret_cast<const uint32_t*>(&v);
+                }
             }
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-                if (8 * n + gid < M)
-                    xv = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * n) * p.x_stride + wi * 64);
+                const uint4 xv = *reinterpret_cast<const uint4*>(xs_tok[n] + xoff + wi * 64);
                 mma_f16(acc[0][n], a[0][0], a[1][0], a[0][1], a[1][1], xv.x, xv.y);
                 mma_f16(acc[1][n], a[2][0], a[3][0], a[2][1], a[3][1], xv.x, xv.y);
                 mma_f16(acc[0][n], a[0][2], a[1][2], a[0][3], a[1][3], xv.z, xv.w);
@@ -284,26 +304,27 @@ __global__ void __launch_bounds__(128 * KW, 1) w4a16_mma_kernel(const GemmParams
     // ---- sum the K-warps of this CTA: red[kw][token][row] ----
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem);
-    constexpr int RS = kRowsPerCta + 4;  // padded row count per token column
+    constexpr int RS = ROWS + 4;  // padded row count per token column
 #pragma unroll
     for (int t = 0; t < 2; ++t)
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-            const int rl = 64 * t + 8 * h + gid;  // local row of c0/c1; c2/c3 are 32 rows further
+            // local row index = hl*32 + d2*8 + gid with d2 = 2t (c0/c1) and 2t+1 (c2/c3)
+            const int rl = hl * 32 + 16 * t + gid;
             const int c = 8 * n + 2 * tg;
             float* base = red + (size_t)kw * MT * RS;
-            // undo the activation power of two and the 2^-8 carried by the f16 block scales
-            const float d0 = __uint_as_float((uint32_t)(127 + 8 + s_pw[c]) << 23);
-            const float d1 = __uint_as_float((uint32_t)(127 + 8 + s_pw[c + 1]) << 23);
+            // undo the activation power of two
+            const float d0 = __uint_as_float((uint32_t)(127 + s_pw[c]) << 23);
+            const float d1 = __uint_as_float((uint32_t)(127 + s_pw[c + 1]) << 23);
             base[(c)*RS + rl] = acc[t][n][0] * d0;
             base[(c + 1) * RS + rl] = acc[t][n][1] * d1;
-            base[(c)*RS + rl + 32] = acc[t][n][2] * d0;
-            base[(c + 1) * RS + rl + 32] = acc[t][n][3] * d1;
+            base[(c)*RS + rl + 8] = acc[t][n][2] * d0;
+            base[(c + 1) * RS + rl + 8] = acc[t][n][3] * d1;
         }
     __syncthreads();
     float* part = red + (size_t)KW * MT * RS;  // [token][row] partial of this CTA
-    for (int i = threadIdx.x; i < M * kRowsPerCta; i += THREADS) {
-        const int m = i >> 7, rl = i & 127;
+    for (int i = threadIdx.x; i < M * ROWS; i += THREADS) {
+        const int m = i / ROWS, rl = i % ROWS;
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < KW; ++w) v += red[((size_t)w * MT + m) * RS + rl];
@@ -314,7 +335,7 @@ __global__ void __launch_bounds__(128 * KW, 1) w4a16_mma_kernel(const GemmParams
     if (nranks > 1) cluster.sync(); else __syncthreads();
     const float alpha = p.alpha[arm];
     uint16_t* __restrict__ y = p.y[arm];
-    const int rows_per_rank = kRowsPerCta / nranks;  // nranks in {1,2,4,8}
+    const int rows_per_rank = ROWS / nranks;  // nranks in {1,2,4,8}
     for (int i = threadIdx.x; i < M * rows_per_rank; i += THREADS) {
         const int m = i / rows_per_rank;
         const int rl = crank * rows_per_rank + (i - m * rows_per_rank);
@@ -327,7 +348,8 @@ __global__ void __launch_bounds__(128 * KW, 1) w4a16_mma_kernel(const GemmParams
         } else {
             v = part[m * RS + rl];
         }
-        const int n_out = mt * kRowsPerCta + rl;
+        // undo the local row numbering: rl = hl*32 + d2*8 + g
+        const int n_out = mt * kRowsPerCta + 32 * ((rl >> 3) & 3) + 8 * ((sub % SUB) * HG + (rl >> 5)) + (rl & 7);
         if (n_out < N) y[(size_t)m * N + n_out] = nvk::f32_to_bf16_bits(v * alpha);
     }
     if (nranks > 1) cluster.sync();  // peers may still be reading this CTA's partial
@@ -382,28 +404,33 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
 }
 
 // ------------------------------------------------------------------------------------------
-int g_force_ksplit = 0;  // test/tuning hook, set through nvk_b200_set_tuning
+// test/tuning hooks, set through nvk_b200_set_tuning (0 = automatic)
+int g_force_ksplit = 0, g_force_hg = 0;
 
-template <int NT, bool DUAL, int PRO, int KW, bool V8>
+template <int NT, bool DUAL, int PRO, int HG, int KW, bool V8>
 int launch_mma_v(cudaStream_t stream, GemmParams& p, int ksplit) {
     constexpr int MT = 8 * NT;
-    constexpr int RS = kRowsPerCta + 4;
+    constexpr int RS = 32 * HG + 4;
+    constexpr int SUB = 4 / HG;
+    p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta) * SUB;
     // phase length: keep the staged activations near 64 KiB
     int ph_cap = (64 * 1024) / (max(p.M, 1) * 512);
     ph_cap = max(KW, (ph_cap / KW) * KW);
     p.spc = nvk::ceil_div(p.nsc, ksplit);
     p.ph = min(ph_cap, nvk::ceil_div(p.spc, KW) * KW);
     p.x_stride = p.ph * 512 + 64;
-    size_t smem_x = (size_t)max(p.M, 8) * p.x_stride;
-    size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
-    size_t smem = max(smem_x, smem_red);
+    const size_t smem_x = (size_t)p.M * p.x_stride;
+    const size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
+    const size_t smem = max(smem_x, smem_red);
     static nvk::SmemOptin optin;
-    auto* kern = w4a16_mma_kernel<NT, DUAL, PRO, KW, V8>;
+    auto* kern = w4a16_mma_kernel<NT, DUAL, PRO, HG, KW, V8>;
     if (int rc = optin.ensure((const void*)kern, smem)) return rc;
+    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
+    if (ctas > 65535) return NVK_ERR_GRID_AXIS;
 
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)((DUAL ? 2 : 1) * p.tiles_per_arm), 1);
-    cfg.blockDim = dim3(128 * KW, 1, 1);
+    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)ctas, 1);
+    cfg.blockDim = dim3(32 * HG * KW, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -412,50 +439,45 @@ int launch_mma_v(cudaStream_t stream, GemmParams& p, int ksplit) {
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
-    return (int)e;
+    cfg.numAttrs = ksplit > 1 ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <int NT, bool DUAL, int PRO, int KW>
-int launch_mma(cudaStream_t stream, GemmParams& p, int ksplit) {
+template <int NT, bool DUAL, int PRO, int HG, int KW>
+int launch_mma(cudaStream_t stream, GemmParams& p) {
     // 256-bit weight loads need K % 64 == 0 and 32-byte aligned matrices.
     const bool v8 = (p.K & 63) == 0 && (reinterpret_cast<uintptr_t>(p.wq[0]) & 31u) == 0 &&
                     (!DUAL || (reinterpret_cast<uintptr_t>(p.wq[1]) & 31u) == 0);
-    return v8 ? launch_mma_v<NT, DUAL, PRO, KW, true>(stream, p, ksplit)
-              : launch_mma_v<NT, DUAL, PRO, KW, false>(stream, p, ksplit);
+    // Split K across a cluster only when the row tiles alone leave most SMs idle and every
+    // K-warp still keeps at least two super-chunks.
+    int ksplit = 1;
+    if (g_force_ksplit > 0) {
+        ksplit = g_force_ksplit;
+    } else {
+        const int ctas = (DUAL ? 2 : 1) * nvk::ceil_div(p.N, kRowsPerCta) * (4 / HG);
+        while (ksplit < 8 && ctas * ksplit < 148 && nvk::ceil_div(p.nsc, ksplit * 2) >= 2 * KW) ksplit *= 2;
+    }
+    return v8 ? launch_mma_v<NT, DUAL, PRO, HG, KW, true>(stream, p, ksplit)
+              : launch_mma_v<NT, DUAL, PRO, HG, KW, false>(stream, p, ksplit);
 }
 
-int pick_ksplit(const GemmParams& p, int kw, int arms) {
-    if (g_force_ksplit > 0) return g_force_ksplit;
-    const int tiles = arms * p.tiles_per_arm;
-    int best = 1;
-    // Split K until the grid covers the SMs about twice, while every warp keeps a super-chunk.
-    for (int s = 1; s <= 8; s *= 2) {
-        if (nvk::ceil_div(p.nsc, s) < kw && s > 1) break;
-        best = s;
-        if (tiles * s >= 2 * 148) break;
-    }
-    return best;
+template <int NT, bool DUAL, int PRO>
+int launch_small_nt(cudaStream_t stream, GemmParams& p, int hg) {
+    if (hg == 1) return launch_mma<NT, DUAL, PRO, 1, 8>(stream, p);
+    if (hg == 2) return launch_mma<NT, DUAL, PRO, 2, 4>(stream, p);
+    return launch_mma<NT, DUAL, PRO, 4, 2>(stream, p);
 }
 
 template <bool DUAL, int PRO>
 int dispatch_mma(cudaStream_t stream, GemmParams& p) {
-    const int arms = DUAL ? 2 : 1;
-    if (p.M <= 8) {
-        int ks = pick_ksplit(p, 4, arms);
-        return launch_mma<1, DUAL, PRO, 4>(stream, p, ks);
-    }
-    if (p.M <= 16) {
-        int ks = pick_ksplit(p, 4, arms);
-        return launch_mma<2, DUAL, PRO, 4>(stream, p, ks);
-    }
-    if (p.M <= 32) {
-        int ks = pick_ksplit(p, 2, arms);
-        return launch_mma<4, DUAL, PRO, 2>(stream, p, ks);
-    }
-    int ks = pick_ksplit(p, 2, arms);
-    return launch_mma<8, DUAL, PRO, 2>(stream, p, ks);
+    // Rows per CTA grow with M: a CTA re-stages the activations of its whole K range, so more
+    // tokens want more weight rows per staged activation byte.
+    int hg = p.M <= 2 ? 1 : (p.M <= 4 ? 2 : 4);
+    if (g_force_hg == 1 || g_force_hg == 2 || g_force_hg == 4) hg = g_force_hg;
+    if (p.M <= 8) return launch_small_nt<1, DUAL, PRO>(stream, p, hg);
+    if (p.M <= 16) return launch_small_nt<2, DUAL, PRO>(stream, p, hg);
+    if (p.M <= 32) return launch_mma<4, DUAL, PRO, 4, 2>(stream, p);
+    return launch_mma<8, DUAL, PRO, 4, 2>(stream, p);
 }
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
@@ -479,7 +501,7 @@ int w4a16_linear(cudaStream_t stream, const uint8_t* wq_a, const uint8_t* sc_a, 
     const bool dual = wq_b != nullptr;
     const bool fast = (K & 31) == 0 && M <= 64 && aligned16(wq_a) && aligned16(sc_a) && aligned16(x) &&
                       (!dual || (aligned16(wq_b) && aligned16(sc_b))) && (pro == 0 || aligned16(x2)) &&
-                      (size_t)(dual ? 2 : 1) * p.tiles_per_arm <= 65535;
+                      (size_t)(dual ? 2 : 1) * p.tiles_per_arm * 4 <= 65535;
     if (fast) {
         if (dual) return pro ? dispatch_mma<true, 1>(stream, p) : dispatch_mma<true, 0>(stream, p);
         return pro ? dispatch_mma<false, 1>(stream, p) : dispatch_mma<false, 0>(stream, p);
@@ -499,10 +521,13 @@ int w4a16_linear(cudaStream_t stream, const uint8_t* wq_a, const uint8_t* sc_a, 
 // C ABI.  Reference-named symbols keep the reference's argument order and refusals.
 extern "C" {
 
-int nvk_b200_set_tuning(int force_ksplit) {
+int nvk_b200_set_tuning(int force_ksplit, int force_rows_per_cta) {
     if (force_ksplit != 0 && force_ksplit != 1 && force_ksplit != 2 && force_ksplit != 4 && force_ksplit != 8)
         return NVK_ERR_ARG;
+    if (force_rows_per_cta != 0 && force_rows_per_cta != 32 && force_rows_per_cta != 64 && force_rows_per_cta != 128)
+        return NVK_ERR_ARG;
     g_force_ksplit = force_ksplit;
+    g_force_hg = force_rows_per_cta / 32;
     return 0;
 }
 
