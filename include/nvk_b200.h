@@ -71,9 +71,15 @@ int nvk_b200_linear_nvfp4_w4a16(void* stream, const uint8_t* wq_a, const uint8_t
                                 uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K);
 
 /* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
- * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 32, 64,
- * 128} fixes the rows one CTA owns (M <= 16 only). */
+ * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 16, 32,
+ * 64, 128} fixes the rows one CTA owns (M <= 16 only). */
 int nvk_b200_set_tuning(int force_ksplit, int force_rows_per_cta);
+
+/* No counterpart in the reference.  The W4A16 launches use programmatic dependent launch: a kernel
+ * starts prefetching its weights while the previous kernel of the stream is still running and waits
+ * for that kernel only before it reads activations or writes outputs.  enabled = 0 turns this off
+ * (plain stream order); the default is on. */
+int nvk_b200_set_pdl(int enabled);
 
 /* bf16 weights, M = 1 (lm_head): y[n] = bf16(sum_k W[n,k] x[k]).
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:116-123

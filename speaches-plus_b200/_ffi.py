@@ -22,6 +22,7 @@ SIGNATURES = {
     "nv_kernels_gemm_nvfp4_w4a16_mk_dual": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
     "nvk_b200_linear_nvfp4_w4a16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
     "nvk_b200_set_tuning": [_i, _i],
+    "nvk_b200_set_pdl": [_i],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _f, _i, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16_rows": [_vp, _vp, _vp, _vp, _f, _i, _i],

@@ -2,13 +2,16 @@
 //
 //   y[m, n] = bf16( alpha * sum_k e2m1(W[n,k]) * ue4m3(S[n, k/16]) * x[m, k] ),  fp32 accumulate
 //
-// Weights are streamed once from HBM with 128-bit loads straight into registers, unpacked with
-// the native e2m1x2 -> f16x2 convert, multiplied by their block scale in f16 (exact: a 2-bit by
-// 4-bit significand product) and contracted against the activations on the tensor cores with
-// fp32 accumulation (m16n8k16).  One CTA owns one 128-row tile of the swizzled scale layout, so
-// every 512-byte scale tile is read as whole 16-byte lines; K is split across the CTAs of a
-// thread-block cluster and the partial tiles are summed through distributed shared memory in a
-// fixed order (deterministic, no global scratch).
+// Weights are streamed once from HBM.  Every thread copies its own fragment bytes with 16-byte
+// cp.async (L1 bypass) into a thread-private slot of a shared-memory ring kDepth iterations ahead
+// of use, so the bytes in flight per SM do not depend on registers or on how many warps share the
+// issue slots.  Fragments are unpacked with the native e2m1x2 -> f16x2 convert, multiplied by their
+// block scale in f16 (exact: a 2-bit by 4-bit significand product; scales come from the native
+// e4m3x2 -> f16x2 convert) and contracted against the activations on the tensor cores with fp32
+// accumulation (m16n8k16).  A warp owns a 16-row unit of the 128x4 swizzled scale layout whose
+// scales are 8 contiguous bytes per (row pair, k-tile); K is split over the warps of a CTA and, for
+// small N, over the CTAs of a thread-block cluster whose partial tiles are summed through
+// distributed shared memory in a fixed order (deterministic, no global scratch).
 //
 // Activations are bf16.  They are staged per CTA into shared memory as f16 after an exact
 // power-of-two pre-scale chosen from the slice's own maximum (bf16 has 8 significand bits, f16
@@ -21,7 +24,6 @@
 namespace cg = cooperative_groups;
 
 namespace {
-
 constexpr int kRowsPerCta = 128;
 constexpr int kSuper = 256;  // K elements one warp consumes per iteration (4 scale k-tiles)
 
@@ -39,6 +41,7 @@ struct GemmParams {
     int spc;            // super-chunks per CTA (the CTA's K slice)
     int ph;             // super-chunks staged per phase
     int x_stride;       // bytes between token rows of the staged activations
+    int ring_off;       // byte offset of the weight ring in dynamic shared memory
 };
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -50,42 +53,55 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
+constexpr int kDepth = 4;           // cp.async groups in flight per thread
+constexpr int kSlotBytes = 2560;    // one warp, one iteration: 4 x 512 B of weights + 2 x 256 B of scales
 
-// Two ue4m3 scale bytes (the low or high half of `w`, bit 7 of each byte already cleared) -> f16x2.
+// 16-byte (weights) and 8-byte (scales) asynchronous global -> shared copies; src_bytes == 0 writes
+// zeros without touching global memory.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Two ue4m3 scale bytes (the low half of `w`, bit 7 of each byte already cleared) -> f16x2.
 // ue4m3 is the non-negative half of e4m3, so the hardware e4m3 convert is exact for 0x00..0x7E;
 // 0x7F (never produced by an NVFP4 encoder, NaN in e4m3) converts to NaN.
-__device__ __forceinline__ __half2 scales2_f16(uint32_t w, int half) {
+__device__ __forceinline__ __half2 scales2_f16(uint32_t w) {
     uint32_t d;
-    asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo;}" : "=r"(d) : "r"(half ? (w >> 16) : w));
+    asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo;}" : "=r"(d) : "r"(w));
     return *reinterpret_cast<__half2*>(&d);
 }
 
-struct WFrag {
-    uint32_t w[4][8];  // the thread's 32-byte run of one k-tile (64 values), rows d2 = 0..3
-    uint4 sc;          // word d2 = the 4 block scales of row d2 in this k-tile
-};
-
-// One 256-bit load: a whole 32-byte sector per thread (address must be 32-byte aligned).
-__device__ __forceinline__ void ldg_nc_v8(uint32_t (&d)[8], const void* p) {
-    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7])
-                 : "l"(p));
+// In place: eight bf16 gate values (as 4 words) -> bf16(SiLU(gate) * up), fp32 math, one rounding.
+__device__ __forceinline__ void silu_mul_bf16x8(uint32_t (&ws)[4], const uint4 u) {
+    const uint32_t us[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float g0 = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu), g1 = nvk::bf16_bits_to_f32(ws[i] >> 16);
+        const float u0 = nvk::bf16_bits_to_f32(us[i] & 0xFFFFu), u1 = nvk::bf16_bits_to_f32(us[i] >> 16);
+        const uint32_t a0 = nvk::f32_to_bf16_bits((g0 / (1.0f + expf(-g0))) * u0);
+        const uint32_t a1 = nvk::f32_to_bf16_bits((g1 / (1.0f + expf(-g1))) * u1);
+        ws[i] = a0 | (a1 << 16);
+    }
 }
 
-// NT: 8-token column tiles; HG: 32-row groups per CTA (rows per CTA = 32*HG); KW: warps along K.
-template <int NT, bool DUAL, int PRO, int HG, int KW, bool V8>
-__global__ void __launch_bounds__(32 * HG * KW, NT <= 2 ? 2 : 1) w4a16_mma_kernel(const GemmParams p) {
-    constexpr int THREADS = 32 * HG * KW;
-    constexpr int MT = 8 * NT;       // token columns
-    constexpr int ROWS = 32 * HG;    // weight rows per CTA
-    constexpr int SUB = 4 / HG;      // CTAs per 128-row scale tile
+// A 128-row scale tile holds eight 16-row units u = 2*h + pair: rows 8h + g + 32*(2*pair + i),
+// g = 0..7, i = 0..1 -- the 16 rows of one m16n8k16 A tile whose scales are 8 contiguous bytes per
+// (g, k-tile).  One warp owns one unit; a CTA owns UG consecutive units and KW warps along K.
+// A warp iteration covers 256 K values ("super-chunk"): lane (g, tg) takes, for each of its two
+// rows, the two 16-byte pieces at K offsets 32*tg and 128 + 32*tg, so that one cp.async instruction
+// moves whole 64-byte runs per row.  NT: number of 8-token column tiles.
+template <int NT, bool DUAL, int PRO, int UG, int KW>
+__global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
+    constexpr int THREADS = 32 * UG * KW;
+    constexpr int MT = 8 * NT;      // token columns
+    constexpr int ROWS = 16 * UG;   // weight rows per CTA
+    constexpr int SUB = 8 / UG;     // CTAs per 128-row scale tile
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ uint32_t s_amax[MT];   // slice maximum (bf16 magnitude bits), then f32 bits of 2^-pw
     __shared__ int s_pw[MT];          // power of two currently folded into the accumulators
@@ -93,139 +109,184 @@ __global__ void __launch_bounds__(32 * HG * KW, NT <= 2 ? 2 : 1) w4a16_mma_kerne
 
     cg::cluster_group cluster = cg::this_cluster();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int hl = warp % HG, kw = warp / HG;  // local row group, K-warp
+    const int ul = warp % UG, kw = warp / UG;  // local unit, K-warp
     const int gid = lane >> 2, tg = lane & 3;
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     const int sub = tile - arm * p.tiles_per_arm;
-    const int mt = sub / SUB;                 // 128-row scale tile
-    const int h = (sub % SUB) * HG + hl;      // 32-row group inside it: rows 8h+gid + 32*d2
+    const int mt = sub / SUB;               // 128-row scale tile
+    const int u = (sub % SUB) * UG + ul;    // unit inside it
+    const int h = u >> 1, pair = u & 1;
     const int crank = blockIdx.x;
     const int nranks = gridDim.x;
     const int M = p.M, N = p.N, K = p.K;
 
     const uint8_t* __restrict__ wq = p.wq[arm];
     const uint8_t* __restrict__ sc = p.sc[arm];
-    const int row0 = mt * kRowsPerCta + 8 * h + gid;  // + 32 * d2
+    const int row0 = mt * kRowsPerCta + 64 * pair + 8 * h + gid;  // second row is 32 further
     const size_t half_k = (size_t)(K >> 1);
-    const uint8_t* sc_thread = sc + (size_t)mt * p.k_tiles * 512 + (size_t)(8 * h + gid) * 16;
+    const bool rv0 = row0 < N, rv1 = row0 + 32 < N;
+    const uint8_t* w_row0 = rv0 ? wq + (size_t)row0 * half_k + tg * 16 : wq;
+    const uint8_t* w_row1 = rv1 ? wq + (size_t)(row0 + 32) * half_k + tg * 16 : wq;
+    const uint8_t* sc_thread =
+        sc + (size_t)mt * p.k_tiles * 512 + (size_t)(8 * h + gid) * 16 + pair * 8 + (size_t)(tg >> 1) * 512;
+
+    // shared memory: [activations / reduction scratch | weight ring]
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)p.ring_off +
+                          (uint32_t)(warp * kDepth * kSlotBytes) + (uint32_t)lane * 16;
+    const uint8_t* ring_g = smem + p.ring_off + warp * kDepth * kSlotBytes + lane * 16;
 
     const int sc_begin = crank * p.spc;
     const int sc_end = min(p.nsc, sc_begin + p.spc);
 
-    float acc[2][NT][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int t = 0; t < 2; ++t)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[t][n][i] = 0.f;
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
-    auto load_frag = [&](WFrag& f, int s) {
-        const int kt = 4 * s + tg;
-        const int k0 = kt * 64;
-        const bool v0 = k0 < K, v1 = (k0 + 32) < K;
-        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    // Enqueue the copies of super-chunk s into ring slot `slot` (a no-op past the end of the slice).
+    auto issue = [&](int s, int slot) {
+        if (s < sc_end) {
+            const uint32_t dst = ring + (uint32_t)(slot * kSlotBytes);
 #pragma unroll
-        for (int d2 = 0; d2 < 4; ++d2) {
-            const int r = row0 + 32 * d2;
-            const uint8_t* src = wq + (size_t)r * half_k + (size_t)(k0 >> 1);
-            const bool rv = r < N;
-            if (V8) {
-                if (rv && v0) {
-                    ldg_nc_v8(f.w[d2], src);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) f.w[d2][i] = 0u;
-                }
-            } else {
-                const uint4 lo = (rv && v0) ? ldg_nc_v4(src) : z;
-                const uint4 hi = (rv && v1) ? ldg_nc_v4(src + 16) : z;
-                f.w[d2][0] = lo.x; f.w[d2][1] = lo.y; f.w[d2][2] = lo.z; f.w[d2][3] = lo.w;
-                f.w[d2][4] = hi.x; f.w[d2][5] = hi.y; f.w[d2][6] = hi.z; f.w[d2][7] = hi.w;
+            for (int pc = 0; pc < 2; ++pc) {
+                const int kk = s * kSuper + 128 * pc + 32 * tg;   // first K value of this piece
+                const int okk = kk < K ? 16 : 0;
+                const size_t off = (size_t)s * 128 + pc * 64;
+                cp_async16(dst + (0 * 2 + pc) * 512, w_row0 + off, rv0 ? okk : 0);
+                cp_async16(dst + (1 * 2 + pc) * 512, w_row1 + off, rv1 ? okk : 0);
+                cp_async8(dst - (uint32_t)lane * 8 + 2048 + pc * 256, sc_thread + (size_t)(4 * s + 2 * pc) * 512,
+                          okk ? 8 : 0);
             }
         }
-        f.sc = v0 ? ldg_nc_v4(sc_thread + (size_t)kt * 512) : z;
+        cp_async_commit();
     };
 
     // B-fragment source rows: token 8n+gid, clamped to the last real token so that no load needs a
     // predicate (columns past M compute a duplicate that is never written out).
-    const uint8_t* xs_tok[NT];
+    uint32_t xs_tok[NT];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) xs_tok[n] = smem + (size_t)min(8 * n + gid, M - 1) * p.x_stride + tg * 16;
+    for (int n = 0; n < NT; ++n) xs_tok[n] = (uint32_t)(min(8 * n + gid, M - 1) * p.x_stride + tg * 16);
 
-    auto compute = [&](const WFrag& f, int s_local) {
-        const int xoff = s_local * 512;
-        const uint32_t scw[4] = {f.sc.x & 0x7F7F7F7Fu, f.sc.y & 0x7F7F7F7Fu, f.sc.z & 0x7F7F7F7Fu,
-                                 f.sc.w & 0x7F7F7F7Fu};
-        __half2 sp[4][2];  // row d2: {s0,s1}, {s2,s3}
+    auto compute = [&](int slot, int s_local) {
+        const uint8_t* src = ring_g + slot * kSlotBytes;
+        const uint8_t* xs = smem + s_local * 512;
+        uint4 w[2][2];
 #pragma unroll
-        for (int d2 = 0; d2 < 4; ++d2) {
-            sp[d2][0] = scales2_f16(scw[d2], 0);
-            sp[d2][1] = scales2_f16(scw[d2], 1);
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int pc = 0; pc < 2; ++pc) w[i][pc] = *reinterpret_cast<const uint4*>(src + (i * 2 + pc) * 512);
+        __half2 sp[2][2];  // [row i][piece]: the two block scales this lane's 32 values use
+#pragma unroll
+        for (int pc = 0; pc < 2; ++pc) {
+            const uint2 sw = *reinterpret_cast<const uint2*>(src - lane * 8 + 2048 + pc * 256);
+            sp[0][pc] = scales2_f16((sw.x & 0x7F7F7F7Fu) >> (16 * (tg & 1)));
+            sp[1][pc] = scales2_f16((sw.y & 0x7F7F7F7Fu) >> (16 * (tg & 1)));
         }
 #pragma unroll
         for (int wi = 0; wi < 8; ++wi) {
-            uint32_t a[4][4];
+            uint32_t a[2][4];
 #pragma unroll
-            for (int d2 = 0; d2 < 4; ++d2) {
-                nvk::e2m1x8_to_f16x2x4(f.w[d2][wi], a[d2][0], a[d2][1], a[d2][2], a[d2][3]);
-                const __half2 pr = sp[d2][wi >> 2];
-                const __half2 s = ((wi >> 1) & 1) ? __high2half2(pr) : __low2half2(pr);
+            for (int i = 0; i < 2; ++i) {
+                const uint4& q = w[i][wi >> 2];
+                const uint32_t word = (wi & 3) == 0 ? q.x : (wi & 3) == 1 ? q.y : (wi & 3) == 2 ? q.z : q.w;
+                nvk::e2m1x8_to_f16x2x4(word, a[i][0], a[i][1], a[i][2], a[i][3]);
+                const __half2 pr = sp[i][wi >> 2];
+                const __half2 sc2 = (wi & 2) ? __high2half2(pr) : __low2half2(pr);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a[d2][i]), s);
-                    a[d2][i] = *reinterpret_cast<const uint32_t*>(&v);
+                for (int j = 0; j < 4; ++j) {
+                    const __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a[i][j]), sc2);
+                    a[i][j] = *reinterpret_cast<const uint32_t*>(&v);
                 }
             }
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xs_tok[n] + xoff + wi * 64);
-                mma_f16(acc[0][n], a[0][0], a[1][0], a[0][1], a[1][1], xv.x, xv.y);
-                mma_f16(acc[1][n], a[2][0], a[3][0], a[2][1], a[3][1], xv.x, xv.y);
-                mma_f16(acc[0][n], a[0][2], a[1][2], a[0][3], a[1][3], xv.z, xv.w);
-                mma_f16(acc[1][n], a[2][2], a[3][2], a[2][3], a[3][3], xv.z, xv.w);
+                const uint4 xv = *reinterpret_cast<const uint4*>(xs + xs_tok[n] + wi * 64);
+                mma_f16(acc[n], a[0][0], a[1][0], a[0][1], a[1][1], xv.x, xv.y);
+                mma_f16(acc[n], a[0][2], a[1][2], a[0][3], a[1][3], xv.z, xv.w);
             }
         }
     };
 
+    // Programmatic dependent launch: let the next kernel in the stream start its own weight
+    // prefetch while this one runs, and prefetch our weights (which no earlier kernel writes) before
+    // waiting for the previous kernel, whose output may be our activations.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    int s_issue = sc_begin + kw, n_issued = 0, n_done = 0;
+#pragma unroll
+    for (int d = 0; d < kDepth - 1; ++d) {
+        issue(s_issue, n_issued % kDepth);
+        s_issue += KW;
+        ++n_issued;
+    }
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
     for (int p0 = sc_begin; p0 < sc_end; p0 += p.ph) {
         const int pend = min(sc_end, p0 + p.ph);
         const int nsp = pend - p0;
-        // Weight loads do not depend on the activations: put the first ones in flight now.
-        WFrag f0, f1;
-        int s = p0 + kw;
-        if (s < pend) load_frag(f0, s);
 
         // ---- stage activations for super-chunks [p0, pend) ----
         if (threadIdx.x < MT) s_amax[threadIdx.x] = 0u;
         __syncthreads();  // also orders the previous phase's reads before this phase's writes
         const int pieces_per_tok = nsp * 32;
         const int total_pieces = M * pieces_per_tok;
-        for (int idx = threadIdx.x; idx < total_pieces; idx += THREADS) {
+        // Each 16-byte piece (8 activations) is loaded once and kept in registers across the
+        // block-wide maximum when the phase is small enough (kXRegs pieces per thread); larger
+        // phases re-read the piece (an L1/L2 hit) for the conversion pass.
+        constexpr int kXRegs = 4;
+        const bool keep = total_pieces <= kXRegs * THREADS;
+        uint4 xr[kXRegs];
+        auto load_piece = [&](int idx, uint32_t (&ws)[4]) -> bool {
             const int m = idx / pieces_per_tok;
             const int rem = idx - m * pieces_per_tok;
             const int k = (p0 + (rem >> 5)) * kSuper + (rem & 31) * 8;
-            uint32_t mx = 0u;
-            if (k < K) {
-                uint4 v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k);
-                uint32_t ws[4] = {v.x, v.y, v.z, v.w};
-                if (PRO == 1) {
-                    uint4 u = *reinterpret_cast<const uint4*>(p.x2 + (size_t)m * K + k);
-                    uint32_t us[4] = {u.x, u.y, u.z, u.w};
+            if (k >= K) return false;
+            const uint4 v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k);
+            ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
+            if (PRO == 1) silu_mul_bf16x8(ws, *reinterpret_cast<const uint4*>(p.x2 + (size_t)m * K + k));
+            return true;
+        };
+        auto store_piece = [&](int idx, const uint32_t (&ws)[4], bool valid) {
+            const int m = idx / pieces_per_tok;
+            const int rem = idx - m * pieces_per_tok;
+            const int scl = rem >> 5, q = rem & 31;
+            uint4 o = make_uint4(0u, 0u, 0u, 0u);
+            if (valid) {
+                const float sc2 = __uint_as_float(s_amax[m]);
+                uint32_t os[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float g0 = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu), g1 = nvk::bf16_bits_to_f32(ws[i] >> 16);
-                        float u0 = nvk::bf16_bits_to_f32(us[i] & 0xFFFFu), u1 = nvk::bf16_bits_to_f32(us[i] >> 16);
-                        uint32_t a0 = nvk::f32_to_bf16_bits((g0 / (1.0f + expf(-g0))) * u0);
-                        uint32_t a1 = nvk::f32_to_bf16_bits((g1 / (1.0f + expf(-g1))) * u1);
-                        ws[i] = a0 | (a1 << 16);
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const float lo = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu) * sc2;
+                    const float hi = nvk::bf16_bits_to_f32(ws[i] >> 16) * sc2;
+                    const __half2 h2 = __floats2half2_rn(lo, hi);
+                    os[i] = *reinterpret_cast<const uint32_t*>(&h2);
                 }
+                o = make_uint4(os[0], os[1], os[2], os[3]);
+            }
+            // 8-value piece q of a super-chunk belongs to lane column tg' = (q % 16) / 4 and is that
+            // lane's fragment word wi = 4*(q / 16) + q % 4; pieces with equal wi are stored adjacently
+            // (conflict-free 128-bit fragment reads).
+            const int off = m * p.x_stride + scl * 512 + ((4 * (q >> 4) + (q & 3)) * 4 + ((q & 15) >> 2)) * 16;
+            *reinterpret_cast<uint4*>(smem + off) = o;
+        };
+#pragma unroll
+        for (int j = 0; j < kXRegs; ++j) xr[j] = make_uint4(0u, 0u, 0u, 0u);
+        {
+            int j = 0;
+            for (int idx = threadIdx.x; idx < total_pieces; idx += THREADS, ++j) {
+                uint32_t ws[4] = {0u, 0u, 0u, 0u};
+                const bool valid = load_piece(idx, ws);
+                uint32_t mx = 0u;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) mx = max(mx, max(ws[i] & 0x7FFFu, (ws[i] >> 16) & 0x7FFFu));
+                if (valid && mx) atomicMax(&s_amax[idx / pieces_per_tok], mx);
+                if (keep) {
+#pragma unroll
+                    for (int r = 0; r < kXRegs; ++r)
+                        if (r == j) xr[r] = make_uint4(ws[0], ws[1], ws[2], ws[3]);
+                }
             }
-            if (mx) atomicMax(&s_amax[m], mx);
         }
         __syncthreads();
         if (threadIdx.x < MT) {
@@ -243,84 +304,79 @@ __global__ void __launch_bounds__(32 * HG * KW, NT <= 2 ? 2 : 1) w4a16_mma_kerne
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const float r0 = s_rescale[8 * n + 2 * tg], r1 = s_rescale[8 * n + 2 * tg + 1];
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    acc[t][n][0] *= r0; acc[t][n][1] *= r1; acc[t][n][2] *= r0; acc[t][n][3] *= r1;
-                }
+                acc[n][0] *= r0; acc[n][1] *= r1; acc[n][2] *= r0; acc[n][3] *= r1;
             }
         }
-        for (int idx = threadIdx.x; idx < total_pieces; idx += THREADS) {
-            const int m = idx / pieces_per_tok;
-            const int rem = idx - m * pieces_per_tok;
-            const int scl = rem >> 5, q = rem & 31;
-            const int k = (p0 + scl) * kSuper + q * 8;
-            uint4 o = make_uint4(0u, 0u, 0u, 0u);
-            if (k < K) {
-                uint4 v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k);
-                uint32_t ws[4] = {v.x, v.y, v.z, v.w};
-                if (PRO == 1) {
-                    uint4 u = *reinterpret_cast<const uint4*>(p.x2 + (size_t)m * K + k);
-                    uint32_t us[4] = {u.x, u.y, u.z, u.w};
+        {
+            int j = 0;
+            for (int idx = threadIdx.x; idx < total_pieces; idx += THREADS, ++j) {
+                uint32_t ws[4] = {0u, 0u, 0u, 0u};
+                bool valid;
+                if (keep) {
+                    uint4 v = xr[0];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float g0 = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu), g1 = nvk::bf16_bits_to_f32(ws[i] >> 16);
-                        float u0 = nvk::bf16_bits_to_f32(us[i] & 0xFFFFu), u1 = nvk::bf16_bits_to_f32(us[i] >> 16);
-                        uint32_t a0 = nvk::f32_to_bf16_bits((g0 / (1.0f + expf(-g0))) * u0);
-                        uint32_t a1 = nvk::f32_to_bf16_bits((g1 / (1.0f + expf(-g1))) * u1);
-                        ws[i] = a0 | (a1 << 16);
-                    }
+                    for (int r = 1; r < kXRegs; ++r)
+                        if (r == j) v = xr[r];
+                    ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
+                    const int rem = idx % pieces_per_tok;
+                    valid = (p0 + (rem >> 5)) * kSuper + (rem & 31) * 8 < K;
+                } else {
+                    valid = load_piece(idx, ws);
                 }
-                const float sc2 = __uint_as_float(s_amax[m]);
-                uint32_t os[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float lo = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu) * sc2;
-                    float hi = nvk::bf16_bits_to_f32(ws[i] >> 16) * sc2;
-                    __half2 h2 = __floats2half2_rn(lo, hi);
-                    os[i] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-                o = make_uint4(os[0], os[1], os[2], os[3]);
+                store_piece(idx, ws, valid);
             }
-            // piece q of a super-chunk: k-tile tg' = q / 8, 16-byte piece j2 = q % 8; stored so that
-            // the four k-tiles' pieces with equal j2 are adjacent (conflict-free fragment reads).
-            const int off = m * p.x_stride + scl * 512 + ((q & 7) * 4 + (q >> 3)) * 16;
-            *reinterpret_cast<uint4*>(smem + off) = o;
         }
         __syncthreads();
-
-        // ---- stream this phase's weights ----
-        for (; s < pend; s += 2 * KW) {
-            const int s1 = s + KW;
-            if (s1 < pend) load_frag(f1, s1);
-            compute(f0, s - p0);
-            if (s1 < pend) {
-                if (s1 + KW < pend) load_frag(f0, s1 + KW);
-                compute(f1, s1 - p0);
-            }
+        // ---- stream this phase's weights through the ring ----
+        for (int s = p0 + kw; s < pend; s += KW) {
+            issue(s_issue, n_issued % kDepth);
+            s_issue += KW;
+            ++n_issued;
+            cp_async_wait<kDepth - 1>();  // this thread's copies for super-chunk s have landed
+            compute(n_done % kDepth, s - p0);
+            ++n_done;
         }
     }
+    cp_async_wait<0>();
     if (sc_begin >= sc_end && threadIdx.x < MT) s_pw[threadIdx.x] = 0;  // empty slice: acc is zero
+
+    if (KW == 1 && nranks == 1) {
+        // One warp saw the whole of K for its rows: the accumulator fragment is the result.
+        const float alpha1 = p.alpha[arm];
+        uint16_t* __restrict__ y1 = p.y[arm];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int m = 8 * n + 2 * tg + (j & 1);
+                const int r = row0 + 32 * (j >> 1);
+                if (m < M && r < N) {
+                    const float d = __uint_as_float((uint32_t)(127 + s_pw[m]) << 23);
+                    y1[(size_t)m * N + r] = nvk::f32_to_bf16_bits((acc[n][j] * d) * alpha1);
+                }
+            }
+        }
+        return;
+    }
 
     // ---- sum the K-warps of this CTA: red[kw][token][row] ----
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem);
     constexpr int RS = ROWS + 4;  // padded row count per token column
 #pragma unroll
-    for (int t = 0; t < 2; ++t)
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            // local row index = hl*32 + d2*8 + gid with d2 = 2t (c0/c1) and 2t+1 (c2/c3)
-            const int rl = hl * 32 + 16 * t + gid;
-            const int c = 8 * n + 2 * tg;
-            float* base = red + (size_t)kw * MT * RS;
-            // undo the activation power of two
-            const float d0 = __uint_as_float((uint32_t)(127 + s_pw[c]) << 23);
-            const float d1 = __uint_as_float((uint32_t)(127 + s_pw[c + 1]) << 23);
-            base[(c)*RS + rl] = acc[t][n][0] * d0;
-            base[(c + 1) * RS + rl] = acc[t][n][1] * d1;
-            base[(c)*RS + rl + 8] = acc[t][n][2] * d0;
-            base[(c + 1) * RS + rl + 8] = acc[t][n][3] * d1;
-        }
+    for (int n = 0; n < NT; ++n) {
+        // local row index = ul*16 + i*8 + gid with i = 0 (c0/c1) and 1 (c2/c3)
+        const int rl = ul * 16 + gid;
+        const int c = 8 * n + 2 * tg;
+        float* base = red + (size_t)kw * MT * RS;
+        // undo the activation power of two
+        const float d0 = __uint_as_float((uint32_t)(127 + s_pw[c]) << 23);
+        const float d1 = __uint_as_float((uint32_t)(127 + s_pw[c + 1]) << 23);
+        base[(c)*RS + rl] = acc[n][0] * d0;
+        base[(c + 1) * RS + rl] = acc[n][1] * d1;
+        base[(c)*RS + rl + 8] = acc[n][2] * d0;
+        base[(c + 1) * RS + rl + 8] = acc[n][3] * d1;
+    }
     __syncthreads();
     float* part = red + (size_t)KW * MT * RS;  // [token][row] partial of this CTA
     for (int i = threadIdx.x; i < M * ROWS; i += THREADS) {
@@ -348,8 +404,9 @@ __global__ void __launch_bounds__(32 * HG * KW, NT <= 2 ? 2 : 1) w4a16_mma_kerne
         } else {
             v = part[m * RS + rl];
         }
-        // undo the local row numbering: rl = hl*32 + d2*8 + g
-        const int n_out = mt * kRowsPerCta + 32 * ((rl >> 3) & 3) + 8 * ((sub % SUB) * HG + (rl >> 5)) + (rl & 7);
+        // undo the local row numbering: rl = ul*16 + i*8 + g, unit = (sub % SUB)*UG + ul
+        const int uu = (sub % SUB) * UG + (rl >> 4);
+        const int n_out = mt * kRowsPerCta + 32 * (2 * (uu & 1) + ((rl >> 3) & 1)) + 8 * (uu >> 1) + (rl & 7);
         if (n_out < N) y[(size_t)m * N + n_out] = nvk::f32_to_bf16_bits(v * alpha);
     }
     if (nranks > 1) cluster.sync();  // peers may still be reading this CTA's partial
@@ -405,79 +462,83 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
 
 // ------------------------------------------------------------------------------------------
 // test/tuning hooks, set through nvk_b200_set_tuning (0 = automatic)
-int g_force_ksplit = 0, g_force_hg = 0;
+int g_force_ksplit = 0, g_force_ug = 0;
+int g_pdl = 1;  // programmatic dependent launch on every tensor-core-route launch
 
-template <int NT, bool DUAL, int PRO, int HG, int KW, bool V8>
-int launch_mma_v(cudaStream_t stream, GemmParams& p, int ksplit) {
-    constexpr int MT = 8 * NT;
-    constexpr int RS = 32 * HG + 4;
-    constexpr int SUB = 4 / HG;
-    p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta) * SUB;
-    // phase length: keep the staged activations near 64 KiB
-    int ph_cap = (64 * 1024) / (max(p.M, 1) * 512);
-    ph_cap = max(KW, (ph_cap / KW) * KW);
-    p.spc = nvk::ceil_div(p.nsc, ksplit);
-    p.ph = min(ph_cap, nvk::ceil_div(p.spc, KW) * KW);
-    p.x_stride = p.ph * 512 + 64;
-    const size_t smem_x = (size_t)p.M * p.x_stride;
-    const size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
-    const size_t smem = max(smem_x, smem_red);
-    static nvk::SmemOptin optin;
-    auto* kern = w4a16_mma_kernel<NT, DUAL, PRO, HG, KW, V8>;
-    if (int rc = optin.ensure((const void*)kern, smem)) return rc;
-    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
-    if (ctas > 65535) return NVK_ERR_GRID_AXIS;
-
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)ctas, 1);
-    cfg.blockDim = dim3(32 * HG * KW, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)ksplit;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = ksplit > 1 ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, kern, p);
-}
-
-template <int NT, bool DUAL, int PRO, int HG, int KW>
+template <int NT, bool DUAL, int PRO, int UG, int KW>
 int launch_mma(cudaStream_t stream, GemmParams& p) {
-    // 256-bit weight loads need K % 64 == 0 and 32-byte aligned matrices.
-    const bool v8 = (p.K & 63) == 0 && (reinterpret_cast<uintptr_t>(p.wq[0]) & 31u) == 0 &&
-                    (!DUAL || (reinterpret_cast<uintptr_t>(p.wq[1]) & 31u) == 0);
+    constexpr int MT = 8 * NT;
+    constexpr int RS = 16 * UG + 4;
+    constexpr int SUB = 8 / UG;
     // Split K across a cluster only when the row tiles alone leave most SMs idle and every
     // K-warp still keeps at least two super-chunks.
     int ksplit = 1;
     if (g_force_ksplit > 0) {
         ksplit = g_force_ksplit;
     } else {
-        const int ctas = (DUAL ? 2 : 1) * nvk::ceil_div(p.N, kRowsPerCta) * (4 / HG);
+        const int ctas = (DUAL ? 2 : 1) * nvk::ceil_div(p.N, kRowsPerCta) * SUB;
         while (ksplit < 8 && ctas * ksplit < 148 && nvk::ceil_div(p.nsc, ksplit * 2) >= 2 * KW) ksplit *= 2;
     }
-    return v8 ? launch_mma_v<NT, DUAL, PRO, HG, KW, true>(stream, p, ksplit)
-              : launch_mma_v<NT, DUAL, PRO, HG, KW, false>(stream, p, ksplit);
+    p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta) * SUB;
+    // phase length: keep the staged activations near 48 KiB
+    int ph_cap = (48 * 1024) / (max(p.M, 1) * 512);
+    ph_cap = max(KW, (ph_cap / KW) * KW);
+    p.spc = nvk::ceil_div(p.nsc, ksplit);
+    p.ph = min(ph_cap, nvk::ceil_div(p.spc, KW) * KW);
+    p.x_stride = p.ph * 512 + 64;
+    const size_t smem_x = (size_t)p.M * p.x_stride;
+    const size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
+    p.ring_off = (int)((max(smem_x, smem_red) + 127) / 128 * 128);
+    const size_t smem = (size_t)p.ring_off + (size_t)UG * KW * kDepth * kSlotBytes;
+    static nvk::SmemOptin optin;
+    auto* kern = w4a16_mma_kernel<NT, DUAL, PRO, UG, KW>;
+    if (int rc = optin.ensure((const void*)kern, smem)) return rc;
+    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
+    if (ctas > 65535) return NVK_ERR_GRID_AXIS;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)ctas, 1);
+    cfg.blockDim = dim3(32 * UG * KW, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (ksplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)ksplit;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (g_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <int NT, bool DUAL, int PRO>
-int launch_small_nt(cudaStream_t stream, GemmParams& p, int hg) {
-    if (hg == 1) return launch_mma<NT, DUAL, PRO, 1, 8>(stream, p);
-    if (hg == 2) return launch_mma<NT, DUAL, PRO, 2, 4>(stream, p);
-    return launch_mma<NT, DUAL, PRO, 4, 2>(stream, p);
+int launch_by_rows(cudaStream_t stream, GemmParams& p, int ug) {
+    if (ug == 1) return launch_mma<NT, DUAL, PRO, 1, 8>(stream, p);
+    if (ug == 2) return launch_mma<NT, DUAL, PRO, 2, 4>(stream, p);
+    if (ug == 4) return launch_mma<NT, DUAL, PRO, 4, 2>(stream, p);
+    return launch_mma<NT, DUAL, PRO, 8, 1>(stream, p);
 }
 
 template <bool DUAL, int PRO>
 int dispatch_mma(cudaStream_t stream, GemmParams& p) {
-    // Rows per CTA grow with M: a CTA re-stages the activations of its whole K range, so more
-    // tokens want more weight rows per staged activation byte.
-    int hg = p.M <= 2 ? 1 : (p.M <= 4 ? 2 : 4);
-    if (g_force_hg == 1 || g_force_hg == 2 || g_force_hg == 4) hg = g_force_hg;
-    if (p.M <= 8) return launch_small_nt<1, DUAL, PRO>(stream, p, hg);
-    if (p.M <= 16) return launch_small_nt<2, DUAL, PRO>(stream, p, hg);
-    if (p.M <= 32) return launch_mma<4, DUAL, PRO, 4, 2>(stream, p);
-    return launch_mma<8, DUAL, PRO, 4, 2>(stream, p);
+    // One CTA owns a whole 128-row scale tile and each warp sums all of its K slice in order, for
+    // every M: the order in which K is summed depends on (N, K) only, so a row gives the same bits
+    // whatever the batch size.  Smaller CTAs (more K-warps) exist for tuning and are tested.
+    int ug = 8;
+    if (g_force_ug == 1 || g_force_ug == 2 || g_force_ug == 4 || g_force_ug == 8) ug = g_force_ug;
+    if (p.M <= 8) return launch_by_rows<1, DUAL, PRO>(stream, p, ug);
+    if (p.M <= 16) return launch_by_rows<2, DUAL, PRO>(stream, p, ug < 2 ? 2 : ug);
+    if (p.M <= 32) return launch_mma<4, DUAL, PRO, 8, 1>(stream, p);
+    return launch_mma<8, DUAL, PRO, 8, 1>(stream, p);
 }
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
@@ -521,13 +582,19 @@ int w4a16_linear(cudaStream_t stream, const uint8_t* wq_a, const uint8_t* sc_a, 
 // C ABI.  Reference-named symbols keep the reference's argument order and refusals.
 extern "C" {
 
+int nvk_b200_set_pdl(int enabled) {
+    g_pdl = enabled ? 1 : 0;
+    return 0;
+}
+
 int nvk_b200_set_tuning(int force_ksplit, int force_rows_per_cta) {
     if (force_ksplit != 0 && force_ksplit != 1 && force_ksplit != 2 && force_ksplit != 4 && force_ksplit != 8)
         return NVK_ERR_ARG;
-    if (force_rows_per_cta != 0 && force_rows_per_cta != 32 && force_rows_per_cta != 64 && force_rows_per_cta != 128)
+    if (force_rows_per_cta != 0 && force_rows_per_cta != 16 && force_rows_per_cta != 32 && force_rows_per_cta != 64 &&
+        force_rows_per_cta != 128)
         return NVK_ERR_ARG;
     g_force_ksplit = force_ksplit;
-    g_force_hg = force_rows_per_cta / 32;
+    g_force_ug = force_rows_per_cta / 16;
     return 0;
 }
 
