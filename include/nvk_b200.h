@@ -187,6 +187,20 @@ int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permu
                            int32_t* expert_offsets, int32_t* inv_perm, int32_t* scratch_counts, int n_tokens, int k,
                            int num_experts);
 
+/* No counterpart in the reference.  The same permutation as nv_kernels_moe_permute for callers that
+ * cannot supply (or allocate) the scratch_counts buffer: the per-expert counters live in a 16 KiB
+ * array inside the library (held by every GPU that loads it, until the process exits), so the call
+ * allocates nothing and takes no scratch argument.  Limits and rules:
+ *   - num_experts <= 4096, otherwise -3 and nothing is launched;
+ *   - the first call on each device looks up the array's device address (a one-time set-up step
+ *     with that device current); make that first call before any stream capture;
+ *   - all calls on a device share the one array, which is cleared at the start of every call:
+ *     two calls that may run on the GPU at the same time (different streams) race -- keep them on
+ *     one stream or otherwise ordered. */
+int nvk_b200_moe_permute_static(void* stream, const int32_t* topk_ids, int32_t* permuted_token_idx,
+                                int32_t* expert_offsets, int32_t* inv_perm, int n_tokens, int k,
+                                int num_experts);
+
 /* Grouped M=1 expert GEMV with NVFP4 weights AND NVFP4 activations: group g multiplies row 0 of its
  * a_tile_stride_rows-row activation tile by expert group_expert_ids[g]; an id outside
  * [0, num_experts_total) writes zeros.  -1 on bad shapes, -2 unless a_packed/b_packed are 8-byte

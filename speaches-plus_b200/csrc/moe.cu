@@ -362,6 +362,51 @@ int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permu
     return err == cudaSuccess ? 0 : (int)err;
 }
 
+// ---- token permutation for callers that may not allocate device memory -------------------------
+// Some hosts of this library cannot hand it a scratch buffer at the point of the call: a serving
+// engine that claimed all of HBM for its KV-cache pool at start-up has nothing left to cudaMalloc
+// from, a decode loop cannot afford the device-wide synchronisation an allocation implies, and an
+// FFI host whose ownership rule is "the C side never allocates" has no allocator to lend.  For them
+// the per-expert counters of the permutation live in the fixed array below instead of in a
+// caller-supplied buffer.  The array is part of the library image: every GPU that loads the library
+// holds these 16 KiB until the process exits.
+constexpr int kStaticPermuteMaxExperts = 4096;
+static __device__ __align__(256) int32_t g_permute_counts[kStaticPermuteMaxExperts];
+
+int nvk_b200_moe_permute_static(void* stream, const int32_t* topk_ids, int32_t* permuted_token_idx,
+                                int32_t* expert_offsets, int32_t* inv_perm, int n_tokens, int k,
+                                int num_experts) {
+    if (n_tokens <= 0 || k <= 0 || num_experts <= 0) return 0;
+    if (num_experts > kStaticPermuteMaxExperts) return NVK_ERR_RESOURCE;  // more experts than the fixed array holds
+    // In host code `g_permute_counts` is only a handle for the symbol, not an address the GPU can
+    // use; the device address is looked up once per device (with that device current) and kept.
+    constexpr int kMaxDevices = 64;
+    static int32_t* dev_ptr[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= kMaxDevices) return NVK_ERR_ARG;
+    if (dev_ptr[dev] == nullptr) {
+        int32_t* ptr = nullptr;
+        err = cudaGetSymbolAddress((void**)&ptr, g_permute_counts);
+        if (err != cudaSuccess) return (int)err;
+        if (ptr == nullptr) return NVK_ERR_RESOURCE;
+        dev_ptr[dev] = ptr;
+    }
+    int32_t* counts = dev_ptr[dev];
+    cudaStream_t s = (cudaStream_t)stream;
+    const int total = n_tokens * k;
+    // The array still holds whatever the previous call left in it: the counters start from zero.
+    err = cudaMemsetAsync(counts, 0, sizeof(int32_t) * num_experts, s);
+    if (err != cudaSuccess) return (int)err;
+    permute_count_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(topk_ids, counts, total);
+    permute_scan_kernel<<<1, 32, 0, s>>>(counts, expert_offsets, num_experts);
+    permute_assign_kernel<<<(unsigned)((num_experts + 127) / 128), 128, 0, s>>>(
+        topk_ids, expert_offsets, permuted_token_idx, inv_perm, n_tokens, k, num_experts);
+    err = cudaGetLastError();
+    return err == cudaSuccess ? 0 : (int)err;
+}
+
 int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packed, const uint8_t* a_scales,
                                             const uint8_t* b_packed, const uint8_t* b_scales, const float* alphas,
                                             uint16_t* d_bf16, const int32_t* group_expert_ids, int num_groups,
