@@ -110,9 +110,15 @@ def run_b200(args) -> dict:
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    def mark(msg):
+        if os.environ.get("NVK_BENCH_VERBOSE"):
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     sp.ffi.lib()
+    mark("process group up")
 
     # ---- synthetic weights: seeded, identical on every rank, then sharded ----
     copies = COPIES
@@ -138,6 +144,7 @@ def run_b200(args) -> dict:
                 lin.forward(x)
 
     launches_per_step = copies * len(SHAPES_KN)
+    mark("weights ready")
 
     # ---- device-resident timing: the step captured once as a CUDA graph ----
     stream = torch.cuda.Stream()
@@ -145,12 +152,15 @@ def run_b200(args) -> dict:
         for _ in range(2):
             one_step()
         stream.synchronize()
+        mark("eager warm-up done")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             one_step()
+        mark("graph captured")
         for _ in range(max(args.warmup, 3)):
             graph.replay()
         stream.synchronize()
+        mark("graph warm-up done")
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -168,6 +178,7 @@ def run_b200(args) -> dict:
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
         ms = e0.elapsed_time(e1)
+        mark("timed region done")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -198,6 +209,7 @@ def run_b200(args) -> dict:
             per_shape[f"K{k}_N{n}"] = {"us_per_launch_eager": round(us, 3),
                                         "gbs": round(algo_bytes(1, n, k) / (us * 1e-6) / 1e9, 1)}
 
+    mark("per-shape done")
     # ---- end to end through the public API with host buffers ----
     pin_x = {k: torch.randn((1, k), dtype=torch.float32).to(torch.bfloat16).pin_memory() for k in xs}
     pin_y = {(k, n): torch.empty((1, n), dtype=torch.bfloat16).pin_memory() for k, n in SHAPES_KN}
@@ -265,10 +277,21 @@ def run_b200(args) -> dict:
         }
         if args.cpu_baseline:
             out["cpu_baseline"] = cpu_reference_leg(passes=3, warm=1)
+    mark("results ready")
+    if out is not None:
+        print(json.dumps(out), flush=True)
     if world > 1:
+        # Tear down in dependency order: the captured graph holds NCCL work, so it goes first.
+        del graph
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
-    return out
+        mark("final barrier passed")
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # The communicator is left to process exit: destroying it after graph capture has been
+        # seen to block, and every result is already printed.
+        os._exit(0)
+    return None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -355,12 +378,12 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         out = run_reference(args)
+        if out is not None:
+            print(json.dumps(out), flush=True)
     else:
         if args.gpus > 1:
             args.cpu_baseline = False
-        out = run_b200(args)
-    if out is not None:
-        print(json.dumps(out), flush=True)
+        run_b200(args)  # prints its own line (before the multi-GPU teardown)
 
 
 if __name__ == "__main__":
