@@ -213,6 +213,26 @@ int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packe
                                             int num_experts_total, int n, int k, int a_tile_stride_rows,
                                             long long d_group_stride_elems);
 
+/* No counterpart in the reference (its grouped decode path quantizes activations to NVFP4 and gives
+ * every (token, expert) pair its own 128-row tile): grouped-expert W4A16 linear with the tokens of
+ * one expert sharing one pass over that expert's weights.
+ *   banks:   expert e's packed weights at wq_bank + e * N*K/2, its swizzled scales at
+ *            sc_bank + e * ceil(N/128)*128 * ceil(K/64)*4 (the layout of MoeGroupedWeights,
+ *            rust/crates/nv-layers/src/moe_grouped.rs:98-281), its alpha at alphas[e] (device).
+ *   tokens:  the routed slots sorted by expert, as nv_kernels_moe_permute produces them: expert e
+ *            owns sorted slots [expert_offsets[e], expert_offsets[e+1]).  Slot i reads activation row
+ *            row_index[i] of x (row i when row_index is NULL) and writes output row i of y.
+ *   arms:    wq_bank_b/sc_bank_b/alphas_b/y_b give a second matrix sharing the activations
+ *            (gate + up); all four NULL for one arm.
+ *   x2:      when not NULL the activation is bf16(SiLU(x) * x2), rows taken the same way.
+ * Experts without tokens cost one empty CTA per row tile.  K % 32 == 0 (-1 otherwise), 16-byte
+ * aligned pointers (-2 otherwise). */
+int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uint8_t* sc_bank_a,
+                               const uint8_t* wq_bank_b, const uint8_t* sc_bank_b, const float* alphas_a,
+                               const float* alphas_b, const uint16_t* x, const uint16_t* x2,
+                               const int32_t* row_index, const int32_t* expert_offsets, uint16_t* y_a,
+                               uint16_t* y_b, int num_experts, int N, int K);
+
 #ifdef __cplusplus
 }
 #endif

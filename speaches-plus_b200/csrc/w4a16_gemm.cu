@@ -96,8 +96,23 @@ __device__ __forceinline__ void silu_mul_bf16x8(uint32_t (&ws)[4], const uint4 u
 // A warp iteration covers 256 K values ("super-chunk"): lane (g, tg) takes, for each of its two
 // rows, the two 16-byte pieces at K offsets 32*tg and 128 + 32*tg, so that one cp.async instruction
 // moves whole 64-byte runs per row.  NT: number of 8-token column tiles.
-template <int NT, bool DUAL, int PRO, int UG, int KW>
-__global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
+// What one CTA works on: one arm's matrix, a set of token rows and where their outputs go.
+struct TileView {
+    const uint8_t* wq;
+    const uint8_t* sc;
+    const uint16_t* x;       // activation rows (gate when PRO == 1)
+    const uint16_t* x2;      // up rows when PRO == 1
+    const int32_t* xrows;    // optional gather: token m reads row xrows[xrow0 + m]; else row xrow0 + m
+    uint16_t* y;             // output row of token m is y + m * N
+    float alpha;
+    int xrow0;
+    int M;                   // tokens (<= 8 * NT)
+    int sub;                 // CTA index within the arm
+    bool pdl;                // signal/await the neighbouring kernels of the stream here
+};
+
+template <int NT, int PRO, int UG, int KW>
+__device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& t) {
     constexpr int THREADS = 32 * UG * KW;
     constexpr int MT = 8 * NT;      // token columns
     constexpr int ROWS = 16 * UG;   // weight rows per CTA
@@ -111,18 +126,16 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int ul = warp % UG, kw = warp / UG;  // local unit, K-warp
     const int gid = lane >> 2, tg = lane & 3;
-    const int tile = blockIdx.y;
-    const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
-    const int sub = tile - arm * p.tiles_per_arm;
+    const int sub = t.sub;
     const int mt = sub / SUB;               // 128-row scale tile
     const int u = (sub % SUB) * UG + ul;    // unit inside it
     const int h = u >> 1, pair = u & 1;
     const int crank = blockIdx.x;
     const int nranks = gridDim.x;
-    const int M = p.M, N = p.N, K = p.K;
+    const int M = t.M, N = p.N, K = p.K;
 
-    const uint8_t* __restrict__ wq = p.wq[arm];
-    const uint8_t* __restrict__ sc = p.sc[arm];
+    const uint8_t* __restrict__ wq = t.wq;
+    const uint8_t* __restrict__ sc = t.sc;
     const int row0 = mt * kRowsPerCta + 64 * pair + 8 * h + gid;  // second row is 32 further
     const size_t half_k = (size_t)(K >> 1);
     const bool rv0 = row0 < N, rv1 = row0 + 32 < N;
@@ -212,7 +225,7 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
     // Programmatic dependent launch: let the next kernel in the stream start its own weight
     // prefetch while this one runs, and prefetch our weights (which no earlier kernel writes) before
     // waiting for the previous kernel, whose output may be our activations.
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    if (t.pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     int s_issue = sc_begin + kw, n_issued = 0, n_done = 0;
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d) {
@@ -220,7 +233,7 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
         s_issue += KW;
         ++n_issued;
     }
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (t.pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     for (int p0 = sc_begin; p0 < sc_end; p0 += p.ph) {
         const int pend = min(sc_end, p0 + p.ph);
@@ -242,9 +255,10 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
             const int rem = idx - m * pieces_per_tok;
             const int k = (p0 + (rem >> 5)) * kSuper + (rem & 31) * 8;
             if (k >= K) return false;
-            const uint4 v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * K + k);
+            const size_t xr0 = (size_t)(t.xrows ? t.xrows[t.xrow0 + m] : t.xrow0 + m) * K + k;
+            const uint4 v = *reinterpret_cast<const uint4*>(t.x + xr0);
             ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
-            if (PRO == 1) silu_mul_bf16x8(ws, *reinterpret_cast<const uint4*>(p.x2 + (size_t)m * K + k));
+            if (PRO == 1) silu_mul_bf16x8(ws, *reinterpret_cast<const uint4*>(t.x2 + xr0));
             return true;
         };
         auto store_piece = [&](int idx, const uint32_t (&ws)[4], bool valid) {
@@ -342,8 +356,8 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
 
     if (KW == 1 && nranks == 1) {
         // One warp saw the whole of K for its rows: the accumulator fragment is the result.
-        const float alpha1 = p.alpha[arm];
-        uint16_t* __restrict__ y1 = p.y[arm];
+        const float alpha1 = t.alpha;
+        uint16_t* __restrict__ y1 = t.y;
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
 #pragma unroll
@@ -389,8 +403,8 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
 
     // ---- sum the CTAs of the cluster through distributed shared memory, fixed order ----
     if (nranks > 1) cluster.sync(); else __syncthreads();
-    const float alpha = p.alpha[arm];
-    uint16_t* __restrict__ y = p.y[arm];
+    const float alpha = t.alpha;
+    uint16_t* __restrict__ y = t.y;
     const int rows_per_rank = ROWS / nranks;  // nranks in {1,2,4,8}
     for (int i = threadIdx.x; i < M * rows_per_rank; i += THREADS) {
         const int m = i / rows_per_rank;
@@ -410,6 +424,65 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
         if (n_out < N) y[(size_t)m * N + n_out] = nvk::f32_to_bf16_bits(v * alpha);
     }
     if (nranks > 1) cluster.sync();  // peers may still be reading this CTA's partial
+}
+
+template <int NT, bool DUAL, int PRO, int UG, int KW>
+__global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
+    const int tile = blockIdx.y;
+    const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
+    TileView t;
+    t.wq = p.wq[arm];
+    t.sc = p.sc[arm];
+    t.x = p.x;
+    t.x2 = p.x2;
+    t.xrows = nullptr;
+    t.y = p.y[arm];
+    t.alpha = p.alpha[arm];
+    t.xrow0 = 0;
+    t.M = p.M;
+    t.sub = tile - arm * p.tiles_per_arm;
+    t.pdl = true;
+    w4a16_tile<NT, PRO, UG, KW>(p, t);
+}
+
+// Grouped experts: blockIdx.z is an expert whose matrices sit at a fixed stride in a bank, whose
+// tokens are the sorted slots [offsets[e], offsets[e+1]) and whose alpha is alphas[e].  A CTA of an
+// expert without tokens exits at once; an expert with more than 8 tokens is walked in chunks of 8
+// (its weights then come from L2).  Outputs are written in sorted-slot order.
+struct GroupedParams {
+    const float* alphas[2];
+    const int32_t* offsets;    // [E + 1]
+    const int32_t* xrows;      // [slots] gather index into x rows, or null (row = slot)
+    size_t w_stride;           // bytes between experts in the packed-weight banks
+    size_t sc_stride;          // bytes between experts in the scale banks
+};
+
+template <bool DUAL, int PRO>
+__global__ void __launch_bounds__(256, 3) w4a16_grouped_kernel(const GemmParams p, const GroupedParams g) {
+    // The routing tables are written by the kernels just before this one in the stream.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int e = blockIdx.z;
+    const int begin = g.offsets[e], end = g.offsets[e + 1];
+    if (end <= begin) return;
+    const int tile = blockIdx.y;
+    const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
+    TileView t;
+    t.wq = p.wq[arm] + (size_t)e * g.w_stride;
+    t.sc = p.sc[arm] + (size_t)e * g.sc_stride;
+    t.x = p.x;
+    t.x2 = p.x2;
+    t.xrows = g.xrows;
+    t.alpha = g.alphas[arm][e];
+    t.sub = tile - arm * p.tiles_per_arm;
+    t.pdl = false;
+    for (int c0 = begin; c0 < end; c0 += 8) {
+        t.xrow0 = c0;
+        t.M = min(8, end - c0);
+        t.y = p.y[arm] + (size_t)c0 * p.N;
+        if (c0 > begin) __syncthreads();  // the previous chunk's shared-memory reads are done
+        w4a16_tile<1, PRO, 8, 1>(p, t);
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -543,6 +616,36 @@ int dispatch_mma(cudaStream_t stream, GemmParams& p) {
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
 
+template <bool DUAL, int PRO>
+int launch_grouped(cudaStream_t stream, GemmParams& p, const GroupedParams& g, int E) {
+    constexpr int MT = 8, RS = 128 + 4, KW = 1;
+    p.M = 8;
+    p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta);
+    p.spc = p.nsc;
+    p.ph = min(max(1, (48 * 1024) / (8 * 512)), p.nsc);
+    p.x_stride = p.ph * 512 + 64;
+    const size_t smem_x = (size_t)8 * p.x_stride;
+    const size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
+    p.ring_off = (int)((max(smem_x, smem_red) + 127) / 128 * 128);
+    const size_t smem = (size_t)p.ring_off + (size_t)8 * kDepth * kSlotBytes;
+    static nvk::SmemOptin optin;
+    auto* kern = w4a16_grouped_kernel<DUAL, PRO>;
+    if (int rc = optin.ensure((const void*)kern, smem)) return rc;
+    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
+    if (ctas > 65535 || E > 65535) return NVK_ERR_GRID_AXIS;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, (unsigned)ctas, (unsigned)E);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p, g);
+}
+
 // Common entry: validates, then picks the tensor-core route or the generic one.
 int w4a16_linear(cudaStream_t stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
                  const uint8_t* sc_b, const uint16_t* x, const uint16_t* x2, uint16_t* y_a, uint16_t* y_b,
@@ -648,6 +751,43 @@ int nvk_b200_linear_nvfp4_w4a16(void* stream, const uint8_t* wq_a, const uint8_t
     if ((wq_b == nullptr) != (sc_b == nullptr)) return NVK_ERR_SHAPE;
     return w4a16_linear((cudaStream_t)stream, wq_a, sc_a, wq_b, sc_b, x, x2, y_a, y_b, alpha_a, alpha_b, M, N, K,
                         x2 ? 1 : 0, 64);
+}
+
+// Grouped-expert W4A16 linear for routed MoE tokens (no counterpart in the reference, whose grouped
+// decode path quantizes activations to NVFP4 and gives every (token, expert) pair its own tile).
+int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uint8_t* sc_bank_a,
+                               const uint8_t* wq_bank_b, const uint8_t* sc_bank_b, const float* alphas_a,
+                               const float* alphas_b, const uint16_t* x, const uint16_t* x2,
+                               const int32_t* row_index, const int32_t* expert_offsets, uint16_t* y_a,
+                               uint16_t* y_b, int num_experts, int N, int K) {
+    if (num_experts <= 0 || N <= 0 || K <= 0) return 0;
+    if ((K & 31) != 0) return NVK_ERR_SHAPE;
+    if ((wq_bank_b == nullptr) != (y_b == nullptr) || (wq_bank_b == nullptr) != (sc_bank_b == nullptr) ||
+        (wq_bank_b == nullptr) != (alphas_b == nullptr))
+        return NVK_ERR_SHAPE;
+    const size_t w_stride = (size_t)N * (K >> 1);
+    const size_t sc_stride = (size_t)nvk::ceil_div(N, 128) * 128 * (size_t)nvk::ceil_div(K, 64) * 4;
+    if ((w_stride & 15) != 0 || !aligned16(wq_bank_a) || !aligned16(sc_bank_a) || !aligned16(x) ||
+        (wq_bank_b && (!aligned16(wq_bank_b) || !aligned16(sc_bank_b))) || (x2 && !aligned16(x2)))
+        return NVK_ERR_ARG;
+    GemmParams p = {};
+    p.wq[0] = wq_bank_a; p.wq[1] = wq_bank_b;
+    p.sc[0] = sc_bank_a; p.sc[1] = sc_bank_b;
+    p.x = x; p.x2 = x2;
+    p.y[0] = y_a; p.y[1] = y_b;
+    p.N = N; p.K = K;
+    p.k_tiles = nvk::ceil_div(K, 64);
+    p.nsc = nvk::ceil_div(K, kSuper);
+    GroupedParams g = {};
+    g.alphas[0] = alphas_a; g.alphas[1] = alphas_b;
+    g.offsets = expert_offsets;
+    g.xrows = row_index;
+    g.w_stride = w_stride;
+    g.sc_stride = sc_stride;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool dual = wq_bank_b != nullptr;
+    if (dual) return x2 ? launch_grouped<true, 1>(s, p, g, num_experts) : launch_grouped<true, 0>(s, p, g, num_experts);
+    return x2 ? launch_grouped<false, 1>(s, p, g, num_experts) : launch_grouped<false, 0>(s, p, g, num_experts);
 }
 
 }  // extern "C"

@@ -351,3 +351,52 @@ def test_grouped_w4a4_expert_gemv(n, k):
     assert U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, 0, 0, 0, 0, 0, 0, 0, 70000, E, n, k, 128, n) == -9
     assert U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, 0, 0, 0, 0, 0, 0, 0, 4, E, n, k, 100, n) == -1
     assert U.ffi.call("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, 4, 0, 0, 0, 0, 0, 0, 4, E, n, k, 128, n) == -2
+
+
+@pytest.mark.parametrize("n_tok", [1, 5, 16, 64])
+def test_grouped_w4a16_moe_decode_matches_the_per_pair_oracle(n_tok):
+    """Tokens grouped per expert must equal the per-(token, expert) computation: route, expert MLP
+    (gate/up W4A16 -> bf16, SiLU(gate)*up rounded to bf16, down W4A16 -> bf16), f32 weighted combine.
+    Router ids and the permutation are exact; outputs are within bf16 rounding of the f64 oracle."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(100 + n_tok)
+    E, top_k, hidden, inter = 16, 4, 256, 384
+    experts, host = [], []
+    for e in range(E):
+        trip, htrip = [], []
+        for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter)):
+            w = U.gauss_bf16(rng, (n, k), 0.05)
+            packed, sw, alpha = ref.quantize_weight_bf16(w)
+            trip.append(sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n))
+            htrip.append((packed, sw, alpha))
+        experts.append(tuple(trip))
+        host.append(htrip)
+    w = sp.MoeGroupedWeights.build_from_experts(experts)
+    ctx = sp.GroupedDecodeContext(w, 64, top_k, "cuda")
+    x = U.gauss_bf16(rng, (n_tok, hidden))
+    logits = rng.standard_normal((n_tok, E)).astype(np.float32)
+    if n_tok >= 16:
+        logits[:, 3] += 4.0  # one hot expert: more than 8 tokens on it (walks the chunk loop)
+    xt = U.dev(x).view(torch.bfloat16)
+    y = sp.forward_grouped_decode(w, ctx, xt, U.dev(logits))
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    ids, wts = ref.moe_route_topk(logits, top_k)
+    assert np.array_equal(ctx.topk_ids[:n_tok].cpu().numpy(), ids)
+    want = np.zeros((n_tok, hidden), np.float64)
+    for t in range(n_tok):
+        for j in range(top_k):
+            e = ids[t, j]
+            (pg, sg, ag), (pu, su, au), (pd, sd, ad) = host[e]
+            gate = ref.f32_to_bf16(ref.linear_w4a16_f64(pg, sg, x[t:t + 1], ag, inter, hidden).astype(np.float32))
+            up = ref.f32_to_bf16(ref.linear_w4a16_f64(pu, su, x[t:t + 1], au, inter, hidden).astype(np.float32))
+            act = ref.f32_to_bf16(ref.silu_mul(gate, up, round_bf16=True))
+            down = ref.f32_to_bf16(ref.linear_w4a16_f64(pd, sd, act, ad, hidden, inter).astype(np.float32))
+            want[t] += np.float64(wts[t, j]) * ref.bf16_to_f32(down)[0].astype(np.float64)
+    assert U.rel_err_floor(got, want) < 1e-2
+    # grouped == per-pair: the same tokens sent one at a time give the same bits
+    if n_tok == 5:
+        for t in range(n_tok):
+            y1 = sp.forward_grouped_decode(w, ctx, xt[t:t + 1].contiguous(), U.dev(logits[t:t + 1])).cpu().numpy().copy()
+            assert np.array_equal(y1[0], got[t])
