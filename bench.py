@@ -277,6 +277,19 @@ def run_b200(args) -> dict:
         }
         if args.cpu_baseline:
             out["cpu_baseline"] = cpu_reference_leg(passes=3, warm=1)
+    if args.extras:
+        # free the sweep's weights before the larger workloads
+        del graph
+        layers.clear()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        stack = [decode_stack_leg(dev, rank, world, b) for b in (1, 16)]
+        moe = [moe_decode_leg(dev, b) for b in (1, 16, 64)] if world == 1 else None
+        if out is not None:
+            out["decode_stack"] = stack
+            if moe is not None:
+                out["moe_decode"] = moe
+        graph = None
     mark("results ready")
     if out is not None:
         print(json.dumps(out), flush=True)
@@ -292,6 +305,178 @@ def run_b200(args) -> dict:
         # seen to block, and every result is already printed.
         os._exit(0)
     return None
+
+
+# ------------------------------------------------------------------------------------------------
+def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, replays: int = 5) -> dict:
+    """BASELINE configs[2]: dense decoder linear stack (hidden 5120, 64 q / 8 kv heads of 128, SwiGLU
+    25600, bf16 lm_head 151936), random-init NVFP4 weights, one decode step of `batch` tokens through
+    every linear.  Attention itself is outside the path: o_proj is fed the q slice of the QKV output.
+    Tensor parallel: QKV and gate/up column-parallel (outputs stay sharded into the row-parallel
+    consumer), o_proj and down row-parallel followed by an all-reduce, lm_head column-parallel +
+    all-gather.  Each rank holds random weights of its shard's shape."""
+    import torch
+    import torch.distributed as dist
+
+    import speaches_plus_b200 as sp
+    ffi = sp.ffi
+    H, QO, KV, F, V = 5120, 8192, 1024, 25600, 151936
+    q_l, kv_l, f_l = QO // world, KV // world, F // world
+    v_l = (V // world + 127) // 128 * 128 if world > 1 else V
+
+    def rand_lin(n, k, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        w = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w)
+        del w
+        return lin
+
+    stack = []
+    for li in range(layers):
+        b = 10 * li + 1000 * rank
+        stack.append((rand_lin(q_l + 2 * kv_l, H, b), rand_lin(H, q_l, b + 1), rand_lin(f_l, H, b + 2),
+                      rand_lin(f_l, H, b + 3), rand_lin(H, f_l, b + 4)))
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    lm_head = sp.Bf16Linear((torch.randn((v_l, H), generator=g, device=dev, dtype=torch.float32) * 0.02)
+                            .to(torch.bfloat16))
+    x0 = torch.randn((batch, H), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    qkv = torch.empty((batch, q_l + 2 * kv_l), **bf)
+    q_in = torch.empty((batch, q_l), **bf)
+    o_out, d_out = torch.empty((batch, H), **bf), torch.empty((batch, H), **bf)
+    gate, up = torch.empty((batch, f_l), **bf), torch.empty((batch, f_l), **bf)
+    logits_l = torch.empty((batch, v_l), **bf)
+    logits = torch.empty((world * batch, v_l), **bf) if world > 1 else logits_l
+
+    from speaches_plus_b200 import linear as L
+
+    def lin_call(lin, lin_b, x, x2, y, y_b):
+        L.linear_w4a16(lin, lin_b, x, x2, y, y_b, batch)
+
+    def step():
+        for (w_qkv, w_o, w_g, w_u, w_d) in stack:
+            lin_call(w_qkv, None, x0, None, qkv, None)
+            if batch == 1:
+                q_view = qkv[:, :q_l]
+            else:
+                q_in.copy_(qkv[:, :q_l])
+                q_view = q_in
+            lin_call(w_o, None, q_view, None, o_out, None)
+            if world > 1:
+                dist.all_reduce(o_out)
+            lin_call(w_g, w_u, o_out, None, gate, up)
+            lin_call(w_d, None, gate, up, d_out, None)
+            if world > 1:
+                dist.all_reduce(d_out)
+        for r in range(batch):
+            ffi.check("nv_kernels_gemv_bf16", torch.cuda.current_stream().cuda_stream, lm_head.weight.data_ptr(),
+                      d_out[r].data_ptr(), logits_l[r].data_ptr(), v_l, H)
+        if world > 1:
+            dist.all_gather_into_tensor(logits, logits_l)
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(2):
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1) / replays
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    per_layer = (algo_bytes(batch, q_l + 2 * kv_l, H) + algo_bytes(batch, H, q_l) + 2 * algo_bytes(batch, f_l, H)
+                 + algo_bytes(batch, H, f_l))
+    bytes_rank = layers * per_layer + 2 * v_l * H + batch * 2 * (v_l + H)
+    out = {"batch": batch, "layers": layers, "tp": world, "ms_per_step": round(ms, 4),
+           "tok_s": round(batch / (ms * 1e-3), 1), "bytes_per_step_per_gpu": bytes_rank,
+           "gbs_per_gpu": round(bytes_rank / (ms * 1e-3) / 1e9, 1),
+           "launches_per_step": layers * 4 + batch, "collectives_per_step": (2 * layers + 1) if world > 1 else 0}
+    del graph, stack, lm_head
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return out
+
+
+def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
+    """BASELINE configs[3] on one GPU: 48 layers x 128 experts (hidden 2048, SwiGLU 768), top-8 with
+    softmax over the winners, router logits ~ N(0,1); one decode step of `batch` tokens through
+    route -> sort -> grouped gate+up -> grouped down (SiLU prologue) -> combine in every layer.
+    Algorithmic bytes count each distinct routed expert once per layer (from the actual routing)."""
+    import numpy as np
+    import torch
+
+    import speaches_plus_b200 as sp
+    from speaches_plus_b200 import linear as L
+    ffi = sp.ffi
+    E, H, F, TOPK = 128, 2048, 768, 8
+
+    def bank(n, k, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        w = (torch.randn((E * n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        amax = w.view(E, -1).abs().amax(1).float()
+        globals_ = (torch.full_like(amax, 448.0 * 6.0) / amax).contiguous()
+        packed = torch.empty((E * n, k // 2), dtype=torch.uint8, device=dev)
+        scales = torch.zeros(L.swizzled_scale_bytes(E * n, k), dtype=torch.uint8, device=dev)
+        ffi.check("nv_kernels_quantize_nvfp4_bf16_per_expert", torch.cuda.current_stream().cuda_stream, w.data_ptr(),
+                  packed.data_ptr(), scales.data_ptr(), globals_.data_ptr(), n, E * n, k)
+        return packed, scales, (1.0 / globals_).contiguous()
+
+    mods = []
+    for li in range(layers):
+        w = sp.MoeGroupedWeights(bank(F, H, 3 * li), bank(F, H, 3 * li + 1), bank(H, F, 3 * li + 2), H, F, E)
+        g = torch.Generator(device=dev).manual_seed(7000 + li)
+        logits = torch.randn((batch, E), generator=g, device=dev, dtype=torch.float32)
+        mods.append((w, logits))
+    ctx = sp.GroupedDecodeContext(mods[0][0], max(batch, 1), TOPK, dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn((batch, H), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    distinct = 0
+    for w, logits in mods:
+        distinct += int(torch.unique(torch.topk(logits, TOPK, dim=1).indices).numel())
+
+    def step():
+        for w, logits in mods:
+            sp.forward_grouped_decode(w, ctx, x, logits)
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(2):
+            graph.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1) / replays
+    per_expert = mods[0][0].per_expert_bytes()
+    nbytes = distinct * per_expert
+    out = {"batch": batch, "layers": layers, "experts": E, "top_k": TOPK, "ms_per_step": round(ms, 4),
+           "tok_s": round(batch / (ms * 1e-3), 1), "distinct_experts_per_layer": round(distinct / layers, 2),
+           "bytes_per_step": nbytes, "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1), "launches_per_step": layers * 8}
+    del graph, mods, ctx
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -368,6 +553,32 @@ def run_reference(args) -> dict | None:
             "gpu_launches": 0}
 
 
+def profile_case(spec: str, copies: int) -> None:
+    """A few eager launches of one (K,N,M) case on cold weights: the small, self-ending workload that
+    profiler captures are taken on (see profiles/)."""
+    import torch
+
+    import speaches_plus_b200 as sp
+    from speaches_plus_b200 import linear as L
+    k, n, m = (int(v) for v in spec.split(","))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    lins = []
+    for c in range(copies):
+        g = torch.Generator(device=dev).manual_seed(c)
+        w = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        lins.append(sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w))
+        del w
+    x = torch.randn((m, k), device=dev, dtype=torch.float32).to(torch.bfloat16)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    for _ in range(2):
+        for lin in lins:
+            lin.forward_into(x, y)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": {"K": k, "N": n, "M": m, "copies": copies, "launches": 2 * copies,
+                                       "bytes_per_launch": algo_bytes(m, n, k)}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -375,7 +586,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="skip the configs[2] decode-stack and configs[3] MoE legs")
+    ap.add_argument("--profile-case", default=None, metavar="K,N,M",
+                    help="run a few eager launches of one case and exit (for profiler captures)")
+    ap.add_argument("--copies", type=int, default=4)
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case, args.copies)
+        return
     if args.impl == "reference":
         out = run_reference(args)
         if out is not None:

@@ -70,6 +70,19 @@ int nvk_b200_linear_nvfp4_w4a16(void* stream, const uint8_t* wq_a, const uint8_t
                                 const uint8_t* sc_b, const uint16_t* x, const uint16_t* x2, uint16_t* y_a,
                                 uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K);
 
+/* No counterpart in the reference: the same linear with a caller-supplied workspace.  For M >= 3
+ * the activations are converted once into the workspace (one small extra launch) and every CTA
+ * streams them from there instead of converting its whole K range itself; results are bit-identical
+ * to nvk_b200_linear_nvfp4_w4a16.  `workspace` is device memory, 16-byte aligned, at least
+ * nvk_b200_linear_workspace_bytes(M, K) bytes, and must not be used by another call until this one
+ * has completed on the GPU (calls on one stream may share it).  workspace == NULL falls back to
+ * nvk_b200_linear_nvfp4_w4a16; a workspace that is too small or misaligned returns -2. */
+size_t nvk_b200_linear_workspace_bytes(int M, int K);
+int nvk_b200_linear_nvfp4_w4a16_ws(void* stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
+                                   const uint8_t* sc_b, const uint16_t* x, const uint16_t* x2, uint16_t* y_a,
+                                   uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K,
+                                   void* workspace, size_t workspace_bytes);
+
 /* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
  * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 16, 32,
  * 64, 128} fixes the rows one CTA owns (M <= 16 only). */

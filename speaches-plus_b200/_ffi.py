@@ -21,6 +21,8 @@ SIGNATURES = {
     "nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1": [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i],
     "nv_kernels_gemm_nvfp4_w4a16_mk_dual": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
     "nvk_b200_linear_nvfp4_w4a16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
+    "nvk_b200_linear_nvfp4_w4a16_ws": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i, _vp, C.c_size_t],
+    "nvk_b200_linear_workspace_bytes": [_i, _i],
     "nvk_b200_set_tuning": [_i, _i],
     "nvk_b200_set_pdl": [_i],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
@@ -70,7 +72,7 @@ def lib() -> C.CDLL:
         for name, args in SIGNATURES.items():
             fn = getattr(L, name)  # AttributeError if a declared symbol is not exported
             fn.argtypes = args
-            fn.restype = C.c_int
+            fn.restype = C.c_size_t if name.endswith("_workspace_bytes") else C.c_int
         _lib = L
     return _lib
 

@@ -109,10 +109,15 @@ struct TileView {
     int M;                   // tokens (<= 8 * NT)
     int sub;                 // CTA index within the arm
     bool pdl;                // signal/await the neighbouring kernels of the stream here
+    const uint8_t* ws;       // prepared activations (XWS only): 256-byte header of int pw[], then f16 stages
 };
 
-template <int NT, int PRO, int UG, int KW>
+// XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
+// in a caller-supplied workspace; the CTA streams them through a shared ring next to the weights
+// instead of converting its whole K range itself.  Needs KW == 1 (all warps walk K together).
+template <int NT, int PRO, int UG, int KW, bool XWS = false>
 __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& t) {
+    static_assert(!XWS || KW == 1, "the shared activation ring needs every warp on the same K step");
     constexpr int THREADS = 32 * UG * KW;
     constexpr int MT = 8 * NT;      // token columns
     constexpr int ROWS = 16 * UG;   // weight rows per CTA
@@ -162,6 +167,13 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     auto issue = [&](int s, int slot) {
         if (s < sc_end) {
             const uint32_t dst = ring + (uint32_t)(slot * kSlotBytes);
+            if (XWS) {
+                // this stage's activations: M rows of 512 bytes, row stride 576 in shared memory
+                const uint8_t* xsrc = t.ws + 256 + (size_t)s * M * 512;
+                const uint32_t xdst = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)(slot * M * 576);
+                for (int idx = threadIdx.x; idx < M * 32; idx += THREADS)
+                    cp_async16(xdst + (idx >> 5) * 576 + (idx & 31) * 16, xsrc + (size_t)idx * 16, 16);
+            }
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
                 const int kk = s * kSuper + 128 * pc + 32 * tg;   // first K value of this piece
@@ -180,11 +192,12 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     // predicate (columns past M compute a duplicate that is never written out).
     uint32_t xs_tok[NT];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) xs_tok[n] = (uint32_t)(min(8 * n + gid, M - 1) * p.x_stride + tg * 16);
+    for (int n = 0; n < NT; ++n)
+        xs_tok[n] = (uint32_t)(min(8 * n + gid, M - 1) * (XWS ? 576 : p.x_stride) + tg * 16);
 
-    auto compute = [&](int slot, int s_local) {
+    auto compute = [&](int slot, int xbase) {
         const uint8_t* src = ring_g + slot * kSlotBytes;
-        const uint8_t* xs = smem + s_local * 512;
+        const uint8_t* xs = smem + xbase;
         uint4 w[2][2];
 #pragma unroll
         for (int i = 0; i < 2; ++i)
@@ -227,6 +240,27 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     // waiting for the previous kernel, whose output may be our activations.
     if (t.pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     int s_issue = sc_begin + kw, n_issued = 0, n_done = 0;
+    if (XWS) {
+        // The prepared activations come from the kernel just before this one.
+        if (t.pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        if (threadIdx.x < MT) s_pw[threadIdx.x] = reinterpret_cast<const int*>(t.ws)[min((int)threadIdx.x, M - 1)];
+#pragma unroll
+        for (int d = 0; d < kDepth - 1; ++d) {
+            issue(s_issue, n_issued % kDepth);
+            s_issue += KW;
+            ++n_issued;
+        }
+        for (int s = sc_begin; s < sc_end; ++s) {
+            cp_async_wait<kDepth - 2>();  // this thread's copies for super-chunk s have landed
+            __syncthreads();              // ... and everyone's; all warps are done with step s - 1
+            issue(s_issue, n_issued % kDepth);  // refills the slot of step s - 1
+            s_issue += KW;
+            ++n_issued;
+            compute(n_done % kDepth, (n_done % kDepth) * M * 576);
+            ++n_done;
+        }
+        cp_async_wait<0>();
+    } else {
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d) {
         issue(s_issue, n_issued % kDepth);
@@ -347,12 +381,13 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             s_issue += KW;
             ++n_issued;
             cp_async_wait<kDepth - 1>();  // this thread's copies for super-chunk s have landed
-            compute(n_done % kDepth, s - p0);
+            compute(n_done % kDepth, (s - p0) * 512);
             ++n_done;
         }
     }
     cp_async_wait<0>();
     if (sc_begin >= sc_end && threadIdx.x < MT) s_pw[threadIdx.x] = 0;  // empty slice: acc is zero
+    }  // !XWS
 
     if (KW == 1 && nranks == 1) {
         // One warp saw the whole of K for its rows: the accumulator fragment is the result.
@@ -442,7 +477,83 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
     t.M = p.M;
     t.sub = tile - arm * p.tiles_per_arm;
     t.pdl = true;
+    t.ws = nullptr;
     w4a16_tile<NT, PRO, UG, KW>(p, t);
+}
+
+template <int NT, bool DUAL>
+__global__ void __launch_bounds__(256, NT >= 4 ? 1 : 2) w4a16_mma_ws_kernel(const GemmParams p, const uint8_t* ws) {
+    const int tile = blockIdx.y;
+    const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
+    TileView t;
+    t.wq = p.wq[arm];
+    t.sc = p.sc[arm];
+    t.x = nullptr;
+    t.x2 = nullptr;
+    t.xrows = nullptr;
+    t.y = p.y[arm];
+    t.alpha = p.alpha[arm];
+    t.xrow0 = 0;
+    t.M = p.M;
+    t.sub = tile - arm * p.tiles_per_arm;
+    t.pdl = true;
+    t.ws = ws;
+    w4a16_tile<NT, 0, 8, 1, true>(p, t);
+}
+
+// Converts the activations of one token (one CTA per token) to f16 once for all CTAs of the GEMM:
+// exact power-of-two pre-scale from the token's maximum, written as ceil(K/256) stages of 512 bytes
+// in the fragment order the GEMM reads, zero-padded past K.  Header word m = the token's power of two.
+template <int PRO>
+__global__ void __launch_bounds__(256) x_prepare_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ x2,
+                                                         uint8_t* __restrict__ ws, int M, int K, int nsc) {
+    __shared__ uint32_t s_max;
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int m = blockIdx.x;
+    if (threadIdx.x == 0) s_max = 0u;
+    __syncthreads();
+    const int pieces = nsc * 32;
+    auto load = [&](int idx, uint32_t (&ws4)[4]) -> bool {
+        const int k = idx * 8;
+        if (k >= K) return false;
+        const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
+        ws4[0] = v.x; ws4[1] = v.y; ws4[2] = v.z; ws4[3] = v.w;
+        if (PRO == 1) silu_mul_bf16x8(ws4, *reinterpret_cast<const uint4*>(x2 + (size_t)m * K + k));
+        return true;
+    };
+    uint32_t mx = 0u;
+    for (int idx = threadIdx.x; idx < pieces; idx += 256) {
+        uint32_t w4[4];
+        if (load(idx, w4)) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mx = max(mx, max(w4[i] & 0x7FFFu, (w4[i] >> 16) & 0x7FFFu));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0 && mx) atomicMax(&s_max, mx);
+    __syncthreads();
+    const int pw = max((int)(s_max >> 7) - 141, -100);
+    if (threadIdx.x == 0) reinterpret_cast<int*>(ws)[m] = pw;
+    const float sc2 = __uint_as_float((uint32_t)(127 - pw) << 23);
+    for (int idx = threadIdx.x; idx < pieces; idx += 256) {
+        uint32_t w4[4];
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (load(idx, w4)) {
+            uint32_t os[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 h2 = __floats2half2_rn(nvk::bf16_bits_to_f32(w4[i] & 0xFFFFu) * sc2,
+                                                     nvk::bf16_bits_to_f32(w4[i] >> 16) * sc2);
+                os[i] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            o = make_uint4(os[0], os[1], os[2], os[3]);
+        }
+        const int sidx = idx >> 5, q = idx & 31;
+        const int perm = (4 * (q >> 4) + (q & 3)) * 4 + ((q & 15) >> 2);
+        *reinterpret_cast<uint4*>(ws + 256 + ((size_t)sidx * M + m) * 512 + perm * 16) = o;
+    }
 }
 
 // Grouped experts: blockIdx.z is an expert whose matrices sit at a fixed stride in a bank, whose
@@ -476,6 +587,7 @@ __global__ void __launch_bounds__(256, 3) w4a16_grouped_kernel(const GemmParams 
     t.alpha = g.alphas[arm][e];
     t.sub = tile - arm * p.tiles_per_arm;
     t.pdl = false;
+    t.ws = nullptr;
     for (int c0 = begin; c0 < end; c0 += 8) {
         t.xrow0 = c0;
         t.M = min(8, end - c0);
@@ -615,6 +727,69 @@ int dispatch_mma(cudaStream_t stream, GemmParams& p) {
 }
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
+
+size_t linear_ws_bytes(int M, int K) { return 256 + (size_t)nvk::ceil_div(K, kSuper) * (size_t)M * 512; }
+
+template <int NT, bool DUAL>
+int launch_mma_ws(cudaStream_t stream, GemmParams& p, const uint8_t* ws) {
+    constexpr int MT = 8 * NT, RS = 128 + 4;
+    int ksplit = 1;
+    if (g_force_ksplit > 0) {
+        ksplit = g_force_ksplit;
+    } else {
+        const int ctas = (DUAL ? 2 : 1) * nvk::ceil_div(p.N, kRowsPerCta);
+        while (ksplit < 8 && ctas * ksplit < 148 && nvk::ceil_div(p.nsc, ksplit * 2) >= 2) ksplit *= 2;
+    }
+    p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta);
+    p.spc = nvk::ceil_div(p.nsc, ksplit);
+    p.ph = p.spc;
+    p.x_stride = 576;
+    const size_t smem_x = (size_t)kDepth * p.M * 576;
+    const size_t smem_red = (size_t)2 * MT * RS * sizeof(float);
+    p.ring_off = (int)((max(smem_x, smem_red) + 127) / 128 * 128);
+    const size_t smem = (size_t)p.ring_off + (size_t)8 * kDepth * kSlotBytes;
+    static nvk::SmemOptin optin;
+    auto* kern = w4a16_mma_ws_kernel<NT, DUAL>;
+    if (int rc = optin.ensure((const void*)kern, smem)) return rc;
+    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
+    if (ctas > 65535) return NVK_ERR_GRID_AXIS;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)ctas, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (ksplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)ksplit;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (g_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p, ws);
+}
+
+int launch_prepare(cudaStream_t stream, const uint16_t* x, const uint16_t* x2, uint8_t* ws, int M, int K, int nsc) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)M, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    if (x2) return (int)cudaLaunchKernelEx(&cfg, x_prepare_kernel<1>, x, x2, ws, M, K, nsc);
+    return (int)cudaLaunchKernelEx(&cfg, x_prepare_kernel<0>, x, x2, ws, M, K, nsc);
+}
 
 template <bool DUAL, int PRO>
 int launch_grouped(cudaStream_t stream, GemmParams& p, const GroupedParams& g, int E) {
@@ -788,6 +963,59 @@ int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uin
     const bool dual = wq_bank_b != nullptr;
     if (dual) return x2 ? launch_grouped<true, 1>(s, p, g, num_experts) : launch_grouped<true, 0>(s, p, g, num_experts);
     return x2 ? launch_grouped<false, 1>(s, p, g, num_experts) : launch_grouped<false, 0>(s, p, g, num_experts);
+}
+
+// Workspace the caller provides to nvk_b200_linear_nvfp4_w4a16_ws for M tokens of K values.
+size_t nvk_b200_linear_workspace_bytes(int M, int K) {
+    if (M <= 0 || K <= 0) return 0;
+    return linear_ws_bytes(M, K);
+}
+
+// The W4A16 linear with a caller-supplied workspace (device memory, 16-byte aligned, at least
+// nvk_b200_linear_workspace_bytes(M, K) bytes, private to this call until it completes).  For M >= 3
+// the activations are converted once into the workspace by a small kernel and every CTA of the GEMM
+// streams them from there; without a workspace (NULL) or for M <= 2 this is
+// nvk_b200_linear_nvfp4_w4a16.  Results are bit-identical either way.
+int nvk_b200_linear_nvfp4_w4a16_ws(void* stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
+                                   const uint8_t* sc_b, const uint16_t* x, const uint16_t* x2, uint16_t* y_a,
+                                   uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K,
+                                   void* workspace, size_t workspace_bytes) {
+    if (N <= 0 || K <= 0) return 0;
+    if ((wq_b == nullptr) != (y_b == nullptr)) return NVK_ERR_SHAPE;
+    if ((wq_b == nullptr) != (sc_b == nullptr)) return NVK_ERR_SHAPE;
+    if (M <= 0 || M > 64 || (K & 15) != 0) return NVK_ERR_SHAPE;
+    const bool dual = wq_b != nullptr;
+    const bool fast = (K & 31) == 0 && aligned16(wq_a) && aligned16(sc_a) && aligned16(x) &&
+                      (!dual || (aligned16(wq_b) && aligned16(sc_b))) && (!x2 || aligned16(x2));
+    // The extra launch pays off once the per-CTA conversion it replaces is large: many tokens, or a
+    // few tokens against a big matrix.  Both routes give the same bits, so the switch is invisible.
+    if (workspace != nullptr && (!aligned16(workspace) || workspace_bytes < linear_ws_bytes(M, K))) return NVK_ERR_ARG;
+    const double elems = (double)N * (double)K * (dual ? 2.0 : 1.0);
+    const bool worth = (M >= 9 && elems >= 32e6) || (M >= 3 && elems >= 100e6);
+    if (workspace == nullptr || !worth || !fast)
+        return w4a16_linear((cudaStream_t)stream, wq_a, sc_a, wq_b, sc_b, x, x2, y_a, y_b, alpha_a, alpha_b, M, N, K,
+                            x2 ? 1 : 0, 64);
+    GemmParams p = {};
+    p.wq[0] = wq_a; p.wq[1] = wq_b;
+    p.sc[0] = sc_a; p.sc[1] = sc_b;
+    p.y[0] = y_a; p.y[1] = y_b;
+    p.alpha[0] = alpha_a; p.alpha[1] = alpha_b;
+    p.M = M; p.N = N; p.K = K;
+    p.k_tiles = nvk::ceil_div(K, 64);
+    p.nsc = nvk::ceil_div(K, kSuper);
+    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    if (int rc = launch_prepare(s, x, x2, ws, M, K, p.nsc)) return rc;
+    if (dual) {
+        if (M <= 8) return launch_mma_ws<1, true>(s, p, ws);
+        if (M <= 16) return launch_mma_ws<2, true>(s, p, ws);
+        if (M <= 32) return launch_mma_ws<4, true>(s, p, ws);
+        return launch_mma_ws<8, true>(s, p, ws);
+    }
+    if (M <= 8) return launch_mma_ws<1, false>(s, p, ws);
+    if (M <= 16) return launch_mma_ws<2, false>(s, p, ws);
+    if (M <= 32) return launch_mma_ws<4, false>(s, p, ws);
+    return launch_mma_ws<8, false>(s, p, ws);
 }
 
 }  // extern "C"

@@ -20,6 +20,33 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_WORKSPACES: dict = {}
+
+
+def linear_workspace(device, m: int, k: int) -> torch.Tensor:
+    """Activation workspace for nvk_b200_linear_nvfp4_w4a16_ws, one per (device, stream), grown on
+    demand.  Launches on one stream are ordered, so consecutive linears may share it."""
+    need = int(_ffi.lib().nvk_b200_linear_workspace_bytes(m, k))
+    key = (torch.device(device).index, torch.cuda.current_stream().cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def linear_w4a16(lin_a, lin_b, x, x2, y_a, y_b, m: int) -> None:
+    """One launch of the decode-sized W4A16 linear (optionally two arms / SiLU prologue) for m <= 64."""
+    n, k = lin_a.out_features, lin_a.in_features
+    ws = linear_workspace(x.device, m, k) if m >= 3 else None
+    _ffi.check("nvk_b200_linear_nvfp4_w4a16_ws", _stream(), lin_a.weight_u8.data_ptr(), lin_a.weight_scales.data_ptr(),
+               lin_b.weight_u8.data_ptr() if lin_b is not None else None,
+               lin_b.weight_scales.data_ptr() if lin_b is not None else None, x.data_ptr(),
+               x2.data_ptr() if x2 is not None else None, y_a.data_ptr(), y_b.data_ptr() if y_b is not None else None,
+               lin_a.weight_alpha, lin_b.weight_alpha if lin_b is not None else 0.0, m, n, k,
+               ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0)
+
+
 def swizzled_scale_bytes(rows: int, cols: int) -> int:
     """Size of the swizzled block-scale buffer (rust/crates/nv-layers/src/linear.rs:2178-2180)."""
     return -(-rows // 128) * 128 * -(-(cols // 16) // 4) * 4
@@ -124,9 +151,7 @@ class Nvfp4Linear:
             return
         for r0 in range(0, m, MAX_DECODE_M):
             mm = min(MAX_DECODE_M, m - r0)
-            _ffi.check("nvk_b200_linear_nvfp4_w4a16", s, self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
-                       None, None, x2[r0:].data_ptr(), None, y[r0:].data_ptr(), None, self.weight_alpha, 0.0, mm,
-                       self.out_features, self.in_features)
+            linear_w4a16(self, None, x2[r0:], None, y[r0:], None, mm)
 
 
 class Bf16Linear:
@@ -171,14 +196,8 @@ class Nvfp4Mlp:
         s = _stream()
         for r0 in range(0, m, MAX_DECODE_M):
             mm = min(MAX_DECODE_M, m - r0)
-            _ffi.check("nvk_b200_linear_nvfp4_w4a16", s, self.gate.weight_u8.data_ptr(),
-                       self.gate.weight_scales.data_ptr(), self.up.weight_u8.data_ptr(),
-                       self.up.weight_scales.data_ptr(), x2[r0:].data_ptr(), None, g[r0:].data_ptr(),
-                       u[r0:].data_ptr(), self.gate.weight_alpha, self.up.weight_alpha, mm, inter,
-                       self.gate.in_features)
-            _ffi.check("nvk_b200_linear_nvfp4_w4a16", s, self.down.weight_u8.data_ptr(),
-                       self.down.weight_scales.data_ptr(), None, None, g[r0:].data_ptr(), u[r0:].data_ptr(),
-                       y[r0:].data_ptr(), None, self.down.weight_alpha, 0.0, mm, hidden, inter)
+            linear_w4a16(self.gate, self.up, x2[r0:], None, g[r0:], u[r0:], mm)
+            linear_w4a16(self.down, None, g[r0:], u[r0:], y[r0:], None, mm)
         return y.reshape(*x.shape[:-1], hidden)
 
     __call__ = forward

@@ -12,7 +12,7 @@ ROOT = pathlib.Path(__file__).resolve().parents[1]
 def declared_symbols():
     text = (ROOT / "include" / "nvk_b200.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\bint\s+((?:nv_kernels|nvk_b200)_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(?:int|size_t)\s+((?:nv_kernels|nvk_b200)_\w+)\s*\(", text)))
 
 
 def test_header_declares_the_path_entry_points():

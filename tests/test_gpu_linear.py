@@ -272,6 +272,42 @@ def test_mk_dual_reference_symbol(m):
     assert np.array_equal(U.host_u16(yc), U.host_u16(ya))
 
 
+@pytest.mark.parametrize("m", [3, 8, 9, 16, 24, 33, 64])
+@pytest.mark.parametrize("n,k", [(8192, 4096), (6200, 5408), (20480, 5120)])
+def test_workspace_path_is_bit_identical(m, n, k):
+    """With a caller workspace the activations are converted once by a separate kernel; the result
+    must equal the in-kernel conversion bit for bit (same products, same order), for one and two arms
+    and with the SiLU prologue."""
+    U.require_gpu()
+    rng = np.random.default_rng(m * 1000 + n + k)
+    pa, sa, aa, _ = U.make_weight(rng, n, k)
+    pb, sb, ab, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    up = U.gauss_bf16(rng, (m, k))
+    nbytes = U.ffi.lib().nvk_b200_linear_workspace_bytes(m, k)
+    ws = torch.zeros(nbytes + 64, dtype=torch.uint8, device="cuda")
+    ws[nbytes:] = 0xEE
+    d = [U.dev(a) for a in (pa, sa, pb, sb, x, up)]
+    for dual, silu in [(False, False), (True, False), (False, True)]:
+        outs = []
+        for use_ws in (False, True):
+            ya = torch.zeros(m * n, dtype=torch.int16, device="cuda")
+            yb = torch.zeros(m * n, dtype=torch.int16, device="cuda")
+            rc = U.ffi.call("nvk_b200_linear_nvfp4_w4a16_ws", U.stream(), d[0].data_ptr(), d[1].data_ptr(),
+                            d[2].data_ptr() if dual else None, d[3].data_ptr() if dual else None, d[4].data_ptr(),
+                            d[5].data_ptr() if silu else None, ya.data_ptr(), yb.data_ptr() if dual else None, aa, ab,
+                            m, n, k, ws.data_ptr() if use_ws else None, nbytes if use_ws else 0)
+            assert rc == 0
+            torch.cuda.synchronize()
+            outs.append((U.host_u16(ya).copy(), U.host_u16(yb).copy()))
+        assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+        assert np.all(ws[nbytes:].cpu().numpy() == 0xEE), "wrote past the workspace"
+        if not silu and not dual and n <= 8192 and m in (3, 16):
+            check_against_oracle(outs[1][0], pa, sa, x, aa, n, k, cpu_backend=False)
+    assert U.ffi.call("nvk_b200_linear_nvfp4_w4a16_ws", U.stream(), d[0].data_ptr(), d[1].data_ptr(), None, None,
+                      d[4].data_ptr(), None, ws.data_ptr(), None, aa, 0.0, m, n, k, ws.data_ptr(), 16) == -2
+
+
 def test_refusals_match_the_reference():
     U.require_gpu()
     t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
