@@ -432,7 +432,7 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
         scales = torch.zeros(L.swizzled_scale_bytes(E * n, k), dtype=torch.uint8, device=dev)
         ffi.check("nv_kernels_quantize_nvfp4_bf16_per_expert", torch.cuda.current_stream().cuda_stream, w.data_ptr(),
                   packed.data_ptr(), scales.data_ptr(), globals_.data_ptr(), n, E * n, k)
-        return packed, scales, (1.0 / globals_).contiguous()
+        return packed.view(E, n, k // 2), scales.view(E, -1), (1.0 / globals_).contiguous()
 
     mods = []
     for li in range(layers):
