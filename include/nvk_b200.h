@@ -226,6 +226,28 @@ int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packe
                                             int num_experts_total, int n, int k, int a_tile_stride_rows,
                                             long long d_group_stride_elems);
 
+/* ---- prefill-sized block-scaled GEMM (both operands NVFP4) --------------------------------------
+ * D[m,n] = bf16(*global_sf * sum_k A[m,k] * B[n,k]); a_fp4 [m, k/2], b_fp4 [n, k/2] packed e2m1, a_sf / b_sf
+ * their 128x4-swizzled ue4m3 scales (padded to 128 rows), global_sf one fp32 in device memory.
+ * Runs tcgen05 kind::mxf4nvf4 block-scaled MMA on sm_100a.  Workspace protocol as in the reference:
+ * *required_workspace is always written; all five data pointers NULL is a pure size query (returns 0,
+ * launches nothing); a workspace that is too small returns -10.  k % 32 != 0 or n % 8 != 0 returns -1.
+ * The `_streamk` / `_tiled` forms select among the reference's sm_120 tile configurations, which
+ * have no counterpart here: all three symbols run the same kernel.
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:1037-1049,1924-1955
+ * (rust/crates/nv-kernels/cuda_sm120/cutlass_fp4_gemm.cu:14-221) */
+int nv_kernels_cutlass_fp4_gemm_sm120_bf16(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
+                                           const void* b_sf, const float* global_sf, void* d_bf16, int m, int n, int k,
+                                           void* workspace, size_t workspace_bytes, size_t* required_workspace);
+int nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk(void* stream, const void* a_fp4, const void* a_sf,
+                                                   const void* b_fp4, const void* b_sf, const float* global_sf,
+                                                   void* d_bf16, int m, int n, int k, void* workspace,
+                                                   size_t workspace_bytes, size_t* required_workspace);
+int nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
+                                                 const void* b_sf, const float* global_sf, void* d_bf16, int m, int n,
+                                                 int k, int tile, int stream_k, void* workspace,
+                                                 size_t workspace_bytes, size_t* required_workspace);
+
 /* No counterpart in the reference (its grouped decode path quantizes activations to NVFP4 and gives
  * every (token, expert) pair its own 128-row tile): grouped-expert W4A16 linear with the tokens of
  * one expert sharing one pass over that expert's weights.

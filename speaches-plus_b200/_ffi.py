@@ -42,6 +42,9 @@ SIGNATURES = {
     "nv_kernels_moe_unpermute_scatter": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "nv_kernels_moe_unpermute_scatter_tail": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "nv_kernels_moe_permute": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_cutlass_fp4_gemm_sm120_bf16": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
+    "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
+    "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled": [_vp] * 7 + [_i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
     "nvk_b200_moe_grouped_w4a16": [_vp] * 13 + [_i, _i, _i],
     "nvk_b200_moe_permute_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_moe_grouped_fp4_gemv_m1_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll],

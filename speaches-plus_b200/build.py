@@ -24,6 +24,31 @@ def sources():
     return sorted(CSRC.glob("*.cu"))
 
 
+def cutlass_include_dirs() -> list[str]:
+    """CUTLASS/CuTe headers for the prefill GEMM: $NVK_CUTLASS_DIR, or a tree vendored inside an
+    installed Python package.  Empty when none is found (the prefill entry points then refuse)."""
+    import importlib.util
+    import os
+    cands = []
+    if os.environ.get("NVK_CUTLASS_DIR"):
+        cands.append(pathlib.Path(os.environ["NVK_CUTLASS_DIR"]))
+    for pkg, rel in (("flashinfer", "data/cutlass"), ("tilelang", "3rdparty/cutlass")):
+        spec = importlib.util.find_spec(pkg)
+        if spec and spec.origin:
+            cands.append(pathlib.Path(spec.origin).parent / rel)
+    for root in cands:
+        if (root / "include" / "cutlass" / "gemm" / "collective" / "builders" / "sm100_blockscaled_umma_builder.inl").exists():
+            dirs = [str(root / "include")]
+            if (root / "tools" / "util" / "include").exists():
+                dirs.append(str(root / "tools" / "util" / "include"))
+            return dirs
+    return []
+
+
+def _newest_header() -> float:
+    return max([f.stat().st_mtime for f in CSRC.glob("*.cuh")] + [0.0])
+
+
 def _newest_dep() -> float:
     return max(f.stat().st_mtime for f in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")))
 
@@ -33,10 +58,16 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
         return LIB
     OBJ.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
+    cutlass = cutlass_include_dirs()
 
     def compile_one(src: pathlib.Path) -> pathlib.Path:
         obj = OBJ / (src.stem + ".o")
-        cmd = ["nvcc", *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
+        per_file = []
+        if src.name == "prefill_fp4_gemm.cu" and cutlass:
+            per_file = ["--expt-relaxed-constexpr", "-DNVK_HAVE_CUTLASS", *[f"-I{d}" for d in cutlass]]
+        if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, _newest_header()):
+            return obj
+        cmd = ["nvcc", *NVCC_FLAGS, *extra, *per_file, "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

@@ -1,0 +1,157 @@
+// Prefill-sized block-scaled NVFP4 GEMM on the 5th-generation tensor cores:
+//
+//   D[m, n] = bf16( alpha * sum_k A[m, k] * B[n, k] ),  A and B packed e2m1 with one ue4m3 scale per 16
+//   values along K (128x4 swizzled scale layout), alpha an fp32 scalar in device memory.
+//
+// The contraction is the CUTLASS sm100 block-scaled collective (tcgen05.mma kind::mxf4nvf4 with the
+// scale factors in tensor memory, TMA operand loads, accumulators in TMEM), instantiated here for a
+// 1-SM 128x128x256 tile with a 1x1x1 cluster -- no multicast loads, so the same kernel is safe under
+// tensor parallelism.  This file is the whole integration: problem setup, workspace protocol and the
+// reference's entry points for this route.
+//
+// Built only when CUTLASS headers are found (NVK_HAVE_CUTLASS); otherwise the entry points refuse
+// with -1 ("route unavailable"), as the reference's GPU-less stubs do.
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "nvk_common.cuh"
+
+#ifdef NVK_HAVE_CUTLASS
+#include "cutlass/cutlass.h"
+#include "cute/tensor.hpp"
+#include "cutlass/detail/sm100_blockscaled_layout.hpp"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/epilogue/thread/linear_combination.h"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/dispatch_policy.hpp"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+#include "cutlass/util/packed_stride.hpp"
+
+namespace {
+
+using namespace cute;
+
+using ElementAB = cutlass::nv_float4_t<cutlass::float_e2m1_t>;
+using ElementD = cutlass::bfloat16_t;
+using ElementAcc = float;
+using LayoutA = cutlass::layout::RowMajor;      // activations [m, k], K contiguous
+using LayoutB = cutlass::layout::ColumnMajor;   // weights [n, k] seen as a K x N column-major operand
+using LayoutD = cutlass::layout::RowMajor;
+constexpr int kAlignAB = 32;                    // elements: 16 bytes of packed e2m1
+constexpr int kAlignD = 128 / cutlass::sizeof_bits<ElementD>::value;
+
+using TileShape = Shape<_128, _128, _256>;
+using ClusterShape = Shape<_1, _1, _1>;
+
+using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+    cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, TileShape, ClusterShape,
+    cutlass::epilogue::collective::EpilogueTileAuto, ElementAcc, ElementAcc, void, LayoutD, kAlignD, ElementD, LayoutD,
+    kAlignD, cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+
+using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+    cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, ElementAB, LayoutA, kAlignAB, ElementAB, LayoutB,
+    kAlignAB, ElementAcc, TileShape, ClusterShape,
+    cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
+    cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
+
+using GemmKernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, void>;
+using Gemm = cutlass::gemm::device::GemmUniversalAdapter<GemmKernel>;
+using SfConfig = typename GemmKernel::CollectiveMainloop::Sm1xxBlkScaledConfig;
+
+typename Gemm::Arguments make_args(const void* a, const void* a_sf, const void* b, const void* b_sf,
+                                   const float* alpha_dev, void* d, int m, int n, int k) {
+    using StrideA = typename Gemm::GemmKernel::StrideA;
+    using StrideB = typename Gemm::GemmKernel::StrideB;
+    using StrideD = typename Gemm::GemmKernel::StrideD;
+    using ElemA = typename Gemm::ElementA;
+    using ElemB = typename Gemm::ElementB;
+    using ElemSF = typename GemmKernel::CollectiveMainloop::ElementSF;
+    typename Gemm::Arguments args{};
+    args.mode = cutlass::gemm::GemmUniversalMode::kGemm;
+    args.problem_shape = {m, n, k, 1};
+    args.mainloop.ptr_A = static_cast<const ElemA*>(a);
+    args.mainloop.dA = cutlass::make_cute_packed_stride(StrideA{}, {m, k, 1});
+    args.mainloop.ptr_B = static_cast<const ElemB*>(b);
+    args.mainloop.dB = cutlass::make_cute_packed_stride(StrideB{}, {n, k, 1});
+    args.mainloop.ptr_SFA = static_cast<const ElemSF*>(a_sf);
+    args.mainloop.layout_SFA = SfConfig::tile_atom_to_shape_SFA(cute::make_shape(m, n, k, 1));
+    args.mainloop.ptr_SFB = static_cast<const ElemSF*>(b_sf);
+    args.mainloop.layout_SFB = SfConfig::tile_atom_to_shape_SFB(cute::make_shape(m, n, k, 1));
+    args.epilogue.thread.alpha = 1.0f;
+    args.epilogue.thread.beta = 0.0f;
+    args.epilogue.thread.alpha_ptr = alpha_dev;
+    args.epilogue.ptr_C = nullptr;
+    args.epilogue.dC = cutlass::make_cute_packed_stride(StrideD{}, {m, n, 1});
+    args.epilogue.ptr_D = static_cast<ElementD*>(d);
+    args.epilogue.dD = cutlass::make_cute_packed_stride(StrideD{}, {m, n, 1});
+    return args;
+}
+
+int run_gemm(cudaStream_t stream, const void* a, const void* a_sf, const void* b, const void* b_sf,
+             const float* alpha_dev, void* d, int m, int n, int k, void* workspace, size_t workspace_bytes,
+             size_t* required_workspace) {
+    if (m <= 0 || n <= 0 || k <= 0) return NVK_ERR_SHAPE;
+    if ((k % 32) != 0 || (n % 8) != 0) return NVK_ERR_SHAPE;  // 16-byte rows of packed operands and of D
+    try {
+        auto args = make_args(a, a_sf, b, b_sf, alpha_dev, d, m, n, k);
+        const size_t need = Gemm::get_workspace_size(args);
+        if (required_workspace) *required_workspace = need;
+        // all data pointers null: a pure workspace query, nothing is launched
+        if (!a && !a_sf && !b && !b_sf && !d) return 0;
+        if (!a || !a_sf || !b || !b_sf || !d || !alpha_dev) return NVK_ERR_ARG;
+        if (need > workspace_bytes || (need > 0 && !workspace)) return -10;
+        Gemm gemm;
+        if (gemm.can_implement(args) != cutlass::Status::kSuccess) return -11;
+        if (gemm.initialize(args, workspace, stream) != cutlass::Status::kSuccess) return -12;
+        if (gemm.run(stream) != cutlass::Status::kSuccess) return -13;
+        return 0;
+    } catch (...) {
+        return NVK_ERR_SHAPE;
+    }
+}
+
+}  // namespace
+#else   // !NVK_HAVE_CUTLASS
+namespace {
+int run_gemm(cudaStream_t, const void*, const void*, const void*, const void*, const float*, void*, int, int, int,
+             void*, size_t, size_t* required_workspace) {
+    if (required_workspace) *required_workspace = 0;
+    return NVK_ERR_SHAPE;
+}
+}  // namespace
+#endif
+
+extern "C" {
+
+// The reference names these after the architecture of its own tensor-core kernels; the symbols are
+// kept so that its call sites bind unchanged.  All three run the same sm_100a kernel: the tile and
+// stream-K knobs of the reference's variants select among its sm_120 configurations and have no
+// meaning here.
+int nv_kernels_cutlass_fp4_gemm_sm120_bf16(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
+                                           const void* b_sf, const float* global_sf, void* d_bf16, int m, int n, int k,
+                                           void* workspace, size_t workspace_bytes, size_t* required_workspace) {
+    return run_gemm((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
+                    workspace_bytes, required_workspace);
+}
+
+int nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk(void* stream, const void* a_fp4, const void* a_sf,
+                                                   const void* b_fp4, const void* b_sf, const float* global_sf,
+                                                   void* d_bf16, int m, int n, int k, void* workspace,
+                                                   size_t workspace_bytes, size_t* required_workspace) {
+    return run_gemm((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
+                    workspace_bytes, required_workspace);
+}
+
+int nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
+                                                 const void* b_sf, const float* global_sf, void* d_bf16, int m, int n,
+                                                 int k, int tile, int stream_k, void* workspace,
+                                                 size_t workspace_bytes, size_t* required_workspace) {
+    (void)tile;
+    (void)stream_k;
+    return run_gemm((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
+                    workspace_bytes, required_workspace);
+}
+
+}  // extern "C"

@@ -6,6 +6,8 @@ CUDA library on the current stream.  There is one route per M class and no fallb
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import numpy as np
 import torch
 
@@ -149,9 +151,33 @@ class Nvfp4Linear:
             _ffi.check("nv_kernels_nvfp4_gemv_bf16act", s, self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
                        x2.data_ptr(), y.data_ptr(), self.weight_alpha, self.out_features, self.in_features)
             return
+        if m > MAX_DECODE_M and self.out_features % 8 == 0 and self.in_features % 32 == 0:
+            self.forward_prefill_into(x2, y)
+            return
         for r0 in range(0, m, MAX_DECODE_M):
             mm = min(MAX_DECODE_M, m - r0)
             linear_w4a16(self, None, x2[r0:], None, y[r0:], None, mm)
+
+    def forward_prefill_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
+        """Prefill-sized M: the reference's default route (rust/crates/nv-layers/src/linear.rs:1590-1795) --
+        quantize the activations to NVFP4 (global 1.0, rows padded to a multiple of 128 with zeros), then one
+        block-scaled FP4 x FP4 tensor-core GEMM with alpha = weight_alpha in device memory."""
+        m, k, n = x2.shape[0], self.in_features, self.out_features
+        m_pad = -(-m // 128) * 128
+        a_packed, a_scales = quantize_nvfp4_bf16(x2, self.input_stored_global, m_padded=m_pad)
+        if getattr(self, "_alpha_dev", None) is None or self._alpha_dev.device != x2.device:
+            self._alpha_dev = torch.tensor([self.weight_alpha / self.input_stored_global], dtype=torch.float32,
+                                           device=x2.device)
+        need = C.c_size_t(0)
+        s = _stream()
+        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", s, None, None, None, None, None, None, m, n, k, None, 0,
+                   C.addressof(need))
+        ws = linear_workspace(x2.device, 1, 16)
+        if ws.numel() < need.value:
+            ws = torch.empty(need.value, dtype=torch.uint8, device=x2.device)
+        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", s, a_packed.data_ptr(), a_scales.data_ptr(),
+                   self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), self._alpha_dev.data_ptr(), y.data_ptr(),
+                   m, n, k, ws.data_ptr(), ws.numel(), C.addressof(need))
 
 
 class Bf16Linear:
