@@ -285,10 +285,13 @@ def run_b200(args) -> dict:
         torch.cuda.empty_cache()
         stack = [decode_stack_leg(dev, rank, world, b) for b in (1, 16)]
         moe = [moe_decode_leg(dev, b) for b in (1, 16, 64)] if world == 1 else None
+        pre = prefill_leg(dev) if world == 1 else None
         if out is not None:
             out["decode_stack"] = stack
             if moe is not None:
                 out["moe_decode"] = moe
+            if pre is not None:
+                out["prefill_gemm"] = pre
         graph = None
     mark("results ready")
     if out is not None:
@@ -476,6 +479,40 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
     del graph, mods, ctx
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
+    return out
+
+
+def prefill_leg(dev, m: int = 2048, reps: int = 10) -> list:
+    """BASELINE configs[4]: M=2048 tokens through FFN up (K=5120, N=25600) and down (K=25600, N=5120),
+    activations quantized online to NVFP4 (global 1.0), block-scaled FP4 x FP4 GEMM, bf16 out.
+    Reported per shape: GEMM-only time and time including the activation quantizer."""
+    import torch
+
+    import speaches_plus_b200 as sp
+    out = []
+    for k, n in ((5120, 25600), (25600, 5120)):
+        g = torch.Generator(device=dev).manual_seed(k)
+        w = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w)
+        del w
+        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            lin.forward_prefill_into(x, y)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            lin.forward_prefill_into(x, y)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        flop = 2.0 * m * n * k
+        out.append({"M": m, "K": k, "N": n, "ms_quantize_plus_gemm": round(ms, 4),
+                    "tflops": round(flop / (ms * 1e-3) / 1e12, 1),
+                    "frac_of_nominal_fp4_dense_9000": round(flop / (ms * 1e-3) / 1e12 / 9000.0, 4)})
+        del lin, x, y
+        torch.cuda.empty_cache()
     return out
 
 
