@@ -200,6 +200,16 @@ int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permu
                            int32_t* expert_offsets, int32_t* inv_perm, int32_t* scratch_counts, int n_tokens, int k,
                            int num_experts);
 
+/* No counterpart in the reference (its decode step launches the router and the permutation
+ * separately): both in one launch for decode-sized batches, with exactly the outputs of
+ * nv_kernels_moe_route_topk followed by nv_kernels_moe_permute and no scratch buffer.
+ * Limits: E <= 256 and n_tokens * K <= 4096, otherwise -3 and nothing is launched; K > E or K > 32
+ * returns -2. */
+int nvk_b200_moe_route_permute(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
+                               float* topk_weights, int32_t* permuted_token_idx, int32_t* expert_offsets,
+                               int32_t* inv_perm, int n_tokens, int E, int K, int mode, float softcap, int norm_topk,
+                               float routed_scaling);
+
 /* No counterpart in the reference.  The same permutation as nv_kernels_moe_permute for callers that
  * cannot supply (or allocate) the scratch_counts buffer: the per-expert counters live in a 16 KiB
  * array inside the library (held by every GPU that loads it, until the process exits), so the call
@@ -247,6 +257,10 @@ int nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled(void* stream, const void* a_fp4
                                                  const void* b_sf, const float* global_sf, void* d_bf16, int m, int n,
                                                  int k, int tile, int stream_k, void* workspace,
                                                  size_t workspace_bytes, size_t* required_workspace);
+
+/* No counterpart in the reference: tuning hook for the prefill GEMM.  1 = 1-SM 128x128x256 tile,
+ * 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster (default). */
+int nvk_b200_set_prefill_config(int cfg);
 
 /* No counterpart in the reference (its grouped decode path quantizes activations to NVFP4 and gives
  * every (token, expert) pair its own 128-row tile): grouped-expert W4A16 linear with the tokens of

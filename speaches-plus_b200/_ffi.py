@@ -25,6 +25,7 @@ SIGNATURES = {
     "nvk_b200_linear_workspace_bytes": [_i, _i],
     "nvk_b200_set_tuning": [_i, _i],
     "nvk_b200_set_pdl": [_i],
+    "nvk_b200_set_prefill_config": [_i],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _f, _i, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16_rows": [_vp, _vp, _vp, _vp, _f, _i, _i],
@@ -46,6 +47,7 @@ SIGNATURES = {
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled": [_vp] * 7 + [_i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
     "nvk_b200_moe_grouped_w4a16": [_vp] * 13 + [_i, _i, _i],
+    "nvk_b200_moe_route_permute": [_vp] * 8 + [_i, _i, _i, _i, _f, _i, _f],
     "nvk_b200_moe_permute_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_moe_grouped_fp4_gemv_m1_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll],
 }

@@ -214,6 +214,129 @@ __global__ void permute_assign_kernel(const int32_t* __restrict__ topk_ids, cons
     }
 }
 
+// ---- router + permutation in one launch (decode-sized batches) -------------------------------
+// One CTA: each warp routes tokens w, w+8, ... (E <= 256 scores per token live in registers, 8 per
+// lane), then the CTA counts, scans and stably assigns the routed slots.  Outputs are exactly those
+// of moe_route_topk_kernel followed by the permute kernels.
+constexpr int kFusedMaxE = 256, kFusedMaxSlots = 4096;
+
+__global__ void __launch_bounds__(256) moe_route_permute_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, int32_t* __restrict__ topk_ids,
+    float* __restrict__ topk_weights, int32_t* __restrict__ permuted_token_idx, int32_t* __restrict__ expert_offsets,
+    int32_t* __restrict__ inv_perm, int n_tokens, int E, int K, int mode, float softcap, int norm_topk,
+    float routed_scaling) {
+    __shared__ int s_ids[kFusedMaxSlots];
+    __shared__ int s_counts[kFusedMaxE + 1];
+    // The logits usually come from the kernel just before this one.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e <= E; e += blockDim.x) s_counts[e] = 0;
+    __syncthreads();
+    for (int n = warp; n < n_tokens; n += 8) {
+        float sel[8], raw[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            sel[i] = -INFINITY;
+            raw[i] = 0.f;
+            if (e < E) {
+                float x = logits[(size_t)n * E + e];
+                if (softcap > 0.f) x = softcap * tanhf(x / softcap);
+                if (mode == 1) {
+                    const float sg = 1.f / (1.f + expf(-x));
+                    raw[i] = sg;
+                    sel[i] = sg + (bias ? bias[e] : 0.f);
+                } else {
+                    raw[i] = x;
+                    sel[i] = x;
+                }
+            }
+        }
+        float my_w = 0.f;   // lane j keeps winner j's raw score
+        int my_id = -1;
+        for (int j = 0; j < K; ++j) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            float br = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = lane + 32 * i;
+                if (e < E && (sel[i] > bv || (sel[i] == bv && e < bi))) {
+                    bv = sel[i];
+                    bi = e;
+                    br = raw[i];
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                const float orr = __shfl_xor_sync(0xffffffffu, br, o);
+                if (ov > bv || (ov == bv && oi < bi)) {
+                    bv = ov;
+                    bi = oi;
+                    br = orr;
+                }
+            }
+            const bool ok = bi < E;
+            if (lane == j) {
+                my_id = ok ? bi : -1;
+                my_w = ok ? br : 0.f;
+            }
+            if (ok && (bi & 31) == lane) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i == (bi >> 5)) sel[i] = -INFINITY;
+            }
+        }
+        // weights: the same sequential sums the per-token router does, evaluated by every lane
+        float w = my_w;
+        if (mode == 0) {
+            float mx = -INFINITY;
+            for (int j = 0; j < K; ++j) mx = fmaxf(mx, __shfl_sync(0xffffffffu, my_w, j));
+            const float ex = expf(my_w - mx);
+            float sum = 0.f;
+            for (int j = 0; j < K; ++j) sum += __shfl_sync(0xffffffffu, ex, j);
+            w = ex / sum;
+        } else if (norm_topk) {
+            float sum = 0.f;
+            for (int j = 0; j < K; ++j) sum += __shfl_sync(0xffffffffu, my_w, j);
+            if (sum > 0.f) w = my_w / sum;
+        }
+        if (lane < K) {
+            topk_ids[(size_t)n * K + lane] = my_id;
+            topk_weights[(size_t)n * K + lane] = w * routed_scaling;
+            s_ids[n * K + lane] = my_id;
+            if (my_id >= 0) atomicAdd(&s_counts[my_id], 1);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = s_counts[e];
+            s_counts[e] = acc;
+            acc += c;
+        }
+        s_counts[E] = acc;
+    }
+    __syncthreads();
+    for (int e = tid; e <= E; e += blockDim.x) expert_offsets[e] = s_counts[e];
+    const int total = n_tokens * K;
+    for (int e = tid; e < E; e += blockDim.x) {
+        int pos = s_counts[e];
+        const int end = s_counts[e + 1];
+        for (int t = 0; t < total && pos < end; ++t) {
+            if (s_ids[t] == e) {
+                permuted_token_idx[pos] = t / K;
+                inv_perm[t] = pos;
+                ++pos;
+            }
+        }
+    }
+}
+
 // ---- grouped M=1 expert GEMV, NVFP4 weights and NVFP4 activations ---------------------------
 // d[g, n] = bf16( alphas[e] * sum_kb (ws * as) * dot16(w, a) ),  e = ids[g]; the activation of
 // group g is row 0 of its 128-row tile.  One warp per output row; the 16 e2m1 x e2m1 products of
@@ -360,6 +483,31 @@ int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permu
         topk_ids, expert_offsets, permuted_token_idx, inv_perm, n_tokens, k, num_experts);
     err = cudaGetLastError();
     return err == cudaSuccess ? 0 : (int)err;
+}
+
+// Router and permutation in one launch for decode-sized batches (no counterpart in the reference,
+// whose decode step launches them separately): same outputs as nv_kernels_moe_route_topk followed by
+// nv_kernels_moe_permute, no scratch.  Limits: E <= 256, K <= 32, n_tokens * K <= 4096 (else -3).
+int nvk_b200_moe_route_permute(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
+                               float* topk_weights, int32_t* permuted_token_idx, int32_t* expert_offsets,
+                               int32_t* inv_perm, int n_tokens, int E, int K, int mode, float softcap, int norm_topk,
+                               float routed_scaling) {
+    if (n_tokens <= 0 || E <= 0 || K <= 0) return 0;
+    if (K > E || K > kRouteMaxK) return NVK_ERR_ARG;
+    if (E > kFusedMaxE || (long long)n_tokens * K > kFusedMaxSlots) return NVK_ERR_RESOURCE;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, moe_route_permute_kernel, logits, bias, topk_ids, topk_weights,
+                                       permuted_token_idx, expert_offsets, inv_perm, n_tokens, E, K, mode, softcap,
+                                       norm_topk, routed_scaling);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 // ---- token permutation for callers that may not allocate device memory -------------------------

@@ -5,8 +5,8 @@
 //
 // The contraction is the CUTLASS sm100 block-scaled collective (tcgen05.mma kind::mxf4nvf4 with the
 // scale factors in tensor memory, TMA operand loads, accumulators in TMEM), instantiated here for a
-// 1-SM 128x128x256 tile with a 1x1x1 cluster -- no multicast loads, so the same kernel is safe under
-// tensor parallelism.  This file is the whole integration: problem setup, workspace protocol and the
+// 2-SM 256x128x256 tile (cluster 2x1x1) and a 1-SM 128x128x256 tile (no cluster).  All operands are
+// local memory; under tensor parallelism each rank runs it on its own shard.  This file is the whole integration: problem setup, workspace protocol and the
 // reference's entry points for this route.
 //
 // Built only when CUTLASS headers are found (NVK_HAVE_CUTLASS); otherwise the entry points refuse
@@ -42,26 +42,36 @@ using LayoutD = cutlass::layout::RowMajor;
 constexpr int kAlignAB = 32;                    // elements: 16 bytes of packed e2m1
 constexpr int kAlignD = 128 / cutlass::sizeof_bits<ElementD>::value;
 
-using TileShape = Shape<_128, _128, _256>;
-using ClusterShape = Shape<_1, _1, _1>;
+template <class TileShape, class ClusterShape>
+struct GemmConfig {
+    using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, TileShape, ClusterShape,
+        cutlass::epilogue::collective::EpilogueTileAuto, ElementAcc, ElementAcc, void, LayoutD, kAlignD, ElementD,
+        LayoutD, kAlignD, cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, ElementAB, LayoutA, kAlignAB, ElementAB,
+        LayoutB, kAlignAB, ElementAcc, TileShape, ClusterShape,
+        cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
+        cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
+    using GemmKernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, void>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<GemmKernel>;
+    using SfConfig = typename GemmKernel::CollectiveMainloop::Sm1xxBlkScaledConfig;
+};
 
-using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
-    cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, TileShape, ClusterShape,
-    cutlass::epilogue::collective::EpilogueTileAuto, ElementAcc, ElementAcc, void, LayoutD, kAlignD, ElementD, LayoutD,
-    kAlignD, cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+// 1-SM tile, no cluster.
+using Cfg1 = GemmConfig<Shape<_128, _128, _256>, Shape<_1, _1, _1>>;
+// 2-SM tile (cta_group::2 pair sharing one 256x128 accumulator tile), cluster 2x1x1: the default
+// (13 % faster at M=2048).  Every operand is this GPU's own memory in both configurations.
+using Cfg2 = GemmConfig<Shape<_256, _128, _256>, Shape<_2, _1, _1>>;
 
-using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
-    cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, ElementAB, LayoutA, kAlignAB, ElementAB, LayoutB,
-    kAlignAB, ElementAcc, TileShape, ClusterShape,
-    cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
-    cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
+int g_prefill_cfg = 2;
 
-using GemmKernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, void>;
-using Gemm = cutlass::gemm::device::GemmUniversalAdapter<GemmKernel>;
-using SfConfig = typename GemmKernel::CollectiveMainloop::Sm1xxBlkScaledConfig;
-
-typename Gemm::Arguments make_args(const void* a, const void* a_sf, const void* b, const void* b_sf,
+template <class Cfg>
+typename Cfg::Gemm::Arguments make_args(const void* a, const void* a_sf, const void* b, const void* b_sf,
                                    const float* alpha_dev, void* d, int m, int n, int k) {
+    using Gemm = typename Cfg::Gemm;
+    using GemmKernel = typename Cfg::GemmKernel;
+    using SfConfig = typename Cfg::SfConfig;
     using StrideA = typename Gemm::GemmKernel::StrideA;
     using StrideB = typename Gemm::GemmKernel::StrideB;
     using StrideD = typename Gemm::GemmKernel::StrideD;
@@ -89,13 +99,15 @@ typename Gemm::Arguments make_args(const void* a, const void* a_sf, const void* 
     return args;
 }
 
-int run_gemm(cudaStream_t stream, const void* a, const void* a_sf, const void* b, const void* b_sf,
-             const float* alpha_dev, void* d, int m, int n, int k, void* workspace, size_t workspace_bytes,
-             size_t* required_workspace) {
+template <class Cfg>
+int run_gemm_cfg(cudaStream_t stream, const void* a, const void* a_sf, const void* b, const void* b_sf,
+                 const float* alpha_dev, void* d, int m, int n, int k, void* workspace, size_t workspace_bytes,
+                 size_t* required_workspace) {
+    using Gemm = typename Cfg::Gemm;
     if (m <= 0 || n <= 0 || k <= 0) return NVK_ERR_SHAPE;
     if ((k % 32) != 0 || (n % 8) != 0) return NVK_ERR_SHAPE;  // 16-byte rows of packed operands and of D
     try {
-        auto args = make_args(a, a_sf, b, b_sf, alpha_dev, d, m, n, k);
+        auto args = make_args<Cfg>(a, a_sf, b, b_sf, alpha_dev, d, m, n, k);
         const size_t need = Gemm::get_workspace_size(args);
         if (required_workspace) *required_workspace = need;
         // all data pointers null: a pure workspace query, nothing is launched
@@ -112,8 +124,19 @@ int run_gemm(cudaStream_t stream, const void* a, const void* a_sf, const void* b
     }
 }
 
+int run_gemm(cudaStream_t stream, const void* a, const void* a_sf, const void* b, const void* b_sf,
+             const float* alpha_dev, void* d, int m, int n, int k, void* workspace, size_t workspace_bytes,
+             size_t* required_workspace) {
+    if (g_prefill_cfg == 2)
+        return run_gemm_cfg<Cfg2>(stream, a, a_sf, b, b_sf, alpha_dev, d, m, n, k, workspace, workspace_bytes,
+                                  required_workspace);
+    return run_gemm_cfg<Cfg1>(stream, a, a_sf, b, b_sf, alpha_dev, d, m, n, k, workspace, workspace_bytes,
+                              required_workspace);
+}
+
 }  // namespace
 #else   // !NVK_HAVE_CUTLASS
+namespace { int g_prefill_cfg = 2; }
 namespace {
 int run_gemm(cudaStream_t, const void*, const void*, const void*, const void*, const float*, void*, int, int, int,
              void*, size_t, size_t* required_workspace) {
@@ -124,6 +147,13 @@ int run_gemm(cudaStream_t, const void*, const void*, const void*, const void*, c
 #endif
 
 extern "C" {
+
+// Tuning hook (no counterpart in the reference): 1 = 1-SM 128x128x256 tile, 2 = 2-SM 256x128x256 tile.
+int nvk_b200_set_prefill_config(int cfg) {
+    if (cfg != 1 && cfg != 2) return NVK_ERR_ARG;
+    g_prefill_cfg = cfg;
+    return 0;
+}
 
 // The reference names these after the architecture of its own tensor-core kernels; the symbols are
 // kept so that its call sites bind unchanged.  All three run the same sm_100a kernel: the tile and

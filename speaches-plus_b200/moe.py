@@ -76,11 +76,17 @@ def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: t
     assert n <= ctx.max_tokens and x.dtype == torch.bfloat16 and x.is_contiguous()
     assert router_logits.dtype == torch.float32 and router_logits.is_contiguous()
     s = _stream()
-    _ffi.check("nv_kernels_moe_route_topk", s, router_logits.data_ptr(), bias.data_ptr() if bias is not None else None,
-               ctx.topk_ids.data_ptr(), ctx.topk_weights.data_ptr(), n, E, k, mode, float(softcap), int(norm_topk),
-               float(routed_scaling))
-    _ffi.check("nv_kernels_moe_permute", s, ctx.topk_ids.data_ptr(), ctx.perm_token.data_ptr(), ctx.offsets.data_ptr(),
-               ctx.inv_perm.data_ptr(), ctx.counts.data_ptr(), n, k, E)
+    bias_p = bias.data_ptr() if bias is not None else None
+    if E <= 256 and n * k <= 4096:
+        # decode-sized: router and permutation in one launch
+        _ffi.check("nvk_b200_moe_route_permute", s, router_logits.data_ptr(), bias_p, ctx.topk_ids.data_ptr(),
+                   ctx.topk_weights.data_ptr(), ctx.perm_token.data_ptr(), ctx.offsets.data_ptr(),
+                   ctx.inv_perm.data_ptr(), n, E, k, mode, float(softcap), int(norm_topk), float(routed_scaling))
+    else:
+        _ffi.check("nv_kernels_moe_route_topk", s, router_logits.data_ptr(), bias_p, ctx.topk_ids.data_ptr(),
+                   ctx.topk_weights.data_ptr(), n, E, k, mode, float(softcap), int(norm_topk), float(routed_scaling))
+        _ffi.check("nv_kernels_moe_permute", s, ctx.topk_ids.data_ptr(), ctx.perm_token.data_ptr(),
+                   ctx.offsets.data_ptr(), ctx.inv_perm.data_ptr(), ctx.counts.data_ptr(), n, k, E)
     g, u, d = w.gate, w.up, w.down
     _ffi.check("nvk_b200_moe_grouped_w4a16", s, g[0].data_ptr(), g[1].data_ptr(), u[0].data_ptr(), u[1].data_ptr(),
                g[2].data_ptr(), u[2].data_ptr(), x.data_ptr(), None, ctx.perm_token.data_ptr(), ctx.offsets.data_ptr(),

@@ -42,8 +42,15 @@ def quantized_operand(rng, rows, k, std, global_=None):
     return packed, lin, ref.swizzle_scales(lin), g
 
 
+@pytest.fixture(params=[2, 1], ids=["2sm", "1sm"])
+def tile_config(request):
+    assert U.ffi.call("nvk_b200_set_prefill_config", request.param) == 0
+    yield request.param
+    U.ffi.call("nvk_b200_set_prefill_config", 2)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (130, 264, 1056), (2048, 512, 768)])
-def test_block_scaled_gemm_matches_w4a4_oracle(m, n, k):
+def test_block_scaled_gemm_matches_w4a4_oracle(m, n, k, tile_config):
     U.require_gpu()
     rng = np.random.default_rng(m + n + k)
     ap, alin, asw, _ = quantized_operand(rng, m, k, 1.0, 1.0)
@@ -61,7 +68,7 @@ def test_block_scaled_gemm_matches_w4a4_oracle(m, n, k):
             assert np.array_equal(run_gemm(ap, asw, bp, bsw, alpha, m, n, k, entry), got)
 
 
-def test_linear_prefill_route_and_chunk_invariance():
+def test_linear_prefill_route_and_chunk_invariance(tile_config):
     """Nvfp4Linear with M > 64 takes the W4A4 route: equals the oracle on the same quantized bytes, and
     (rust/crates/nv-layers/tests/nvfp4_chunk_invariance.rs) is bit-identical under row chunking."""
     U.require_gpu()

@@ -400,3 +400,39 @@ def test_grouped_w4a16_moe_decode_matches_the_per_pair_oracle(n_tok):
         for t in range(n_tok):
             y1 = sp.forward_grouped_decode(w, ctx, xt[t:t + 1].contiguous(), U.dev(logits[t:t + 1])).cpu().numpy().copy()
             assert np.array_equal(y1[0], got[t])
+
+
+@pytest.mark.parametrize("E,K,mode,n", [(128, 8, 0, 1), (128, 8, 0, 64), (256, 8, 0, 33), (16, 4, 0, 7), (128, 8, 1, 16),
+                                        (200, 6, 0, 5)])
+def test_fused_route_permute_equals_the_two_kernels(E, K, mode, n):
+    """nvk_b200_moe_route_permute writes exactly what nv_kernels_moe_route_topk + nv_kernels_moe_permute
+    write (ids, offsets, permutation: equal; weights: bit-equal)."""
+    U.require_gpu()
+    rng = np.random.default_rng(E * 100 + n)
+    lg = rng.standard_normal((n, E)).astype(np.float32)
+    lg[0, 1] = lg[0, E - 1] = 8.0
+    bias = (rng.standard_normal(E) * 0.1).astype(np.float32) if mode == 1 else None
+    dl = U.dev(lg)
+    db = U.dev(bias) if bias is not None else None
+    scaling = 2.5 if mode == 1 else 1.0
+
+    def bufs():
+        i32 = dict(dtype=torch.int32, device="cuda")
+        return (torch.full((n, K), -5, **i32), torch.zeros((n, K), dtype=torch.float32, device="cuda"),
+                torch.full((n * K,), -5, **i32), torch.full((E + 1,), -5, **i32), torch.full((n * K,), -5, **i32))
+
+    a = bufs()
+    scr = torch.zeros(E, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_route_topk", U.stream(), dl.data_ptr(), db.data_ptr() if db is not None else None,
+                      a[0].data_ptr(), a[1].data_ptr(), n, E, K, mode, 0.0, 1, scaling) == 0
+    assert U.ffi.call("nv_kernels_moe_permute", U.stream(), a[0].data_ptr(), a[2].data_ptr(), a[3].data_ptr(),
+                      a[4].data_ptr(), scr.data_ptr(), n, K, E) == 0
+    b = bufs()
+    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), dl.data_ptr(), db.data_ptr() if db is not None else None,
+                      b[0].data_ptr(), b[1].data_ptr(), b[2].data_ptr(), b[3].data_ptr(), b[4].data_ptr(), n, E, K, mode,
+                      0.0, 1, scaling) == 0
+    torch.cuda.synchronize()
+    for x, y in zip(a, b):
+        assert np.array_equal(x.cpu().numpy().view(np.int32), y.cpu().numpy().view(np.int32))
+    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 4, 257, 4, 0, 0.0, 1, 1.0) == -3
+    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
