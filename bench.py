@@ -10,9 +10,10 @@ all four shapes, so a step streams ~1 GB of weights (far larger than the 126 MB 
 reads cold weights).  value = algorithmic bytes of the step / device time, where
 bytes(M,N,K) = N*K/2 + N*K/16 + 2*M*K + 2*M*N + 4.
 
-At N > 1 the same matrices are sharded tensor-parallel over the ranks (strong scaling): the three
-K=4096 shapes column-parallel (rows split, all-gather of y), the K=14336 shape row-parallel (K
-split, all-reduce of the partial y), one process per GPU over NCCL.
+At N > 1 the same matrices are sharded tensor-parallel over the ranks (strong scaling): the QKV and
+gate+up shapes column-parallel (rows split, output left sharded for the consumer), the o_proj and
+down shapes row-parallel (K split, all-reduce of the partial y over peer memory, or NCCL with
+--collective nccl), one process per GPU.
 
 `--impl reference` times the reference's CPU path for the same linears (weights dequantized to
 bf16 once, then bf16 x bf16 -> f32 -> bf16, all host cores) through the CPU oracle.
@@ -33,7 +34,8 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 SHAPES_KN = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]  # (K, N)
-ROW_PARALLEL = {(14336, 4096)}  # split along K at N > 1; the others split along N
+ROW_PARALLEL = {(4096, 4096), (14336, 4096)}  # o_proj / down: split along K at N > 1, all-reduce of y;
+# the other two (QKV, gate+up) split along N and their outputs stay sharded into the consumer
 COPIES = 8
 METRIC = "nvfp4_decode_gemv_hbm_gbs"
 
@@ -120,6 +122,11 @@ def run_b200(args) -> dict:
     sp.ffi.lib()
     mark("process group up")
 
+    peer_ar = None
+    if world > 1 and args.collective == "peer":
+        peer_ar = tpmod.PeerAllReduce(None, 64 * 5120, dev)
+        mark("peer all-reduce ready")
+
     # ---- synthetic weights: seeded, identical on every rank, then sharded ----
     copies = COPIES
     layers = []  # (K, N, [TpLinear per copy])
@@ -129,7 +136,9 @@ def run_b200(args) -> dict:
         for c in range(copies):
             gen = torch.Generator(device=dev).manual_seed(1000 * si + c)
             w = (torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-            per_copy.append(tpmod.TpNvfp4Linear.from_bf16(w, mode, rank, world))
+            lin = tpmod.TpNvfp4Linear.from_bf16(w, mode, rank, world)
+            lin.peer_ar = peer_ar
+            per_copy.append(lin)
             del w
         layers.append((k, n, per_copy))
     gen = torch.Generator(device=dev).manual_seed(7)
@@ -141,7 +150,7 @@ def run_b200(args) -> dict:
         for k, n, per_copy in layers:
             x = xs[k]
             for lin in per_copy:
-                lin.forward(x)
+                lin.forward(x, gather=False)
 
     launches_per_step = copies * len(SHAPES_KN)
     mark("weights ready")
@@ -210,6 +219,8 @@ def run_b200(args) -> dict:
                                         "gbs": round(algo_bytes(1, n, k) / (us * 1e-6) / 1e9, 1)}
 
     mark("per-shape done")
+    if peer_ar is not None:
+        peer_ar.check()
     # ---- end to end through the public API with host buffers ----
     pin_x = {k: torch.randn((1, k), dtype=torch.float32).to(torch.bfloat16).pin_memory() for k in xs}
     pin_y = {(k, n): torch.empty((1, n), dtype=torch.bfloat16).pin_memory() for k, n in SHAPES_KN}
@@ -261,6 +272,7 @@ def run_b200(args) -> dict:
             "config": {"workload": "configs[1] NVFP4 GEMV shape sweep, M=1", "shapes_KN": SHAPES_KN,
                        "weight_copies_per_shape": copies, "launches_per_step": launches_per_step,
                        "parallelism": f"tp{world}" if world > 1 else "single",
+                       "collective": (args.collective if world > 1 else None),
                        "l2": f"inputs larger than L2: {total_bytes / 1e6:.0f} MB of cold weights per step",
                        "timing": "CUDA events around K replays of a CUDA graph of one step"},
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
@@ -287,9 +299,12 @@ def run_b200(args) -> dict:
         layers.clear()
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
-        stack = [decode_stack_leg(dev, rank, world, b) for b in (1, 16)]
+        stack = [decode_stack_leg(dev, rank, world, b, peer_ar=peer_ar) for b in (1, 16)]
         moe = [moe_decode_leg(dev, b) for b in (1, 16, 64)] if world == 1 else None
-        pre = prefill_leg(dev) if world == 1 else None
+        pre = None
+        if world == 1:
+            pre = (prefill_leg(dev) if sp.ffi.prefill_available()
+                   else "unavailable: libnvk_b200_prefill.so is not part of this run")
         if out is not None:
             out["decode_stack"] = stack
             if moe is not None:
@@ -315,7 +330,7 @@ def run_b200(args) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
-def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, replays: int = 5) -> dict:
+def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, replays: int = 5, peer_ar=None) -> dict:
     """BASELINE configs[2]: dense decoder linear stack (hidden 5120, 64 q / 8 kv heads of 128, SwiGLU
     25600, bf16 lm_head 151936), random-init NVFP4 weights, one decode step of `batch` tokens through
     every linear.  Attention itself is outside the path: o_proj is fed the q slice of the QKV output.
@@ -360,6 +375,12 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, r
     def lin_call(lin, lin_b, x, x2, y, y_b):
         L.linear_w4a16(lin, lin_b, x, x2, y, y_b, batch)
 
+    def reduce_(t):
+        if peer_ar is not None:
+            peer_ar.all_reduce_(t)
+        else:
+            dist.all_reduce(t)
+
     def step():
         for (w_qkv, w_o, w_g, w_u, w_d) in stack:
             lin_call(w_qkv, None, x0, None, qkv, None)
@@ -370,11 +391,11 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, r
                 q_view = q_in
             lin_call(w_o, None, q_view, None, o_out, None)
             if world > 1:
-                dist.all_reduce(o_out)
+                reduce_(o_out)
             lin_call(w_g, w_u, o_out, None, gate, up)
             lin_call(w_d, None, gate, up, d_out, None)
             if world > 1:
-                dist.all_reduce(d_out)
+                reduce_(d_out)
         for r in range(batch):
             ffi.check("nv_kernels_gemv_bf16", torch.cuda.current_stream().cuda_stream, lm_head.weight.data_ptr(),
                       d_out[r].data_ptr(), logits_l[r].data_ptr(), v_l, H)
@@ -629,6 +650,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="skip the configs[2] decode-stack and configs[3] MoE legs")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="row-parallel sum at --gpus > 1: one-shot all-reduce over peer memory, or NCCL")
     ap.add_argument("--profile-case", default=None, metavar="K,N,M",
                     help="run a few eager launches of one case and exit (for profiler captures)")
     ap.add_argument("--copies", type=int, default=4)

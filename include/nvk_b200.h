@@ -282,6 +282,21 @@ int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uin
                                const int32_t* row_index, const int32_t* expert_offsets, uint16_t* y_a,
                                uint16_t* y_b, int num_experts, int N, int K);
 
+/* ---- tensor-parallel exchange (no counterpart in the reference, which has no multi-GPU code) ---
+ * One-shot all-reduce of a small bf16 vector over peer memory for the row-parallel linears of a
+ * decode step: every rank stores its partial into an inbox on every peer (plain peer stores, no
+ * multicast), flags it, waits (bounded) for all peers and sums the slots in rank order in fp32, so
+ * every rank gets the same bits.  The call number lives in device memory, so captured graphs replay.
+ *   peer_bufs  `world` device pointers: the symmetric buffer of each rank as mapped here, each of
+ *              nvk_b200_tp_allreduce_buffer_bytes(world, max_elems) bytes, zero-filled before first use
+ *   epoch      32 uint32 of local device memory, zero-filled before first use
+ *   err        one int of local device memory; non-zero (1 + missing peer) if a wait gave up
+ * n % 8 == 0, n <= max_elems <= 262144, 16-byte aligned x and y, world <= 8; every rank must issue
+ * the same sequence of calls.  -2 bad argument, -3 vector too long. */
+size_t nvk_b200_tp_allreduce_buffer_bytes(int world, int max_elems);
+int nvk_b200_tp_allreduce_bf16(void* stream, const void* const* peer_bufs, int rank, int world, const uint16_t* x,
+                               uint16_t* y, int n, int max_elems, uint32_t* epoch, int* err);
+
 #ifdef __cplusplus
 }
 #endif

@@ -10,6 +10,7 @@ import pathlib
 
 _HERE = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libnvk_b200.so"
+PREFILL_LIB_PATH = _HERE / "libnvk_b200_prefill.so"  # the prefill GEMM lives in a library of its own
 
 _vp, _i, _f, _ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 
@@ -25,7 +26,6 @@ SIGNATURES = {
     "nvk_b200_linear_workspace_bytes": [_i, _i],
     "nvk_b200_set_tuning": [_i, _i],
     "nvk_b200_set_pdl": [_i],
-    "nvk_b200_set_prefill_config": [_i],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _f, _i, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16_rows": [_vp, _vp, _vp, _vp, _f, _i, _i],
@@ -43,16 +43,24 @@ SIGNATURES = {
     "nv_kernels_moe_unpermute_scatter": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "nv_kernels_moe_unpermute_scatter_tail": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "nv_kernels_moe_permute": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
-    "nv_kernels_cutlass_fp4_gemm_sm120_bf16": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
-    "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
-    "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled": [_vp] * 7 + [_i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
     "nvk_b200_moe_grouped_w4a16": [_vp] * 13 + [_i, _i, _i],
+    "nvk_b200_tp_allreduce_buffer_bytes": [_i, _i],
+    "nvk_b200_tp_allreduce_bf16": [_vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp],
     "nvk_b200_moe_route_permute": [_vp] * 8 + [_i, _i, _i, _i, _f, _i, _f],
     "nvk_b200_moe_permute_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_moe_grouped_fp4_gemv_m1_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll],
 }
 
+# symbols exported by the prefill library
+PREFILL_SIGNATURES = {
+    "nvk_b200_set_prefill_config": [_i],
+    "nv_kernels_cutlass_fp4_gemm_sm120_bf16": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
+    "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
+    "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled": [_vp] * 7 + [_i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
+}
+
 _lib = None
+_prefill_lib = None
 
 
 class NvkError(RuntimeError):
@@ -77,13 +85,36 @@ def lib() -> C.CDLL:
         for name, args in SIGNATURES.items():
             fn = getattr(L, name)  # AttributeError if a declared symbol is not exported
             fn.argtypes = args
-            fn.restype = C.c_size_t if name.endswith("_workspace_bytes") else C.c_int
+            fn.restype = C.c_size_t if name.endswith("_bytes") else C.c_int
         _lib = L
     return _lib
 
 
+def prefill_available() -> bool:
+    return PREFILL_LIB_PATH.exists()
+
+
+def prefill_lib() -> C.CDLL:
+    """Load the prefill-GEMM library.  A missing build is an error, not a fallback."""
+    global _prefill_lib
+    if _prefill_lib is None:
+        if not PREFILL_LIB_PATH.exists():
+            raise RuntimeError(
+                f"{PREFILL_LIB_PATH} is missing: the prefill (M > 64) route needs it; build it with "
+                "`python speaches-plus_b200/build.py` (needs CUTLASS headers; there is no fallback)")
+        L = C.CDLL(str(PREFILL_LIB_PATH))
+        for name, args in PREFILL_SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+        _prefill_lib = L
+    return _prefill_lib
+
+
 def call(name: str, *args) -> int:
     """Call a launcher and return its raw status."""
+    if name in PREFILL_SIGNATURES:
+        return int(getattr(prefill_lib(), name)(*args))
     return int(getattr(lib(), name)(*args))
 
 

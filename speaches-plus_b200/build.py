@@ -2,8 +2,10 @@
 
     python speaches-plus_b200/build.py [--force] [--verbose]
 
-The library is a plain C-ABI shared object (see include/nvk_b200.h); it links the CUDA
-runtime statically so that it loads next to any other CUDA user in the process.
+Two plain C-ABI shared objects (see include/nvk_b200.h), each linking the CUDA runtime statically:
+libnvk_b200.so (csrc/: every decode-path kernel) and libnvk_b200_prefill.so (csrc_prefill/: the
+prefill block-scaled GEMM, built from CUTLASS headers when they are found).  The split keeps the
+CUTLASS-derived kernel out of multi-GPU runs, which only need the first library.
 """
 from __future__ import annotations
 
@@ -14,8 +16,10 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
+CSRC_PREFILL = HERE / "csrc_prefill"
 OBJ = HERE / "build"
 LIB = HERE / "libnvk_b200.so"
+LIB_PREFILL = HERE / "libnvk_b200_prefill.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 
@@ -50,11 +54,16 @@ def _newest_header() -> float:
 
 
 def _newest_dep() -> float:
-    return max(f.stat().st_mtime for f in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")))
+    return max(f.stat().st_mtime for f in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) +
+               list(CSRC_PREFILL.glob("*.cu")))
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
-    if not force and LIB.exists() and LIB.stat().st_mtime >= _newest_dep():
+    have_prefill_src = CSRC_PREFILL.exists() and any(CSRC_PREFILL.glob("*.cu"))
+    up_to_date = LIB.exists() and LIB.stat().st_mtime >= _newest_dep()
+    if have_prefill_src:
+        up_to_date = up_to_date and LIB_PREFILL.exists() and LIB_PREFILL.stat().st_mtime >= _newest_dep()
+    if not force and up_to_date:
         return LIB
     OBJ.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
@@ -75,11 +84,14 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
             raise RuntimeError(f"nvcc failed on {src.name}")
         return obj
 
+    prefill_srcs = sorted(CSRC_PREFILL.glob("*.cu")) if have_prefill_src else []
     with ThreadPoolExecutor(max_workers=8) as ex:
-        objs = list(ex.map(compile_one, sources()))
-    cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs),
-           "-cudart", "static"]
-    subprocess.run(cmd, check=True)
+        all_objs = list(ex.map(compile_one, sources() + prefill_srcs))
+    objs, pre_objs = all_objs[:len(sources())], all_objs[len(sources()):]
+    link = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"]
+    subprocess.run([*link, "-o", str(LIB), *map(str, objs)], check=True)
+    if pre_objs:
+        subprocess.run([*link, "-o", str(LIB_PREFILL), *map(str, pre_objs)], check=True)
     return LIB
 
 

@@ -15,7 +15,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
-#include "nvk_common.cuh"
+#include "../csrc/nvk_common.cuh"
 
 #ifdef NVK_HAVE_CUTLASS
 #include "cutlass/cutlass.h"

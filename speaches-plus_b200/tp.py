@@ -53,13 +53,58 @@ def shard_nvfp4(packed: torch.Tensor, scales_swz: torch.Tensor, n: int, k: int, 
     raise ValueError(f"unknown tensor-parallel mode {mode!r}")
 
 
+class PeerAllReduce:
+    """One-shot all-reduce over peer memory (nvk_b200_tp_allreduce_bf16) for vectors of up to
+    `max_elems` bf16 values.  The symmetric buffer comes from torch's symmetric-memory allocator, which
+    maps every rank's buffer into this process; everything else is local device memory."""
+
+    def __init__(self, group, max_elems: int, device):
+        import ctypes as C
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _ffi
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.max_elems = (max_elems + 7) // 8 * 8
+        nbytes = int(_ffi.lib().nvk_b200_tp_allreduce_buffer_bytes(self.world, self.max_elems))
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._ptr_array = (C.c_void_p * self.world)(*ptrs)
+        self.epoch = torch.zeros(32, dtype=torch.int32, device=device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # every inbox is zeroed before anyone pushes
+
+    def all_reduce_(self, y: torch.Tensor) -> torch.Tensor:
+        """In-place sum of a contiguous bf16 tensor across the group."""
+        import ctypes as C
+
+        from . import _ffi
+        n = y.numel()
+        _ffi.check("nvk_b200_tp_allreduce_bf16", torch.cuda.current_stream().cuda_stream,
+                   C.addressof(self._ptr_array), self.rank, self.world, y.data_ptr(), y.data_ptr(), n, self.max_elems,
+                   self.epoch.data_ptr(), self.err.data_ptr())
+        return y
+
+    def check(self) -> None:
+        """Raise if any wait gave up since the last check (reads one int back; synchronises)."""
+        e = int(self.err.item())
+        if e:
+            self.err.zero_()
+            raise RuntimeError(f"peer all-reduce: rank {e - 1} never arrived within the wait limit")
+
+
 class TpNvfp4Linear:
     """One rank's shard of an NVFP4 linear plus the collective that completes it."""
 
     def __init__(self, local: L.Nvfp4Linear | None, mode: str, rank: int, world: int, n: int, k: int, offset: int,
-                 group=None):
+                 group=None, peer_ar: "PeerAllReduce | None" = None):
         self.local, self.mode, self.rank, self.world = local, mode, rank, world
         self.n, self.k, self.offset, self.group = n, k, offset, group
+        self.peer_ar = peer_ar  # when set, row-parallel sums go over peer memory instead of NCCL
         self._bufs = {}
 
     @classmethod
@@ -109,5 +154,8 @@ class TpNvfp4Linear:
             xs = xs.contiguous()
         y = self._buf("yr", (m, self.n), x.device)
         self.local.forward_into(xs, y)
-        dist.all_reduce(y, group=self.group)
+        if self.peer_ar is not None and y.numel() % 8 == 0 and y.numel() <= self.peer_ar.max_elems:
+            self.peer_ar.all_reduce_(y)
+        else:
+            dist.all_reduce(y, group=self.group)
         return y

@@ -25,14 +25,18 @@ def test_header_declares_the_path_entry_points():
 
 
 def test_library_exports_every_declared_symbol():
+    """The decode-path symbols come from libnvk_b200.so, the prefill GEMM's from libnvk_b200_prefill.so."""
     lib = ctypes.CDLL(str(sp.ffi.LIB_PATH))
+    pre = ctypes.CDLL(str(sp.ffi.PREFILL_LIB_PATH))
     for name in declared_symbols():
-        assert hasattr(lib, name), f"{name} declared in include/nvk_b200.h but not exported"
+        owner = pre if name in sp.ffi.PREFILL_SIGNATURES else lib
+        assert hasattr(owner, name), f"{name} declared in include/nvk_b200.h but not exported"
 
 
 def test_binding_matches_header():
-    assert sorted(sp.ffi.SIGNATURES) == declared_symbols()
+    assert sorted(list(sp.ffi.SIGNATURES) + list(sp.ffi.PREFILL_SIGNATURES)) == declared_symbols()
     sp.ffi.lib()  # resolves every symbol, raises if one is missing
+    sp.ffi.prefill_lib()
 
 
 def test_header_compiles_as_c(tmp_path):
