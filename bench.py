@@ -117,15 +117,18 @@ def run_b200(args) -> dict:
             print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
 
     if world > 1:
-        import datetime
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
+        tpmod.init_process_group_for_node(dev)  # NVLS off, see tp.init_process_group_for_node
     sp.ffi.lib()
     mark("process group up")
 
     peer_ar = None
     if world > 1 and args.collective == "peer":
-        peer_ar = tpmod.PeerAllReduce(None, 64 * 5120, dev)
-        mark("peer all-reduce ready")
+        try:
+            peer_ar = tpmod.PeerAllReduce(None, 64 * 5120, dev)
+            mark("peer all-reduce ready")
+        except RuntimeError as e:  # raised on every rank together; the sums then go through NCCL
+            args.collective = f"nccl ({e})"
+            mark(str(e))
 
     # ---- synthetic weights: seeded, identical on every rank, then sharded ----
     copies = COPIES
@@ -316,16 +319,17 @@ def run_b200(args) -> dict:
     if out is not None:
         print(json.dumps(out), flush=True)
     if world > 1:
-        # Tear down in dependency order: the captured graph holds NCCL work, so it goes first.
-        del graph
-        torch.cuda.synchronize()
-        dist.barrier()
-        mark("final barrier passed")
+        # Tear down in dependency order: captured graphs (they hold collective work) first, then the
+        # peer mappings, then the process group.
+        graph = None
+        if peer_ar is not None:
+            peer_ar.close()
+        clean = tpmod.shutdown_process_group()
+        mark(f"process group destroyed: {clean}")
         sys.stdout.flush()
         sys.stderr.flush()
-        # The communicator is left to process exit: destroying it after graph capture has been
-        # seen to block, and every result is already printed.
-        os._exit(0)
+        if not clean:
+            os._exit(0)  # every rank is past the final barrier; nothing of ours is mapped any more
     return None
 
 

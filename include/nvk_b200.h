@@ -294,6 +294,15 @@ int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uin
  * n % 8 == 0, n <= max_elems <= 262144, 16-byte aligned x and y, world <= 8; every rank must issue
  * the same sequence of calls.  -2 bad argument, -3 vector too long. */
 size_t nvk_b200_tp_allreduce_buffer_bytes(int world, int max_elems);
+/* Set-up helpers for that buffer (host side, they allocate and synchronise; never on the launch path):
+ * plain cudaMalloc'd, zero-filled device memory shared between the ranks of one node with CUDA IPC
+ * handles (64 bytes each, exchanged by the caller over its own host-side channel).  No memory is bound
+ * to a multicast object.  Each returns 0 or a cudaError_t (-2 on a null argument). */
+int nvk_b200_tp_buffer_alloc(size_t bytes, void** dev_ptr);
+int nvk_b200_tp_buffer_free(void* dev_ptr);
+int nvk_b200_tp_ipc_export(void* dev_ptr, void* handle_out_64_bytes);
+int nvk_b200_tp_ipc_open(const void* handle_64_bytes, void** dev_ptr);
+int nvk_b200_tp_ipc_close(void* dev_ptr);
 int nvk_b200_tp_allreduce_bf16(void* stream, const void* const* peer_bufs, int rank, int world, const uint16_t* x,
                                uint16_t* y, int n, int max_elems, uint32_t* epoch, int* err);
 

@@ -45,6 +45,11 @@ SIGNATURES = {
     "nv_kernels_moe_permute": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nvk_b200_moe_grouped_w4a16": [_vp] * 13 + [_i, _i, _i],
     "nvk_b200_tp_allreduce_buffer_bytes": [_i, _i],
+    "nvk_b200_tp_buffer_alloc": [C.c_size_t, _vp],
+    "nvk_b200_tp_buffer_free": [_vp],
+    "nvk_b200_tp_ipc_export": [_vp, _vp],
+    "nvk_b200_tp_ipc_open": [_vp, _vp],
+    "nvk_b200_tp_ipc_close": [_vp],
     "nvk_b200_tp_allreduce_bf16": [_vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp],
     "nvk_b200_moe_route_permute": [_vp] * 8 + [_i, _i, _i, _i, _f, _i, _f],
     "nvk_b200_moe_permute_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],

@@ -6,7 +6,8 @@
 // multicast, no TMA), raises a flag on each peer, waits for the flags of all peers and sums the
 // inbox slots in rank order in fp32 -- the same order on every rank, so all ranks get the same bits.
 //
-// Memory (one symmetric buffer per rank, same layout everywhere; peers' base pointers are passed in):
+// Memory (one buffer per rank, same layout everywhere, shared with CUDA IPC; peers' base pointers
+// are passed in):
 //   [0, 4096)            flags: uint32 flags[kMaxCtas][kMaxRanks], written by peers
 //   [4096, ...)          inbox: 2 parities x world x max_elems bf16
 // The call number ("epoch") lives in device memory and is advanced by the kernel itself, so a
@@ -16,6 +17,8 @@
 //
 // Every wait is bounded: after kSpinLimit polls the kernel records an error and returns, leaving the
 // context usable.  The caller must run the same sequence of calls on every rank.
+#include <string.h>
+
 #include "nvk_common.cuh"
 
 namespace {
@@ -110,6 +113,38 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const ArParams p) {
 }  // namespace
 
 extern "C" {
+
+// ---- set-up helpers (host side, not on the launch path) ------------------------------------------
+// The exchange buffer is plain device memory shared between the ranks of one node with CUDA IPC
+// handles: each rank allocates its buffer, exports a 64-byte handle, the handles travel over the
+// host-side process group, and every rank opens its peers' handles.  Nothing here binds memory to a
+// multicast object, so a rank that exits leaves its peers' GPUs alone.
+int nvk_b200_tp_buffer_alloc(size_t bytes, void** dev_ptr) {
+    if (!dev_ptr || bytes == 0) return NVK_ERR_ARG;
+    cudaError_t e = cudaMalloc(dev_ptr, bytes);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemset(*dev_ptr, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return (int)e;
+}
+
+int nvk_b200_tp_buffer_free(void* dev_ptr) { return dev_ptr ? (int)cudaFree(dev_ptr) : 0; }
+
+// handle_out: 64 bytes (sizeof(cudaIpcMemHandle_t)).
+int nvk_b200_tp_ipc_export(void* dev_ptr, void* handle_out) {
+    if (!dev_ptr || !handle_out) return NVK_ERR_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    return (int)cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle_out), dev_ptr);
+}
+
+int nvk_b200_tp_ipc_open(const void* handle, void** dev_ptr) {
+    if (!handle || !dev_ptr) return NVK_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    return (int)cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+
+int nvk_b200_tp_ipc_close(void* dev_ptr) { return dev_ptr ? (int)cudaIpcCloseMemHandle(dev_ptr) : 0; }
 
 // Bytes of the symmetric buffer every rank must provide for vectors of up to max_elems bf16 values.
 size_t nvk_b200_tp_allreduce_buffer_bytes(int world, int max_elems) {

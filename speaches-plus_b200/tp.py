@@ -55,38 +55,61 @@ def shard_nvfp4(packed: torch.Tensor, scales_swz: torch.Tensor, n: int, k: int, 
 
 class PeerAllReduce:
     """One-shot all-reduce over peer memory (nvk_b200_tp_allreduce_bf16) for vectors of up to
-    `max_elems` bf16 values.  The symmetric buffer comes from torch's symmetric-memory allocator, which
-    maps every rank's buffer into this process; everything else is local device memory."""
+    `max_elems` bf16 values.  Each rank's exchange buffer is plain device memory that the other ranks
+    of the node map through CUDA IPC handles (exchanged over the process group's host side); no
+    memory is bound to a multicast object.  Call `close()` on every rank before the process group is
+    torn down."""
 
     def __init__(self, group, max_elems: int, device):
         import ctypes as C
 
-        import torch.distributed._symmetric_memory as symm_mem
-
         from . import _ffi
+        self._C, self._ffi = C, _ffi
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.max_elems = (max_elems + 7) // 8 * 8
         nbytes = int(_ffi.lib().nvk_b200_tp_allreduce_buffer_bytes(self.world, self.max_elems))
-        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        self.handle = symm_mem.rendezvous(self.buf, self.group)
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        own = C.c_void_p(0)
+        _ffi.check("nvk_b200_tp_buffer_alloc", nbytes, C.addressof(own))   # zero-filled
+        self._own = own.value
+        handle = (C.c_ubyte * 64)()
+        _ffi.check("nvk_b200_tp_ipc_export", self._own, C.addressof(handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=self.group)
+        self._opened = []
+        ptrs = []
+        failure = None
+        for r in range(self.world):
+            if r == self.rank:
+                ptrs.append(self._own)
+                continue
+            raw = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+            peer = C.c_void_p(0)
+            rc = _ffi.call("nvk_b200_tp_ipc_open", C.addressof(raw), C.addressof(peer))
+            if rc != 0:
+                failure = f"opening rank {r}'s buffer failed with CUDA error {rc}"
+                break
+            self._opened.append(peer.value)
+            ptrs.append(peer.value)
+        # Every rank learns whether every mapping succeeded, so that all of them either go on or
+        # all of them give the buffers back and raise.
+        ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            self.close()
+            raise RuntimeError("peer all-reduce unavailable: " + (failure or "a peer could not map the buffers"))
         self._ptr_array = (C.c_void_p * self.world)(*ptrs)
         self.epoch = torch.zeros(32, dtype=torch.int32, device=device)
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(self.group)  # every inbox is zeroed before anyone pushes
+        dist.barrier(self.group)  # every inbox exists and is zeroed before anyone pushes
 
     def all_reduce_(self, y: torch.Tensor) -> torch.Tensor:
         """In-place sum of a contiguous bf16 tensor across the group."""
-        import ctypes as C
-
-        from . import _ffi
         n = y.numel()
-        _ffi.check("nvk_b200_tp_allreduce_bf16", torch.cuda.current_stream().cuda_stream,
-                   C.addressof(self._ptr_array), self.rank, self.world, y.data_ptr(), y.data_ptr(), n, self.max_elems,
-                   self.epoch.data_ptr(), self.err.data_ptr())
+        self._ffi.check("nvk_b200_tp_allreduce_bf16", torch.cuda.current_stream().cuda_stream,
+                        self._C.addressof(self._ptr_array), self.rank, self.world, y.data_ptr(), y.data_ptr(), n,
+                        self.max_elems, self.epoch.data_ptr(), self.err.data_ptr())
         return y
 
     def check(self) -> None:
@@ -95,6 +118,52 @@ class PeerAllReduce:
         if e:
             self.err.zero_()
             raise RuntimeError(f"peer all-reduce: rank {e - 1} never arrived within the wait limit")
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free ours.  Collective: every rank calls it, with no
+        all-reduce in flight; peers unmap before anyone frees."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        for p in self._opened:
+            self._ffi.call("nvk_b200_tp_ipc_close", p)
+        self._opened = []
+        dist.barrier(self.group)
+        self._ffi.call("nvk_b200_tp_buffer_free", self._own)
+        self._own = None
+
+
+def init_process_group_for_node(device, timeout_s: int = 90):
+    """NCCL process group for the GPUs of one node with in-switch multicast (NVLS) turned off: on
+    shared machines a rank that goes away while its memory is bound to an NVLink multicast object
+    disturbs its peers' GPUs, and nothing on this path needs it."""
+    import datetime
+    import os
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=timeout_s))
+
+
+def shutdown_process_group(join_s: float = 30.0) -> bool:
+    """Orderly end of a multi-GPU run: the caller has deleted its CUDA graphs and closed its
+    PeerAllReduce; this synchronises, meets the other ranks at a barrier and destroys the process
+    group.  Returns False if the destroy call did not come back within `join_s` seconds (every rank
+    is past the barrier by then, so the caller may simply exit)."""
+    import threading
+    torch.cuda.synchronize()
+    dist.barrier()
+    done = threading.Event()
+
+    def _destroy():
+        try:
+            dist.destroy_process_group()
+        finally:
+            done.set()
+
+    th = threading.Thread(target=_destroy, daemon=True)
+    th.start()
+    return done.wait(join_s)
 
 
 class TpNvfp4Linear:

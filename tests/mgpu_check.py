@@ -1,7 +1,6 @@
 """Multi-GPU checks, run as `torchrun --nproc-per-node N tests/mgpu_check.py` (one rank per GPU):
 the peer-memory all-reduce equals the fp32 rank-order sum bit for bit (eagerly and replayed from a
 CUDA graph), and tensor-parallel NVFP4 linears (column and row) equal the unsharded linear."""
-import datetime
 import os
 import pathlib
 import sys
@@ -19,7 +18,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
+    tp.init_process_group_for_node(dev, timeout_s=60)
     ar = tp.PeerAllReduce(None, 64 * 5120, dev)
 
     def expected(parts):
@@ -76,11 +75,13 @@ def main():
                 err = ((got - want).abs() / torch.clamp(want.abs(), min=max(rms, 1e-3))).max().item()
                 assert err < 1e-2, f"row-parallel error {err}"
     ar.check()
-    dist.barrier()
     if rank == 0:
         print("mgpu_check ok", flush=True)
+    ar.close()
+    clean = tp.shutdown_process_group()
     sys.stdout.flush()
-    os._exit(0)
+    if not clean:
+        os._exit(0)
 
 
 if __name__ == "__main__":

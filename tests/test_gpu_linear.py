@@ -361,3 +361,38 @@ def test_bf16_lm_head_gemv():
         assert U.rel_err_floor(ref.bf16_to_f32(U.host_u16(y)).reshape(1, n), want) < 1e-2
         cpu = ref.linear_cpu_backend(w, x)
         assert U.bf16_ulp_diff(U.host_u16(y), cpu[0]).max() <= 2
+
+
+@pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)])
+@pytest.mark.parametrize("m", [1, 4, 16, 64])
+def test_configs1_full_size_sweep(k, n, m):
+    """BASELINE configs[1] at full size: every (K, N) x M against the f64 oracle on a seeded subset of
+    rows (all tokens; 512 output rows spread over the matrix, so every launch path is exercised while
+    the CPU side stays at seconds), plus a size-independent property on the whole output: rows computed
+    as part of the full matrix equal rows computed from a 128-row-aligned slice of it, bit for bit."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    torch.manual_seed(k + n)
+    w = (torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16)
+    lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w)
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    y = lin(x)
+    torch.cuda.synchronize()
+    packed = lin.weight_u8.cpu().numpy().reshape(n, k // 2)
+    sw = lin.weight_scales.cpu().numpy()
+    xb = U.host_u16(x).reshape(m, k)
+    got = U.host_u16(y).reshape(m, n)
+    rng = np.random.default_rng(n)
+    tiles = rng.choice(n // 128, size=4, replace=False)
+    lin_scales = ref.unswizzle_scales(sw, n, k // 16)
+    for t in tiles:
+        r0 = int(t) * 128
+        sub_p, sub_s = packed[r0:r0 + 128], ref.swizzle_scales(lin_scales[r0:r0 + 128])
+        want = ref.linear_w4a16_f64(sub_p, sub_s, xb, lin.weight_alpha, 128, k)
+        e = U.rel_err_floor(ref.bf16_to_f32(got[:, r0:r0 + 128]), want)
+        assert e < TOL_F64, f"tile {t}: {e}"
+        # property: the same rows from a stand-alone 128-row linear give the same bits
+        small = sp.Nvfp4Linear.new_nvfp4(U.dev(sub_p), U.dev(sub_s), lin.weight_alpha, k, 128)
+        ys = small(x)
+        torch.cuda.synchronize()
+        assert np.array_equal(U.host_u16(ys).reshape(m, 128), got[:, r0:r0 + 128])
