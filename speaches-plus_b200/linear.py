@@ -45,7 +45,7 @@ def linear_w4a16(lin_a, lin_b, x, x2, y_a, y_b, m: int) -> None:
                lin_b.weight_u8.data_ptr() if lin_b is not None else None,
                lin_b.weight_scales.data_ptr() if lin_b is not None else None, x.data_ptr(),
                x2.data_ptr() if x2 is not None else None, y_a.data_ptr(), y_b.data_ptr() if y_b is not None else None,
-               lin_a.weight_alpha, lin_b.weight_alpha if lin_b is not None else 0.0, m, n, k,
+               lin_a.alpha_w4a16, lin_b.alpha_w4a16 if lin_b is not None else 0.0, m, n, k,
                ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0)
 
 
@@ -118,6 +118,14 @@ class Nvfp4Linear:
         return cls(weight_u8, weight_scales_swizzled, weight_alpha, in_features, out_features, bias)
 
     @classmethod
+    def new_nvfp4_scaled(cls, weight_u8, weight_scales_swizzled, in_features, out_features, bias, weight_alpha,
+                         input_stored_global):
+        """A checkpoint's linear: `weight_alpha` = 1/(weight global) x 1/(input global), and the stored input
+        global the activations are quantized with on the FP4 x FP4 route (linear.rs:2080-2115)."""
+        return cls(weight_u8, weight_scales_swizzled, weight_alpha, in_features, out_features, bias,
+                   input_stored_global)
+
+    @classmethod
     def from_bf16_quantized_nvfp4_dev(cls, weight: torch.Tensor, bias: torch.Tensor | None = None):
         n, k = weight.shape
         packed, scales, alpha, _ = quantize_weight_nvfp4(weight)
@@ -126,6 +134,18 @@ class Nvfp4Linear:
     def nvfp4_parts(self):
         """(packed weights, swizzled scales, weight_alpha) -- linear.rs:411-451."""
         return self.weight_u8, self.weight_scales, self.weight_alpha
+
+    def nvfp4_parts_full(self):
+        """The same plus the stored input global (linear.rs:411-427)."""
+        return self.weight_u8, self.weight_scales, self.weight_alpha, self.input_stored_global
+
+    @property
+    def alpha_w4a16(self) -> float:
+        """Output multiplier when the activations stay bf16: the reciprocal of the weight global alone.
+        `weight_alpha` also carries the reciprocal of the input global, which only the route that
+        quantizes activations needs, so it is multiplied back out here, as the reference's W4A16 call
+        sites do (rust/crates/nv-models/src/qwen3_5_moe.rs:718-727)."""
+        return float(np.float32(self.weight_alpha) * np.float32(self.input_stored_global))
 
     # -- forward --
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -149,7 +169,7 @@ class Nvfp4Linear:
         s = _stream()
         if m == 1:
             _ffi.check("nv_kernels_nvfp4_gemv_bf16act", s, self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
-                       x2.data_ptr(), y.data_ptr(), self.weight_alpha, self.out_features, self.in_features)
+                       x2.data_ptr(), y.data_ptr(), self.alpha_w4a16, self.out_features, self.in_features)
             return
         if m > MAX_DECODE_M and self.out_features % 8 == 0 and self.in_features % 32 == 0:
             self.forward_prefill_into(x2, y)
@@ -166,7 +186,7 @@ class Nvfp4Linear:
         m_pad = -(-m // 128) * 128
         a_packed, a_scales = quantize_nvfp4_bf16(x2, self.input_stored_global, m_padded=m_pad)
         if getattr(self, "_alpha_dev", None) is None or self._alpha_dev.device != x2.device:
-            self._alpha_dev = torch.tensor([self.weight_alpha / self.input_stored_global], dtype=torch.float32,
+            self._alpha_dev = torch.tensor([self.weight_alpha], dtype=torch.float32,
                                            device=x2.device)
         need = C.c_size_t(0)
         s = _stream()

@@ -39,7 +39,7 @@ class MoeGroupedWeights:
             packed = torch.stack([l.weight_u8.reshape(l.out_features, l.in_features // 2) for l in lins]).contiguous()
             nbytes = L.swizzled_scale_bytes(lins[0].out_features, lins[0].in_features)
             scales = torch.stack([l.weight_scales[:nbytes] for l in lins]).contiguous()
-            alphas = torch.tensor([l.weight_alpha for l in lins], dtype=torch.float32, device=packed.device)
+            alphas = torch.tensor([l.alpha_w4a16 for l in lins], dtype=torch.float32, device=packed.device)
             return packed, scales, alphas
 
         return cls(bank(0), bank(1), bank(2), hidden, inter, len(experts))
