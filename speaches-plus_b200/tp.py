@@ -53,6 +53,23 @@ def shard_nvfp4(packed: torch.Tensor, scales_swz: torch.Tensor, n: int, k: int, 
     raise ValueError(f"unknown tensor-parallel mode {mode!r}")
 
 
+def shard_nvfp4_fused(packed: torch.Tensor, scales_swz: torch.Tensor, parts: int, n_each: int, k: int, rank: int,
+                      world: int):
+    """Column shard of a matrix that is `parts` matrices of `n_each` rows stacked ([gate; up],
+    [q; k; v] with equal parts): every rank takes its row range of EACH part, so outputs that are
+    combined element by element (SiLU(gate) * up) stay on one rank.  `n_each` must be a multiple of
+    128 so that each part is whole scale tiles.  Returns (packed, scales, rows per part on this rank,
+    first row within a part)."""
+    if n_each % 128 != 0:
+        raise ValueError(f"fused column shard: each part needs a multiple of 128 rows, got {n_each}")
+    k_tiles = -(-(k // 16) // 4)
+    sc = scales_swz[: parts * (n_each // 128) * k_tiles * 512].reshape(parts, n_each // 128, k_tiles * 512)
+    pk = packed.reshape(parts, n_each, k // 2)
+    r0, r1 = column_shard_rows(n_each, rank, world)
+    return (pk[:, r0:r1].reshape(parts * (r1 - r0), k // 2).contiguous(),
+            sc[:, r0 // 128: r1 // 128].reshape(-1).contiguous(), r1 - r0, r0)
+
+
 class PeerAllReduce:
     """One-shot all-reduce over peer memory (nvk_b200_tp_allreduce_bf16) for vectors of up to
     `max_elems` bf16 values.  Each rank's exchange buffer is plain device memory that the other ranks
@@ -183,15 +200,36 @@ class TpNvfp4Linear:
         return cls.from_parts(packed, scales, alpha, n, k, mode, rank, world, group)
 
     @classmethod
-    def from_parts(cls, packed, scales, alpha, n, k, mode, rank, world, group=None):
+    def from_parts(cls, packed, scales, alpha, n, k, mode, rank, world, group=None, input_stored_global=1.0,
+                   device=None):
+        """Shard (packed [n, k/2], swizzled scales) for this rank; with `device`, the shard is cut
+        where the tensors are (e.g. on the host) and only the shard is moved there."""
+        def place(t):
+            return t if device is None else t.to(device)
         if world == 1:
-            return cls(L.Nvfp4Linear(packed, scales, alpha, k, n), mode, 0, 1, n, k, 0, group)
+            return cls(L.Nvfp4Linear(place(packed), place(scales), alpha, k, n, None, input_stored_global), mode, 0,
+                       1, n, k, 0, group)
         if mode == "column" and n % (128 * world) != 0:
             raise ValueError(f"column-parallel needs N={n} to be a multiple of 128*{world}")
         if mode == "row" and k % (64 * world) != 0:
             raise ValueError(f"row-parallel needs K={k} to be a multiple of 64*{world}")
         p, s, nl, kl, off = shard_nvfp4(packed, scales, n, k, mode, rank, world)
-        return cls(L.Nvfp4Linear(p, s, alpha, kl, nl), mode, rank, world, n, k, off, group)
+        return cls(L.Nvfp4Linear(place(p), place(s), alpha, kl, nl, None, input_stored_global), mode, rank, world, n, k,
+                   off, group)
+
+    @classmethod
+    def from_disk(cls, weights, module: str, n: int, k: int, mode: str, rank: int, world: int, device, sfx=None,
+                  group=None):
+        """One rank's shard of a checkpoint module: read and swizzle on the host, cut the shard there,
+        upload only the shard."""
+        import numpy as np
+
+        from . import weights as W
+        parts = W.read_nvfp4_module(weights, module, n, k, sfx or W.Nvfp4Suffixes.QWEN_COMPRESSED_TENSORS)
+        packed = torch.from_numpy(np.array(parts.packed, copy=True))
+        scales = torch.from_numpy(np.array(parts.scales_swizzled, copy=True))
+        return cls.from_parts(packed, scales, float(parts.weight_alpha), n, k, mode, rank, world, group,
+                              float(parts.stored_input_global), device)
 
     def _buf(self, name, shape, device):
         key = (name, tuple(shape))

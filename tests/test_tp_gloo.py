@@ -97,3 +97,51 @@ def test_shard_ranges_cover_everything():
         assert edges[0][0] == 0 and edges[-1][1] == k
         for a, b in zip(edges, edges[1:]):
             assert a[1] == b[0] and a[0] % 64 == 0
+
+
+def test_fused_column_shard_keeps_pairs_together():
+    """[gate; up] sharded per part: rank r holds gate rows [r0, r1) and the same up rows, and its
+    scale tiles are those rows' tiles."""
+    import numpy as np
+    import torch
+
+    from oracle import ref
+    from speaches_plus_b200 import tp
+    rng = np.random.default_rng(3)
+    n_each, k, world = 512, 256, 4
+    packed = rng.integers(0, 256, (2 * n_each, k // 2), dtype=np.uint8)
+    lin = rng.integers(0, 0x7F, (2 * n_each, k // 16), dtype=np.uint8)
+    sw = ref.swizzle_scales(lin)
+    for rank in range(world):
+        p, s, nl, r0 = tp.shard_nvfp4_fused(torch.from_numpy(packed), torch.from_numpy(sw), 2, n_each, k, rank, world)
+        assert (nl, r0) == (128, 128 * rank)
+        rows = np.r_[r0:r0 + nl, n_each + r0:n_each + r0 + nl]
+        assert np.array_equal(p.numpy(), packed[rows])
+        assert np.array_equal(s.numpy(), ref.swizzle_scales(lin[rows]))
+    import pytest
+    with pytest.raises(ValueError, match="multiple of 128"):
+        tp.shard_nvfp4_fused(torch.from_numpy(packed), torch.from_numpy(sw), 2, 192, k, 0, 2)
+
+
+def test_shard_from_disk_equals_shard_of_the_whole(tmp_path):
+    """A rank's shard cut on the host from a checkpoint is the slice `shard_nvfp4` cuts from the whole
+    matrix (checked on the host: the constructor itself needs a CUDA device only to run)."""
+    import numpy as np
+    import torch
+
+    from oracle import ref
+    from speaches_plus_b200 import tp, weights as W
+    from tests.test_weights_ingest import ct_tensors, make_module, write_safetensors
+    rng = np.random.default_rng(4)
+    n, k = 512, 512
+    packed, lin, g = make_module(rng, n, k)
+    wl = W.WeightLoader.open_file(write_safetensors(tmp_path / "m.safetensors", ct_tensors("a", packed, lin, g, 2.0)))
+    for mode in ("column", "row"):
+        for rank in range(2):
+            t = tp.TpNvfp4Linear.from_disk(wl, "a", n, k, mode, rank, 2, device=None)
+            p, s, nl, kl, off = tp.shard_nvfp4(torch.from_numpy(packed), torch.from_numpy(ref.swizzle_scales(lin)), n, k,
+                                               mode, rank, 2)
+            assert torch.equal(t.local.weight_u8, p) and torch.equal(t.local.weight_scales, s)
+            assert (t.local.out_features, t.local.in_features, t.offset) == (nl, kl, off)
+            assert t.local.input_stored_global == 2.0
+            assert abs(t.local.alpha_w4a16 * float(g) - 1) < 3e-7
