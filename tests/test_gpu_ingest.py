@@ -98,7 +98,7 @@ def test_expert_banks_from_disk_equal_banks_from_device_linears(tmp_path):
     U.require_gpu()
     import speaches_plus_b200 as sp
     rng = np.random.default_rng(24)
-    E, hidden, inter = 4, 256, 384
+    E, hidden, inter = 16, 256, 384
     t, experts = {}, []
     for e in range(E):
         trip = []
@@ -117,7 +117,7 @@ def test_expert_banks_from_disk_equal_banks_from_device_linears(tmp_path):
         assert torch.equal(a[1].reshape(-1), b[1].reshape(-1))
         assert torch.equal(a[2], b[2])
     # and the banks run: one decode step over them agrees between the two constructions
-    ctx = sp.GroupedDecodeContext(disk, 8, 2, "cuda")
+    ctx = sp.GroupedDecodeContext(disk, 8, 4, "cuda")
     x = U.dev(U.gauss_bf16(rng, (3, hidden))).view(torch.bfloat16)
     logits = U.dev(rng.standard_normal((3, E)).astype(np.float32))
     y1 = sp.forward_grouped_decode(disk, ctx, x, logits).clone()
