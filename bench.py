@@ -303,7 +303,7 @@ def run_b200(args) -> dict:
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
         stack = [decode_stack_leg(dev, rank, world, b, peer_ar=peer_ar) for b in (1, 16)]
-        moe = [moe_decode_leg(dev, b) for b in (1, 16, 64)] if world == 1 else None
+        moe = [moe_decode_leg(dev, b, rank=rank, world=world) for b in (1, 16, 64)]
         pre = None
         if world == 1:
             pre = (prefill_leg(dev) if sp.ffi.prefill_available()
@@ -442,13 +442,18 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, r
     return out
 
 
-def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
-    """BASELINE configs[3] on one GPU: 48 layers x 128 experts (hidden 2048, SwiGLU 768), top-8 with
+def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5, rank: int = 0, world: int = 1) -> dict:
+    """BASELINE configs[3]: 48 layers x 128 experts (hidden 2048, SwiGLU 768), top-8 with
     softmax over the winners, router logits ~ N(0,1); one decode step of `batch` tokens through
     route -> sort -> grouped gate+up -> grouped down (SiLU prologue) -> combine in every layer.
-    Algorithmic bytes count each distinct routed expert once per layer (from the actual routing)."""
+    Algorithmic bytes count each distinct routed expert once per layer (from the actual routing).
+    With world > 1 the experts are dealt out in blocks (16 per GPU at 8): every rank routes all
+    tokens, runs the slots of its own experts and the f32 partial outputs are summed with one
+    all-reduce per layer."""
     import numpy as np
     import torch
+
+    import torch.distributed as dist
 
     import speaches_plus_b200 as sp
     from speaches_plus_b200 import linear as L
@@ -469,6 +474,11 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
     mods = []
     for li in range(layers):
         w = sp.MoeGroupedWeights(bank(F, H, 3 * li), bank(F, H, 3 * li + 1), bank(H, F, 3 * li + 2), H, F, E)
+        if world > 1:  # keep this rank's block of experts only
+            v = w.shard_experts(rank, world)
+            w = sp.MoeGroupedWeights(*[tuple(t.clone() for t in b) for b in (v.gate, v.up, v.down)], H, F,
+                                     v.num_experts, v.first_expert, E)
+            del v
         g = torch.Generator(device=dev).manual_seed(7000 + li)
         logits = torch.randn((batch, E), generator=g, device=dev, dtype=torch.float32)
         mods.append((w, logits))
@@ -493,6 +503,8 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
         for _ in range(2):
             graph.replay()
         stream.synchronize()
+        if world > 1:
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(replays):
@@ -500,11 +512,16 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5) -> dict:
         e1.record(stream)
         stream.synchronize()
         ms = e0.elapsed_time(e1) / replays
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     per_expert = mods[0][0].per_expert_bytes()
     nbytes = distinct * per_expert
-    out = {"batch": batch, "layers": layers, "experts": E, "top_k": TOPK, "ms_per_step": round(ms, 4),
+    out = {"batch": batch, "layers": layers, "experts": E, "top_k": TOPK, "ep": world, "ms_per_step": round(ms, 4),
            "tok_s": round(batch / (ms * 1e-3), 1), "distinct_experts_per_layer": round(distinct / layers, 2),
-           "bytes_per_step": nbytes, "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1), "launches_per_step": layers * 8}
+           "bytes_per_step": nbytes, "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+           "launches_per_step": layers * (4 if world == 1 else 5), "collectives_per_step": layers if world > 1 else 0}
     del graph, mods, ctx
     torch.cuda.synchronize()
     torch.cuda.empty_cache()

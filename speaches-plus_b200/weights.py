@@ -565,24 +565,28 @@ def load_linear_maybe_quant(weights: WeightLoader, name: str, out_features: int,
 
 def moe_grouped_weights_from_disk(weights: WeightLoader, expert_prefixes: Iterable[str], hidden: int, inter: int,
                                   device, sfx: Nvfp4Suffixes = Nvfp4Suffixes.QWEN_COMPRESSED_TENSORS,
-                                  names=("gate_proj", "up_proj", "down_proj")):
+                                  names=("gate_proj", "up_proj", "down_proj"), rank: int = 0, world: int = 1):
     """Expert banks for the grouped decode path straight from a checkpoint: for each prefix
     `<prefix>.{gate,up,down}_proj`, the same per-expert layout `MoeGroupedWeights.build_from_experts`
     produces (rust/crates/nv-layers/src/moe_grouped.rs:97-280), without a device round trip.  Gate and
-    up of one expert must share their input global."""
+    up of one expert must share their input global.  With world > 1 only this rank's block of experts
+    is read and uploaded (expert parallelism)."""
     _require_cuda(device)
     import torch
 
-    from .moe import MoeGroupedWeights
+    from .moe import MoeGroupedWeights, expert_shard_range
     prefixes = list(expert_prefixes)
     if not prefixes:
         raise WeightError("MoeGroupedWeights: no experts")
+    total = len(prefixes)
+    first, last = expert_shard_range(total, rank, world)
+    prefixes = prefixes[first:last]
     dims = {0: (inter, hidden), 1: (inter, hidden), 2: (hidden, inter)}
     banks = []
     per_expert = [[read_nvfp4_module(weights, f"{p}.{names[i]}", *dims[i], sfx) for i in range(3)] for p in prefixes]
     for e, (g, u, _) in enumerate(per_expert):
         if abs(float(g.stored_input_global) - float(u.stored_input_global)) > 1e-6:
-            raise WeightError(f"expert {e}: gate and up have different input_global_scale "
+            raise WeightError(f"expert {first + e}: gate and up have different input_global_scale "
                               f"({g.stored_input_global} vs {u.stored_input_global})")
     for i in range(3):
         parts = [pe[i] for pe in per_expert]
@@ -592,4 +596,4 @@ def moe_grouped_weights_from_disk(weights: WeightLoader, expert_prefixes: Iterab
         alphas = torch.tensor([float(np.float32(p.weight_alpha) * np.float32(p.stored_input_global)) for p in parts],
                               dtype=torch.float32, device=device)
         banks.append((packed, scales, alphas))
-    return MoeGroupedWeights(banks[0], banks[1], banks[2], hidden, inter, len(prefixes))
+    return MoeGroupedWeights(banks[0], banks[1], banks[2], hidden, inter, len(prefixes), first, total)

@@ -75,6 +75,29 @@ def main():
                 err = ((got - want).abs() / torch.clamp(want.abs(), min=max(rms, 1e-3))).max().item()
                 assert err < 1e-2, f"row-parallel error {err}"
     ar.check()
+
+    # expert parallelism: the ranks' partial MoE outputs sum to the single-GPU result
+    import numpy as np
+    E, top_k, hidden, inter, n_tok = 16, 4, 256, 384, 7
+    gen = torch.Generator(device=dev).manual_seed(9)
+    experts = []
+    for e in range(E):
+        trip = []
+        for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter)):
+            w = (torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * 0.05).to(torch.bfloat16)
+            trip.append(sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w))
+        experts.append(tuple(trip))
+    whole = sp.MoeGroupedWeights.build_from_experts(experts)
+    mine = whole.shard_experts(rank, world)
+    ctx = sp.GroupedDecodeContext(whole, 8, top_k, dev)
+    x = torch.randn((n_tok, hidden), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    logits = torch.randn((n_tok, E), generator=gen, device=dev, dtype=torch.float32)
+    want = sp.forward_grouped_decode(whole, ctx, x, logits).clone()
+    got = sp.forward_grouped_decode(mine, ctx, x, logits).clone()
+    torch.cuda.synchronize()
+    scale = float(want.abs().max().item())
+    assert float((got - want).abs().max().item()) <= 1e-5 * scale, f"expert-parallel sum differs (rank {rank})"
+
     if rank == 0:
         print("mgpu_check ok", flush=True)
     ar.close()

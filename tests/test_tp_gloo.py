@@ -145,3 +145,79 @@ def test_shard_from_disk_equals_shard_of_the_whole(tmp_path):
             assert (t.local.out_features, t.local.in_features, t.offset) == (nl, kl, off)
             assert t.local.input_stored_global == 2.0
             assert abs(t.local.alpha_w4a16 * float(g) - 1) < 3e-7
+
+
+def test_expert_shard_ranges():
+    from speaches_plus_b200.moe import expert_shard_range
+    assert [expert_shard_range(128, r, 8) for r in range(8)] == [(16 * r, 16 * r + 16) for r in range(8)]
+    for E, world in [(128, 8), (60, 8), (7, 2), (3, 4)]:
+        edges = [expert_shard_range(E, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == E
+        assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+        sizes = [b - a for a, b in edges]
+        assert max(sizes) - min(sizes) <= 1
+
+
+def _ep_worker(rank, world, port, q):
+    """Expert parallelism on the host: every rank routes all tokens, computes the slots of ITS experts
+    (here through the oracle), leaves zeros elsewhere, combines, and the partial outputs are summed."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from speaches_plus_b200.moe import expert_shard_range
+        rng = np.random.default_rng(11)
+        E, top_k, hidden, inter, n_tok = 8, 2, 128, 256, 5
+        host = []
+        for e in range(E):
+            trip = []
+            for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter)):
+                w = ref.f32_to_bf16((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+                trip.append(ref.quantize_weight_bf16(w))
+            host.append(trip)
+        x = ref.f32_to_bf16(rng.standard_normal((n_tok, hidden)).astype(np.float32))
+        logits = rng.standard_normal((n_tok, E)).astype(np.float32)
+        ids, wts = ref.moe_route_topk(logits, top_k)
+        e0, e1 = expert_shard_range(E, rank, world)
+
+        def expert_out(e, t):
+            (pg, sg, ag), (pu, su, au), (pd, sd, ad) = host[e]
+            gate = ref.f32_to_bf16(ref.linear_w4a16_f64(pg, sg, x[t:t + 1], ag, inter, hidden).astype(np.float32))
+            up = ref.f32_to_bf16(ref.linear_w4a16_f64(pu, su, x[t:t + 1], au, inter, hidden).astype(np.float32))
+            act = ref.f32_to_bf16(ref.silu_mul(gate, up, round_bf16=True))
+            return ref.f32_to_bf16(ref.linear_w4a16_f64(pd, sd, act, ad, hidden, inter).astype(np.float32))[0]
+
+        # sorted-slot layout, as the permutation produces it; rows of other ranks' experts stay zero
+        order = np.argsort(ids.reshape(-1), kind="stable")
+        inv = np.empty_like(order)
+        inv[order] = np.arange(order.size)
+        down = np.zeros((n_tok * top_k, hidden), np.uint16)
+        for slot in range(n_tok * top_k):
+            e = int(ids.reshape(-1)[slot])
+            if e0 <= e < e1:
+                down[inv[slot]] = expert_out(e, slot // top_k)
+        part = ref.moe_unpermute_scatter(down, wts, inv.reshape(n_tok, top_k).astype(np.int32), hidden, hidden)
+        y = torch.from_numpy(part.copy())
+        dist.all_reduce(y)
+        if rank == 0:
+            full = np.zeros_like(down)
+            for slot in range(n_tok * top_k):
+                full[inv[slot]] = expert_out(int(ids.reshape(-1)[slot]), slot // top_k)
+            want = ref.moe_unpermute_scatter(full, wts, inv.reshape(n_tok, top_k).astype(np.int32), hidden, hidden)
+            q.put((y.numpy(), want))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_expert_parallel_sum_equals_the_whole():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got, want = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # each token's k products are the same numbers; only the order of the f32 additions differs
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-6 * float(np.abs(want).max()))
