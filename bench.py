@@ -295,7 +295,7 @@ def run_b200(args) -> dict:
             "clocks": clocks,
         }
         if args.cpu_baseline:
-            out["cpu_baseline"] = cpu_reference_leg(passes=3, warm=1)
+            out["cpu_baseline"] = cpu_reference_leg(passes=15, warm=2)
     if args.extras:
         # free the sweep's weights before the larger workloads
         del graph
@@ -585,13 +585,19 @@ def _cpu_weights():
     return _CPU_CACHE["w"]
 
 
-def cpu_pass() -> float:
-    """One pass over the four shapes on the host cores; returns seconds."""
+def cpu_pass(scalar_one_core: bool = False) -> float:
+    """One pass over the four shapes on the host cores; returns seconds.  The timed linear keeps 16
+    partial sums per output, the order a SIMD matmul such as the reference's adds in, on every host
+    thread; `scalar_one_core` times the sequential scalar dot of the reference's hand-written CPU GEMV
+    on one thread instead."""
     from oracle import ref
     ws, xs = _cpu_weights()
     t0 = time.perf_counter()
     for k, n, w in ws:
-        ref.linear_cpu_backend(w, xs[k], threads=0)
+        if scalar_one_core:
+            ref.linear_cpu_backend(w, xs[k], threads=1)
+        else:
+            ref.linear_cpu_backend_lanes16(w, xs[k], threads=0)
     return time.perf_counter() - t0
 
 
@@ -601,11 +607,15 @@ def cpu_reference_leg(passes: int, warm: int) -> dict:
         cpu_pass()
     ts = [cpu_pass() for _ in range(passes)]
     t = statistics.median(ts)
+    t1 = cpu_pass(scalar_one_core=True)
     b = sum(algo_bytes(1, n, k) for k, n in SHAPES_KN)
     return {"value": round(b / t / 1e9, 3), "unit": "GB/s", "cores": ref.num_threads(), "kind": "port",
             "sample": f"one weight set of each of the 4 shapes (M=1), median of {passes} passes; weights "
-                      "dequantized to bf16 beforehand (untimed), as the reference's Cpu backend holds them",
-            "ms_per_pass": round(t * 1e3, 2)}
+                      "dequantized to bf16 beforehand (untimed), as the reference's Cpu backend holds them; "
+                      "16 partial sums per output (SIMD order), all host threads",
+            "ms_per_pass": round(t * 1e3, 2),
+            "scalar_one_core": {"value": round(b / t1 / 1e9, 3), "unit": "GB/s", "cores": 1,
+                                "sample": "the same pass with the sequential scalar dot on one thread"}}
 
 
 def run_reference(args) -> dict | None:
@@ -624,7 +634,7 @@ def run_reference(args) -> dict | None:
     b = sum(algo_bytes(1, n, k) for k, n in SHAPES_KN)
     v = round(b / dt / 1e9, 3)
     sample = ("each step = one weight set of each of the 4 shapes at M=1 (1/%d of the B200 arm's step), CPU oracle "
-              "port of the reference's Cpu-backend linear, all host threads" % COPIES)
+              "port of the reference's Cpu-backend linear (16 partial sums per output), all host threads" % COPIES)
     return {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
             "warmup": warm, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
             "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16 x bf16 -> f32",

@@ -293,6 +293,53 @@ int nvo_linear_cpu_backend(const uint16_t* w_bf16, const uint16_t* x_bf16, uint1
     return 0;
 }
 
+/* The same linear with the summation order of a SIMD matmul: the reference's Cpu backend multiplies
+ * through the `gemm` crate, which keeps several partial sums per output and adds them at the end
+ * (its exact blocking is not in the reference tree).  Here each output keeps 16 partial sums -- lane j
+ * takes k = j, j+16, j+32, ... in order -- which are then added pairwise (8+8, 4+4, 2+2, 1+1).  Every
+ * product and sum is a separate f32 operation (no FMA), so the result is the same on every host; the
+ * compiler turns the 16 lanes into vector instructions (AVX-512 / AVX2 / SSE chosen at load time).
+ * This is the variant timed as the CPU baseline: a sequential scalar dot would understate what the
+ * reference's multithreaded SIMD matmul does on the same cores. */
+__attribute__((target_clones("avx512f", "avx2", "default"), optimize("O3")))
+static float nvo_dot_bf16_f32_lanes16(const uint16_t* w, const float* x, int K) {
+    float acc[16];
+    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    int k = 0;
+    for (; k + 16 <= K; k += 16) {
+        for (int j = 0; j < 16; ++j) {
+            union { uint32_t u; float f; } c;
+            c.u = (uint32_t)w[k + j] << 16;
+            acc[j] += c.f * x[k + j];
+        }
+    }
+    for (; k < K; ++k) acc[k & 15] += nvo_bf16_to_f32(w[k]) * x[k];
+    for (int s = 8; s >= 1; s >>= 1)
+        for (int j = 0; j < s; ++j) acc[j] += acc[j + s];
+    return acc[0];
+}
+
+int nvo_linear_cpu_backend_lanes16(const uint16_t* w_bf16, const uint16_t* x_bf16, uint16_t* y_bf16, int M,
+                                   int N, int K, int threads) {
+#ifdef _OPENMP
+    int nt = threads > 0 ? threads : omp_get_max_threads();
+#else
+    int nt = 1;
+    (void)threads;
+#endif
+    float* xf = (float*)__builtin_malloc((size_t)M * K * sizeof(float));
+    if (!xf) return -1;
+    for (size_t i = 0; i < (size_t)M * K; ++i) xf[i] = nvo_bf16_to_f32(x_bf16[i]);
+#pragma omp parallel for schedule(static) num_threads(nt)
+    for (int n = 0; n < N; ++n) {
+        const uint16_t* wr = w_bf16 + (size_t)n * K;
+        for (int m = 0; m < M; ++m)
+            y_bf16[(size_t)m * N + n] = nvo_f32_to_bf16(nvo_dot_bf16_f32_lanes16(wr, xf + (size_t)m * K, K));
+    }
+    __builtin_free(xf);
+    return 0;
+}
+
 /* ---- exact-ish statement of the W4A16 contraction, f64 accumulate ----
  * y[m,n] = alpha * sum_k dequant(W)[n,k] * x[m,k]; the form the reference's GPU
  * parity test uses as its oracle (rust/crates/nv-quant/tests/nvfp4_m1_gemv_ab.rs:93-102:

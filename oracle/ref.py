@@ -61,6 +61,8 @@ def lib() -> C.CDLL:
         L.nvo_dequantize_to_bf16.argtypes = [u8p, u8p, C.c_int, C.c_int, C.c_float, u16p]
         L.nvo_linear_cpu_backend.restype = C.c_int
         L.nvo_linear_cpu_backend.argtypes = [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.nvo_linear_cpu_backend_lanes16.restype = C.c_int
+        L.nvo_linear_cpu_backend_lanes16.argtypes = [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]
         L.nvo_linear_w4a16_f64.restype = C.c_int
         L.nvo_linear_w4a16_f64.argtypes = [u8p, u8p, u16p, C.c_float, C.c_int, C.c_int, C.c_int, f64p]
         L.nvo_matmul_w4a4.restype = C.c_int
@@ -227,6 +229,16 @@ def linear_cpu_backend(w_bf16_bits, x_bits, threads: int = 0) -> np.ndarray:
     m = x.shape[0]
     y = np.zeros((m, n), np.uint16)
     assert lib().nvo_linear_cpu_backend(_p(w, u16p), _p(x, u16p), _p(y, u16p), m, n, k, threads) == 0
+    return y
+
+
+def linear_cpu_backend_lanes16(w_bf16_bits, x_bits, threads: int = 0) -> np.ndarray:
+    """The Cpu-backend linear with 16 partial sums per output (the order a SIMD matmul adds in)."""
+    w, x = _c(w_bf16_bits, np.uint16), _c(x_bits, np.uint16)
+    n, k = w.shape
+    m = x.shape[0]
+    y = np.zeros((m, n), np.uint16)
+    assert lib().nvo_linear_cpu_backend_lanes16(_p(w, u16p), _p(x, u16p), _p(y, u16p), m, n, k, threads) == 0
     return y
 
 

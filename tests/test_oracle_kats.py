@@ -369,3 +369,33 @@ def test_router_matches_closed_form_and_tie_breaks_low():
         e = np.exp(lg[t, order] - lg[t, order].max())
         np.testing.assert_allclose(w[t], e / e.sum(), rtol=1e-5)
         assert abs(w[t].sum() - 1) < 1e-5
+
+
+def test_cpu_linear_with_simd_summation_order():
+    """The timed CPU baseline keeps 16 partial sums per output.  Its order is fixed (lane j takes
+    k = j, j+16, ...; lanes added 8+8, 4+4, 2+2, 1+1; separate multiply and add), so it can be
+    restated in numpy exactly, and it stays within bf16 rounding of the sequential statement."""
+    rng = np.random.default_rng(12)
+    n, k = 64, 4096 + 16 + 5   # a ragged tail after the last full group of 16
+    w = ref.f32_to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    x = ref.f32_to_bf16(rng.standard_normal((2, k)).astype(np.float32))
+    got = ref.linear_cpu_backend_lanes16(w, x)
+    wf, xf = ref.bf16_to_f32(w), ref.bf16_to_f32(x)
+    k16 = k // 16 * 16
+    for m in range(2):
+        for r in range(0, n, 7):
+            acc = np.zeros(16, np.float32)
+            for kk in range(0, k16, 16):
+                acc += (wf[r, kk:kk + 16] * xf[m, kk:kk + 16]).astype(np.float32)
+            for kk in range(k16, k):
+                acc[kk & 15] += f32(wf[r, kk] * xf[m, kk])
+            s = 8
+            while s >= 1:
+                acc[:s] += acc[s:2 * s]
+                s //= 2
+            assert ref.f32_to_bf16(acc[:1])[0] == got[m, r]
+    seq = ref.bf16_to_f32(ref.linear_cpu_backend(w, x))
+    lanes = ref.bf16_to_f32(got)
+    rms = float(np.sqrt(np.mean(seq ** 2)))
+    assert np.max(np.abs(seq - lanes) / np.maximum(np.abs(seq), max(rms, 1e-3))) < 1e-2
+    assert np.array_equal(ref.linear_cpu_backend_lanes16(w, x, threads=1), got)   # thread count does not matter
