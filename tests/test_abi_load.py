@@ -53,3 +53,55 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(sp.ffi, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         sp.ffi.lib()
+
+
+def declared_prototypes():
+    """name -> list of parameter kinds ('ptr', 'int', 'i64', 'float', 'size_t') parsed from the header."""
+    text = (ROOT / "include" / "nvk_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    out = {}
+    for name, params in re.findall(r"\b(?:int|size_t)\s+((?:nv_kernels|nvk_b200)_\w+)\s*\(([^)]*)\)\s*;", text):
+        kinds = []
+        for prm in (q.strip() for q in params.split(",")):
+            if prm in ("", "void"):
+                continue
+            if "*" in prm:
+                kinds.append("ptr")
+            elif re.match(r"(const\s+)?(long long|int64_t)\b", prm):
+                kinds.append("i64")
+            elif re.match(r"(const\s+)?size_t\b", prm):
+                kinds.append("size_t")
+            elif re.match(r"(const\s+)?float\b", prm):
+                kinds.append("float")
+            elif re.match(r"(const\s+)?(int|int32_t)\b", prm):
+                kinds.append("int")
+            else:
+                raise AssertionError(f"{name}: parameter type not understood: {prm!r}")
+        out[name] = kinds
+    return out
+
+
+def test_binding_argument_types_match_the_header():
+    """Every ctypes signature has the header's parameter count and kinds, in order: a drifted binding
+    would pass garbage through the C ABI without any error."""
+    kind = {ctypes.c_void_p: "ptr", ctypes.c_int: "int", ctypes.c_float: "float", ctypes.c_size_t: "size_t",
+            ctypes.c_longlong: "i64"}
+    protos = declared_prototypes()
+    sigs = dict(sp.ffi.SIGNATURES)
+    sigs.update(sp.ffi.PREFILL_SIGNATURES)
+    assert sorted(protos) == sorted(sigs)
+    for name, argtypes in sigs.items():
+        assert [kind[a] for a in argtypes] == protos[name], name
+
+
+def test_header_prototypes_equal_the_reference_headers():
+    """tests/golden/reference_prototypes.json holds what the reference's own header declares for these
+    entry points (written by tests/golden/extract_reference_prototypes.py): same parameter kinds in
+    the same order, so an existing caller binds to this library unchanged."""
+    import json
+    ref = json.loads((ROOT / "tests" / "golden" / "reference_prototypes.json").read_text())["prototypes"]
+    mine = declared_prototypes()
+    shared = sorted(n for n in mine if n.startswith("nv_kernels_"))
+    assert shared == sorted(ref)
+    for name in shared:
+        assert mine[name] == ref[name]["kinds"], name
