@@ -17,7 +17,9 @@
  *       ((n/128 * ceil(K/64) + kb/4) * 32 + n%32) * 16 + ((n/32)%4) * 4 + kb%4.
  *   - Return value: 0 = enqueued (or an empty problem); -1 = shape/route refused, nothing
  *     launched; -2 = bad argument or alignment; -3 = resource limit; -9 = grid axis too large;
- *     a positive value is a cudaError_t.
+ *     a positive value is a cudaError_t.  Checks run in that order; a NULL operand that a launch
+ *     would dereference is refused with -2 after the shape checks (the reference does not check
+ *     for NULL; a call it would accept with valid pointers is accepted here unchanged).
  */
 #pragma once
 #include <stddef.h>

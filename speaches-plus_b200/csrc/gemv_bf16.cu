@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t* __restri
 
 extern "C" int nv_kernels_gemv_bf16(void* stream, const uint16_t* W, const uint16_t* x, uint16_t* y, int N, int K) {
     if (N <= 0 || K <= 0) return 0;
+    if (nvk::any_null(W, x, y)) return NVK_ERR_ARG;
     const unsigned grid = (unsigned)((N + 7) / 8);
     const bool vec = (K & 7) == 0 && ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15u) == 0;
     if (vec)

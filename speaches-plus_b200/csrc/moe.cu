@@ -396,6 +396,7 @@ int nv_kernels_moe_route_topk(void* stream, const float* logits, const float* bi
                               int norm_topk, float routed_scaling) {
     if (n_tokens <= 0 || E <= 0 || K <= 0) return 0;
     if (E > kRouteMaxE || K > kRouteMaxK || K > E) return NVK_ERR_ARG;
+    if (nvk::any_null(logits, topk_ids, topk_weights)) return NVK_ERR_ARG;
     return launch_route(stream, logits, bias, topk_ids, topk_weights, n_tokens, E, K, mode, softcap, norm_topk,
                         routed_scaling, K, -1);
 }
@@ -406,6 +407,7 @@ int nv_kernels_moe_route_topk_shared_tail(void* stream, const float* logits, con
     if (n_tokens <= 0 || E <= 0 || K <= 0) return 0;
     if (E > kRouteMaxE || K + 1 > kRouteMaxK || K > E) return NVK_ERR_ARG;
     if (shared_tail_id < 0) return NVK_ERR_RESOURCE;
+    if (nvk::any_null(logits, topk_ids, topk_weights)) return NVK_ERR_ARG;
     return launch_route(stream, logits, bias, topk_ids, topk_weights, n_tokens, E, K, mode, softcap, norm_topk,
                         routed_scaling, K + 1, shared_tail_id);
 }
@@ -424,6 +426,7 @@ static int gather_rows(void* stream, const uint16_t* x, const int32_t* src_idx, 
 int nv_kernels_gather_rows_bf16(void* stream, const uint16_t* x_bf16, const int32_t* src_idx, uint16_t* out_bf16,
                                 int m_total_padded, int hidden, int n_tokens) {
     if (m_total_padded <= 0 || hidden <= 0) return 0;
+    if (nvk::any_null(x_bf16, src_idx, out_bf16)) return NVK_ERR_ARG;
     return gather_rows(stream, x_bf16, src_idx, out_bf16, m_total_padded, hidden, n_tokens, 1);
 }
 
@@ -432,11 +435,13 @@ int nv_kernels_gather_rows_bf16_strided(void* stream, const uint16_t* x_bf16, co
                                         int row_stride) {
     if (m_total_padded <= 0 || hidden <= 0) return 0;
     if (row_stride <= 0 || (m_total_padded % row_stride) != 0) return NVK_ERR_RESOURCE;
+    if (nvk::any_null(x_bf16, src_idx, out_bf16)) return NVK_ERR_ARG;
     return gather_rows(stream, x_bf16, src_idx, out_bf16, m_total_padded, hidden, n_tokens, row_stride);
 }
 
 int nv_kernels_gather_f32_by_ids(void* stream, const float* src, const int32_t* ids, float* dst, int n) {
     if (n <= 0) return 0;
+    if (nvk::any_null(src, ids, dst)) return NVK_ERR_ARG;
     gather_f32_by_ids_kernel<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)stream>>>(src, ids, dst, n);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
@@ -447,6 +452,7 @@ int nv_kernels_moe_unpermute_scatter(void* stream, const uint16_t* y_sorted_bf16
                                      int y_sorted_row_stride) {
     if (n_tokens <= 0 || k <= 0 || hidden <= 0) return 0;
     if (y_sorted_row_stride < hidden) return NVK_ERR_ARG;
+    if (nvk::any_null(y_sorted_bf16, topk_weights, inv_perm, y_acc_f32)) return NVK_ERR_ARG;
     dim3 grid((unsigned)n_tokens, (unsigned)((hidden + 255) / 256));
     moe_unpermute_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(y_sorted_bf16, topk_weights, inv_perm,
                                                                         y_acc_f32, nullptr, nullptr, nullptr,
@@ -461,6 +467,7 @@ int nv_kernels_moe_unpermute_scatter_tail(void* stream, const uint16_t* y_sorted
                                           int hidden, int y_sorted_row_stride) {
     if (n_tokens <= 0 || k <= 0 || hidden <= 0) return 0;
     if (y_sorted_row_stride < hidden) return NVK_ERR_ARG;
+    if (nvk::any_null(y_sorted_bf16, topk_weights, inv_perm, out_bf16)) return NVK_ERR_ARG;
     dim3 grid((unsigned)n_tokens, (unsigned)((hidden + 255) / 256));
     moe_unpermute_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(y_sorted_bf16, topk_weights, inv_perm, nullptr,
                                                                        shared_f32, resid_bf16, out_bf16, n_tokens, k,
@@ -473,6 +480,7 @@ int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permu
                            int32_t* expert_offsets, int32_t* inv_perm, int32_t* scratch_counts, int n_tokens, int k,
                            int num_experts) {
     if (n_tokens <= 0 || k <= 0 || num_experts <= 0) return 0;
+    if (nvk::any_null(topk_ids, permuted_token_idx, expert_offsets, inv_perm, scratch_counts)) return NVK_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int total = n_tokens * k;
     cudaError_t err = cudaMemsetAsync(scratch_counts, 0, sizeof(int32_t) * num_experts, s);
@@ -495,6 +503,7 @@ int nvk_b200_moe_route_permute(void* stream, const float* logits, const float* b
     if (n_tokens <= 0 || E <= 0 || K <= 0) return 0;
     if (K > E || K > kRouteMaxK) return NVK_ERR_ARG;
     if (E > kFusedMaxE || (long long)n_tokens * K > kFusedMaxSlots) return NVK_ERR_RESOURCE;
+    if (nvk::any_null(logits, topk_ids, topk_weights, permuted_token_idx, expert_offsets, inv_perm)) return NVK_ERR_ARG;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
@@ -526,6 +535,7 @@ int nvk_b200_moe_permute_static(void* stream, const int32_t* topk_ids, int32_t* 
                                 int num_experts) {
     if (n_tokens <= 0 || k <= 0 || num_experts <= 0) return 0;
     if (num_experts > kStaticPermuteMaxExperts) return NVK_ERR_RESOURCE;  // more experts than the fixed array holds
+    if (nvk::any_null(topk_ids, permuted_token_idx, expert_offsets, inv_perm)) return NVK_ERR_ARG;
     // In host code `g_permute_counts` is only a handle for the symbol, not an address the GPU can
     // use; the device address is looked up once per device (with that device current) and kept.
     constexpr int kMaxDevices = 64;
@@ -567,6 +577,7 @@ int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packe
     if ((reinterpret_cast<uintptr_t>(a_packed) & 7) != 0 || (reinterpret_cast<uintptr_t>(b_packed) & 7) != 0)
         return NVK_ERR_ARG;
     if (num_groups > 65535) return NVK_ERR_GRID_AXIS;
+    if (nvk::any_null(a_packed, a_scales, b_packed, b_scales, alphas, d_bf16, group_expert_ids)) return NVK_ERR_ARG;
     dim3 grid((unsigned)((n + 7) / 8), (unsigned)num_groups);
     moe_grouped_fp4_gemv_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         a_packed, a_scales, b_packed, b_scales, alphas, d_bf16, group_expert_ids, num_experts_total, n, k,

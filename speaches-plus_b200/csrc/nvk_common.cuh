@@ -17,6 +17,17 @@
 
 namespace nvk {
 
+// True if any of the pointers is null.  Launchers refuse null operands (NVK_ERR_ARG) after their
+// shape checks instead of handing them to a kernel.
+template <typename... P>
+inline bool any_null(P... ptrs) {
+    const void* v[] = {static_cast<const void*>(ptrs)...};
+    for (const void* q : v)
+        if (q == nullptr) return true;
+    return false;
+}
+
+
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Byte offset of the ue4m3 scale of (row m, 16-block kb) in the 128x4 swizzled layout

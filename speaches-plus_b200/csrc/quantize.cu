@@ -159,6 +159,8 @@ int nv_kernels_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16, uint8_t
     if (m_logical < 0 || m_logical > m_padded) return NVK_ERR_ARG;
     if ((K % 16) != 0) return NVK_ERR_SHAPE;
     if (!aligned16(x_bf16) || (reinterpret_cast<uintptr_t>(packed_out) & 7u)) return NVK_ERR_ARG;
+    // x is not read when every row is a pad row
+    if (nvk::any_null(packed_out, scales_out_swizzled) || (m_logical > 0 && x_bf16 == nullptr)) return NVK_ERR_ARG;
     QuantParams p = {};
     p.x = x_bf16; p.packed = packed_out; p.scales = scales_out_swizzled;
     p.global = stored_global; p.rows = m_padded; p.rows_logical = m_logical; p.K = K;
@@ -179,6 +181,7 @@ int nv_kernels_nvfp4_quantize_row_bf16(void* stream, const uint16_t* x, uint8_t*
     if (K <= 0) return 0;
     if ((K & 15) != 0) return NVK_ERR_SHAPE;
     if (!aligned16(x) || (reinterpret_cast<uintptr_t>(packed_out) & 7u)) return NVK_ERR_ARG;
+    if (nvk::any_null(x, packed_out, scales_out)) return NVK_ERR_ARG;
     QuantParams p = {};
     p.x = x; p.packed = packed_out; p.scales = scales_out;
     p.global = stored_global; p.rows = 1; p.rows_logical = 1; p.K = K;
@@ -192,6 +195,7 @@ static int per_expert(void* stream, const uint16_t* a, const uint16_t* b, uint8_
     if ((K % 16) != 0) return NVK_ERR_SHAPE;
     if (strided && (m_total % m_per_expert) != 0) return NVK_ERR_RESOURCE;
     if (!aligned16(a) || (silu && !aligned16(b)) || (reinterpret_cast<uintptr_t>(packed) & 7u)) return NVK_ERR_ARG;
+    if (nvk::any_null(a, packed, scales, globals) || (silu && b == nullptr)) return NVK_ERR_ARG;
     QuantParams p = {};
     p.x = a; p.x2 = b; p.packed = packed; p.scales = scales; p.globals = globals;
     p.K = K; p.m_per_expert = m_per_expert;
@@ -241,6 +245,8 @@ int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16,
     const size_t smem = (size_t)K * sizeof(uint16_t);
     if (smem > 48 * 1024) return NVK_ERR_RESOURCE;
     if (reinterpret_cast<uintptr_t>(packed_out) & 7u) return NVK_ERR_ARG;
+    if (nvk::any_null(weight_bf16, packed_out, scales_out_swizzled) || (m_logical > 0 && x_bf16 == nullptr))
+        return NVK_ERR_ARG;
     QuantParams p = {};
     p.x = x_bf16; p.norm_w = weight_bf16; p.packed = packed_out; p.scales = scales_out_swizzled;
     p.global = stored_global; p.eps = eps; p.rows = m_padded; p.rows_logical = m_logical; p.K = K;

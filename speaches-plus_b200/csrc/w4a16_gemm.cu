@@ -827,6 +827,7 @@ int w4a16_linear(cudaStream_t stream, const uint8_t* wq_a, const uint8_t* sc_a, 
                  float alpha_a, float alpha_b, int M, int N, int K, int pro, int max_m) {
     if (M <= 0 || M > max_m) return NVK_ERR_SHAPE;
     if ((K & 15) != 0) return NVK_ERR_SHAPE;
+    if (nvk::any_null(wq_a, sc_a, x, y_a) || (pro && x2 == nullptr)) return NVK_ERR_ARG;
     GemmParams p = {};
     p.wq[0] = wq_a; p.wq[1] = wq_b;
     p.sc[0] = sc_a; p.sc[1] = sc_b;
@@ -945,6 +946,7 @@ int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uin
     if ((w_stride & 15) != 0 || !aligned16(wq_bank_a) || !aligned16(sc_bank_a) || !aligned16(x) ||
         (wq_bank_b && (!aligned16(wq_bank_b) || !aligned16(sc_bank_b))) || (x2 && !aligned16(x2)))
         return NVK_ERR_ARG;
+    if (nvk::any_null(wq_bank_a, sc_bank_a, alphas_a, x, expert_offsets, y_a)) return NVK_ERR_ARG;
     GemmParams p = {};
     p.wq[0] = wq_bank_a; p.wq[1] = wq_bank_b;
     p.sc[0] = sc_bank_a; p.sc[1] = sc_bank_b;
@@ -995,6 +997,7 @@ int nvk_b200_linear_nvfp4_w4a16_ws(void* stream, const uint8_t* wq_a, const uint
     if (workspace == nullptr || !worth || !fast)
         return w4a16_linear((cudaStream_t)stream, wq_a, sc_a, wq_b, sc_b, x, x2, y_a, y_b, alpha_a, alpha_b, M, N, K,
                             x2 ? 1 : 0, 64);
+    if (nvk::any_null(wq_a, sc_a, x, y_a)) return NVK_ERR_ARG;
     GemmParams p = {};
     p.wq[0] = wq_a; p.wq[1] = wq_b;
     p.sc[0] = sc_a; p.sc[1] = sc_b;

@@ -1,0 +1,71 @@
+"""Refusals of the C ABI, checked without a GPU: a refused call returns its code before any CUDA
+call is made, so these run anywhere.  Order of the checks: empty problem (0), shape (-1), argument /
+alignment (-2), resource (-3), grid axis (-9); a NULL operand is refused with -2 after the shape
+checks."""
+import speaches_plus_b200 as sp
+
+f = sp.ffi.call
+P = 0x1000   # a 16-byte aligned, non-null address; never dereferenced on a refused call
+S = 0        # the default stream
+
+
+def test_empty_problems_are_no_ops():
+    assert f("nv_kernels_nvfp4_gemv_bf16act", S, 0, 0, 0, 0, 1.0, 0, 128) == 0
+    assert f("nvk_b200_linear_nvfp4_w4a16", S, 0, 0, None, None, 0, None, 0, None, 1.0, 0.0, 4, 0, 128) == 0
+    assert f("nv_kernels_quantize_nvfp4_bf16", S, 0, 0, 0, 1.0, 0, 0, 64) == 0
+    assert f("nv_kernels_gemv_bf16", S, 0, 0, 0, 0, 64) == 0
+    assert f("nv_kernels_moe_route_topk", S, 0, 0, 0, 0, 0, 8, 2, 0, 0.0, 1, 1.0) == 0
+    assert f("nv_kernels_moe_permute", S, 0, 0, 0, 0, 0, 0, 2, 8) == 0
+    assert f("nvk_b200_tp_allreduce_bf16", S, 0, 0, 2, 0, 0, 0, 64, 0, 0) == 0
+
+
+def test_shape_refusals():
+    assert f("nv_kernels_nvfp4_gemv_bf16act", S, P, P, P, P, 1.0, 64, 250) == -1              # K % 16
+    assert f("nv_kernels_gemv_nvfp4_w4a16_dual_m1", S, P, P, None, None, P, P, None, 1.0, 1.0, 64, 48) == -1  # K % 32
+    assert f("nv_kernels_gemv_nvfp4_w4a16_dual_m1", S, P, P, P, None, P, P, None, 1.0, 1.0, 64, 64) == -1     # half-null arm
+    assert f("nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1", S, P, P, P, P, P, 1.0, 0, 64) == -1
+    assert f("nv_kernels_gemm_nvfp4_w4a16_mk_dual", S, P, P, None, None, P, P, None, 1.0, 1.0, 17, 64, 64) == -1  # M > 16
+    assert f("nv_kernels_gemm_nvfp4_w4a16_mk_dual", S, P, P, None, None, P, P, None, 1.0, 1.0, 4, 48, 64) == -1   # N % 32
+    assert f("nvk_b200_linear_nvfp4_w4a16", S, P, P, None, None, P, None, P, None, 1.0, 0.0, 65, 128, 128) == -1  # M > 64
+    assert f("nv_kernels_quantize_nvfp4_bf16", S, P, P, P, 1.0, 4, 4, 40) == -1
+    assert f("nvk_b200_moe_grouped_w4a16", S, P, P, None, None, P, None, P, None, None, P, P, None, 4, 64, 48) == -1
+    assert f("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", S, P, P, P, P, P, P, P, 4, 8, 64, 64, 100, 64) == -1    # tile stride
+
+
+def test_argument_refusals():
+    assert f("nv_kernels_nvfp4_gemv_bf16act", S, 0, 0, 0, 0, 1.0, 128, 128) == -2             # NULL operands
+    assert f("nv_kernels_nvfp4_gemv_bf16act", S, P, P, P, 0, 1.0, 128, 128) == -2             # NULL output
+    assert f("nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1", S, P, P, P, 0, P, 1.0, 128, 128) == -2  # NULL up
+    assert f("nv_kernels_quantize_nvfp4_bf16", S, P, P, P, 1.0, 4, 5, 64) == -2               # logical > padded rows
+    assert f("nv_kernels_quantize_nvfp4_bf16", S, P + 2, P, P, 1.0, 4, 4, 64) == -2           # misaligned x
+    assert f("nv_kernels_quantize_nvfp4_bf16", S, 0, P, P, 1.0, 4, 4, 64) == -2               # NULL x with live rows
+    assert f("nv_kernels_gemv_bf16", S, 0, 0, 0, 4, 8) == -2
+    assert f("nv_kernels_moe_route_topk", S, P, 0, P, P, 1, 8, 9, 0, 0.0, 1, 1.0) == -2       # K > E
+    assert f("nv_kernels_moe_route_topk", S, 0, 0, 0, 0, 1, 8, 2, 0, 0.0, 1, 1.0) == -2       # NULL operands
+    assert f("nv_kernels_moe_permute", S, 0, 0, 0, 0, 0, 4, 2, 8) == -2
+    assert f("nv_kernels_moe_unpermute_scatter", S, P, P, P, P, 4, 2, 64, 32) == -2           # row stride < hidden
+    assert f("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", S, 4, P, P, P, P, P, P, 4, 8, 64, 64, 128, 64) == -2     # alignment
+    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
+    assert f("nvk_b200_set_tuning", 3, 0) == -2 and f("nvk_b200_set_tuning", 0, 48) == -2
+    assert f("nvk_b200_set_tuning", 0, 0) == 0
+    assert f("nvk_b200_tp_allreduce_bf16", S, P, 2, 2, P, P, 8, 64, P, P) == -2               # rank outside the world
+    assert f("nvk_b200_tp_allreduce_bf16", S, P, 0, 2, P, P, 12, 64, P, P) == -2              # n % 8
+    assert f("nvk_b200_tp_allreduce_bf16", S, P, 0, 9, P, P, 8, 64, P, P) == -2               # more than 8 ranks
+
+
+def test_resource_and_grid_refusals():
+    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, 4, 257, 4, 0, 0.0, 1, 1.0) == -3   # > 256 experts
+    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, 2000, 8, 4, 0, 0.0, 1, 1.0) == -3  # > 4096 slots
+    assert f("nvk_b200_moe_permute_static", S, P, P, P, P, 4, 2, 4097) == -3
+    assert f("nv_kernels_rmsnorm_quantize_nvfp4_bf16", S, P, P, P, P, 1.0, 1e-6, 1, 1, 32768) == -3  # row > 48 KiB
+    assert f("nv_kernels_gather_rows_bf16_strided", S, P, P, P, 9, 64, 4, 4) == -3
+    assert f("nv_kernels_moe_route_topk_shared_tail", S, P, 0, P, P, 1, 8, 2, 0, 0.0, 1, 1.0, -1) == -3
+    assert f("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", S, P, P, P, P, P, P, P, 70000, 8, 64, 64, 128, 64) == -9
+
+
+def test_buffer_size_queries():
+    lib = sp.ffi.lib()
+    assert lib.nvk_b200_tp_allreduce_buffer_bytes(8, 64 * 5120) == 4096 + 2 * 8 * 64 * 5120 * 2
+    assert lib.nvk_b200_tp_allreduce_buffer_bytes(9, 64) == 0 and lib.nvk_b200_tp_allreduce_buffer_bytes(2, 0) == 0
+    assert lib.nvk_b200_linear_workspace_bytes(16, 4096) == 256 + 16 * 16 * 512
+    assert lib.nvk_b200_linear_workspace_bytes(0, 4096) == 0
