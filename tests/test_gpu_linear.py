@@ -368,8 +368,9 @@ def test_bf16_lm_head_gemv():
 def test_configs1_full_size_sweep(k, n, m):
     """BASELINE configs[1] at full size: every (K, N) x M against the f64 oracle on a seeded subset of
     rows (all tokens; 512 output rows spread over the matrix, so every launch path is exercised while
-    the CPU side stays at seconds), plus a size-independent property on the whole output: rows computed
-    as part of the full matrix equal rows computed from a 128-row-aligned slice of it, bit for bit."""
+    the CPU side stays at seconds), plus a size-independent property on the whole output: with the
+    split of K pinned (it is otherwise chosen from the number of row tiles), rows computed as part of
+    the full matrix equal rows computed from a 128-row-aligned slice of it, bit for bit."""
     U.require_gpu()
     import speaches_plus_b200 as sp
     torch.manual_seed(k + n)
@@ -385,14 +386,20 @@ def test_configs1_full_size_sweep(k, n, m):
     rng = np.random.default_rng(n)
     tiles = rng.choice(n // 128, size=4, replace=False)
     lin_scales = ref.unswizzle_scales(sw, n, k // 16)
+    subs = []
     for t in tiles:
         r0 = int(t) * 128
         sub_p, sub_s = packed[r0:r0 + 128], ref.swizzle_scales(lin_scales[r0:r0 + 128])
         want = ref.linear_w4a16_f64(sub_p, sub_s, xb, lin.weight_alpha, 128, k)
         e = U.rel_err_floor(ref.bf16_to_f32(got[:, r0:r0 + 128]), want)
         assert e < TOL_F64, f"tile {t}: {e}"
-        # property: the same rows from a stand-alone 128-row linear give the same bits
-        small = sp.Nvfp4Linear.new_nvfp4(U.dev(sub_p), U.dev(sub_s), lin.weight_alpha, k, 128)
-        ys = small(x)
-        torch.cuda.synchronize()
-        assert np.array_equal(U.host_u16(ys).reshape(m, 128), got[:, r0:r0 + 128])
+        subs.append((r0, sp.Nvfp4Linear.new_nvfp4(U.dev(sub_p), U.dev(sub_s), lin.weight_alpha, k, 128)))
+    assert U.ffi.call("nvk_b200_set_tuning", 1, 0) == 0   # every warp sums all of K for its rows, in order
+    try:
+        pinned = U.host_u16(lin(x)).reshape(m, n)
+        for r0, small in subs:
+            assert np.array_equal(U.host_u16(small(x)).reshape(m, 128), pinned[:, r0:r0 + 128]), f"rows {r0}.."
+    finally:
+        U.ffi.call("nvk_b200_set_tuning", 0, 0)
+    # the default split changes only the order of the fp32 additions
+    assert U.rel_err_floor(ref.bf16_to_f32(pinned), ref.bf16_to_f32(got).astype(np.float64)) < 1e-2
