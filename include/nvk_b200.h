@@ -260,6 +260,30 @@ int nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled(void* stream, const void* a_fp4
                                                  int k, int tile, int stream_k, void* workspace,
                                                  size_t workspace_bytes, size_t* required_workspace);
 
+/* Grouped block-scaled FP4 x FP4 GEMM for prefill-sized MoE steps: for every group g,
+ * D_g[m_g, N] = bf16(alphas[e_g] * A_g B[e_g]^T) with every size and offset in device memory.
+ *   group g: rows [expert_offsets[g], +m_g) of the stacked packed activations and of D; activation
+ *   scales from row sf_offsets[g] (a multiple of 128) of the stacked swizzled scale buffer; weights of
+ *   expert e_g = active_expert_indices ? active_expert_indices[g] : g; (m_g, n_g, k_g) =
+ *   problem_sizes[3g .. 3g+2].  meta_scratch (>= 64 KiB, device) receives the per-group argument
+ *   arrays; all of a_packed, b_packed, d_bf16 NULL is a workspace query.  -10 meta scratch too small,
+ *   -11 meta scratch overflow, -12 workspace too small, -13..-15 set-up stages of the GEMM.
+ * Both symbols run the same sm_100a kernel (1-SM 128x128x256 tile, tcgen05 kind::mxf4nvf4).
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:970-1018
+ * (rust/crates/nv-kernels/cuda_sm120/moe_grouped_fp4_gemm.cu:116-470) */
+int nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16(
+    void* stream, const void* a_packed, const void* a_scales, const void* b_packed, const void* b_scales,
+    const float* alphas, void* d_bf16, const int32_t* expert_offsets, const int32_t* sf_offsets,
+    const int32_t* problem_sizes, const int32_t* active_expert_indices, int N, int K, int num_experts,
+    int64_t a_row_stride_elems, int64_t b_row_stride_elems, int64_t c_row_stride_elems, void* meta_scratch,
+    size_t meta_scratch_bytes, void* gemm_workspace, size_t gemm_workspace_bytes, size_t* required_workspace);
+int nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode(
+    void* stream, const void* a_packed, const void* a_scales, const void* b_packed, const void* b_scales,
+    const float* alphas, void* d_bf16, const int32_t* expert_offsets, const int32_t* sf_offsets,
+    const int32_t* problem_sizes, const int32_t* active_expert_indices, int N, int K, int num_experts,
+    int64_t a_row_stride_elems, int64_t b_row_stride_elems, int64_t c_row_stride_elems, void* meta_scratch,
+    size_t meta_scratch_bytes, void* gemm_workspace, size_t gemm_workspace_bytes, size_t* required_workspace);
+
 /* No counterpart in the reference: tuning hook for the prefill GEMM.  1 = 1-SM 128x128x256 tile,
  * 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster (default). */
 int nvk_b200_set_prefill_config(int cfg);

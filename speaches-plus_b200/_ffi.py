@@ -62,6 +62,10 @@ PREFILL_SIGNATURES = {
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled": [_vp] * 7 + [_i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
+    "nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16":
+        [_vp] * 11 + [_i, _i, _i, _ll, _ll, _ll, _vp, C.c_size_t, _vp, C.c_size_t, _vp],
+    "nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode":
+        [_vp] * 11 + [_i, _i, _i, _ll, _ll, _ll, _vp, C.c_size_t, _vp, C.c_size_t, _vp],
 }
 
 _lib = None

@@ -72,7 +72,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     def compile_one(src: pathlib.Path) -> pathlib.Path:
         obj = OBJ / (src.stem + ".o")
         per_file = []
-        if src.name == "prefill_fp4_gemm.cu" and cutlass:
+        if src.parent == CSRC_PREFILL and cutlass:
             per_file = ["--expt-relaxed-constexpr", "-DNVK_HAVE_CUTLASS", *[f"-I{d}" for d in cutlass]]
         if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, _newest_header()):
             return obj

@@ -141,3 +141,125 @@ def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: t
         import torch.distributed as dist
         dist.all_reduce(ctx.y_acc[:n], group=group)
     return ctx.y_acc[:n]
+
+
+# ------------------------------------------------------------------------------------------------
+# prefill-sized steps: block-scaled FP4 x FP4 grouped GEMM (activations quantized online)
+MIN_TILE = 128               # rows of one expert tile (rust/crates/nv-quant/src/nvfp4.rs:2)
+MAX_GROUPS_PER_CALL = 1024   # groups one grouped-GEMM call takes
+
+
+def plan_routing(topk_ids, num_experts: int) -> dict:
+    """Host-side plan of a prefill-sized routed step (rust/crates/nv-layers/src/moe_grouped.rs:310-350):
+    every expert that received tokens gets one 128-row tile; `src_idx[row]` is the token a tile row
+    reads (-1 for padding), `inv_perm[token, slot]` the tile row that holds that routed slot.  Rows of
+    one expert keep (token, slot) order.  `overflow` is set when an expert received more than 128
+    rows: the caller must split the token range."""
+    import numpy as np
+    ids = np.asarray(topk_ids).astype(np.int64)
+    n, k = ids.shape
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")                 # by expert, (token, slot) order inside
+    counts = np.bincount(flat, minlength=num_experts)
+    active = np.nonzero(counts)[0]
+    tile_of = np.full(num_experts, -1, np.int64)
+    tile_of[active] = np.arange(active.size)
+    first = np.concatenate([[0], np.cumsum(counts)[:-1]])   # first sorted position of each expert
+    pos_in_expert = np.arange(flat.size) - first[flat[order]]
+    rows = tile_of[flat[order]] * MIN_TILE + pos_in_expert
+    ok = pos_in_expert < MIN_TILE
+    src_idx = np.full(active.size * MIN_TILE, -1, np.int32)
+    inv_perm = np.full(n * k, -1, np.int32)
+    src_idx[rows[ok]] = (order[ok] // k).astype(np.int32)
+    inv_perm[order[ok]] = rows[ok].astype(np.int32)
+    return {"active_experts": active.astype(np.int32), "real_m_per_active": counts[active].astype(np.int32),
+            "m_total_padded": int(active.size * MIN_TILE), "src_idx": src_idx, "inv_perm": inv_perm.reshape(n, k),
+            "overflow": bool((~ok).any())}
+
+
+def grouped_gemm_chunked(a_packed, a_scales, bank, alphas_w4a4, d, active_ids, n: int, k: int, meta_scratch,
+                         gemm_ws) -> None:
+    """One grouped-GEMM call per chunk of active experts, each expert a 128-row tile of the stacked
+    activations (moe_grouped.rs:1656-1760)."""
+    import ctypes as C
+    import numpy as np
+    dev = d.device
+    total = int(active_ids.numel())
+    kb_pad = -(-(k // 16) // 4) * 4
+    s = _stream()
+    for c0 in range(0, total, MAX_GROUPS_PER_CALL):
+        g = min(MAX_GROUPS_PER_CALL, total - c0)
+        rows0 = c0 * MIN_TILE
+        offs = torch.arange(g, dtype=torch.int32, device=dev) * MIN_TILE
+        sizes = torch.tensor(np.tile(np.array([MIN_TILE, n, k], np.int32), g), dtype=torch.int32, device=dev)
+        need = C.c_size_t(0)
+        _ffi.check("nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16", s,
+                   a_packed.data_ptr() + rows0 * (k // 2), a_scales.data_ptr() + rows0 * kb_pad, bank[0].data_ptr(),
+                   bank[1].data_ptr(), alphas_w4a4.data_ptr(), d.data_ptr() + rows0 * n * 2, offs.data_ptr(),
+                   offs.data_ptr(), sizes.data_ptr(), active_ids[c0:].data_ptr(), n, k, g, k, k, n,
+                   meta_scratch.data_ptr(), meta_scratch.numel(), gemm_ws.data_ptr(), gemm_ws.numel(),
+                   C.addressof(need))
+
+
+def forward_grouped(w: MoeGroupedWeights, x: torch.Tensor, topk_ids, topk_weights, input_globals_gate_up=None,
+                    input_globals_down=None) -> torch.Tensor:
+    """Prefill-shaped MoE step on the FP4 x FP4 route (moe_grouped.rs:352-573): gather the routed rows
+    into one 128-row tile per active expert, quantize them with that expert's input global, gate and up
+    as grouped block-scaled GEMMs, SiLU(gate)*up quantized in one pass, down as a grouped GEMM, f32
+    weighted combine.  x [n, hidden] bf16; topk_ids [n, k] (host or device integers); topk_weights
+    [n, k] f32.  Returns [n, hidden] f32.  `input_globals_*`: per-expert activation globals (host
+    sequences of num_experts floats; 1.0 when omitted); `w`'s alphas are reciprocals of the weight
+    globals alone, so the GEMM multiplier is alpha / input_global."""
+    import numpy as np
+    if w.sharded:
+        raise ValueError("forward_grouped: expert-parallel shards run through forward_grouped_decode")
+    dev = x.device
+    n, hidden, inter, E = x.shape[0], w.hidden, w.inter, w.num_experts
+    ids_host = topk_ids.cpu().numpy() if isinstance(topk_ids, torch.Tensor) else np.asarray(topk_ids)
+    k = ids_host.shape[1]
+    plan = plan_routing(ids_host, E)
+    if plan["overflow"]:
+        raise ValueError(f"forward_grouped: an expert received more than {MIN_TILE} rows -- split the token range")
+    a = int(plan["active_experts"].size)
+    if a == 0:
+        return torch.zeros((n, hidden), dtype=torch.float32, device=dev)
+    m_total = plan["m_total_padded"]
+    gu = np.ones(E, np.float32) if input_globals_gate_up is None else np.asarray(input_globals_gate_up, np.float32)
+    dn = np.ones(E, np.float32) if input_globals_down is None else np.asarray(input_globals_down, np.float32)
+    act = plan["active_experts"]
+    gu_dev = torch.from_numpy(gu[act].copy()).to(dev)
+    dn_dev = torch.from_numpy(dn[act].copy()).to(dev)
+    active_ids = torch.from_numpy(act.copy()).to(dev)
+    src_idx = torch.from_numpy(plan["src_idx"]).to(dev)
+    inv_perm = torch.from_numpy(np.ascontiguousarray(plan["inv_perm"])).to(dev)
+    wts = topk_weights.to(device=dev, dtype=torch.float32).contiguous()
+    s = _stream()
+    u8 = dict(dtype=torch.uint8, device=dev)
+    bf = dict(dtype=torch.bfloat16, device=dev)
+
+    x_sorted = torch.empty((m_total, hidden), **bf)
+    _ffi.check("nv_kernels_gather_rows_bf16", s, x.data_ptr(), src_idx.data_ptr(), x_sorted.data_ptr(), m_total,
+               hidden, n)
+    x_fp4 = torch.empty((m_total, hidden // 2), **u8)
+    x_sf = torch.zeros(L.swizzled_scale_bytes(m_total, hidden), **u8)
+    _ffi.check("nv_kernels_quantize_nvfp4_bf16_per_expert", s, x_sorted.data_ptr(), x_fp4.data_ptr(), x_sf.data_ptr(),
+               gu_dev.data_ptr(), MIN_TILE, m_total, hidden)
+    meta = torch.empty(128 * 1024, **u8)
+    ws = torch.empty(16 * 1024 * 1024, **u8)
+    gu_all, dn_all = torch.from_numpy(gu).to(dev), torch.from_numpy(dn).to(dev)
+    y_gate = torch.empty((m_total, inter), **bf)
+    y_up = torch.empty((m_total, inter), **bf)
+    grouped_gemm_chunked(x_fp4, x_sf, w.gate, (w.gate[2] / gu_all).contiguous(), y_gate, active_ids, inter, hidden,
+                         meta, ws)
+    grouped_gemm_chunked(x_fp4, x_sf, w.up, (w.up[2] / gu_all).contiguous(), y_up, active_ids, inter, hidden, meta, ws)
+    act_fp4 = torch.empty((m_total, inter // 2), **u8)
+    act_sf = torch.zeros(L.swizzled_scale_bytes(m_total, inter), **u8)
+    _ffi.check("nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert", s, y_gate.data_ptr(), y_up.data_ptr(),
+               act_fp4.data_ptr(), act_sf.data_ptr(), dn_dev.data_ptr(), MIN_TILE, m_total, inter)
+    y_down = torch.empty((m_total, hidden), **bf)
+    grouped_gemm_chunked(act_fp4, act_sf, w.down, (w.down[2] / dn_all).contiguous(), y_down, active_ids, hidden,
+                         inter, meta, ws)
+    y_acc = torch.empty((n, hidden), dtype=torch.float32, device=dev)
+    _ffi.check("nv_kernels_moe_unpermute_scatter", s, y_down.data_ptr(), wts.data_ptr(), inv_perm.data_ptr(),
+               y_acc.data_ptr(), n, k, hidden, hidden)
+    return y_acc

@@ -108,3 +108,107 @@ def test_refusals_and_workspace_protocol():
     assert f(e, U.stream(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None, t.data_ptr(), 128, 128, 128,
              None, 0, ctypes.addressof(need)) == -2
     torch.cuda.synchronize()
+
+
+def _ulp_close(got, want):
+    ulp = U.bf16_ulp_diff(got, want)
+    absd = np.abs(ref.bf16_to_f32(got) - ref.bf16_to_f32(want))
+    return bool(np.all((ulp <= 2) | (absd <= 1e-3)))
+
+
+@pytest.mark.parametrize("entry", ["nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16",
+                                   "nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode"])
+def test_grouped_block_scaled_gemm_matches_w4a4_oracle(entry):
+    """Three groups with different row counts against a bank of five experts, picked through
+    active_expert_indices: every group equals the single-problem W4A4 oracle on its own rows; rows of D
+    outside the groups are left alone."""
+    U.require_gpu()
+    rng = np.random.default_rng(31)
+    E, n, k = 5, 256, 512
+    bank = [quantized_operand(rng, n, k, 0.02) for _ in range(E)]
+    b_packed = np.stack([b[0] for b in bank])
+    b_sw = np.stack([b[2] for b in bank])
+    alphas = np.array([np.float32(1.0) / np.float32(b[3]) for b in bank], np.float32)
+    active = np.array([3, 0, 4], np.int32)
+    m_real = [128, 40, 97]                       # rows of each group; every group owns a 128-row slot
+    slots = len(active)
+    a_packed = np.zeros((slots * 128, k // 2), np.uint8)
+    a_lin = np.zeros((slots * 128, k // 16), np.uint8)
+    for g in range(slots):
+        ap, alin, _, _ = quantized_operand(rng, 128, k, 1.0, 1.0)
+        a_packed[g * 128:(g + 1) * 128], a_lin[g * 128:(g + 1) * 128] = ap, alin
+    a_sw = ref.swizzle_scales(a_lin)             # 128-row tiles, one after the other
+    offs = (np.arange(slots) * 128).astype(np.int32)
+    sizes = np.array([[m, n, k] for m in m_real], np.int32).reshape(-1)
+    d = [U.dev(t) for t in (a_packed, a_sw, b_packed, b_sw, alphas, offs, sizes, active)]
+    out = torch.full((slots * 128 * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    meta = torch.zeros(128 * 1024, dtype=torch.uint8, device="cuda")
+    need = ctypes.c_size_t(0)
+    f = U.ffi.call
+    assert f(entry, U.stream(), None, None, None, None, None, None, None, None, d[6].data_ptr(), None, n, k, slots,
+             k, k, n, None, 0, None, 0, ctypes.addressof(need)) == 0       # workspace query
+    ws = torch.zeros(max(need.value, 16), dtype=torch.uint8, device="cuda")
+    rc = f(entry, U.stream(), d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(),
+           out.data_ptr(), d[5].data_ptr(), d[5].data_ptr(), d[6].data_ptr(), d[7].data_ptr(), n, k, slots, k, k, n,
+           meta.data_ptr(), meta.numel(), ws.data_ptr(), ws.numel(), ctypes.addressof(need))
+    assert rc == 0
+    torch.cuda.synchronize()
+    o = U.host_u16(out)
+    assert np.all(o[slots * 128 * n:] == 0x7FC0)
+    got = o[:slots * 128 * n].reshape(slots * 128, n)
+    for g in range(slots):
+        e, m = int(active[g]), m_real[g]
+        r0 = g * 128
+        want = ref.matmul_w4a4(a_packed[r0:r0 + m], a_lin[r0:r0 + m], bank[e][0], bank[e][1], m, n, k, float(alphas[e]))
+        assert _ulp_close(got[r0:r0 + m], want), f"group {g}"
+        assert np.all(got[r0 + m:r0 + 128] == 0x7FC0), f"group {g} wrote past its {m} rows"
+    # refusals: meta scratch below the minimum, workspace too small, ragged K
+    args = [d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(), out.data_ptr(),
+            d[5].data_ptr(), d[5].data_ptr(), d[6].data_ptr(), d[7].data_ptr()]
+    assert f(entry, U.stream(), *args, n, k, slots, k, k, n, meta.data_ptr(), 1024, ws.data_ptr(), ws.numel(),
+             ctypes.addressof(need)) == -10
+    if need.value > 0:
+        assert f(entry, U.stream(), *args, n, k, slots, k, k, n, meta.data_ptr(), meta.numel(), ws.data_ptr(), 0,
+                 ctypes.addressof(need)) == -12
+    assert f(entry, U.stream(), *args, n, 500, slots, k, k, n, meta.data_ptr(), meta.numel(), ws.data_ptr(), ws.numel(),
+             ctypes.addressof(need)) == -1
+
+
+def test_forward_grouped_matches_the_per_pair_w4a4_oracle():
+    """The prefill-shaped MoE step (gather -> quantize -> grouped gate/up -> SiLU*up quantize -> grouped
+    down -> combine) against the same chain restated with the oracle per (token, expert) pair."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(32)
+    E, top_k, hidden, inter, n_tok = 8, 2, 256, 384, 24
+    experts, host = [], []
+    for e in range(E):
+        trip, htrip = [], []
+        for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter)):
+            w = U.gauss_bf16(rng, (n, k), 0.05)
+            packed, sw, alpha = ref.quantize_weight_bf16(w)
+            trip.append(sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n))
+            htrip.append((packed, ref.unswizzle_scales(sw, n, k // 16), alpha))
+        experts.append(tuple(trip))
+        host.append(htrip)
+    w = sp.MoeGroupedWeights.build_from_experts(experts)
+    x = U.gauss_bf16(rng, (n_tok, hidden))
+    logits = rng.standard_normal((n_tok, E)).astype(np.float32)
+    ids, wts = ref.moe_route_topk(logits, top_k)
+    y = sp.forward_grouped(w, U.dev(x).view(torch.bfloat16), ids, U.dev(wts))
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    want = np.zeros((n_tok, hidden), np.float64)
+    for t in range(n_tok):
+        xp, xl = ref.quantize_rows_bf16(x[t:t + 1], 1.0)
+        for j in range(top_k):
+            (pg, lg, ag), (pu, lu, au), (pd, ld, ad) = host[ids[t, j]]
+            gate = ref.matmul_w4a4(xp, xl, pg, lg, 1, inter, hidden, ag)
+            up = ref.matmul_w4a4(xp, xl, pu, lu, 1, inter, hidden, au)
+            act = ref.silu_mul(gate, up, round_bf16=False)             # f32, quantized without a bf16 rounding
+            ap, al = ref.quantize_rows(act.reshape(1, inter), 1.0)
+            down = ref.matmul_w4a4(ap, al, pd, ld, 1, hidden, inter, ad)
+            want[t] += np.float64(wts[t, j]) * ref.bf16_to_f32(down)[0].astype(np.float64)
+    # a gate/up value that lands one bf16 ulp away can move an activation code: the bound is the
+    # linear path's, not bit equality
+    assert U.rel_err_floor(got, want) < 2e-2

@@ -221,3 +221,36 @@ def test_two_rank_expert_parallel_sum_equals_the_whole():
         assert p.exitcode == 0
     # each token's k products are the same numbers; only the order of the f32 additions differs
     assert np.allclose(got, want, rtol=1e-6, atol=1e-6 * float(np.abs(want).max()))
+
+
+def test_prefill_routing_plan_equals_the_bucket_walk():
+    """plan_routing against a direct restatement of the reference's plan
+    (rust/crates/nv-layers/src/moe_grouped.rs:310-350): buckets filled in (token, slot) order, one
+    128-row tile per expert that received tokens, overflow past 128 rows."""
+    import numpy as np
+
+    from speaches_plus_b200.moe import plan_routing
+    rng = np.random.default_rng(0)
+    for n, k, E in [(5, 2, 8), (64, 4, 16), (300, 2, 4), (1, 1, 3)]:
+        ids = np.stack([rng.choice(E, k, replace=False) for _ in range(n)])
+        p = plan_routing(ids, E)
+        buckets = [[] for _ in range(E)]
+        for t in range(n):
+            for j in range(k):
+                buckets[ids[t, j]].append((t, j))
+        active = [e for e in range(E) if buckets[e]]
+        src = np.full(len(active) * 128, -1, np.int32)
+        inv = np.full(n * k, -1, np.int32)
+        overflow = False
+        for i, e in enumerate(active):
+            for j, (t, slot) in enumerate(buckets[e]):
+                if j >= 128:
+                    overflow = True
+                    break
+                src[i * 128 + j] = t
+                inv[t * k + slot] = i * 128 + j
+        assert list(p["active_experts"]) == active and p["m_total_padded"] == 128 * len(active)
+        assert list(p["real_m_per_active"]) == [len(buckets[e]) for e in active]
+        assert np.array_equal(p["src_idx"], src) and np.array_equal(p["inv_perm"].reshape(-1), inv)
+        assert p["overflow"] == overflow
+    assert plan_routing(np.zeros((300, 1), np.int64), 2)["overflow"]
