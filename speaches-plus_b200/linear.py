@@ -139,6 +139,17 @@ class Nvfp4Linear:
         """The same plus the stored input global (linear.rs:411-427)."""
         return self.weight_u8, self.weight_scales, self.weight_alpha, self.input_stored_global
 
+    def dequant_weight(self) -> torch.Tensor:
+        """The bf16 weight this linear stands for, [out, in] on the linear's device.  Load-time /
+        diagnostic helper done on the host, as in the reference (linear.rs:508-539): download the packed
+        bytes and scales, value = e2m1 * (ue4m3 * weight_alpha) in f32, round to bf16, upload."""
+        from . import weights as W
+        kb = self.in_features // BLOCK_SIZE
+        packed = self.weight_u8.cpu().numpy()
+        lin = W.unswizzle_scales(self.weight_scales.cpu().numpy(), self.out_features, kb)
+        bits = W.dequantize_packed_to_bf16_bits(packed, lin, self.out_features, self.in_features, self.weight_alpha)
+        return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).to(self.weight_u8.device)
+
     @property
     def alpha_w4a16(self) -> float:
         """Output multiplier when the activations stay bf16: the reciprocal of the weight global alone.

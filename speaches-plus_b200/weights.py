@@ -482,23 +482,36 @@ def _f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
     return np.where(np.isnan(x), np.uint16(0x7FC0), r).astype(np.uint16)
 
 
-def dequantize_nvfp4_to_bf16(weights: WeightLoader, module: str, out_features: int, in_features: int) -> np.ndarray:
-    """A module too small for the NVFP4 kernels, expanded to bf16 bits on the host
-    (moe.rs:955-992): value = e2m1 * (ue4m3 * 1/stored_global), each product in f32, rounded to
-    bf16 (nearest even).  Reads the compressed-tensors names, as the reference does."""
-    packed = weights.raw_bytes(f"{module}.weight_packed")
-    scales = weights.raw_bytes(f"{module}.weight_scale")
-    g = weights.scalar_f32(f"{module}.weight_global_scale")
-    inv = np.float32(1.0) if g == 0 else np.float32(1.0) / g
-    kb = in_features // BLOCK_SIZE
-    if packed.size < out_features * in_features // 2 or scales.size < out_features * kb:
-        raise WeightError(f"nvfp4 {module}: too few bytes for [{out_features}, {in_features}]")
-    block = (_UE4M3[scales[: out_features * kb]] * inv).astype(np.float32).reshape(out_features, kb, 1)
-    p = packed[: out_features * in_features // 2].reshape(out_features, kb, BLOCK_SIZE // 2)
-    vals = np.empty((out_features, kb, BLOCK_SIZE), dtype=np.float32)
+def dequantize_packed_to_bf16_bits(packed: np.ndarray, scales_linear: np.ndarray, rows: int, cols: int,
+                                   weight_mult) -> np.ndarray:
+    """Packed e2m1 [rows, cols/2] + row-major ue4m3 scales [rows, cols/16] -> bf16 bits [rows, cols]:
+    value = e2m1 * (ue4m3 * weight_mult), each product one f32 operation, rounded to bf16 (nearest
+    even) -- rust/crates/nv-quant/src/nvfp4.rs:266-292 followed by the bf16 cast of its callers."""
+    kb = cols // BLOCK_SIZE
+    packed = np.asarray(packed, dtype=np.uint8).reshape(-1)
+    scales_linear = np.asarray(scales_linear, dtype=np.uint8).reshape(-1)
+    if cols % BLOCK_SIZE != 0 or packed.size < rows * cols // 2 or scales_linear.size < rows * kb:
+        raise WeightError(f"nvfp4 dequantize: too few bytes for [{rows}, {cols}]")
+    block = (_UE4M3[scales_linear[: rows * kb]] * np.float32(weight_mult)).astype(np.float32).reshape(rows, kb, 1)
+    p = packed[: rows * cols // 2].reshape(rows, kb, BLOCK_SIZE // 2)
+    vals = np.empty((rows, kb, BLOCK_SIZE), dtype=np.float32)
     vals[:, :, 0::2] = _E2M1[p & 0xF] * block
     vals[:, :, 1::2] = _E2M1[p >> 4] * block
-    return _f32_to_bf16_bits(vals.reshape(out_features, in_features))
+    return _f32_to_bf16_bits(vals.reshape(rows, cols))
+
+
+def dequantize_nvfp4_to_bf16(weights: WeightLoader, module: str, out_features: int, in_features: int) -> np.ndarray:
+    """A module too small for the NVFP4 kernels, expanded to bf16 bits on the host
+    (moe.rs:955-992), with 1/stored_global as the multiplier.  Reads the compressed-tensors names, as
+    the reference does."""
+    g = weights.scalar_f32(f"{module}.weight_global_scale")
+    inv = np.float32(1.0) if g == 0 else np.float32(1.0) / g
+    try:
+        return dequantize_packed_to_bf16_bits(weights.raw_bytes(f"{module}.weight_packed"),
+                                              weights.raw_bytes(f"{module}.weight_scale"), out_features, in_features,
+                                              inv)
+    except WeightError as e:
+        raise WeightError(f"nvfp4 {module}: {e}") from e
 
 
 # ------------------------------------------------------------------------------------------------

@@ -1,0 +1,54 @@
+"""Host-side rules of the NVFP4 linear that need no GPU: constructor refusals
+(rust/crates/nv-layers/src/linear.rs:1565-1579, 2059-2120; tests/linear_quant.rs bad-shape cases),
+buffer sizes, the W4A16 multiplier."""
+import numpy as np
+import pytest
+import torch
+
+import speaches_plus_b200 as sp
+from speaches_plus_b200 import linear as L
+
+
+def parts(n, k):
+    return (torch.zeros((n, k // 2), dtype=torch.uint8), torch.zeros(L.swizzled_scale_bytes(n, k), dtype=torch.uint8))
+
+
+def test_swizzled_scale_bytes():
+    assert L.swizzled_scale_bytes(4096, 4096) == 4096 * 256          # no padding at the BASELINE shapes
+    assert L.swizzled_scale_bytes(130, 144) == 256 * 12               # rows to 128, blocks to 4
+    assert L.swizzled_scale_bytes(768, 2048) * 2 + 768 * 2048 // 2 * 2 + L.swizzled_scale_bytes(2048, 768) + 2048 * 768 // 2 \
+        == 2_654_208                                                  # bytes of one configs[3] expert
+
+
+def test_constructor_refusals():
+    p, s = parts(128, 128)
+    sp.Nvfp4Linear.new_nvfp4(p, s, 0.5, 128, 128)
+    with pytest.raises(ValueError, match="multiple of 16"):
+        sp.Nvfp4Linear.new_nvfp4(p, s, 0.5, 136, 128)
+    with pytest.raises(ValueError, match="MIN_TILE"):
+        sp.Nvfp4Linear.new_nvfp4(*parts(64, 128), 0.5, 128, 64)
+    with pytest.raises(ValueError, match="MIN_TILE"):
+        sp.Nvfp4Linear.new_nvfp4(*parts(128, 64), 0.5, 64, 128)
+    with pytest.raises(ValueError, match="wrong number of bytes"):
+        sp.Nvfp4Linear.new_nvfp4(p[:100], s, 0.5, 128, 128)
+    with pytest.raises(ValueError, match="scale buffer too small"):
+        sp.Nvfp4Linear.new_nvfp4(p, s[:100], 0.5, 128, 128)
+
+
+def test_forward_checks_the_input_width_before_any_launch():
+    lin = sp.Nvfp4Linear.new_nvfp4(*parts(128, 128), 0.5, 128, 128)
+    with pytest.raises(ValueError, match="input last dim 64 != 128"):
+        lin.forward(torch.zeros((1, 64), dtype=torch.bfloat16))
+
+
+def test_w4a16_multiplier_drops_the_input_global():
+    p, s = parts(128, 128)
+    plain = sp.Nvfp4Linear.new_nvfp4(p, s, 0.25, 128, 128)
+    assert plain.alpha_w4a16 == 0.25 and plain.nvfp4_parts()[2] == 0.25
+    ckpt = sp.Nvfp4Linear.new_nvfp4_scaled(p, s, 128, 128, None, float(np.float32(0.25) * np.float32(1 / 8)), 8.0)
+    assert ckpt.alpha_w4a16 == 0.25 and ckpt.nvfp4_parts_full()[3] == 8.0
+
+
+def test_stored_global_rule():
+    assert L.stored_global_from_amax(0.0) == 1.0 and L.stored_global_from_amax(float("inf")) == 1.0
+    assert L.stored_global_from_amax(0.5) == 448.0 * 6.0 / 0.5

@@ -295,3 +295,21 @@ def test_device_constructors_refuse_a_cpu_device(tmp_path):
         W.nvfp4_linear_from_disk(wl, "a", 128, 128, "cpu")
     with pytest.raises(W.WeightError, match="requires a CUDA device"):
         W.moe_grouped_weights_from_disk(wl, ["a"], 128, 128, "cpu")
+
+
+def test_host_dequantize_equals_the_oracle_and_serves_dequant_weight():
+    """dequantize_packed_to_bf16_bits == the oracle's bf16 expansion, bit for bit; Nvfp4Linear.dequant_weight
+    (a host-side helper, run here on CPU tensors) returns it for the linear's own buffers."""
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(13)
+    n, k = 256, 384
+    packed, lin, g = make_module(rng, n, k)
+    alpha = np.float32(1) / g
+    want = ref.dequantize_to_bf16(packed, ref.swizzle_scales(lin), n, k, float(alpha))
+    assert np.array_equal(W.dequantize_packed_to_bf16_bits(packed, lin, n, k, alpha), want)
+    layer = sp.Nvfp4Linear.new_nvfp4(torch.from_numpy(packed), torch.from_numpy(ref.swizzle_scales(lin)), float(alpha), k, n)
+    got = layer.dequant_weight()
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (n, k)
+    assert np.array_equal(got.view(torch.int16).numpy().view(np.uint16), want)
+    with pytest.raises(W.WeightError, match="too few bytes"):
+        W.dequantize_packed_to_bf16_bits(packed[:10], lin, n, k, alpha)
