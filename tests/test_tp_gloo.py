@@ -254,3 +254,45 @@ def test_prefill_routing_plan_equals_the_bucket_walk():
         assert np.array_equal(p["src_idx"], src) and np.array_equal(p["inv_perm"].reshape(-1), inv)
         assert p["overflow"] == overflow
     assert plan_routing(np.zeros((300, 1), np.int64), 2)["overflow"]
+
+
+def _leaver_worker(rank, world, port, q):
+    """Failure made on the host: rank 1 completes one step and leaves between steps; rank 0's next
+    collective must end with an error within the process group's timeout, not hang."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from speaches_plus_b200 import tp
+    n, k = 256, 512
+    rng = np.random.default_rng(5)
+    w = ref.f32_to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    x = torch.from_numpy(ref.f32_to_bf16(rng.standard_normal((1, k)).astype(np.float32)).view(np.int16)).view(torch.bfloat16)
+    p, s, nl, kl, off = tp.shard_nvfp4(torch.from_numpy(packed), torch.from_numpy(sw), n, k, "row", rank, world)
+    t = tp.TpNvfp4Linear(OracleLocal(p, s, alpha, kl, nl), "row", rank, world, n, k, off)
+    t.forward(x)                      # step 1: both ranks take part
+    if rank == 1:
+        os._exit(0)                   # leaves between steps, nothing of its own in flight
+    time.sleep(1.0)
+    t0 = time.time()
+    try:
+        t.forward(x)                  # step 2: the peer is gone
+        q.put(("no error", time.time() - t0))
+    except Exception as e:           # noqa: BLE001 - any collective error is the expected outcome
+        q.put((type(e).__name__, time.time() - t0))
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_between_steps_surfaces_as_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    kind, seconds = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+    assert kind != "no error", "the collective completed although the peer had left"
+    assert seconds < 30, f"took {seconds:.1f} s to notice"
