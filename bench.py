@@ -287,9 +287,11 @@ def run_b200(args) -> dict:
                          "frac_of_nominal_8TBs": round(per_gpu_gbs / 8000.0, 4),
                          # DRAM read+write bytes per launch: the ncu capture of the K=4096, N=28672 case
                          # (profiles/) measured 1.012 x the algorithmic bytes; scaled to the average launch.
-                         "traffic": int(1.012 * (total_bytes // launches_per_step)),
+                         # Per GPU: each rank's launch streams 1/world of the matrix.
+                         "traffic": int(1.012 * (total_bytes // launches_per_step // world)),
                          "traffic_source": "ncu dram__bytes_read+write on K4096_N28672_M1, scaled by bytes",
-                         "kernel": "w4a16_mma_kernel", "bytes_per_launch_avg": total_bytes // launches_per_step,
+                         "kernel": "w4a16_mma_kernel",
+                         "bytes_per_launch_avg": total_bytes // launches_per_step // world,
                          "us_per_launch_avg": round(ms_per_step * 1e3 / launches_per_step, 3)},
             "per_shape": per_shape,
             "clocks": clocks,
