@@ -281,7 +281,9 @@ def _leaver_worker(rank, world, port, q):
         q.put(("no error", time.time() - t0))
     except Exception as e:           # noqa: BLE001 - any collective error is the expected outcome
         q.put((type(e).__name__, time.time() - t0))
-    os._exit(0)
+    q.close()
+    q.join_thread()                   # the result must reach the parent before this process goes away
+    os._exit(0)                       # the group cannot be torn down in order: its peer is gone
 
 
 def test_a_rank_that_leaves_between_steps_surfaces_as_an_error_not_a_hang():
