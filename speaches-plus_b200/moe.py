@@ -263,3 +263,112 @@ def forward_grouped(w: MoeGroupedWeights, x: torch.Tensor, topk_ids, topk_weight
     _ffi.check("nv_kernels_moe_unpermute_scatter", s, y_down.data_ptr(), wts.data_ptr(), inv_perm.data_ptr(),
                y_acc.data_ptr(), n, k, hidden, hidden)
     return y_acc
+
+
+# ------------------------------------------------------------------------------------------------
+# the MoE block around the expert dispatch
+import dataclasses  # noqa: E402
+
+
+@dataclasses.dataclass(frozen=True)
+class MoeConfig:
+    """rust/crates/nv-layers/src/moe.rs:12-19."""
+    hidden_size: int
+    num_experts: int
+    num_experts_per_tok: int
+    moe_intermediate_size: int
+    shared_expert_intermediate_size: int = 0
+
+
+class MoeBlock:
+    """Router + routed experts + gated shared expert (rust/crates/nv-layers/src/moe.rs:21-401):
+
+        y = sum_j softmax(top-k logits)_j * expert_j(x)  +  sigmoid(x . w_shared_gate) * shared_expert(x)
+
+    `gate` is the bf16 router linear [num_experts, hidden]; `experts` the routed experts' banks
+    (`MoeGroupedWeights`); `shared_expert` an `Nvfp4Mlp` with its bf16 gate linear [1, hidden], or both
+    None.  Up to `decode_tokens` tokens run the capture-safe decode path (tokens grouped per expert,
+    activations kept in bf16); larger batches take the prefill route (`forward_grouped`)."""
+
+    def __init__(self, cfg: MoeConfig, gate: L.Bf16Linear, experts: MoeGroupedWeights, shared_expert=None,
+                 shared_expert_gate=None, decode_tokens: int = 64):
+        if experts.total_experts != cfg.num_experts:
+            raise ValueError(f"MoeBlock: experts={experts.total_experts} != cfg.num_experts={cfg.num_experts}")
+        if cfg.num_experts_per_tok == 0 or cfg.num_experts_per_tok > cfg.num_experts:
+            raise ValueError(f"MoeBlock: num_experts_per_tok={cfg.num_experts_per_tok} invalid for "
+                             f"num_experts={cfg.num_experts}")
+        if gate.in_features != cfg.hidden_size or gate.out_features != cfg.num_experts:
+            raise ValueError(f"MoeBlock: gate shape mismatch -- expected [{cfg.num_experts}, {cfg.hidden_size}], "
+                             f"got [{gate.out_features}, {gate.in_features}]")
+        if (experts.hidden, experts.inter) != (cfg.hidden_size, cfg.moe_intermediate_size):
+            raise ValueError("MoeBlock: expert banks do not have the configured sizes")
+        if (shared_expert is None) != (shared_expert_gate is None):
+            raise ValueError("MoeBlock: the shared expert and its gate come together")
+        if shared_expert_gate is not None and (shared_expert_gate.out_features != 1 or
+                                               shared_expert_gate.in_features != cfg.hidden_size):
+            raise ValueError("MoeBlock: shared_expert_gate must be [1, hidden]")
+        self.cfg, self.gate, self.experts = cfg, gate, experts
+        self.shared_expert, self.shared_expert_gate = shared_expert, shared_expert_gate
+        self.decode_tokens = decode_tokens
+        self._ctx = None
+
+    def shared_contribution(self, x_flat: torch.Tensor) -> torch.Tensor:
+        """sigmoid(gate logit) * shared_expert(x), f32 [n, hidden] (moe.rs:386-398)."""
+        out = self.shared_expert.forward(x_flat).float()
+        return torch.sigmoid(self.shared_expert_gate.forward(x_flat).float()) * out
+
+    def forward(self, x: torch.Tensor, group=None) -> torch.Tensor:
+        cfg = self.cfg
+        if x.shape[-1] != cfg.hidden_size:
+            raise ValueError(f"MoeBlock: last dim {x.shape[-1]} != hidden_size {cfg.hidden_size}")
+        lead = x.shape[:-1]
+        x_flat = x.reshape(-1, cfg.hidden_size).to(torch.bfloat16).contiguous()
+        n = x_flat.shape[0]
+        logits = self.gate.forward(x_flat).float().contiguous()     # the router's bf16 output, widened
+        if n <= self.decode_tokens:
+            if self._ctx is None or self._ctx.topk_ids.device != x.device:
+                self._ctx = GroupedDecodeContext(self.experts, self.decode_tokens, cfg.num_experts_per_tok, x.device)
+            y = forward_grouped_decode(self.experts, self._ctx, x_flat, logits, group=group).clone()
+        else:
+            ids = torch.zeros((n, cfg.num_experts_per_tok), dtype=torch.int32, device=x.device)
+            wts = torch.zeros((n, cfg.num_experts_per_tok), dtype=torch.float32, device=x.device)
+            _ffi.check("nv_kernels_moe_route_topk", _stream(), logits.data_ptr(), None, ids.data_ptr(),
+                       wts.data_ptr(), n, cfg.num_experts, cfg.num_experts_per_tok, 0, 0.0, 1, 1.0)
+            y = self._forward_prefill(x_flat, ids, wts)
+        if self.shared_expert is not None:
+            y = y + self.shared_contribution(x_flat)
+        return y.reshape(*lead, cfg.hidden_size).to(x.dtype)
+
+    __call__ = forward
+
+    def _forward_prefill(self, x_flat, ids, wts):
+        """Token ranges small enough that no expert receives more than one 128-row tile."""
+        n = x_flat.shape[0]
+        out = torch.empty((n, self.cfg.hidden_size), dtype=torch.float32, device=x_flat.device)
+        ids_host = ids.cpu().numpy()
+        r0 = 0
+        while r0 < n:
+            r1 = min(n, r0 + MIN_TILE)   # at most 128 tokens: no expert can receive more than 128 rows
+            out[r0:r1] = forward_grouped(self.experts, x_flat[r0:r1].contiguous(), ids_host[r0:r1],
+                                         wts[r0:r1].contiguous())
+            r0 = r1
+        return out
+
+    @classmethod
+    def from_loader(cls, cfg: MoeConfig, prefix: str, weights, qconfig, device, sfx=None, decode_tokens: int = 64):
+        """`<prefix>.gate.weight`, `<prefix>.experts.<i>.{gate,up,down}_proj.*`,
+        `<prefix>.shared_expert.{gate,up,down}_proj.*`, `<prefix>.shared_expert_gate.weight`
+        (moe.rs:176-290)."""
+        from . import weights as W
+        sfx = sfx or W.Nvfp4Suffixes.QWEN_COMPRESSED_TENSORS
+        gate = W.load_linear(weights, f"{prefix}.gate.weight", cfg.num_experts, cfg.hidden_size, device)
+        banks = W.moe_grouped_weights_from_disk(weights, [f"{prefix}.experts.{i}" for i in range(cfg.num_experts)],
+                                                cfg.hidden_size, cfg.moe_intermediate_size, device, sfx)
+        shared = shared_gate = None
+        if cfg.shared_expert_intermediate_size:
+            f, h = cfg.shared_expert_intermediate_size, cfg.hidden_size
+            mk = lambda name, n, k: W.nvfp4_linear_from_disk_with_suffixes(  # noqa: E731
+                weights, f"{prefix}.shared_expert.{name}", n, k, device, sfx)
+            shared = L.Nvfp4Mlp(mk("gate_proj", f, h), mk("up_proj", f, h), mk("down_proj", h, f))
+            shared_gate = W.load_linear(weights, f"{prefix}.shared_expert_gate.weight", 1, h, device)
+        return cls(cfg, gate, banks, shared, shared_gate, decode_tokens)

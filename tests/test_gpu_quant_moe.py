@@ -436,3 +436,71 @@ def test_fused_route_permute_equals_the_two_kernels(E, K, mode, n):
         assert np.array_equal(x.cpu().numpy().view(np.int32), y.cpu().numpy().view(np.int32))
     assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 4, 257, 4, 0, 0.0, 1, 1.0) == -3
     assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
+
+
+@pytest.mark.parametrize("n_tok", [3, 200])
+def test_moe_block_matches_the_mixture_formula(n_tok):
+    """MoeBlock.forward == sum_j softmax(top-k logits)_j * expert_j(x) + sigmoid(x . w_g) * shared(x)
+    (rust/crates/nv-layers/src/moe.rs:1035-1133 checks the same closed form on the Cpu backend).
+    3 tokens take the decode path (W4A16 experts), 200 the prefill route (FP4 x FP4 experts); the oracle
+    follows each route's own numerics."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(500 + n_tok)
+    E, top_k, hidden, inter, sh_inter = 8, 2, 256, 384, 512
+
+    def make(n, k, std=0.05):
+        w = U.gauss_bf16(rng, (n, k), std)
+        packed, sw, alpha = ref.quantize_weight_bf16(w)
+        return sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n), (packed, sw, alpha)
+
+    experts, host = [], []
+    for e in range(E):
+        trip = [make(inter, hidden), make(inter, hidden), make(hidden, inter)]
+        experts.append(tuple(t[0] for t in trip))
+        host.append([t[1] for t in trip])
+    shared = [make(sh_inter, hidden), make(sh_inter, hidden), make(hidden, sh_inter)]
+    w_router = U.gauss_bf16(rng, (E, hidden), 0.5)
+    w_sgate = U.gauss_bf16(rng, (1, hidden), 0.1)
+    cfg = sp.MoeConfig(hidden, E, top_k, inter, sh_inter)
+    blk = sp.MoeBlock(cfg, sp.Bf16Linear(U.dev(w_router).view(torch.bfloat16)),
+                      sp.MoeGroupedWeights.build_from_experts(experts),
+                      sp.Nvfp4Mlp(*[s[0] for s in shared]), sp.Bf16Linear(U.dev(w_sgate).view(torch.bfloat16)))
+    x = U.gauss_bf16(rng, (n_tok, hidden))
+    y = blk.forward(U.dev(x).view(torch.bfloat16))
+    torch.cuda.synchronize()
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (n_tok, hidden)
+    got = y.float().cpu().numpy()
+
+    # router: bf16 GEMV output widened to f32, top-k, softmax over the winners
+    logits = ref.bf16_to_f32(ref.linear_cpu_backend(w_router, x))
+    ids, wts = ref.moe_route_topk(logits, top_k)
+
+    def mlp_w4a16(h, xrow, n_int):
+        (pg, sg, ag), (pu, su, au), (pd, sd, ad) = h
+        gate = ref.f32_to_bf16(ref.linear_w4a16_f64(pg, sg, xrow, ag, n_int, hidden).astype(np.float32))
+        up = ref.f32_to_bf16(ref.linear_w4a16_f64(pu, su, xrow, au, n_int, hidden).astype(np.float32))
+        act = ref.f32_to_bf16(ref.silu_mul(gate, up, round_bf16=True))
+        return ref.bf16_to_f32(ref.f32_to_bf16(ref.linear_w4a16_f64(pd, sd, act, ad, hidden, n_int).astype(np.float32)))[0]
+
+    def mlp_w4a4(h, xrow):
+        (pg, sg, ag), (pu, su, au), (pd, sd, ad) = h
+        lg, lu, ld = (ref.unswizzle_scales(s, n, k // 16) for s, n, k in ((sg, inter, hidden), (su, inter, hidden),
+                                                                          (sd, hidden, inter)))
+        xp, xl = ref.quantize_rows_bf16(xrow, 1.0)
+        gate = ref.matmul_w4a4(xp, xl, pg, lg, 1, inter, hidden, ag)
+        up = ref.matmul_w4a4(xp, xl, pu, lu, 1, inter, hidden, au)
+        ap, al = ref.quantize_rows(ref.silu_mul(gate, up, round_bf16=False).reshape(1, inter), 1.0)
+        return ref.bf16_to_f32(ref.matmul_w4a4(ap, al, pd, ld, 1, hidden, inter, ad))[0]
+
+    sg_logit = ref.bf16_to_f32(ref.linear_cpu_backend(w_sgate, x))[:, 0]
+    want = np.zeros((n_tok, hidden), np.float64)
+    for t in range(n_tok):
+        for j in range(top_k):
+            h = host[ids[t, j]]
+            out = mlp_w4a16(h, x[t:t + 1], inter) if n_tok <= 64 else mlp_w4a4(h, x[t:t + 1])
+            want[t] += np.float64(wts[t, j]) * out.astype(np.float64)
+        sh = mlp_w4a16([s[1] for s in shared], x[t:t + 1], sh_inter)
+        want[t] += (1.0 / (1.0 + np.exp(-np.float64(sg_logit[t])))) * sh.astype(np.float64)
+    # the router's logits are bf16 GEMV outputs: a logit one ulp off can only matter at an exact tie
+    assert U.rel_err_floor(got, want) < 2e-2

@@ -52,3 +52,31 @@ def test_w4a16_multiplier_drops_the_input_global():
 def test_stored_global_rule():
     assert L.stored_global_from_amax(0.0) == 1.0 and L.stored_global_from_amax(float("inf")) == 1.0
     assert L.stored_global_from_amax(0.5) == 448.0 * 6.0 / 0.5
+
+
+def test_moe_block_constructor_refusals():
+    """rust/crates/nv-layers/src/moe.rs:33-80: expert count, top-k range, router shape."""
+    def banks(E, hidden=128, inter=128):
+        z = (torch.zeros((E, 1), dtype=torch.uint8),) * 2 + (torch.zeros(E),)
+        return sp.MoeGroupedWeights(z, z, z, hidden, inter, E)
+
+    def router(E, hidden=128):
+        return sp.Bf16Linear(torch.zeros((E, hidden), dtype=torch.bfloat16))
+
+    cfg = sp.MoeConfig(128, 4, 2, 128)
+    sp.MoeBlock(cfg, router(4), banks(4))
+    with pytest.raises(ValueError, match="experts=3"):
+        sp.MoeBlock(cfg, router(4), banks(3))
+    with pytest.raises(ValueError, match="num_experts_per_tok=5"):
+        sp.MoeBlock(sp.MoeConfig(128, 4, 5, 128), router(4), banks(4))
+    with pytest.raises(ValueError, match="num_experts_per_tok=0"):
+        sp.MoeBlock(sp.MoeConfig(128, 4, 0, 128), router(4), banks(4))
+    with pytest.raises(ValueError, match="gate shape mismatch"):
+        sp.MoeBlock(cfg, router(5), banks(4))
+    with pytest.raises(ValueError, match="configured sizes"):
+        sp.MoeBlock(cfg, router(4), banks(4, inter=256))
+    with pytest.raises(ValueError, match="come together"):
+        sp.MoeBlock(cfg, router(4), banks(4), shared_expert=object())
+    blk = sp.MoeBlock(cfg, router(4), banks(4))
+    with pytest.raises(ValueError, match="last dim 64 != hidden_size 128"):
+        blk.forward(torch.zeros((1, 64), dtype=torch.bfloat16))
