@@ -472,8 +472,12 @@ def test_moe_block_matches_the_mixture_formula(n_tok):
     assert y.dtype == torch.bfloat16 and tuple(y.shape) == (n_tok, hidden)
     got = y.float().cpu().numpy()
 
-    # router: bf16 GEMV output widened to f32, top-k, softmax over the winners
-    logits = ref.bf16_to_f32(ref.linear_cpu_backend(w_router, x))
+    # router: bf16 GEMV output widened to f32, top-k, softmax over the winners.  The routing decision
+    # is taken from the device's own logits (the GEMV has its parity test; a logit one bf16 ulp away
+    # from the host's could otherwise swap two near-equal experts), after checking them against the host.
+    logits = blk.gate.forward(U.dev(x).view(torch.bfloat16)).float().cpu().numpy()
+    host_logits = ref.bf16_to_f32(ref.linear_cpu_backend(w_router, x))
+    assert U.rel_err_floor(logits, host_logits.astype(np.float64)) < 1e-2
     ids, wts = ref.moe_route_topk(logits, top_k)
 
     def mlp_w4a16(h, xrow, n_int):
@@ -502,5 +506,4 @@ def test_moe_block_matches_the_mixture_formula(n_tok):
             want[t] += np.float64(wts[t, j]) * out.astype(np.float64)
         sh = mlp_w4a16([s[1] for s in shared], x[t:t + 1], sh_inter)
         want[t] += (1.0 / (1.0 + np.exp(-np.float64(sg_logit[t])))) * sh.astype(np.float64)
-    # the router's logits are bf16 GEMV outputs: a logit one ulp off can only matter at an exact tie
     assert U.rel_err_floor(got, want) < 2e-2
