@@ -189,23 +189,55 @@ class Nvfp4Linear:
             mm = min(MAX_DECODE_M, m - r0)
             linear_w4a16(self, None, x2[r0:], None, y[r0:], None, mm)
 
+    def prenorm_nvfp4_eligible(self) -> bool:
+        """linear.rs:648-651: an NVFP4 projection without bias (and without an adapter)."""
+        return self.bias is None
+
+    def forward_prenorm_nvfp4(self, x_pre: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """RMSNorm fused into the activation quantizer, then the FP4 x FP4 GEMM (linear.rs:653-689 with
+        `FusedPreNorm`): y = (rmsnorm(x_pre) * norm_weight) W^T, the normalised row rounded to bf16 once
+        before it is quantized.  One row of K bf16 values must fit the quantizer's 48 KiB of shared
+        memory (K <= 24576)."""
+        if not self.prenorm_nvfp4_eligible():
+            raise ValueError("forward_prenorm_nvfp4: linear is not an eligible NVFP4 projection")
+        if x_pre.shape[-1] != self.in_features:
+            raise ValueError(f"forward_prenorm_nvfp4: input last dim {x_pre.shape[-1]} != in_features "
+                             f"{self.in_features}")
+        lead = x_pre.shape[:-1]
+        x2 = x_pre.reshape(-1, self.in_features).contiguous()
+        assert x2.is_cuda and x2.dtype == torch.bfloat16 and norm_weight.dtype == torch.bfloat16
+        m, k = x2.shape
+        m_pad = -(-m // 128) * 128
+        a_packed = torch.empty((m_pad, k // 2), dtype=torch.uint8, device=x2.device)
+        a_scales = torch.zeros(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=x2.device)
+        _ffi.check("nv_kernels_rmsnorm_quantize_nvfp4_bf16", _stream(), x2.data_ptr(), norm_weight.data_ptr(),
+                   a_packed.data_ptr(), a_scales.data_ptr(), float(self.input_stored_global), float(eps), m_pad, m, k)
+        y = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=x2.device)
+        self._fp4_gemm(a_packed, a_scales, y, m)
+        return y.reshape(*lead, self.out_features)
+
     def forward_prefill_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
         """Prefill-sized M: the reference's default route (rust/crates/nv-layers/src/linear.rs:1590-1795) --
         quantize the activations to NVFP4 (global 1.0, rows padded to a multiple of 128 with zeros), then one
         block-scaled FP4 x FP4 tensor-core GEMM with alpha = weight_alpha in device memory."""
-        m, k, n = x2.shape[0], self.in_features, self.out_features
+        m = x2.shape[0]
         m_pad = -(-m // 128) * 128
         a_packed, a_scales = quantize_nvfp4_bf16(x2, self.input_stored_global, m_padded=m_pad)
-        if getattr(self, "_alpha_dev", None) is None or self._alpha_dev.device != x2.device:
-            self._alpha_dev = torch.tensor([self.weight_alpha], dtype=torch.float32,
-                                           device=x2.device)
+        self._fp4_gemm(a_packed, a_scales, y, m)
+
+    def _fp4_gemm(self, a_packed: torch.Tensor, a_scales: torch.Tensor, y: torch.Tensor, m: int) -> None:
+        """y [m, out] = alpha * A W^T for activations already quantized (rows padded to 128)."""
+        k, n = self.in_features, self.out_features
+        dev = a_packed.device
+        if getattr(self, "_alpha_dev", None) is None or self._alpha_dev.device != dev:
+            self._alpha_dev = torch.tensor([self.weight_alpha], dtype=torch.float32, device=dev)
         need = C.c_size_t(0)
         s = _stream()
         _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", s, None, None, None, None, None, None, m, n, k, None, 0,
                    C.addressof(need))
-        ws = linear_workspace(x2.device, 1, 16)
+        ws = linear_workspace(dev, 1, 16)
         if ws.numel() < need.value:
-            ws = torch.empty(need.value, dtype=torch.uint8, device=x2.device)
+            ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
         _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", s, a_packed.data_ptr(), a_scales.data_ptr(),
                    self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), self._alpha_dev.data_ptr(), y.data_ptr(),
                    m, n, k, ws.data_ptr(), ws.numel(), C.addressof(need))

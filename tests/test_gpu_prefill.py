@@ -212,3 +212,36 @@ def test_forward_grouped_matches_the_per_pair_w4a4_oracle():
     # a gate/up value that lands one bf16 ulp away can move an activation code: the bound is the
     # linear path's, not bit equality
     assert U.rel_err_floor(got, want) < 2e-2
+
+
+def test_forward_prenorm_nvfp4():
+    """RMSNorm fused into the activation quantizer, then the FP4 x FP4 GEMM
+    (rust/crates/nv-layers/src/linear.rs:653-689): equals norm -> bf16 -> quantize -> W4A4 oracle.  The
+    device's rsqrt and sum order differ from the host's by an ulp, which can move a few 4-bit codes, so
+    the bound is the linear path's relative one, not 2 ulp."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(41)
+    m, n, k, eps = 70, 512, 1024, 1e-6
+    w = U.gauss_bf16(rng, (n, k), 0.02)
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    lin = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+    x = U.gauss_bf16(rng, (m, k), 1.5)
+    nw = U.gauss_bf16(rng, (k,), 1.0)
+    y = lin.forward_prenorm_nvfp4(U.dev(x).view(torch.bfloat16), U.dev(nw).view(torch.bfloat16), eps)
+    torch.cuda.synchronize()
+    assert tuple(y.shape) == (m, n)
+    xf, wf = ref.bf16_to_f32(x), ref.bf16_to_f32(nw)
+    rstd = (1.0 / np.sqrt((xf.astype(np.float64) ** 2).mean(1) + eps)).astype(np.float32)
+    normed = ref.f32_to_bf16((xf * rstd[:, None]) * wf[None, :])
+    ap, alin = ref.quantize_rows_bf16(normed, 1.0)
+    want = ref.matmul_w4a4(ap, alin, packed, ref.unswizzle_scales(sw, n, k // 16), m, n, k, alpha)
+    assert U.rel_err_floor(y.float().cpu().numpy(), ref.bf16_to_f32(want).astype(np.float64)) < 2e-2
+    # the same rows through the unfused pair (norm on the host, then the linear's own prefill route)
+    y2 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    lin.forward_prefill_into(U.dev(normed).view(torch.bfloat16), y2)
+    torch.cuda.synchronize()
+    assert U.rel_err_floor(y.float().cpu().numpy(), y2.float().cpu().numpy().astype(np.float64)) < 2e-2
+    biased = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n, bias=torch.zeros(n, device="cuda"))
+    with pytest.raises(ValueError, match="not an eligible"):
+        biased.forward_prenorm_nvfp4(U.dev(x).view(torch.bfloat16), U.dev(nw).view(torch.bfloat16), eps)
