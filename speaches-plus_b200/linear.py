@@ -131,6 +131,17 @@ class Nvfp4Linear:
         packed, scales, alpha, _ = quantize_weight_nvfp4(weight)
         return cls(packed, scales, alpha, k, n, bias)
 
+    @classmethod
+    def from_bf16_quantized_nvfp4(cls, weight: torch.Tensor, bias: torch.Tensor | None = None):
+        """The reference's host-quantized constructor (linear.rs:2228-2275): blocks quantized with a
+        global of 1.0 (no per-tensor rescale) and alpha 1.0.  The bytes are produced by the device
+        quantizer, which is byte-exact against the host rule."""
+        if weight.dim() != 2:
+            raise ValueError(f"Linear weight must be 2-D, got rank {weight.dim()}")
+        n, k = weight.shape
+        packed, scales = quantize_nvfp4_bf16(weight.to(torch.bfloat16).contiguous(), 1.0)
+        return cls(packed, scales, 1.0, k, n, bias)
+
     def nvfp4_parts(self):
         """(packed weights, swizzled scales, weight_alpha) -- linear.rs:411-451."""
         return self.weight_u8, self.weight_scales, self.weight_alpha
@@ -250,6 +261,14 @@ class Bf16Linear:
         assert weight.dtype == torch.bfloat16 and weight.dim() == 2
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
+
+    def nvfp4_draft_twin_rows(self, row0: int, rows: int) -> "Nvfp4Linear":
+        """An NVFP4 copy of rows [row0, row0 + rows) of this weight, quantized on the device with the
+        global of those rows; this linear stays as it is (linear.rs:2277-2296)."""
+        if rows < 1 or row0 < 0 or row0 + rows > self.out_features:
+            raise ValueError(f"nvfp4 draft twin: rows [{row0}, {row0}+{rows}) out of range for out_features "
+                             f"{self.out_features}")
+        return Nvfp4Linear.from_bf16_quantized_nvfp4_dev(self.weight[row0:row0 + rows].contiguous())
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, self.in_features).contiguous()

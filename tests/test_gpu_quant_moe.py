@@ -507,3 +507,26 @@ def test_moe_block_matches_the_mixture_formula(n_tok):
         sh = mlp_w4a16([s[1] for s in shared], x[t:t + 1], sh_inter)
         want[t] += (1.0 / (1.0 + np.exp(-np.float64(sg_logit[t])))) * sh.astype(np.float64)
     assert U.rel_err_floor(got, want) < 2e-2
+
+
+def test_host_rule_constructor_and_draft_twin():
+    """from_bf16_quantized_nvfp4: global 1.0, alpha 1.0, bytes of the host quantizer
+    (rust/crates/nv-layers/src/linear.rs:2228-2275); a bf16 linear's draft twin is the device-quantized
+    NVFP4 copy of a row range, with that range's own global (linear.rs:2277-2296)."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(77)
+    n, k = 256, 512
+    w = U.gauss_bf16(rng, (n, k), 0.5)
+    wt = U.dev(w).view(torch.bfloat16)
+    lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4(wt)
+    packed, lw = ref.quantize_rows_bf16(w, 1.0)
+    assert lin.weight_alpha == 1.0
+    assert np.array_equal(lin.weight_u8.cpu().numpy(), packed)
+    assert np.array_equal(lin.weight_scales.cpu().numpy(), ref.swizzle_scales(lw))
+    twin = sp.Bf16Linear(wt).nvfp4_draft_twin_rows(128, 128)
+    p2, s2, a2 = ref.quantize_weight_bf16(w[128:256])
+    assert np.array_equal(twin.weight_u8.cpu().numpy(), p2) and np.array_equal(twin.weight_scales.cpu().numpy(), s2)
+    assert twin.weight_alpha == a2 and (twin.out_features, twin.in_features) == (128, k)
+    with pytest.raises(ValueError, match="out of range"):
+        sp.Bf16Linear(wt).nvfp4_draft_twin_rows(200, 128)

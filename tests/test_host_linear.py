@@ -80,3 +80,13 @@ def test_moe_block_constructor_refusals():
     blk = sp.MoeBlock(cfg, router(4), banks(4))
     with pytest.raises(ValueError, match="last dim 64 != hidden_size 128"):
         blk.forward(torch.zeros((1, 64), dtype=torch.bfloat16))
+
+
+def test_draft_twin_range_check_needs_no_device():
+    lin = sp.Bf16Linear(torch.zeros((256, 128), dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="out of range"):
+        lin.nvfp4_draft_twin_rows(200, 128)
+    with pytest.raises(ValueError, match="out of range"):
+        lin.nvfp4_draft_twin_rows(0, 0)
+    with pytest.raises(ValueError, match="2-D"):
+        sp.Nvfp4Linear.from_bf16_quantized_nvfp4(torch.zeros(4, dtype=torch.bfloat16))
