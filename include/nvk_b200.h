@@ -40,6 +40,15 @@ int nv_kernels_capability(int* sm_major, int* sm_minor);
 int nv_kernels_nvfp4_gemv_bf16act(void* stream, const uint8_t* W_packed, const uint8_t* W_scales,
                                   const uint16_t* x_bf16, uint16_t* y, float alpha, int N, int K);
 
+/* M = 1 with the activation row in NVFP4 as well (packed e2m1 + a FLAT [K/16] ue4m3 scale array, as
+ * nv_kernels_nvfp4_quantize_row_bf16 writes it): y = bf16(alpha * sum_kb ws*xs * dot16(w, x)).  The
+ * reference keeps this pair for tests and as the mirror of its WGSL kernel; its serving path does
+ * not call it.  Refuses K % 16 != 0 with -1, packed pointers not 8-byte aligned with -2.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:545-555
+ * (rust/crates/nv-kernels/cuda/gemv_nvfp4.cu:117-177,314-340) */
+int nv_kernels_nvfp4_gemv_bf16(void* stream, const uint8_t* W_packed, const uint8_t* W_scales, const uint8_t* x_packed,
+                               const uint8_t* x_scales, uint16_t* y, float alpha, int N, int K);
+
 /* M = 1, two weight matrices sharing one x (gate + up); wq_b == sc_b == y_b == NULL runs one arm.
  * Refuses K % 32 != 0, N <= 0, K <= 0 or a half-null second arm with -1.
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:584-597

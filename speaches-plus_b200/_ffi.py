@@ -18,6 +18,7 @@ _vp, _i, _f, _ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 SIGNATURES = {
     "nv_kernels_capability": [_vp, _vp],
     "nv_kernels_nvfp4_gemv_bf16act": [_vp, _vp, _vp, _vp, _vp, _f, _i, _i],
+    "nv_kernels_nvfp4_gemv_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i],
     "nv_kernels_gemv_nvfp4_w4a16_dual_m1": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i],
     "nv_kernels_gemv_nvfp4_w4a16_silu_gate_up_in_m1": [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i],
     "nv_kernels_gemm_nvfp4_w4a16_mk_dual": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],

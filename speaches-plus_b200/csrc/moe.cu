@@ -387,9 +387,58 @@ __global__ void __launch_bounds__(256) moe_grouped_fp4_gemv_kernel(
     if (lane == 0) d[d_idx] = nvk::f32_to_bf16_bits(acc * __ldg(&alphas[e]));
 }
 
+// ---- single M=1 GEMV with NVFP4 weights and an NVFP4 activation row ---------------------------
+// y[n] = bf16( alpha * sum_kb (ws[n,kb] * xs[kb]) * dot16(w, x) ): the grouped kernel's block dot for
+// one matrix; the activation's scales are a flat [K/16] array (the row quantizer's layout), the
+// weight's are swizzled.  One warp per output row.
+__global__ void __launch_bounds__(256) nvfp4_w4a4_gemv_kernel(const uint8_t* __restrict__ w_packed,
+                                                              const uint8_t* __restrict__ w_scales,
+                                                              const uint8_t* __restrict__ x_packed,
+                                                              const uint8_t* __restrict__ x_scales,
+                                                              uint16_t* __restrict__ y, float alpha, int n_dim,
+                                                              int k_dim) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (n >= n_dim) return;
+    const int half_k = k_dim >> 1, group_k = k_dim >> 4;
+    const uint2* w_row = reinterpret_cast<const uint2*>(w_packed + (size_t)n * half_k);
+    const uint2* x_row = reinterpret_cast<const uint2*>(x_packed);
+    float acc = 0.f;
+    for (int kb = lane; kb < group_k; kb += 32) {
+        const float ws = nvk::ue4m3_to_f32(w_scales[nvk::swz_offset(n, kb, group_k)]);
+        const float xs = nvk::ue4m3_to_f32(x_scales[kb]);
+        const uint2 wq = __ldg(&w_row[kb]);
+        const uint2 xq = __ldg(&x_row[kb]);
+        uint32_t wh[8], xh[8];
+        nvk::e2m1x8_to_f16x2x4(wq.x, wh[0], wh[1], wh[2], wh[3]);
+        nvk::e2m1x8_to_f16x2x4(wq.y, wh[4], wh[5], wh[6], wh[7]);
+        nvk::e2m1x8_to_f16x2x4(xq.x, xh[0], xh[1], xh[2], xh[3]);
+        nvk::e2m1x8_to_f16x2x4(xq.y, xh[4], xh[5], xh[6], xh[7]);
+        uint32_t s2 = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s2 = nvk::hfma2_u32(wh[i], xh[i], s2);
+        const float2 sf = __half22float2(*reinterpret_cast<__half2*>(&s2));
+        acc += (ws * xs) * (sf.x + sf.y);
+    }
+    acc = nvk::warp_sum(acc);
+    if (lane == 0) y[n] = nvk::f32_to_bf16_bits(acc * alpha);
+}
+
 }  // namespace
 
 extern "C" {
+
+int nv_kernels_nvfp4_gemv_bf16(void* stream, const uint8_t* W_packed, const uint8_t* W_scales, const uint8_t* x_packed,
+                               const uint8_t* x_scales, uint16_t* y, float alpha, int N, int K) {
+    if (N <= 0 || K <= 0) return 0;
+    if ((K & 15) != 0) return NVK_ERR_SHAPE;
+    if (nvk::any_null(W_packed, W_scales, x_packed, x_scales, y)) return NVK_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(W_packed) & 7) != 0 || (reinterpret_cast<uintptr_t>(x_packed) & 7) != 0)
+        return NVK_ERR_ARG;
+    nvfp4_w4a4_gemv_kernel<<<(unsigned)((N + 7) / 8), 256, 0, (cudaStream_t)stream>>>(W_packed, W_scales, x_packed,
+                                                                                       x_scales, y, alpha, N, K);
+    return (int)cudaGetLastError();
+}
 
 int nv_kernels_moe_route_topk(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
                               float* topk_weights, int n_tokens, int E, int K, int mode, float softcap,

@@ -69,3 +69,10 @@ def test_buffer_size_queries():
     assert lib.nvk_b200_tp_allreduce_buffer_bytes(9, 64) == 0 and lib.nvk_b200_tp_allreduce_buffer_bytes(2, 0) == 0
     assert lib.nvk_b200_linear_workspace_bytes(16, 4096) == 256 + 16 * 16 * 512
     assert lib.nvk_b200_linear_workspace_bytes(0, 4096) == 0
+
+
+def test_w4a4_single_gemv_refusals():
+    assert f("nv_kernels_nvfp4_gemv_bf16", S, P, P, P, P, P, 1.0, 0, 64) == 0
+    assert f("nv_kernels_nvfp4_gemv_bf16", S, P, P, P, P, P, 1.0, 8, 40) == -1
+    assert f("nv_kernels_nvfp4_gemv_bf16", S, P, P, 0, P, P, 1.0, 8, 64) == -2
+    assert f("nv_kernels_nvfp4_gemv_bf16", S, P + 4, P, P, P, P, 1.0, 8, 64) == -2

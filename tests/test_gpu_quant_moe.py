@@ -530,3 +530,35 @@ def test_host_rule_constructor_and_draft_twin():
     assert twin.weight_alpha == a2 and (twin.out_features, twin.in_features) == (128, k)
     with pytest.raises(ValueError, match="out of range"):
         sp.Bf16Linear(wt).nvfp4_draft_twin_rows(200, 128)
+
+
+@pytest.mark.parametrize("n,k", [(64, 256), (129, 1024), (512, 2048), (7, 48)])
+def test_w4a4_single_gemv_matches_the_oracle(n, k):
+    """nv_kernels_nvfp4_gemv_bf16 with an activation row quantized by nv_kernels_nvfp4_quantize_row_bf16
+    (flat scales): equals the W4A4 host oracle (rust/crates/nv-quant/src/nvfp4.rs:1086-1106) within 2 bf16
+    ulp -- the block dots are exact, only the order of the f32 block sum differs."""
+    U.require_gpu()
+    rng = np.random.default_rng(n * 7 + k)
+    w = U.gauss_bf16(rng, (n, k), 0.02)
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    x = U.gauss_bf16(rng, (1, k))
+    dx = U.dev(x)
+    xp = torch.zeros(k // 2, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(k // 16, dtype=torch.uint8, device="cuda")
+    assert U.ffi.call("nv_kernels_nvfp4_quantize_row_bf16", U.stream(), dx.data_ptr(), xp.data_ptr(), xs.data_ptr(),
+                      1.0, k) == 0
+    y = torch.full((n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    dw, ds = U.dev(packed), U.dev(sw)
+    assert U.ffi.call("nv_kernels_nvfp4_gemv_bf16", U.stream(), dw.data_ptr(), ds.data_ptr(), xp.data_ptr(),
+                      xs.data_ptr(), y.data_ptr(), alpha, n, k) == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[n:] == 0x7FC0)
+    ap, alin = ref.quantize_rows_bf16(x, 1.0)
+    assert np.array_equal(xp.cpu().numpy(), ap[0]) and np.array_equal(xs.cpu().numpy(), alin[0])
+    want = ref.matmul_w4a4(ap, alin, packed, ref.unswizzle_scales(sw, n, k // 16), 1, n, k, alpha)[0]
+    ulp = U.bf16_ulp_diff(out[:n], want)
+    absd = np.abs(ref.bf16_to_f32(out[:n]) - ref.bf16_to_f32(want))
+    assert np.all((ulp <= 2) | (absd <= 1e-3))
+    assert U.ffi.call("nv_kernels_nvfp4_gemv_bf16", U.stream(), dw.data_ptr(), ds.data_ptr(), xp.data_ptr(),
+                      xs.data_ptr(), y.data_ptr(), alpha, n, 40) == -1
