@@ -17,449 +17,9 @@
 // power-of-two pre-scale chosen from the slice's own maximum (bf16 has 8 significand bits, f16
 // has 11, so every value within 2^31 of the slice maximum converts exactly); the power of two is
 // undone in fp32 before alpha is applied.
-#include <cooperative_groups.h>
-
-#include "nvk_common.cuh"
-
-namespace cg = cooperative_groups;
+#include "w4a16_tile.cuh"
 
 namespace {
-constexpr int kRowsPerCta = 128;
-constexpr int kSuper = 256;  // K elements one warp consumes per iteration (4 scale k-tiles)
-
-struct GemmParams {
-    const uint8_t* wq[2];
-    const uint8_t* sc[2];
-    const uint16_t* x;    // [M, K] bf16, or gate when PRO == 1
-    const uint16_t* x2;   // up when PRO == 1
-    uint16_t* y[2];       // [M, N] bf16 per arm
-    float alpha[2];
-    int M, N, K;
-    int tiles_per_arm;  // ceil(N / 128)
-    int k_tiles;        // ceil(K / 64): scale tiles along K
-    int nsc;            // ceil(K / 256)
-    int spc;            // super-chunks per CTA (the CTA's K slice)
-    int ph;             // super-chunks staged per phase
-    int x_stride;       // bytes between token rows of the staged activations
-    int ring_off;       // byte offset of the weight ring in dynamic shared memory
-};
-
-__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-constexpr int kDepth = 4;           // cp.async groups in flight per thread
-constexpr int kSlotBytes = 2560;    // one warp, one iteration: 4 x 512 B of weights + 2 x 256 B of scales
-
-// 16-byte (weights) and 8-byte (scales) asynchronous global -> shared copies; src_bytes == 0 writes
-// zeros without touching global memory.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-
-// Two ue4m3 scale bytes (the low half of `w`, bit 7 of each byte already cleared) -> f16x2.
-// ue4m3 is the non-negative half of e4m3, so the hardware e4m3 convert is exact for 0x00..0x7E;
-// 0x7F (never produced by an NVFP4 encoder, NaN in e4m3) converts to NaN.
-__device__ __forceinline__ __half2 scales2_f16(uint32_t w) {
-    uint32_t d;
-    asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo;}" : "=r"(d) : "r"(w));
-    return *reinterpret_cast<__half2*>(&d);
-}
-
-// In place: eight bf16 gate values (as 4 words) -> bf16(SiLU(gate) * up), fp32 math, one rounding.
-__device__ __forceinline__ void silu_mul_bf16x8(uint32_t (&ws)[4], const uint4 u) {
-    const uint32_t us[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float g0 = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu), g1 = nvk::bf16_bits_to_f32(ws[i] >> 16);
-        const float u0 = nvk::bf16_bits_to_f32(us[i] & 0xFFFFu), u1 = nvk::bf16_bits_to_f32(us[i] >> 16);
-        const uint32_t a0 = nvk::f32_to_bf16_bits((g0 / (1.0f + expf(-g0))) * u0);
-        const uint32_t a1 = nvk::f32_to_bf16_bits((g1 / (1.0f + expf(-g1))) * u1);
-        ws[i] = a0 | (a1 << 16);
-    }
-}
-
-// A 128-row scale tile holds eight 16-row units u = 2*h + pair: rows 8h + g + 32*(2*pair + i),
-// g = 0..7, i = 0..1 -- the 16 rows of one m16n8k16 A tile whose scales are 8 contiguous bytes per
-// (g, k-tile).  One warp owns one unit; a CTA owns UG consecutive units and KW warps along K.
-// A warp iteration covers 256 K values ("super-chunk"): lane (g, tg) takes, for each of its two
-// rows, the two 16-byte pieces at K offsets 32*tg and 128 + 32*tg, so that one cp.async instruction
-// moves whole 64-byte runs per row.  NT: number of 8-token column tiles.
-// What one CTA works on: one arm's matrix, a set of token rows and where their outputs go.
-struct TileView {
-    const uint8_t* wq;
-    const uint8_t* sc;
-    const uint16_t* x;       // activation rows (gate when PRO == 1)
-    const uint16_t* x2;      // up rows when PRO == 1
-    const int32_t* xrows;    // optional gather: token m reads row xrows[xrow0 + m]; else row xrow0 + m
-    uint16_t* y;             // output row of token m is y + m * N
-    float alpha;
-    int xrow0;
-    int M;                   // tokens (<= 8 * NT)
-    int sub;                 // CTA index within the arm
-    bool pdl;                // signal/await the neighbouring kernels of the stream here
-    const uint8_t* ws;       // prepared activations (XWS only): 256-byte header of int pw[], then f16 stages
-};
-
-// XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
-// in a caller-supplied workspace; the CTA streams them through a shared ring next to the weights
-// instead of converting its whole K range itself.  Needs KW == 1 (all warps walk K together).
-template <int NT, int PRO, int UG, int KW, bool XWS = false>
-__device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& t) {
-    static_assert(!XWS || KW == 1, "the shared activation ring needs every warp on the same K step");
-    constexpr int THREADS = 32 * UG * KW;
-    constexpr int MT = 8 * NT;      // token columns
-    constexpr int ROWS = 16 * UG;   // weight rows per CTA
-    constexpr int SUB = 8 / UG;     // CTAs per 128-row scale tile
-    extern __shared__ __align__(16) uint8_t smem[];
-    __shared__ uint32_t s_amax[MT];   // slice maximum (bf16 magnitude bits), then f32 bits of 2^-pw
-    __shared__ int s_pw[MT];          // power of two currently folded into the accumulators
-    __shared__ float s_rescale[MT];   // 2^(pw_old - pw_new) at a phase boundary
-
-    cg::cluster_group cluster = cg::this_cluster();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int ul = warp % UG, kw = warp / UG;  // local unit, K-warp
-    const int gid = lane >> 2, tg = lane & 3;
-    const int sub = t.sub;
-    const int mt = sub / SUB;               // 128-row scale tile
-    const int u = (sub % SUB) * UG + ul;    // unit inside it
-    const int h = u >> 1, pair = u & 1;
-    const int crank = blockIdx.x;
-    const int nranks = gridDim.x;
-    const int M = t.M, N = p.N, K = p.K;
-
-    const uint8_t* __restrict__ wq = t.wq;
-    const uint8_t* __restrict__ sc = t.sc;
-    const int row0 = mt * kRowsPerCta + 64 * pair + 8 * h + gid;  // second row is 32 further
-    const size_t half_k = (size_t)(K >> 1);
-    const bool rv0 = row0 < N, rv1 = row0 + 32 < N;
-    const uint8_t* w_row0 = rv0 ? wq + (size_t)row0 * half_k + tg * 16 : wq;
-    const uint8_t* w_row1 = rv1 ? wq + (size_t)(row0 + 32) * half_k + tg * 16 : wq;
-    const uint8_t* sc_thread =
-        sc + (size_t)mt * p.k_tiles * 512 + (size_t)(8 * h + gid) * 16 + pair * 8 + (size_t)(tg >> 1) * 512;
-
-    // shared memory: [activations / reduction scratch | weight ring]
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)p.ring_off +
-                          (uint32_t)(warp * kDepth * kSlotBytes) + (uint32_t)lane * 16;
-    const uint8_t* ring_g = smem + p.ring_off + warp * kDepth * kSlotBytes + lane * 16;
-
-    const int sc_begin = crank * p.spc;
-    const int sc_end = min(p.nsc, sc_begin + p.spc);
-
-    float acc[NT][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-
-    // Enqueue the copies of super-chunk s into ring slot `slot` (a no-op past the end of the slice).
-    auto issue = [&](int s, int slot) {
-        if (s < sc_end) {
-            const uint32_t dst = ring + (uint32_t)(slot * kSlotBytes);
-            if (XWS) {
-                // this stage's activations: M rows of 512 bytes, row stride 576 in shared memory
-                const uint8_t* xsrc = t.ws + 256 + (size_t)s * M * 512;
-                const uint32_t xdst = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)(slot * M * 576);
-                for (int idx = threadIdx.x; idx < M * 32; idx += THREADS)
-                    cp_async16(xdst + (idx >> 5) * 576 + (idx & 31) * 16, xsrc + (size_t)idx * 16, 16);
-            }
-#pragma unroll
-            for (int pc = 0; pc < 2; ++pc) {
-                const int kk = s * kSuper + 128 * pc + 32 * tg;   // first K value of this piece
-                const int okk = kk < K ? 16 : 0;
-                const size_t off = (size_t)s * 128 + pc * 64;
-                cp_async16(dst + (0 * 2 + pc) * 512, w_row0 + off, rv0 ? okk : 0);
-                cp_async16(dst + (1 * 2 + pc) * 512, w_row1 + off, rv1 ? okk : 0);
-                cp_async8(dst - (uint32_t)lane * 8 + 2048 + pc * 256, sc_thread + (size_t)(4 * s + 2 * pc) * 512,
-                          okk ? 8 : 0);
-            }
-        }
-        cp_async_commit();
-    };
-
-    // B-fragment source rows: token 8n+gid, clamped to the last real token so that no load needs a
-    // predicate (columns past M compute a duplicate that is never written out).
-    uint32_t xs_tok[NT];
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-        xs_tok[n] = (uint32_t)(min(8 * n + gid, M - 1) * (XWS ? 576 : p.x_stride) + tg * 16);
-
-    auto compute = [&](int slot, int xbase) {
-        const uint8_t* src = ring_g + slot * kSlotBytes;
-        const uint8_t* xs = smem + xbase;
-        uint4 w[2][2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-#pragma unroll
-            for (int pc = 0; pc < 2; ++pc) w[i][pc] = *reinterpret_cast<const uint4*>(src + (i * 2 + pc) * 512);
-        __half2 sp[2][2];  // [row i][piece]: the two block scales this lane's 32 values use
-#pragma unroll
-        for (int pc = 0; pc < 2; ++pc) {
-            const uint2 sw = *reinterpret_cast<const uint2*>(src - lane * 8 + 2048 + pc * 256);
-            sp[0][pc] = scales2_f16((sw.x & 0x7F7F7F7Fu) >> (16 * (tg & 1)));
-            sp[1][pc] = scales2_f16((sw.y & 0x7F7F7F7Fu) >> (16 * (tg & 1)));
-        }
-#pragma unroll
-        for (int wi = 0; wi < 8; ++wi) {
-            uint32_t a[2][4];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const uint4& q = w[i][wi >> 2];
-                const uint32_t word = (wi & 3) == 0 ? q.x : (wi & 3) == 1 ? q.y : (wi & 3) == 2 ? q.z : q.w;
-                nvk::e2m1x8_to_f16x2x4(word, a[i][0], a[i][1], a[i][2], a[i][3]);
-                const __half2 pr = sp[i][wi >> 2];
-                const __half2 sc2 = (wi & 2) ? __high2half2(pr) : __low2half2(pr);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a[i][j]), sc2);
-                    a[i][j] = *reinterpret_cast<const uint32_t*>(&v);
-                }
-            }
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xs + xs_tok[n] + wi * 64);
-                mma_f16(acc[n], a[0][0], a[1][0], a[0][1], a[1][1], xv.x, xv.y);
-                mma_f16(acc[n], a[0][2], a[1][2], a[0][3], a[1][3], xv.z, xv.w);
-            }
-        }
-    };
-
-    // Programmatic dependent launch: let the next kernel in the stream start its own weight
-    // prefetch while this one runs, and prefetch our weights (which no earlier kernel writes) before
-    // waiting for the previous kernel, whose output may be our activations.
-    if (t.pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    int s_issue = sc_begin + kw, n_issued = 0, n_done = 0;
-    if (XWS) {
-        // The prepared activations come from the kernel just before this one.
-        if (t.pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-        if (threadIdx.x < MT) s_pw[threadIdx.x] = reinterpret_cast<const int*>(t.ws)[min((int)threadIdx.x, M - 1)];
-#pragma unroll
-        for (int d = 0; d < kDepth - 1; ++d) {
-            issue(s_issue, n_issued % kDepth);
-            s_issue += KW;
-            ++n_issued;
-        }
-        for (int s = sc_begin; s < sc_end; ++s) {
-            cp_async_wait<kDepth - 2>();  // this thread's copies for super-chunk s have landed
-            __syncthreads();              // ... and everyone's; all warps are done with step s - 1
-            issue(s_issue, n_issued % kDepth);  // refills the slot of step s - 1
-            s_issue += KW;
-            ++n_issued;
-            compute(n_done % kDepth, (n_done % kDepth) * M * 576);
-            ++n_done;
-        }
-        cp_async_wait<0>();
-    } else {
-#pragma unroll
-    for (int d = 0; d < kDepth - 1; ++d) {
-        issue(s_issue, n_issued % kDepth);
-        s_issue += KW;
-        ++n_issued;
-    }
-    if (t.pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
-
-    for (int p0 = sc_begin; p0 < sc_end; p0 += p.ph) {
-        const int pend = min(sc_end, p0 + p.ph);
-        const int nsp = pend - p0;
-
-        // ---- stage activations for super-chunks [p0, pend) ----
-        if (threadIdx.x < MT) s_amax[threadIdx.x] = 0u;
-        __syncthreads();  // also orders the previous phase's reads before this phase's writes
-        const int pieces_per_tok = nsp * 32;
-        const int total_pieces = M * pieces_per_tok;
-        // Each 16-byte piece (8 activations) is loaded once and kept in registers across the
-        // block-wide maximum when the phase is small enough (kXRegs pieces per thread); larger
-        // phases re-read the piece (an L1/L2 hit) for the conversion pass.
-        constexpr int kXRegs = 4;
-        const bool keep = total_pieces <= kXRegs * THREADS;
-        uint4 xr[kXRegs];
-        auto load_piece = [&](int idx, uint32_t (&ws)[4]) -> bool {
-            const int m = idx / pieces_per_tok;
-            const int rem = idx - m * pieces_per_tok;
-            const int k = (p0 + (rem >> 5)) * kSuper + (rem & 31) * 8;
-            if (k >= K) return false;
-            const size_t xr0 = (size_t)(t.xrows ? t.xrows[t.xrow0 + m] : t.xrow0 + m) * K + k;
-            const uint4 v = *reinterpret_cast<const uint4*>(t.x + xr0);
-            ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
-            if (PRO == 1) silu_mul_bf16x8(ws, *reinterpret_cast<const uint4*>(t.x2 + xr0));
-            return true;
-        };
-        auto store_piece = [&](int idx, const uint32_t (&ws)[4], bool valid) {
-            const int m = idx / pieces_per_tok;
-            const int rem = idx - m * pieces_per_tok;
-            const int scl = rem >> 5, q = rem & 31;
-            uint4 o = make_uint4(0u, 0u, 0u, 0u);
-            if (valid) {
-                const float sc2 = __uint_as_float(s_amax[m]);
-                uint32_t os[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float lo = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu) * sc2;
-                    const float hi = nvk::bf16_bits_to_f32(ws[i] >> 16) * sc2;
-                    const __half2 h2 = __floats2half2_rn(lo, hi);
-                    os[i] = *reinterpret_cast<const uint32_t*>(&h2);
-                }
-                o = make_uint4(os[0], os[1], os[2], os[3]);
-            }
-            // 8-value piece q of a super-chunk belongs to lane column tg' = (q % 16) / 4 and is that
-            // lane's fragment word wi = 4*(q / 16) + q % 4; pieces with equal wi are stored adjacently
-            // (conflict-free 128-bit fragment reads).
-            const int off = m * p.x_stride + scl * 512 + ((4 * (q >> 4) + (q & 3)) * 4 + ((q & 15) >> 2)) * 16;
-            *reinterpret_cast<uint4*>(smem + off) = o;
-        };
-#pragma unroll
-        for (int j = 0; j < kXRegs; ++j) xr[j] = make_uint4(0u, 0u, 0u, 0u);
-        {
-            int j = 0;
-            for (int idx = threadIdx.x; idx < total_pieces; idx += THREADS, ++j) {
-                uint32_t ws[4] = {0u, 0u, 0u, 0u};
-                const bool valid = load_piece(idx, ws);
-                uint32_t mx = 0u;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) mx = max(mx, max(ws[i] & 0x7FFFu, (ws[i] >> 16) & 0x7FFFu));
-                if (valid && mx) atomicMax(&s_amax[idx / pieces_per_tok], mx);
-                if (keep) {
-#pragma unroll
-                    for (int r = 0; r < kXRegs; ++r)
-                        if (r == j) xr[r] = make_uint4(ws[0], ws[1], ws[2], ws[3]);
-                }
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x < MT) {
-            // bf16 magnitude bits -> biased exponent; map the slice maximum into [2^14, 2^15).
-            const int e8 = (int)(s_amax[threadIdx.x] >> 7);
-            const int pw = max(e8 - 141, -100);  // x' = x * 2^-pw
-            const int diff = p0 > sc_begin ? min(max(s_pw[threadIdx.x] - pw, -126), 126) : 0;
-            s_rescale[threadIdx.x] = __uint_as_float((uint32_t)(127 + diff) << 23);
-            s_pw[threadIdx.x] = pw;
-            s_amax[threadIdx.x] = (uint32_t)(127 - pw) << 23;  // f32 bits of 2^-pw
-        }
-        __syncthreads();
-        if (p0 > sc_begin) {
-            // accumulators carry 2^-pw_old; move them to this phase's power of two (exact)
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                const float r0 = s_rescale[8 * n + 2 * tg], r1 = s_rescale[8 * n + 2 * tg + 1];
-                acc[n][0] *= r0; acc[n][1] *= r1; acc[n][2] *= r0; acc[n][3] *= r1;
-            }
-        }
-        {
-            int j = 0;
-            for (int idx = threadIdx.x; idx < total_pieces; idx += THREADS, ++j) {
-                uint32_t ws[4] = {0u, 0u, 0u, 0u};
-                bool valid;
-                if (keep) {
-                    uint4 v = xr[0];
-#pragma unroll
-                    for (int r = 1; r < kXRegs; ++r)
-                        if (r == j) v = xr[r];
-                    ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
-                    const int rem = idx % pieces_per_tok;
-                    valid = (p0 + (rem >> 5)) * kSuper + (rem & 31) * 8 < K;
-                } else {
-                    valid = load_piece(idx, ws);
-                }
-                store_piece(idx, ws, valid);
-            }
-        }
-        __syncthreads();
-        // ---- stream this phase's weights through the ring ----
-        for (int s = p0 + kw; s < pend; s += KW) {
-            issue(s_issue, n_issued % kDepth);
-            s_issue += KW;
-            ++n_issued;
-            cp_async_wait<kDepth - 1>();  // this thread's copies for super-chunk s have landed
-            compute(n_done % kDepth, (s - p0) * 512);
-            ++n_done;
-        }
-    }
-    cp_async_wait<0>();
-    if (sc_begin >= sc_end && threadIdx.x < MT) s_pw[threadIdx.x] = 0;  // empty slice: acc is zero
-    }  // !XWS
-
-    if (KW == 1 && nranks == 1) {
-        // One warp saw the whole of K for its rows: the accumulator fragment is the result.
-        const float alpha1 = t.alpha;
-        uint16_t* __restrict__ y1 = t.y;
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int m = 8 * n + 2 * tg + (j & 1);
-                const int r = row0 + 32 * (j >> 1);
-                if (m < M && r < N) {
-                    const float d = __uint_as_float((uint32_t)(127 + s_pw[m]) << 23);
-                    y1[(size_t)m * N + r] = nvk::f32_to_bf16_bits((acc[n][j] * d) * alpha1);
-                }
-            }
-        }
-        return;
-    }
-
-    // ---- sum the K-warps of this CTA: red[kw][token][row] ----
-    __syncthreads();
-    float* red = reinterpret_cast<float*>(smem);
-    constexpr int RS = ROWS + 4;  // padded row count per token column
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
-        // local row index = ul*16 + i*8 + gid with i = 0 (c0/c1) and 1 (c2/c3)
-        const int rl = ul * 16 + gid;
-        const int c = 8 * n + 2 * tg;
-        float* base = red + (size_t)kw * MT * RS;
-        // undo the activation power of two
-        const float d0 = __uint_as_float((uint32_t)(127 + s_pw[c]) << 23);
-        const float d1 = __uint_as_float((uint32_t)(127 + s_pw[c + 1]) << 23);
-        base[(c)*RS + rl] = acc[n][0] * d0;
-        base[(c + 1) * RS + rl] = acc[n][1] * d1;
-        base[(c)*RS + rl + 8] = acc[n][2] * d0;
-        base[(c + 1) * RS + rl + 8] = acc[n][3] * d1;
-    }
-    __syncthreads();
-    float* part = red + (size_t)KW * MT * RS;  // [token][row] partial of this CTA
-    for (int i = threadIdx.x; i < M * ROWS; i += THREADS) {
-        const int m = i / ROWS, rl = i % ROWS;
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < KW; ++w) v += red[((size_t)w * MT + m) * RS + rl];
-        part[m * RS + rl] = v;
-    }
-
-    // ---- sum the CTAs of the cluster through distributed shared memory, fixed order ----
-    if (nranks > 1) cluster.sync(); else __syncthreads();
-    const float alpha = t.alpha;
-    uint16_t* __restrict__ y = t.y;
-    const int rows_per_rank = ROWS / nranks;  // nranks in {1,2,4,8}
-    for (int i = threadIdx.x; i < M * rows_per_rank; i += THREADS) {
-        const int m = i / rows_per_rank;
-        const int rl = crank * rows_per_rank + (i - m * rows_per_rank);
-        float v = 0.f;
-        if (nranks > 1) {
-            for (int r = 0; r < nranks; ++r) {
-                const float* rp = cluster.map_shared_rank(part, r);
-                v += rp[m * RS + rl];
-            }
-        } else {
-            v = part[m * RS + rl];
-        }
-        // undo the local row numbering: rl = ul*16 + i*8 + g, unit = (sub % SUB)*UG + ul
-        const int uu = (sub % SUB) * UG + (rl >> 4);
-        const int n_out = mt * kRowsPerCta + 32 * (2 * (uu & 1) + ((rl >> 3) & 1)) + 8 * (uu >> 1) + (rl & 7);
-        if (n_out < N) y[(size_t)m * N + n_out] = nvk::f32_to_bf16_bits(v * alpha);
-    }
-    if (nranks > 1) cluster.sync();  // peers may still be reading this CTA's partial
-}
 
 template <int NT, bool DUAL, int PRO, int UG, int KW>
 __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
