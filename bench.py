@@ -298,6 +298,8 @@ def run_b200(args) -> dict:
         }
         if args.cpu_baseline:
             out["cpu_baseline"] = cpu_reference_leg(passes=15, warm=2)
+    if args.persistent and world == 1 and out is not None:
+        out["persistent_step"] = persistent_step_leg(dev, layers, xs, max(args.steps, 5))
     if args.extras:
         # free the sweep's weights before the larger workloads
         del graph
@@ -333,6 +335,48 @@ def run_b200(args) -> dict:
         if not clean:
             os._exit(0)  # every rank is past the final barrier; nothing of ours is mapped any more
     return None
+
+
+# ------------------------------------------------------------------------------------------------
+def persistent_step_leg(dev, layers, xs, replays: int) -> dict:
+    """The configs[1] M=1 sweep as one persistent launch: the same GEMVs, each made to wait for the one
+    before it (as consecutive linears of a decode step do), timed over graph replays."""
+    import torch
+
+    import speaches_plus_b200 as sp
+    step = sp.DecodeStep(1, dev)
+    dep, outs = -1, []
+    for k, n, per_copy in layers:
+        for lin in per_copy:
+            y = torch.empty((1, n), dtype=torch.bfloat16, device=dev)
+            outs.append(y)
+            dep = step.add(lin.local, xs[k], y, dep=dep)
+    step.build()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step.run()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step.run()
+        for _ in range(3):
+            graph.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1) / replays
+    step.check()
+    n_ops = sum(len(pc) for _, _, pc in layers)
+    nbytes = sum(algo_bytes(1, n, k) * len(pc) for k, n, pc in layers)
+    out = {"launches_per_step": 1, "operations": n_ops, "ms_per_step": round(ms, 4),
+           "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1), "us_per_gemv": round(ms * 1e3 / n_ops, 3),
+           "grid": step._launch[0], "smem_bytes": step._launch[1]}
+    del graph
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -688,6 +732,8 @@ def main():
     ap.add_argument("--profile-case", default=None, metavar="K,N,M",
                     help="run a few eager launches of one case and exit (for profiler captures)")
     ap.add_argument("--copies", type=int, default=4)
+    ap.add_argument("--persistent", action="store_true",
+                    help="also time the sweep as ONE persistent launch (DecodeStep); reported as 'persistent_step'")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case, args.copies)

@@ -297,6 +297,43 @@ int nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode(
  * 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster (default). */
 int nvk_b200_set_prefill_config(int cfg);
 
+/* No counterpart in the reference: a decode step's W4A16 linears (M <= 8 tokens) as ONE persistent
+ * cooperative launch.  The step is a list of operations; operation i may name one EARLIER operation
+ * `dep` whose outputs are its activations (x, and x2 for the SiLU(x) * x2 prologue), and is then held
+ * back until that operation has completed -- inside the kernel, with the weight prefetch of the
+ * waiting tiles already in flight.  An operation may overwrite a buffer only if every reader of the
+ * old contents is, directly or through the chain of `dep`s, one of its dependencies.  Every item
+ * computes exactly what nvk_b200_linear_nvfp4_w4a16 computes for the same rows with no split of K:
+ * with nvk_b200_set_tuning(1, rows_per_item) the stand-alone launches give the same bits.
+ *   nvk_b200_stack_plan_bytes(n_ops)   device bytes the plan needs (0 if n_ops is out of range)
+ *   nvk_b200_stack_build(...)          SET-UP call: validates, writes the plan to plan_dev (host->device
+ *                                      copy, synchronises) and returns launch_out[0] = CTAs,
+ *                                      launch_out[1] = dynamic shared memory bytes.  -1 shape (K % 32,
+ *                                      M > 8, half-null second arm), -2 argument / alignment / dep not
+ *                                      earlier, -3 too many operations (> 1024) or no resident CTA
+ *   nvk_b200_stack_run(...)            enqueue one step: clears the plan's counters on the stream and
+ *                                      launches; allocates nothing, never synchronises.  `err` is a
+ *                                      device int owned and zeroed by the caller, set to 1 if a wait
+ *                                      inside the kernel ran out (about a second). */
+typedef struct NvkStackOp {
+    const uint8_t* wq_a;   /* packed weights [N, K/2] and swizzled scales of the (first) matrix */
+    const uint8_t* sc_a;
+    const uint8_t* wq_b;   /* optional second matrix sharing x (gate + up); all three NULL for one arm */
+    const uint8_t* sc_b;
+    const uint16_t* x;     /* [M, K] bf16 */
+    const uint16_t* x2;    /* optional: the activation is bf16(SiLU(x) * x2) */
+    uint16_t* y_a;         /* [M, N] bf16 */
+    uint16_t* y_b;
+    float alpha_a, alpha_b;
+    int N, K;
+    int dep;               /* index of the earlier operation that writes x (and x2), or -1 */
+    int rows_per_item;     /* 0 = chosen from the shape; 128 or 16 */
+} NvkStackOp;
+size_t nvk_b200_stack_plan_bytes(int n_ops);
+int nvk_b200_stack_build(const NvkStackOp* ops, int n_ops, int M, void* plan_dev, size_t plan_dev_bytes,
+                         int* launch_out);
+int nvk_b200_stack_run(void* stream, void* plan_dev, int n_ops, int M, int grid, int smem_bytes, int* err);
+
 /* No counterpart in the reference (its grouped decode path quantizes activations to NVFP4 and gives
  * every (token, expert) pair its own 128-row tile): grouped-expert W4A16 linear with the tokens of
  * one expert sharing one pass over that expert's weights.

@@ -25,6 +25,9 @@ SIGNATURES = {
     "nvk_b200_linear_nvfp4_w4a16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
     "nvk_b200_linear_nvfp4_w4a16_ws": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i, _vp, C.c_size_t],
     "nvk_b200_linear_workspace_bytes": [_i, _i],
+    "nvk_b200_stack_plan_bytes": [_i],
+    "nvk_b200_stack_build": [_vp, _i, _i, _vp, C.c_size_t, _vp],
+    "nvk_b200_stack_run": [_vp, _vp, _i, _i, _i, _i, _vp],
     "nvk_b200_set_tuning": [_i, _i],
     "nvk_b200_set_pdl": [_i],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
@@ -68,6 +71,15 @@ PREFILL_SIGNATURES = {
     "nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode":
         [_vp] * 11 + [_i, _i, _i, _ll, _ll, _ll, _vp, C.c_size_t, _vp, C.c_size_t, _vp],
 }
+
+
+
+class NvkStackOp(C.Structure):
+    """One linear of a persistent decode step (include/nvk_b200.h: NvkStackOp)."""
+    _fields_ = [("wq_a", _vp), ("sc_a", _vp), ("wq_b", _vp), ("sc_b", _vp), ("x", _vp), ("x2", _vp), ("y_a", _vp),
+                ("y_b", _vp), ("alpha_a", _f), ("alpha_b", _f), ("N", _i), ("K", _i), ("dep", _i),
+                ("rows_per_item", _i)]
+
 
 _lib = None
 _prefill_lib = None

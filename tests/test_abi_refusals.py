@@ -76,3 +76,65 @@ def test_w4a4_single_gemv_refusals():
     assert f("nv_kernels_nvfp4_gemv_bf16", S, P, P, P, P, P, 1.0, 8, 40) == -1
     assert f("nv_kernels_nvfp4_gemv_bf16", S, P, P, 0, P, P, 1.0, 8, 64) == -2
     assert f("nv_kernels_nvfp4_gemv_bf16", S, P + 4, P, P, P, P, 1.0, 8, 64) == -2
+
+
+def _stack_op(**kw):
+    o = sp.ffi.NvkStackOp()
+    for k, v in dict(wq_a=P, sc_a=P, x=P, y_a=P, N=128, K=128, dep=-1).items():
+        setattr(o, k, v)
+    for k, v in kw.items():
+        setattr(o, k, v)
+    return o
+
+
+def _stack_build(ops, m=1, plan=P, nbytes=1 << 20):
+    import ctypes as C
+    arr = (sp.ffi.NvkStackOp * len(ops))(*ops)
+    out = (C.c_int * 2)()
+    return f("nvk_b200_stack_build", C.addressof(arr), len(ops), m, plan, nbytes, C.addressof(out))
+
+
+def test_persistent_step_refusals():
+    """nvk_b200_stack_build validates every operation before it touches the device."""
+    lib = sp.ffi.lib()
+    assert lib.nvk_b200_stack_plan_bytes(0) == 0 and lib.nvk_b200_stack_plan_bytes(1025) == 0
+    assert lib.nvk_b200_stack_plan_bytes(4) >= 4 * 88 + 2 * 16
+    assert _stack_build([_stack_op(K=48)]) == -1                  # K % 32
+    assert _stack_build([_stack_op()], m=9) == -1                 # more than 8 tokens
+    assert _stack_build([_stack_op(wq_b=P)]) == -1                # half-null second arm
+    assert _stack_build([_stack_op(dep=0)]) == -2                 # may only wait for an earlier operation
+    assert _stack_build([_stack_op(), _stack_op(dep=1)]) == -2
+    assert _stack_build([_stack_op(x=0)]) == -2                   # NULL operand
+    assert _stack_build([_stack_op(wq_a=P + 4)]) == -2            # alignment
+    assert _stack_build([_stack_op(rows_per_item=64)]) == -2
+    assert _stack_build([_stack_op()], nbytes=16) == -2           # plan buffer too small
+    assert _stack_build([_stack_op()], plan=0) == -2
+    assert f("nvk_b200_stack_run", S, 0, 1, 1, 148, 1024, P) == -2
+    assert f("nvk_b200_stack_run", S, P, 1, 9, 148, 1024, P) == -2
+    assert f("nvk_b200_stack_run", S, P, 1, 1, 0, 1024, P) == -2
+
+
+def test_decode_step_wrapper_checks():
+    import pytest
+    import torch
+    z = torch.zeros
+    lin = sp.Nvfp4Linear.new_nvfp4(z((128, 64), dtype=torch.uint8), z(128 * 8, dtype=torch.uint8), 1.0, 128, 128)
+    wide = sp.Nvfp4Linear.new_nvfp4(z((256, 64), dtype=torch.uint8), z(256 * 8, dtype=torch.uint8), 1.0, 128, 256)
+    x, y = z((1, 128), dtype=torch.bfloat16), z((1, 128), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="1..8"):
+        sp.DecodeStep(9, "cpu")
+    step = sp.DecodeStep(1, "cpu")
+    assert step.add(lin, x, y) == 0
+    with pytest.raises(ValueError, match="earlier operation"):
+        step.add(lin, x, y, dep=1)
+    with pytest.raises(ValueError, match="come together"):
+        step.add(lin, x, y, lin_b=lin)
+    with pytest.raises(ValueError, match="same shape"):
+        step.add(lin, x, y, lin_b=wide, y_b=z((1, 256), dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="contiguous bf16"):
+        step.add(lin, z((1, 128)), y)
+    with pytest.raises(ValueError, match="contiguous bf16"):
+        step.add(lin, z((2, 128), dtype=torch.bfloat16), y)
+    assert step.add(lin, y, x, x2=y, dep=0) == 1
+    with pytest.raises(RuntimeError, match="build"):
+        step.run()

@@ -403,3 +403,79 @@ def test_configs1_full_size_sweep(k, n, m):
         U.ffi.call("nvk_b200_set_tuning", 0, 0)
     # the default split changes only the order of the fp32 additions
     assert U.rel_err_floor(ref.bf16_to_f32(pinned), ref.bf16_to_f32(got).astype(np.float64)) < 1e-2
+
+
+@pytest.mark.parametrize("m", [1, 4, 8])
+@pytest.mark.parametrize("rows", [0, 16, 128])
+def test_persistent_step_equals_the_standalone_launches(m, rows):
+    """Two SwiGLU MLP layers (gate+up sharing x -> down with the SiLU(gate)*up prologue) as ONE persistent
+    launch: every output equals, bit for bit, the chain of stand-alone launches with the same rows per
+    CTA and no split of K; the wait flag stays clear; a second run and a replay from a CUDA graph give
+    the same bits."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    from speaches_plus_b200 import linear as L
+    rng = np.random.default_rng(900 + m)
+    hidden, inter = 512, 1536
+
+    def make(n, k):
+        packed, sw, alpha, _ = U.make_weight(rng, n, k, 0.05)
+        return sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+
+    layers = [(make(inter, hidden), make(inter, hidden), make(hidden, inter)) for _ in range(2)]
+    x0 = U.dev(U.gauss_bf16(rng, (m, hidden))).view(torch.bfloat16)
+    bf = dict(dtype=torch.bfloat16, device="cuda")
+
+    def buffers():
+        return [(torch.zeros((m, inter), **bf), torch.zeros((m, inter), **bf), torch.zeros((m, hidden), **bf))
+                for _ in layers]
+
+    # stand-alone launches; the persistent step picks 16-row items for these shapes unless told otherwise
+    tune_rows = 16 if rows == 0 else rows
+    want = buffers()
+    assert U.ffi.call("nvk_b200_set_tuning", 1, tune_rows) == 0
+    try:
+        x = x0
+        for (g, u, d), (yg, yu, yd) in zip(layers, want):
+            L.linear_w4a16(g, u, x, None, yg, yu, m)
+            L.linear_w4a16(d, None, yg, yu, yd, None, m)
+            x = yd
+        torch.cuda.synchronize()
+    finally:
+        U.ffi.call("nvk_b200_set_tuning", 0, 0)
+
+    got = buffers()
+    step = sp.DecodeStep(m, "cuda")
+    x, dep = x0, -1
+    for (g, u, d), (yg, yu, yd) in zip(layers, got):
+        gu = step.add(g, x, yg, lin_b=u, y_b=yu, dep=dep, rows_per_item=rows)
+        dep = step.add(d, yg, yd, x2=yu, dep=gu, rows_per_item=rows)
+        x = yd
+    step.build()
+
+    def same():
+        return all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for w, g_ in zip(want, got) for a, b in zip(w, g_))
+
+    for _ in range(2):
+        for t in got:
+            for b in t:
+                b.zero_()
+        step.run()
+        torch.cuda.synchronize()
+        step.check()
+        assert same()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        step.run()
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            step.run()
+        for t in got:
+            for b in t:
+                b.zero_()
+        graph.replay()
+        s.synchronize()
+    step.check()
+    assert same()
+    del graph
