@@ -90,3 +90,46 @@ def test_draft_twin_range_check_needs_no_device():
         lin.nvfp4_draft_twin_rows(0, 0)
     with pytest.raises(ValueError, match="2-D"):
         sp.Nvfp4Linear.from_bf16_quantized_nvfp4(torch.zeros(4, dtype=torch.bfloat16))
+
+
+def test_persistent_step_protocol_cannot_deadlock():
+    """A model of the persistent step's scheduling (csrc/w4a16_stack.cu): every CTA walks the
+    operations in order, claims items from a per-operation counter, and an item may only run once the
+    operation it depends on has counted all of its items.  Under any interleaving -- here random
+    ones, with far fewer CTAs than items -- every item runs exactly once and never before its
+    dependency is complete; a CTA blocked on a dependency is always waiting for items that other CTAs
+    hold and can finish."""
+    import random
+    for seed in range(50):
+        rnd = random.Random(seed)
+        n_ops = rnd.randint(1, 8)
+        items = [rnd.randint(1, 12) for _ in range(n_ops)]
+        deps = [rnd.randint(-1, o - 1) for o in range(n_ops)]
+        n_cta = rnd.randint(1, 5)
+        next_item, done = [0] * n_ops, [0] * n_ops
+        ran = [[0] * items[o] for o in range(n_ops)]
+        # per CTA: (operation, claimed item or None)
+        state = [[0, None] for _ in range(n_cta)]
+        steps = 0
+        while any(s[0] < n_ops for s in state):
+            steps += 1
+            assert steps < 100000, "no progress: deadlock"
+            live = [c for c in range(n_cta) if state[c][0] < n_ops]
+            c = rnd.choice(live)
+            o, item = state[c]
+            if item is None:                      # claim
+                item = next_item[o]
+                next_item[o] += 1
+                if item >= items[o]:
+                    state[c] = [o + 1, None]      # nothing left in this operation
+                else:
+                    state[c][1] = item
+                continue
+            if deps[o] >= 0 and done[deps[o]] < items[deps[o]]:
+                continue                          # still waiting (weights already in flight)
+            ran[o][item] += 1
+            if deps[o] >= 0:
+                assert done[deps[o]] == items[deps[o]]
+            done[o] += 1
+            state[c][1] = None
+        assert all(all(v == 1 for v in r) for r in ran) and done == items
