@@ -297,6 +297,13 @@ int nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode(
  * 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster (default). */
 int nvk_b200_set_prefill_config(int cfg);
 
+/* y[r, h] = x[r, h] * sigmoid(gate_logits[r]), fp32: the gate of the MoE block's shared expert
+ * (rust/crates/nv-layers/src/moe.rs:386-398).  y may alias x.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1424-1431
+ * (rust/crates/nv-kernels/cuda/capture_copy.cu:52-85) */
+int nv_kernels_mul_sigmoid_rowgate_f32(void* stream, const float* x, const float* gate_logits, float* y, int rows,
+                                       int hidden);
+
 /* No counterpart in the reference: a decode step's W4A16 linears (M <= 8 tokens) as ONE persistent
  * cooperative launch.  The step is a list of operations; operation i may name one EARLIER operation
  * `dep` whose outputs are its activations (x, and x2 for the SiLU(x) * x2 prologue), and is then held

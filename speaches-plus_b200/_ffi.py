@@ -46,6 +46,7 @@ SIGNATURES = {
     "nv_kernels_gather_f32_by_ids": [_vp, _vp, _vp, _vp, _i],
     "nv_kernels_moe_unpermute_scatter": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "nv_kernels_moe_unpermute_scatter_tail": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "nv_kernels_mul_sigmoid_rowgate_f32": [_vp, _vp, _vp, _vp, _i, _i],
     "nv_kernels_moe_permute": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nvk_b200_moe_grouped_w4a16": [_vp] * 13 + [_i, _i, _i],
     "nvk_b200_tp_allreduce_buffer_bytes": [_i, _i],

@@ -424,9 +424,31 @@ __global__ void __launch_bounds__(256) nvfp4_w4a4_gemv_kernel(const uint8_t* __r
     if (lane == 0) y[n] = nvk::f32_to_bf16_bits(acc * alpha);
 }
 
+// y[r, h] = x[r, h] * sigmoid(gate_logits[r]): the shared expert's gate (one logit per token).
+__global__ void __launch_bounds__(256) mul_sigmoid_rowgate_kernel(const float* __restrict__ x,
+                                                                  const float* __restrict__ gate_logits,
+                                                                  float* __restrict__ y, int rows, int hidden) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * hidden) return;
+    const float g = 1.f / (1.f + expf(-gate_logits[(int)(i / hidden)]));
+    y[i] = x[i] * g;
+}
+
 }  // namespace
 
 extern "C" {
+
+int nv_kernels_mul_sigmoid_rowgate_f32(void* stream, const float* x, const float* gate_logits, float* y, int rows,
+                                       int hidden) {
+    if (rows <= 0 || hidden <= 0) return 0;
+    if (nvk::any_null(x, gate_logits, y)) return NVK_ERR_ARG;
+    const long long total = (long long)rows * hidden;
+    const long long grid = (total + 255) / 256;
+    if (grid > 0x7FFFFFFFLL) return NVK_ERR_GRID_AXIS;
+    mul_sigmoid_rowgate_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(x, gate_logits, y, rows, hidden);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
 
 int nv_kernels_nvfp4_gemv_bf16(void* stream, const uint8_t* W_packed, const uint8_t* W_scales, const uint8_t* x_packed,
                                const uint8_t* x_scales, uint16_t* y, float alpha, int N, int K) {

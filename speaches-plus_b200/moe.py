@@ -314,8 +314,11 @@ class MoeBlock:
 
     def shared_contribution(self, x_flat: torch.Tensor) -> torch.Tensor:
         """sigmoid(gate logit) * shared_expert(x), f32 [n, hidden] (moe.rs:386-398)."""
-        out = self.shared_expert.forward(x_flat).float()
-        return torch.sigmoid(self.shared_expert_gate.forward(x_flat).float()) * out
+        out = self.shared_expert.forward(x_flat).float().contiguous()
+        gate_logits = self.shared_expert_gate.forward(x_flat).float().contiguous()   # [n, 1]
+        _ffi.check("nv_kernels_mul_sigmoid_rowgate_f32", _stream(), out.data_ptr(), gate_logits.data_ptr(),
+                   out.data_ptr(), out.shape[0], out.shape[1])
+        return out
 
     def forward(self, x: torch.Tensor, group=None) -> torch.Tensor:
         cfg = self.cfg

@@ -138,3 +138,8 @@ def test_decode_step_wrapper_checks():
     assert step.add(lin, y, x, x2=y, dep=0) == 1
     with pytest.raises(RuntimeError, match="build"):
         step.run()
+
+
+def test_rowgate_refusals():
+    assert f("nv_kernels_mul_sigmoid_rowgate_f32", S, P, P, P, 0, 64) == 0
+    assert f("nv_kernels_mul_sigmoid_rowgate_f32", S, P, 0, P, 2, 64) == -2

@@ -562,3 +562,23 @@ def test_w4a4_single_gemv_matches_the_oracle(n, k):
     assert np.all((ulp <= 2) | (absd <= 1e-3))
     assert U.ffi.call("nv_kernels_nvfp4_gemv_bf16", U.stream(), dw.data_ptr(), ds.data_ptr(), xp.data_ptr(),
                       xs.data_ptr(), y.data_ptr(), alpha, n, 40) == -1
+
+
+def test_sigmoid_rowgate():
+    U.require_gpu()
+    rng = np.random.default_rng(8)
+    rows, hidden = 5, 300
+    x = rng.standard_normal((rows, hidden)).astype(np.float32)
+    g = (rng.standard_normal(rows) * 3).astype(np.float32)
+    dx, dg = U.dev(x), U.dev(g)
+    y = torch.zeros((rows, hidden), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_mul_sigmoid_rowgate_f32", U.stream(), dx.data_ptr(), dg.data_ptr(), y.data_ptr(),
+                      rows, hidden) == 0
+    torch.cuda.synchronize()
+    want = x * (1.0 / (1.0 + np.exp(-g.astype(np.float64))))[:, None]
+    np.testing.assert_allclose(y.cpu().numpy(), want, rtol=2e-6, atol=1e-7)
+    # in place
+    assert U.ffi.call("nv_kernels_mul_sigmoid_rowgate_f32", U.stream(), dx.data_ptr(), dg.data_ptr(), dx.data_ptr(),
+                      rows, hidden) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dx, y)
