@@ -313,3 +313,24 @@ def test_host_dequantize_equals_the_oracle_and_serves_dequant_weight():
     assert np.array_equal(got.view(torch.int16).numpy().view(np.uint16), want)
     with pytest.raises(W.WeightError, match="too few bytes"):
         W.dequantize_packed_to_bf16_bits(packed[:10], lin, n, k, alpha)
+
+
+def test_interoperates_with_the_safetensors_library(tmp_path):
+    """Files written by the `safetensors` package load here, and files written by this test's
+    minimal writer load there (skipped when the package is not installed)."""
+    st = pytest.importorskip("safetensors.numpy")
+    rng = np.random.default_rng(14)
+    a = rng.standard_normal((3, 5)).astype(np.float32)
+    b = rng.integers(0, 255, (4, 8), dtype=np.uint8)
+    c = np.array([7, -9], np.int64)
+    path = tmp_path / "lib.safetensors"
+    st.save_file({"a": a, "b": b, "c": c}, str(path), metadata={"format": "np"})
+    wl = W.WeightLoader.open_file(path)
+    assert wl.names() == ["a", "b", "c"]
+    assert np.array_equal(wl.get("a").numpy(), a) and wl.shape_of("b") == [4, 8]
+    assert np.array_equal(np.asarray(wl.raw_bytes("b")).reshape(4, 8), b)
+    assert wl.get("c").tolist() == [7, -9]
+    mine = write_safetensors(tmp_path / "mine.safetensors", {"a": ("F32", a.shape, a.tobytes()),
+                                                             "b": ("U8", b.shape, b.tobytes())})
+    back = st.load_file(str(mine))
+    assert np.array_equal(back["a"], a) and np.array_equal(back["b"], b)
