@@ -10,6 +10,8 @@ goes to the current stream, nothing synchronises: the step can be captured in a 
 """
 from __future__ import annotations
 
+import dataclasses
+
 import torch
 
 from . import _ffi
@@ -267,9 +269,6 @@ def forward_grouped(w: MoeGroupedWeights, x: torch.Tensor, topk_ids, topk_weight
 
 # ------------------------------------------------------------------------------------------------
 # the MoE block around the expert dispatch
-import dataclasses  # noqa: E402
-
-
 @dataclasses.dataclass(frozen=True)
 class MoeConfig:
     """rust/crates/nv-layers/src/moe.rs:12-19."""
