@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr unsigned kGateSpinLimit = 4000000u;   // about a second of polling
+constexpr unsigned kGateSpinLimit = 1000000u;   // roughly a second of polling
 constexpr int kStackThreads = 256;
 constexpr int kMaxOps = 1024;
 
