@@ -168,7 +168,8 @@ def shutdown_process_group(join_s: float = 30.0) -> bool:
     group.  Returns False if the destroy call did not come back within `join_s` seconds (every rank
     is past the barrier by then, so the caller may simply exit)."""
     import threading
-    torch.cuda.synchronize()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
     dist.barrier()
     done = threading.Event()
 

@@ -56,7 +56,7 @@ def _worker(rank, world, port, n, k, m, q):
         if rank == 0:
             q.put((res, want))
     finally:
-        dist.destroy_process_group()
+        assert tp.shutdown_process_group(join_s=60.0)   # the package's own orderly teardown
 
 
 def _free_port():
