@@ -297,6 +297,13 @@ int nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode(
  * 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster (default). */
 int nvk_b200_set_prefill_config(int cfg);
 
+/* RMSNorm over bf16 rows, y = bf16(x * rsqrt(mean(x^2) + eps) * weight): the launch the reference's
+ * M = 1 GEMV route puts in front of nv_kernels_nvfp4_gemv_bf16act when a norm precedes the linear
+ * (rust/crates/nv-layers/src/linear.rs:1475-1510).  y may alias x.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:23-31 (rust/crates/nv-kernels/cuda/rmsnorm.cu:46-120) */
+int nv_kernels_rmsnorm_bf16(void* stream, const uint16_t* x, const uint16_t* weight, uint16_t* y, size_t batch,
+                            size_t hidden, float eps);
+
 /* y[r, h] = x[r, h] * sigmoid(gate_logits[r]), fp32: the gate of the MoE block's shared expert
  * (rust/crates/nv-layers/src/moe.rs:386-398).  y may alias x.
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:1424-1431

@@ -38,6 +38,7 @@ SIGNATURES = {
     "nv_kernels_quantize_nvfp4_bf16_per_expert_strided": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert_strided": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "nv_kernels_rmsnorm_bf16": [_vp, _vp, _vp, _vp, C.c_size_t, C.c_size_t, _f],
     "nv_kernels_rmsnorm_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i],
     "nv_kernels_moe_route_topk": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _f],
     "nv_kernels_moe_route_topk_shared_tail": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _f, _i],

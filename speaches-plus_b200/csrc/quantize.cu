@@ -136,6 +136,30 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const QuantParams
     }
 }
 
+// Plain RMSNorm over bf16 rows: y = bf16(x * rsqrt(mean(x^2) + eps) * w), fp32 arithmetic, one
+// rounding -- the statement the fused quantizer above applies before it quantizes.  One CTA per row.
+__global__ void __launch_bounds__(256) rmsnorm_bf16_kernel(const uint16_t* __restrict__ x,
+                                                           const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
+                                                           size_t hidden, float eps) {
+    __shared__ float red[8];
+    const uint16_t* xr = x + (size_t)blockIdx.x * hidden;
+    uint16_t* yr = y + (size_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (size_t i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float f = nvk::bf16_bits_to_f32(xr[i]);
+        ss += f * f;
+    }
+    ss = nvk::warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float rstd = rsqrtf(tot / (float)hidden + eps);
+    for (size_t i = threadIdx.x; i < hidden; i += blockDim.x)
+        yr[i] = nvk::f32_to_bf16_bits(nvk::bf16_bits_to_f32(xr[i]) * rstd * nvk::bf16_bits_to_f32(w[i]));
+}
+
 template <int SRC>
 int launch_blocks(cudaStream_t s, const QuantParams& p) {
     const long long total = (long long)p.rows * (p.K >> 4);
@@ -234,6 +258,16 @@ int nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert_strided(void* stream, con
                                                                int m_total, int K) {
     return per_expert(stream, y_gate_bf16, y_up_bf16, packed_out, scales_out_swizzled, stored_globals,
                       m_per_expert, m_total, K, true, true);
+}
+
+int nv_kernels_rmsnorm_bf16(void* stream, const uint16_t* x, const uint16_t* weight, uint16_t* y, size_t batch,
+                            size_t hidden, float eps) {
+    if (batch == 0 || hidden == 0) return 0;
+    if (nvk::any_null(x, weight, y)) return NVK_ERR_ARG;
+    if (batch > 0x7FFFFFFFull) return NVK_ERR_GRID_AXIS;
+    rmsnorm_bf16_kernel<<<(unsigned)batch, 256, 0, (cudaStream_t)stream>>>(x, weight, y, hidden, eps);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16, const uint16_t* weight_bf16,

@@ -227,6 +227,27 @@ class Nvfp4Linear:
         self._fp4_gemm(a_packed, a_scales, y, m)
         return y.reshape(*lead, self.out_features)
 
+    def forward_prenorm_decode(self, x_pre: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """Decode-sized rows with an RMSNorm in front, on the route that keeps activations in bf16
+        (linear.rs:1444-1542 with a pre-norm): one RMSNorm launch into a bf16 buffer, then the W4A16
+        linear.  x_pre [..., in] bf16 with at most 64 rows."""
+        if x_pre.shape[-1] != self.in_features:
+            raise ValueError(f"forward_prenorm_decode: input last dim {x_pre.shape[-1]} != in_features "
+                             f"{self.in_features}")
+        lead = x_pre.shape[:-1]
+        x2 = x_pre.reshape(-1, self.in_features).contiguous()
+        if x2.shape[0] > MAX_DECODE_M:
+            raise ValueError(f"forward_prenorm_decode: {x2.shape[0]} rows; the decode route takes up to {MAX_DECODE_M}")
+        assert x2.is_cuda and x2.dtype == torch.bfloat16 and norm_weight.dtype == torch.bfloat16
+        xn = torch.empty_like(x2)
+        _ffi.check("nv_kernels_rmsnorm_bf16", _stream(), x2.data_ptr(), norm_weight.data_ptr(), xn.data_ptr(),
+                   x2.shape[0], self.in_features, float(eps))
+        y = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x2.device)
+        self.forward_into(xn, y)
+        if self.bias is not None:
+            y += self.bias
+        return y.reshape(*lead, self.out_features)
+
     def forward_prefill_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
         """Prefill-sized M: the reference's default route (rust/crates/nv-layers/src/linear.rs:1590-1795) --
         quantize the activations to NVFP4 (global 1.0, rows padded to a multiple of 128 with zeros), then one

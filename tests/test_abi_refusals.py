@@ -143,3 +143,8 @@ def test_decode_step_wrapper_checks():
 def test_rowgate_refusals():
     assert f("nv_kernels_mul_sigmoid_rowgate_f32", S, P, P, P, 0, 64) == 0
     assert f("nv_kernels_mul_sigmoid_rowgate_f32", S, P, 0, P, 2, 64) == -2
+
+
+def test_rmsnorm_refusals():
+    assert f("nv_kernels_rmsnorm_bf16", S, P, P, P, 0, 64, 1e-6) == 0
+    assert f("nv_kernels_rmsnorm_bf16", S, P, 0, P, 2, 64, 1e-6) == -2

@@ -582,3 +582,32 @@ def test_sigmoid_rowgate():
                       rows, hidden) == 0
     torch.cuda.synchronize()
     assert torch.equal(dx, y)
+
+
+def test_rmsnorm_bf16_and_the_prenorm_decode_route():
+    """nv_kernels_rmsnorm_bf16 == bf16((x * rstd) * w) up to the device's rsqrt / sum order (at most one
+    bf16 ulp on a few elements); Nvfp4Linear.forward_prenorm_decode == the linear applied to that."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(61)
+    m, k, n, eps = 3, 1024, 256, 1e-6
+    x = U.gauss_bf16(rng, (m, k), 1.5)
+    nw = U.gauss_bf16(rng, (k,), 1.0)
+    dx, dw = U.dev(x), U.dev(nw)
+    y = torch.zeros((m, k), dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_rmsnorm_bf16", U.stream(), dx.data_ptr(), dw.data_ptr(), y.data_ptr(), m, k, eps) == 0
+    torch.cuda.synchronize()
+    xf, wf = ref.bf16_to_f32(x), ref.bf16_to_f32(nw)
+    rstd = (1.0 / np.sqrt((xf.astype(np.float64) ** 2).mean(1) + eps)).astype(np.float32)
+    normed = ref.f32_to_bf16((xf * rstd[:, None]) * wf[None, :])
+    got = U.host_u16(y)
+    assert U.bf16_ulp_diff(got, normed).max() <= 1 and (got == normed).mean() > 0.99
+    w = U.gauss_bf16(rng, (n, k), 0.02)
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    lin = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+    out = lin.forward_prenorm_decode(dx.view(torch.bfloat16), dw.view(torch.bfloat16), eps)
+    direct = lin.forward(y.view(torch.bfloat16))
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), direct.view(torch.int16))
+    want = ref.linear_w4a16_f64(packed, sw, got, alpha, n, k)
+    assert U.rel_err_floor(out.float().cpu().numpy(), want) < 1e-4 + 1e-2
