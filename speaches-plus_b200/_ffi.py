@@ -114,13 +114,45 @@ def lib() -> C.CDLL:
     return _lib
 
 
+class MultiGpuRefused(RuntimeError):
+    """The prefill library was asked for in a process that is one rank of several."""
+
+
+def distributed_world() -> int:
+    """Ranks this process is one of: the size of torch.distributed's default group once it exists,
+    else what the launcher's WORLD_SIZE says, else 1."""
+    import os
+    import sys
+    td = sys.modules.get("torch.distributed")
+    if td is not None and td.is_available() and td.is_initialized():
+        return int(td.get_world_size())
+    try:
+        return max(1, int(os.environ.get("WORLD_SIZE", "1")))
+    except ValueError:
+        return 1
+
+
+def _refuse_prefill_on_several_gpus(what: str) -> None:
+    """libnvk_b200_prefill.so holds a 2-SM tile whose TMA operand loads use cluster multicast.  Its
+    tensor maps are built over this GPU's own memory only, and it stays that way because no process
+    that is one rank of a multi-GPU job may load or call the library at all: tensor- and
+    expert-parallel code keeps M > 64 on the decode-sized kernels of libnvk_b200.so."""
+    world = distributed_world()
+    if world > 1:
+        raise MultiGpuRefused(
+            f"{what}: libnvk_b200_prefill.so is for single-GPU processes only (this process is one of "
+            f"{world} ranks); multi-GPU code runs rows in chunks of 64 on libnvk_b200.so instead")
+
+
 def prefill_available() -> bool:
-    return PREFILL_LIB_PATH.exists()
+    return PREFILL_LIB_PATH.exists() and distributed_world() == 1
 
 
 def prefill_lib() -> C.CDLL:
-    """Load the prefill-GEMM library.  A missing build is an error, not a fallback."""
+    """Load the prefill-GEMM library.  A missing build is an error, not a fallback; so is asking for
+    it from one rank of a multi-GPU job."""
     global _prefill_lib
+    _refuse_prefill_on_several_gpus("prefill_lib()")
     if _prefill_lib is None:
         if not PREFILL_LIB_PATH.exists():
             raise RuntimeError(
@@ -138,6 +170,7 @@ def prefill_lib() -> C.CDLL:
 def call(name: str, *args) -> int:
     """Call a launcher and return its raw status."""
     if name in PREFILL_SIGNATURES:
+        _refuse_prefill_on_several_gpus(name)
         return int(getattr(prefill_lib(), name)(*args))
     return int(getattr(lib(), name)(*args))
 

@@ -5,9 +5,13 @@
 //
 // The contraction is the CUTLASS sm100 block-scaled collective (tcgen05.mma kind::mxf4nvf4 with the
 // scale factors in tensor memory, TMA operand loads, accumulators in TMEM), instantiated here for a
-// 2-SM 256x128x256 tile (cluster 2x1x1) and a 1-SM 128x128x256 tile (no cluster).  All operands are
-// local memory; under tensor parallelism each rank runs it on its own shard.  This file is the whole integration: problem setup, workspace protocol and the
-// reference's entry points for this route.
+// 1-SM 128x128x256 tile (no cluster; the default) and a 2-SM 256x128x256 tile (cluster 2x1x1).  The
+// 2-SM collective loads its operands with TMA cluster multicast, and its tensor maps are built over
+// the pointers the caller passes: they must be this GPU's own memory.  The library is therefore for
+// single-GPU processes only -- the host binding refuses to load or call it from one rank of a
+// multi-GPU job, where rows beyond 64 run in chunks on the decode-sized kernels instead.  This file
+// is the whole integration: problem setup, workspace protocol and the reference's entry points for
+// this route.
 //
 // Built only when CUTLASS headers are found (NVK_HAVE_CUTLASS); otherwise the entry points refuse
 // with -1 ("route unavailable"), as the reference's GPU-less stubs do.
@@ -58,13 +62,15 @@ struct GemmConfig {
     using SfConfig = typename GemmKernel::CollectiveMainloop::Sm1xxBlkScaledConfig;
 };
 
-// 1-SM tile, no cluster.
+// 1-SM tile, no cluster, no multicast: the default.
 using Cfg1 = GemmConfig<Shape<_128, _128, _256>, Shape<_1, _1, _1>>;
-// 2-SM tile (cta_group::2 pair sharing one 256x128 accumulator tile), cluster 2x1x1: the default
-// (13 % faster at M=2048).  Every operand is this GPU's own memory in both configurations.
+// 2-SM tile (cta_group::2 pair sharing one 256x128 accumulator tile), cluster 2x1x1, operands loaded
+// with cluster multicast: opt-in through nvk_b200_set_prefill_config(2), single-GPU processes only,
+// every operand this GPU's own memory.
 using Cfg2 = GemmConfig<Shape<_256, _128, _256>, Shape<_2, _1, _1>>;
 
-int g_prefill_cfg = 2;
+// The tile choice is per calling thread (the entry points may be called from any thread).
+thread_local int g_prefill_cfg = 1;
 
 template <class Cfg>
 typename Cfg::Gemm::Arguments make_args(const void* a, const void* a_sf, const void* b, const void* b_sf,
@@ -136,7 +142,7 @@ int run_gemm(cudaStream_t stream, const void* a, const void* a_sf, const void* b
 
 }  // namespace
 #else   // !NVK_HAVE_CUTLASS
-namespace { int g_prefill_cfg = 2; }
+namespace { thread_local int g_prefill_cfg = 1; }
 namespace {
 int run_gemm(cudaStream_t, const void*, const void*, const void*, const void*, const float*, void*, int, int, int,
              void*, size_t, size_t* required_workspace) {
@@ -148,7 +154,9 @@ int run_gemm(cudaStream_t, const void*, const void*, const void*, const void*, c
 
 extern "C" {
 
-// Tuning hook (no counterpart in the reference): 1 = 1-SM 128x128x256 tile, 2 = 2-SM 256x128x256 tile.
+// Tuning hook (no counterpart in the reference): 1 = 1-SM 128x128x256 tile (default), 2 = 2-SM
+// 256x128x256 tile with cluster-multicast operand loads (single-GPU processes, local operands only).
+// Applies to later calls made by the calling thread.
 int nvk_b200_set_prefill_config(int cfg) {
     if (cfg != 1 && cfg != 2) return NVK_ERR_ARG;
     g_prefill_cfg = cfg;

@@ -183,22 +183,38 @@ class Nvfp4Linear:
 
     __call__ = forward
 
-    def forward_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
-        """x2 [M, in] bf16 contiguous -> y [M, out]; rows are independent, so M > 64 runs as row
-        chunks (results are bit-identical under any row chunking)."""
+    def forward_into(self, x2: torch.Tensor, y: torch.Tensor, allow_prefill: bool = True) -> None:
+        """x2 [M, in] bf16 contiguous -> y [M, out].  M <= 64 is one launch of the W4A16 kernel.  Larger
+        M takes the FP4 x FP4 tensor-core GEMM of the prefill library -- in a single-GPU process only:
+        with `allow_prefill=False`, or when this process is one rank of several, the rows run as chunks
+        of 64 on the W4A16 kernel instead (rows are independent there, so the result does not depend on
+        the chunking), and the prefill library is never touched."""
         assert x2.is_cuda and x2.dtype == torch.bfloat16 and x2.is_contiguous() and y.is_contiguous()
         m = x2.shape[0]
         s = _stream()
-        if m == 1:
+        route = self.route_for(m, allow_prefill)
+        if route == "gemv":
             _ffi.check("nv_kernels_nvfp4_gemv_bf16act", s, self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
                        x2.data_ptr(), y.data_ptr(), self.alpha_w4a16, self.out_features, self.in_features)
             return
-        if m > MAX_DECODE_M and self.out_features % 8 == 0 and self.in_features % 32 == 0:
+        if route == "prefill":
             self.forward_prefill_into(x2, y)
             return
         for r0 in range(0, m, MAX_DECODE_M):
             mm = min(MAX_DECODE_M, m - r0)
             linear_w4a16(self, None, x2[r0:], None, y[r0:], None, mm)
+
+    def route_for(self, m: int, allow_prefill: bool = True) -> str:
+        """Which kernels M rows take: "gemv" (M = 1), "decode" (row chunks of up to 64 on the W4A16
+        kernel) or "prefill" (the FP4 x FP4 GEMM of the prefill library).  The last is chosen only in
+        a single-GPU process: the prefill library holds a tile that loads with TMA cluster multicast
+        and is never used from one rank of several."""
+        if m == 1:
+            return "gemv"
+        if (m > MAX_DECODE_M and allow_prefill and _ffi.distributed_world() == 1
+                and self.out_features % 8 == 0 and self.in_features % 32 == 0):
+            return "prefill"
+        return "decode"
 
     def prenorm_nvfp4_eligible(self) -> bool:
         """linear.rs:648-651: an NVFP4 projection without bias (and without an adapter)."""

@@ -246,9 +246,10 @@ class TpNvfp4Linear:
             y = self._buf("y", (m, self.n), x.device)
             self.local.forward_into(x, y)
             return y
+        # Sharded: the prefill library (cluster-multicast tile) is off limits, whatever M is.
         if self.mode == "column":
             yl = self._buf("yl", (m, self.local.out_features), x.device)
-            self.local.forward_into(x, yl)
+            self.local.forward_into(x, yl, allow_prefill=False)
             if not gather:
                 return yl
             nl = self.local.out_features
@@ -261,7 +262,7 @@ class TpNvfp4Linear:
         if m > 1:
             xs = xs.contiguous()
         y = self._buf("yr", (m, self.n), x.device)
-        self.local.forward_into(xs, y)
+        self.local.forward_into(xs, y, allow_prefill=False)
         if self.peer_ar is not None and y.numel() % 8 == 0 and y.numel() <= self.peer_ar.max_elems:
             self.peer_ar.all_reduce_(y)
         else:

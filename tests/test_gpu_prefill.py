@@ -46,7 +46,7 @@ def quantized_operand(rng, rows, k, std, global_=None):
 def tile_config(request):
     assert U.ffi.call("nvk_b200_set_prefill_config", request.param) == 0
     yield request.param
-    U.ffi.call("nvk_b200_set_prefill_config", 2)
+    U.ffi.call("nvk_b200_set_prefill_config", 1)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (130, 264, 1056), (2048, 512, 768)])

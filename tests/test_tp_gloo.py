@@ -20,7 +20,8 @@ class OracleLocal:
         self.p, self.s, self.alpha = packed.numpy(), scales.numpy(), alpha
         self.in_features, self.out_features = k, n
 
-    def forward_into(self, x, y):
+    def forward_into(self, x, y, allow_prefill=True):
+        assert not allow_prefill or dist.get_world_size() == 1   # sharded linears never ask for the prefill library
         xb = x.contiguous().view(torch.int16).numpy().view(np.uint16)
         out = ref.linear_w4a16_f64(self.p, self.s, xb, self.alpha, self.out_features, self.in_features)
         y.copy_(torch.from_numpy(ref.f32_to_bf16(out.astype(np.float32)).view(np.int16)).view(torch.bfloat16))
@@ -298,3 +299,74 @@ def test_a_rank_that_leaves_between_steps_surfaces_as_an_error_not_a_hang():
         p.join(timeout=60)
     assert kind != "no error", "the collective completed although the peer had left"
     assert seconds < 30, f"took {seconds:.1f} s to notice"
+
+
+def _prefill_refusal_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import speaches_plus_b200 as sp
+        from speaches_plus_b200 import tp
+        ffi = sp.ffi
+        seen = {"world": ffi.distributed_world(), "available": ffi.prefill_available()}
+        for what, fn in (("load", ffi.prefill_lib),
+                         ("config2", lambda: ffi.call("nvk_b200_set_prefill_config", 2)),
+                         ("gemm", lambda: ffi.call("nv_kernels_cutlass_fp4_gemm_sm120_bf16", *([None] * 13)))):
+            try:
+                fn()
+                seen[what] = "ran"
+            except ffi.MultiGpuRefused:
+                seen[what] = "refused"
+        # a linear whose shapes would qualify for the tensor-core GEMM: 65 rows still stay on the decode kernels
+        n, k = 256, 256
+        lin = sp.Nvfp4Linear(torch.zeros(n * k // 2, dtype=torch.uint8), torch.zeros(n * k // 16, dtype=torch.uint8),
+                             1.0, k, n)
+        seen["route65"] = lin.route_for(65)
+        seen["route2048"] = lin.route_for(2048)
+
+        calls = []
+
+        class Recorder(OracleLocal):
+            def forward_into(self, x, y, allow_prefill=True):
+                calls.append(allow_prefill)
+                y.zero_()
+
+        z = torch.zeros
+        for mode in ("column", "row"):
+            nl, kl = (n // world, k) if mode == "column" else (n, k // world)
+            t = tp.TpNvfp4Linear(Recorder(z(1, dtype=torch.uint8), z(1, dtype=torch.uint8), 1.0, kl, nl), mode, rank,
+                                 world, n, k, 0)
+            t.forward(torch.zeros((65, k), dtype=torch.bfloat16))
+        seen["tp_allow_prefill"] = calls
+        if rank == 0:
+            q.put(seen)
+    finally:
+        assert tp.shutdown_process_group(join_s=60.0)
+
+
+def test_prefill_library_is_unreachable_from_a_rank_of_several():
+    """The prefill library's 2-SM tile loads with TMA cluster multicast; no multi-GPU process may load
+    it, select that tile, call its GEMM, or be routed to it by a linear, whatever M is."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_prefill_refusal_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    seen = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert seen == {"world": 2, "available": False, "load": "refused", "config2": "refused", "gemm": "refused",
+                    "route65": "decode", "route2048": "decode", "tp_allow_prefill": [False, False]}
+
+
+def test_single_process_still_routes_large_m_to_the_prefill_gemm():
+    import speaches_plus_b200 as sp
+    n, k = 256, 256
+    lin = sp.Nvfp4Linear(torch.zeros(n * k // 2, dtype=torch.uint8), torch.zeros(n * k // 16, dtype=torch.uint8), 1.0,
+                         k, n)
+    assert sp.ffi.distributed_world() == 1
+    assert [lin.route_for(m) for m in (1, 2, 64, 65)] == ["gemv", "decode", "decode", "prefill"]
+    assert lin.route_for(65, allow_prefill=False) == "decode"
