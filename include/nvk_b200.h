@@ -166,8 +166,11 @@ int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16,
 /* ---- MoE decode ------------------------------------------------------------------------------ */
 
 /* mode 0: top-K of the (optionally tanh soft-capped) logits, softmax over the K winners;
- * mode 1: sigmoid scores, selection on score + bias, optional renormalisation.  Ties go to the
- * lower expert id; weights are multiplied by routed_scaling.  -2 if E > 4096, K > 32 or K > E.
+ * mode 1: sigmoid scores, selection on score + bias, optional renormalisation.  Larger score first,
+ * ties to the lower expert id; weights are multiplied by routed_scaling.  A NaN score never wins and
+ * an expert wins at most once: a row with fewer than K usable scores is padded with id -1 /
+ * weight 0 (the reference re-selects an expert it already chose there).  -2 if E > 4096, K > 32 or
+ * K > E.
  * replace rust/crates/nv-kernels/include/nv_kernels.h:1538-1567
  * (rust/crates/nv-kernels/cuda/moe_route.cu:75-329) */
 int nv_kernels_moe_route_topk(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
@@ -190,7 +193,8 @@ int nv_kernels_gather_rows_bf16_strided(void* stream, const uint16_t* x_bf16, co
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:1593-1599 (cuda/moe_route.cu:536-561) */
 int nv_kernels_gather_f32_by_ids(void* stream, const float* src, const int32_t* ids, float* dst, int n);
 
-/* y_acc[n,h] = sum_s w[n,s] * y_sorted[inv_perm[n,s], h] in fp32, s ascending.
+/* y_acc[n,h] = sum_s w[n,s] * y_sorted[inv_perm[n,s], h] in fp32, s ascending; a slot with a
+ * negative inv_perm (one the sort left out) contributes nothing.
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:1526-1536 (cuda/moe_unpermute_scatter.cu:6-32) */
 int nv_kernels_moe_unpermute_scatter(void* stream, const uint16_t* y_sorted_bf16, const float* topk_weights,
                                      const int32_t* inv_perm, float* y_acc_f32, int n_tokens, int k, int hidden,
@@ -203,9 +207,18 @@ int nv_kernels_moe_unpermute_scatter_tail(void* stream, const uint16_t* y_sorted
                                           const uint16_t* resid_bf16, uint16_t* out_bf16, int n_tokens, int k,
                                           int hidden, int y_sorted_row_stride);
 
+/* No counterpart in the reference (whose entry point trusts inv_perm): the same combine with the
+ * sorted buffer's row count known.  A row index not below sorted_rows is skipped and reported in
+ * bit 2 of *status (one device int the caller zeroes; may be NULL). */
+int nvk_b200_moe_combine(void* stream, const uint16_t* y_sorted_bf16, const float* topk_weights, const int32_t* inv_perm,
+                         float* y_acc_f32, int n_tokens, int k, int hidden, int y_sorted_row_stride, int sorted_rows,
+                         int* status);
+
 /* Sort the n_tokens*k routed slots by expert: expert_offsets[E+1], permuted_token_idx[pos] = token,
  * inv_perm[slot] = pos.  Slots of one expert keep their original order (the reference leaves that
- * order to atomics).  scratch_counts is E int32 of caller scratch.
+ * order to atomics).  An expert id outside [0, E) -- a router's -1 included -- is never used as an
+ * index: that slot gets inv_perm = -1 and is left out.  scratch_counts is E int32 of caller scratch
+ * (any contents).  One launch.
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:1601-1611 (cuda/moe_permute.cu) */
 int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permuted_token_idx,
                            int32_t* expert_offsets, int32_t* inv_perm, int32_t* scratch_counts, int n_tokens, int k,
@@ -213,13 +226,33 @@ int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permu
 
 /* No counterpart in the reference (its decode step launches the router and the permutation
  * separately): both in one launch for decode-sized batches, with exactly the outputs of
- * nv_kernels_moe_route_topk followed by nv_kernels_moe_permute and no scratch buffer.
+ * nv_kernels_moe_route_topk followed by nv_kernels_moe_permute and no scratch buffer.  When
+ * active_experts / n_active are given (both or neither), the ascending list of experts that
+ * received at least one slot ([min(E, n_tokens*K)] int32) and its length are written as well, for
+ * nvk_b200_moe_grouped_w4a16.
  * Limits: E <= 256 and n_tokens * K <= 4096, otherwise -3 and nothing is launched; K > E or K > 32
  * returns -2. */
 int nvk_b200_moe_route_permute(void* stream, const float* logits, const float* bias, int32_t* topk_ids,
                                float* topk_weights, int32_t* permuted_token_idx, int32_t* expert_offsets,
-                               int32_t* inv_perm, int n_tokens, int E, int K, int mode, float softcap, int norm_topk,
-                               float routed_scaling);
+                               int32_t* inv_perm, int32_t* active_experts, int32_t* n_active, int n_tokens, int E,
+                               int K, int mode, float softcap, int norm_topk, float routed_scaling);
+
+/* One decode token: route it, copy each winner's (and the shared tail's, when shared_tail_id >= 0)
+ * stored activation globals into gu_mini / dn_mini, and quantize the token's row once per tile with
+ * that tile's gate/up global into row t * min_tile of x_fp4 (swizzled scale in x_sf).
+ * -1 non-positive sizes, -2 E > 256 / K + 1 > 32 / K > E / misaligned or NULL pointers,
+ * -3 hidden % 16 != 0 or min_tile % 128 != 0.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1569-1591 (cuda/moe_route.cu:331-470) */
+int nv_kernels_moe_route_gather_quant_m1(void* stream, const float* logits, const float* bias, const uint16_t* x_bf16,
+                                         const float* globals_gu, const float* globals_dn, int32_t* topk_ids,
+                                         float* topk_weights, float* gu_mini, float* dn_mini, uint8_t* x_fp4,
+                                         uint8_t* x_sf, int E, int K, int mode, float softcap, int norm_topk,
+                                         float routed_scaling, int shared_tail_id, int hidden, int min_tile);
+
+/* Writes the GPU's global nanosecond timer into *out when the stream reaches this point (also
+ * inside a captured graph): two stamps time the kernels between them.
+ * replaces rust/crates/nv-kernels/include/nv_kernels.h:1701-1704 (cuda/laguna_step.cu:565-576) */
+int nv_kernels_prof_timestamp(void* stream, unsigned long long* out);
 
 /* No counterpart in the reference.  The same permutation as nv_kernels_moe_permute for callers that
  * cannot supply (or allocate) the scratch_counts buffer: the per-expert counters live in a 16 KiB
@@ -228,7 +261,7 @@ int nvk_b200_moe_route_permute(void* stream, const float* logits, const float* b
  *   - num_experts <= 4096, otherwise -3 and nothing is launched;
  *   - the first call on each device looks up the array's device address (a one-time set-up step
  *     with that device current); make that first call before any stream capture;
- *   - all calls on a device share the one array, which is cleared at the start of every call:
+ *   - all calls on a device share the one array, whose counters the kernel clears before it counts:
  *     two calls that may run on the GPU at the same time (different streams) race -- keep them on
  *     one stream or otherwise ordered. */
 int nvk_b200_moe_permute_static(void* stream, const int32_t* topk_ids, int32_t* permuted_token_idx,
@@ -360,13 +393,22 @@ int nvk_b200_stack_run(void* stream, void* plan_dev, int n_ops, int M, int grid,
  *   arms:    wq_bank_b/sc_bank_b/alphas_b/y_b give a second matrix sharing the activations
  *            (gate + up); all four NULL for one arm.
  *   x2:      when not NULL the activation is bf16(SiLU(x) * x2), rows taken the same way.
- * Experts without tokens cost one empty CTA per row tile.  K % 32 == 0 (-1 otherwise), 16-byte
- * aligned pointers (-2 otherwise). */
+ *   active:  active_experts / n_active (device; both or neither) as nvk_b200_moe_route_permute
+ *            writes them: the launch then covers min(num_experts, num_slots) experts instead of
+ *            all of them, and experts without tokens cost nothing.  Without the list an expert
+ *            without tokens costs one empty CTA per row tile.
+ *   bounds:  num_slots = rows of y (and entries of row_index), x_rows = rows of x.  Offsets and row
+ *            indices outside them are never followed: such slots are skipped (offset) or read as
+ *            zeros (row) and bit 0 / bit 1 of *status (one device int the caller zeroes; may be
+ *            NULL) is set.
+ * K % 32 == 0 (-1 otherwise), 16-byte aligned pointers (-2 otherwise). */
 int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uint8_t* sc_bank_a,
                                const uint8_t* wq_bank_b, const uint8_t* sc_bank_b, const float* alphas_a,
                                const float* alphas_b, const uint16_t* x, const uint16_t* x2,
-                               const int32_t* row_index, const int32_t* expert_offsets, uint16_t* y_a,
-                               uint16_t* y_b, int num_experts, int N, int K);
+                               const int32_t* row_index, const int32_t* expert_offsets,
+                               const int32_t* active_experts, const int32_t* n_active, uint16_t* y_a,
+                               uint16_t* y_b, int num_experts, int N, int K, int num_slots, int x_rows,
+                               int* status);
 
 /* ---- tensor-parallel exchange (no counterpart in the reference, which has no multi-GPU code) ---
  * One-shot all-reduce of a small bf16 vector over peer memory for the row-parallel linears of a

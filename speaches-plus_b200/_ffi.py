@@ -49,7 +49,7 @@ SIGNATURES = {
     "nv_kernels_moe_unpermute_scatter_tail": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "nv_kernels_mul_sigmoid_rowgate_f32": [_vp, _vp, _vp, _vp, _i, _i],
     "nv_kernels_moe_permute": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
-    "nvk_b200_moe_grouped_w4a16": [_vp] * 13 + [_i, _i, _i],
+    "nvk_b200_moe_grouped_w4a16": [_vp] * 15 + [_i, _i, _i, _i, _i, _vp],
     "nvk_b200_tp_allreduce_buffer_bytes": [_i, _i],
     "nvk_b200_tp_buffer_alloc": [C.c_size_t, _vp],
     "nvk_b200_tp_buffer_free": [_vp],
@@ -57,7 +57,10 @@ SIGNATURES = {
     "nvk_b200_tp_ipc_open": [_vp, _vp],
     "nvk_b200_tp_ipc_close": [_vp],
     "nvk_b200_tp_allreduce_bf16": [_vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp],
-    "nvk_b200_moe_route_permute": [_vp] * 8 + [_i, _i, _i, _i, _f, _i, _f],
+    "nvk_b200_moe_route_permute": [_vp] * 10 + [_i, _i, _i, _i, _f, _i, _f],
+    "nvk_b200_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "nv_kernels_moe_route_gather_quant_m1": [_vp] * 12 + [_i, _i, _i, _f, _i, _f, _i, _i, _i],
+    "nv_kernels_prof_timestamp": [_vp, _vp],
     "nvk_b200_moe_permute_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_moe_grouped_fp4_gemv_m1_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll],
 }

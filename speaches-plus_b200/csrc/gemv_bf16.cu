@@ -5,13 +5,7 @@
 
 namespace {
 
-__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
+using nvk::ptx::ldg_stream_v4;
 
 __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w}, xs[4] = {x.x, x.y, x.z, x.w};
@@ -60,11 +54,8 @@ extern "C" int nv_kernels_gemv_bf16(void* stream, const uint16_t* W, const uint1
     if (nvk::any_null(W, x, y)) return NVK_ERR_ARG;
     const unsigned grid = (unsigned)((N + 7) / 8);
     const bool vec = (K & 7) == 0 && ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15u) == 0;
-    if (vec)
-        gemv_bf16_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(W, x, y, N, K);
-    else
-        gemv_bf16_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(W, x, y, N, K);
-    return (int)cudaGetLastError();
+    const nvk::Launch l = nvk::launch_1d((cudaStream_t)stream, grid, 256);
+    return vec ? nvk::launch(l, gemv_bf16_kernel<true>, W, x, y, N, K) : nvk::launch(l, gemv_bf16_kernel<false>, W, x, y, N, K);
 }
 
 extern "C" int nv_kernels_capability(int* sm_major, int* sm_minor) {

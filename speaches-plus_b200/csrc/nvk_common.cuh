@@ -6,6 +6,10 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <mutex>
+
+#include "nvk_launch.cuh"
+
 // Return codes follow the reference launchers: 0 = enqueued, -1 = shape/route refused
 // without launching, -2 = bad argument/alignment, -3 = resource limit, -9 = grid axis too
 // large; a positive value is a cudaError_t.
@@ -56,29 +60,10 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
 // Four packed e2m1 bytes (8 values, even element in the low nibble) -> four f16x2.
 __device__ __forceinline__ void e2m1x8_to_f16x2x4(uint32_t w, uint32_t& h0, uint32_t& h1, uint32_t& h2,
                                                   uint32_t& h3) {
-    asm("{\n"
-        ".reg .b8 b0, b1, b2, b3;\n"
-        "mov.b32 {b0, b1, b2, b3}, %4;\n"
-        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
-        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
-        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
-        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
-        "}\n"
-        : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
-        : "r"(w));
+    ptx::e2m1x8_to_f16x2x4(w, h0, h1, h2, h3);
 }
-
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-
-__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) { return ptx::hmul2(a, b); }
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) { return ptx::hfma2(a, b, c); }
 
 // e2m1 nearest-code search, first minimum wins (ties go to the lower code).
 __device__ __forceinline__ uint32_t encode_e2m1(float x) {
@@ -119,14 +104,23 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// Raise the dynamic shared memory limit of a kernel once, never lower it.
+// Raise the dynamic shared memory limit of a kernel, never lower it.  The attribute belongs to the
+// current device's context, so the raised size is remembered per device; callable from any thread.
 struct SmemOptin {
-    size_t raised = 48 * 1024;
+    static constexpr int kMaxDevices = 64;
+    size_t raised[kMaxDevices] = {};
+    std::mutex mu;
     int ensure(const void* func, size_t bytes) {
-        if (bytes <= raised) return 0;
-        cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (bytes <= 48 * 1024) return 0;
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return (int)e;
-        raised = bytes;
+        if (dev < 0 || dev >= kMaxDevices) return NVK_ERR_ARG;
+        std::lock_guard<std::mutex> lock(mu);
+        if (bytes <= raised[dev]) return 0;
+        e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return (int)e;
+        raised[dev] = bytes;
         return 0;
     }
 };

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) quantize_blocks_kernel(const QuantParams 
 // The quantized value is bf16(x * rsqrt(mean(x^2) + eps) * w): one rounding to bf16, then the
 // plain block quantizer.
 __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const QuantParams p) {
-    extern __shared__ __align__(16) uint16_t row_s[];
+    NVK_DYN_SMEM_AS(uint16_t, row_s);
     __shared__ float red[8];
     const int row = blockIdx.x;
     const int bpr = p.K >> 4;
@@ -165,9 +165,7 @@ int launch_blocks(cudaStream_t s, const QuantParams& p) {
     const long long total = (long long)p.rows * (p.K >> 4);
     const long long grid = (total + 255) / 256;
     if (grid > 0x7FFFFFFFLL) return NVK_ERR_GRID_AXIS;
-    quantize_blocks_kernel<SRC><<<(unsigned)grid, 256, 0, s>>>(p);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : (int)e;
+    return nvk::launch(nvk::launch_1d(s, (unsigned)grid, 256), quantize_blocks_kernel<SRC>, p);
 }
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
@@ -265,9 +263,8 @@ int nv_kernels_rmsnorm_bf16(void* stream, const uint16_t* x, const uint16_t* wei
     if (batch == 0 || hidden == 0) return 0;
     if (nvk::any_null(x, weight, y)) return NVK_ERR_ARG;
     if (batch > 0x7FFFFFFFull) return NVK_ERR_GRID_AXIS;
-    rmsnorm_bf16_kernel<<<(unsigned)batch, 256, 0, (cudaStream_t)stream>>>(x, weight, y, hidden, eps);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : (int)e;
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)batch, 256), rmsnorm_bf16_kernel, x, weight, y,
+                       hidden, eps);
 }
 
 int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16, const uint16_t* weight_bf16,
@@ -285,9 +282,7 @@ int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16,
     p.x = x_bf16; p.norm_w = weight_bf16; p.packed = packed_out; p.scales = scales_out_swizzled;
     p.global = stored_global; p.eps = eps; p.rows = m_padded; p.rows_logical = m_logical; p.K = K;
     p.row_mul = 1; p.m_per_expert = 1;
-    rmsnorm_quantize_kernel<<<(unsigned)m_padded, 256, smem, (cudaStream_t)stream>>>(p);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : (int)e;
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)m_padded, 256, smem), rmsnorm_quantize_kernel, p);
 }
 
 }  // extern "C"

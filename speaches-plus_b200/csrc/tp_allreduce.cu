@@ -38,21 +38,15 @@ struct ArParams {
     int rank, world, n, max_elems;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+using nvk::ptx::ld_acquire_sys;
+using nvk::ptx::st_release_sys;
 
 __global__ void __launch_bounds__(512) tp_allreduce_kernel(const ArParams p) {
     __shared__ int s_ok;
     // Programmatic dependent launch: x is the output of the kernel before this one; the kernel after
     // this one may start prefetching its weights now and waits for our completion before it reads y.
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int cta = blockIdx.x;
     const int e0 = cta * kElemsPerCta;
     const int cnt = min(kElemsPerCta, p.n - e0);           // elements of this CTA (multiple of 8)
@@ -174,16 +168,7 @@ int nvk_b200_tp_allreduce_bf16(void* stream, const void* const* peer_bufs, int r
     }
     p.x = x; p.y = y; p.epoch = epoch; p.err = err;
     p.rank = rank; p.world = world; p.n = n; p.max_elems = max_elems;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ctas, 1, 1);
-    cfg.blockDim = dim3(512, 1, 1);
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, tp_allreduce_kernel, p);
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)ctas, 512, 0, true), tp_allreduce_kernel, p);
 }
 
 }  // extern "C"

@@ -31,6 +31,8 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
     t.x = p.x;
     t.x2 = p.x2;
     t.xrows = nullptr;
+    t.x_rows = 0;
+    t.status = nullptr;
     t.y = p.y[arm];
     t.alpha = p.alpha[arm];
     t.xrow0 = 0;
@@ -51,6 +53,8 @@ __global__ void __launch_bounds__(256, NT >= 4 ? 1 : 2) w4a16_mma_ws_kernel(cons
     t.x = nullptr;
     t.x2 = nullptr;
     t.xrows = nullptr;
+    t.x_rows = 0;
+    t.status = nullptr;
     t.y = p.y[arm];
     t.alpha = p.alpha[arm];
     t.xrow0 = 0;
@@ -68,8 +72,8 @@ template <int PRO>
 __global__ void __launch_bounds__(256) x_prepare_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ x2,
                                                          uint8_t* __restrict__ ws, int M, int K, int nsc) {
     __shared__ uint32_t s_max;
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int m = blockIdx.x;
     if (threadIdx.x == 0) s_max = 0u;
     __syncthreads();
@@ -126,15 +130,36 @@ struct GroupedParams {
     const int32_t* xrows;      // [slots] gather index into x rows, or null (row = slot)
     size_t w_stride;           // bytes between experts in the packed-weight banks
     size_t sc_stride;          // bytes between experts in the scale banks
+    const int32_t* active;     // optional: the experts that have slots; blockIdx.z indexes this list
+    const int32_t* n_active;   // its length (device)
+    int n_experts;
+    int n_slots;               // rows of the output buffers (and entries of xrows)
+    int x_rows;                // rows of x
+    int* status;               // optional: bit 0 set when an offset, bit 1 when a row index was out of range
 };
 
 template <bool DUAL, int PRO>
 __global__ void __launch_bounds__(256, 3) w4a16_grouped_kernel(const GemmParams p, const GroupedParams g) {
     // The routing tables are written by the kernels just before this one in the stream.
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    const int e = blockIdx.z;
-    const int begin = g.offsets[e], end = g.offsets[e + 1];
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
+    int e = blockIdx.z;
+    if (g.active != nullptr) {
+        // grid z covers the most experts that can be active; entries past the list's end have no work
+        if ((int)blockIdx.z >= min(*g.n_active, g.n_experts)) return;
+        e = g.active[blockIdx.z];
+        if (e < 0 || e >= g.n_experts) {
+            if (g.status != nullptr && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(g.status, 1);
+            return;
+        }
+    }
+    // Offsets are data, not trusted: a slot range is cut to the buffers' rows, and a range that had
+    // to be cut is reported instead of followed.
+    const int raw_begin = g.offsets[e], raw_end = g.offsets[e + 1];
+    const int begin = min(max(raw_begin, 0), g.n_slots);
+    const int end = min(max(raw_end, begin), g.n_slots);
+    if ((begin != raw_begin || end != raw_end) && g.status != nullptr && threadIdx.x == 0 && blockIdx.y == 0)
+        atomicOr(g.status, 1);
     if (end <= begin) return;
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
@@ -144,6 +169,8 @@ __global__ void __launch_bounds__(256, 3) w4a16_grouped_kernel(const GemmParams 
     t.x = p.x;
     t.x2 = p.x2;
     t.xrows = g.xrows;
+    t.x_rows = g.x_rows;
+    t.status = g.status;
     t.alpha = g.alphas[arm][e];
     t.sub = tile - arm * p.tiles_per_arm;
     t.pdl = false;
@@ -182,13 +209,21 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t byte = wrow[kb * 8 + i];
-                uint32_t h2;
-                asm("{ .reg .b8 t, z; .reg .b16 w; cvt.u16.u32 w, %1; mov.b16 {t, z}, w; cvt.rn.f16x2.e2m1x2 %0, t; }\n"
-                    : "=r"(h2)
-                    : "r"(byte));
+                uint32_t h2 = nvk::ptx::e2m1x2_to_f16x2(byte);
                 float2 wf = __half22float2(*reinterpret_cast<__half2*>(&h2));
-                float x0 = nvk::bf16_bits_to_f32(xr[kb * 16 + 2 * i]);
-                float x1 = nvk::bf16_bits_to_f32(xr[kb * 16 + 2 * i + 1]);
+                float x0, x1;
+                if (PRO >= 2) {
+                    const uint8_t* xa = reinterpret_cast<const uint8_t*>(p.x) + (size_t)m * (p.K >> 1);
+                    const uint8_t* xs = reinterpret_cast<const uint8_t*>(p.x2);
+                    const float sf = nvk::ue4m3_to_f32(PRO == 2 ? xs[(size_t)(kb >> 2) * 512 + (kb & 3)] : xs[kb]);
+                    uint32_t a2 = nvk::ptx::e2m1x2_to_f16x2(xa[kb * 8 + i]);
+                    const float2 af = __half22float2(*reinterpret_cast<__half2*>(&a2));
+                    x0 = af.x * sf;
+                    x1 = af.y * sf;
+                } else {
+                    x0 = nvk::bf16_bits_to_f32(xr[kb * 16 + 2 * i]);
+                    x1 = nvk::bf16_bits_to_f32(xr[kb * 16 + 2 * i + 1]);
+                }
                 if (PRO == 1) {
                     float u0 = nvk::bf16_bits_to_f32(ur[kb * 16 + 2 * i]);
                     float u1 = nvk::bf16_bits_to_f32(ur[kb * 16 + 2 * i + 1]);
@@ -206,9 +241,11 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
 }
 
 // ------------------------------------------------------------------------------------------
-// test/tuning hooks, set through nvk_b200_set_tuning (0 = automatic)
-int g_force_ksplit = 0, g_force_ug = 0;
-int g_pdl = 1;  // programmatic dependent launch on every tensor-core-route launch
+// Test/tuning hooks (0 = automatic), set through nvk_b200_set_tuning / nvk_b200_set_pdl.  They are
+// per calling thread: the entry points may be called from any thread, and one thread's experiment
+// must not change another thread's launches.
+thread_local int g_force_ksplit = 0, g_force_ug = 0;
+thread_local int g_pdl = 1;  // programmatic dependent launch on every tensor-core-route launch
 
 template <int NT, bool DUAL, int PRO, int UG, int KW>
 int launch_mma(cudaStream_t stream, GemmParams& p) {
@@ -241,28 +278,14 @@ int launch_mma(cudaStream_t stream, GemmParams& p) {
     const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
     if (ctas > 65535) return NVK_ERR_GRID_AXIS;
 
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)ctas, 1);
-    cfg.blockDim = dim3(32 * UG * KW, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (ksplit > 1) {
-        attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)ksplit;
-        attr[na].val.clusterDim.y = 1;
-        attr[na].val.clusterDim.z = 1;
-        ++na;
-    }
-    if (g_pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    return (int)cudaLaunchKernelEx(&cfg, kern, p);
+    nvk::Launch l;
+    l.grid = dim3((unsigned)ksplit, (unsigned)ctas, 1);
+    l.block = dim3(32 * UG * KW, 1, 1);
+    l.smem = smem;
+    l.stream = stream;
+    l.cluster_x = (unsigned)ksplit;
+    l.pdl = g_pdl != 0;
+    return nvk::launch(l, kern, p);
 }
 
 template <int NT, bool DUAL, int PRO>
@@ -313,42 +336,20 @@ int launch_mma_ws(cudaStream_t stream, GemmParams& p, const uint8_t* ws) {
     if (int rc = optin.ensure((const void*)kern, smem)) return rc;
     const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
     if (ctas > 65535) return NVK_ERR_GRID_AXIS;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ksplit, (unsigned)ctas, 1);
-    cfg.blockDim = dim3(256, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (ksplit > 1) {
-        attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)ksplit;
-        attr[na].val.clusterDim.y = 1;
-        attr[na].val.clusterDim.z = 1;
-        ++na;
-    }
-    if (g_pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    return (int)cudaLaunchKernelEx(&cfg, kern, p, ws);
+    nvk::Launch l;
+    l.grid = dim3((unsigned)ksplit, (unsigned)ctas, 1);
+    l.block = dim3(256, 1, 1);
+    l.smem = smem;
+    l.stream = stream;
+    l.cluster_x = (unsigned)ksplit;
+    l.pdl = g_pdl != 0;
+    return nvk::launch(l, kern, p, ws);
 }
 
 int launch_prepare(cudaStream_t stream, const uint16_t* x, const uint16_t* x2, uint8_t* ws, int M, int K, int nsc) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)M, 1, 1);
-    cfg.blockDim = dim3(256, 1, 1);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_pdl ? 1 : 0;
-    if (x2) return (int)cudaLaunchKernelEx(&cfg, x_prepare_kernel<1>, x, x2, ws, M, K, nsc);
-    return (int)cudaLaunchKernelEx(&cfg, x_prepare_kernel<0>, x, x2, ws, M, K, nsc);
+    const nvk::Launch l = nvk::launch_1d(stream, (unsigned)M, 256, 0, g_pdl != 0);
+    if (x2) return nvk::launch(l, x_prepare_kernel<1>, x, x2, ws, M, K, nsc);
+    return nvk::launch(l, x_prepare_kernel<0>, x, x2, ws, M, K, nsc);
 }
 
 template <bool DUAL, int PRO>
@@ -368,17 +369,15 @@ int launch_grouped(cudaStream_t stream, GemmParams& p, const GroupedParams& g, i
     if (int rc = optin.ensure((const void*)kern, smem)) return rc;
     const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
     if (ctas > 65535 || E > 65535) return NVK_ERR_GRID_AXIS;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1, (unsigned)ctas, (unsigned)E);
-    cfg.blockDim = dim3(256, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_pdl ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, kern, p, g);
+    nvk::Launch l;
+    // with a list of active experts the grid covers only as many experts as there are slots
+    const int grid_z = g.active != nullptr ? max(1, min(E, g.n_slots)) : E;
+    l.grid = dim3(1, (unsigned)ctas, (unsigned)grid_z);
+    l.block = dim3(256, 1, 1);
+    l.smem = smem;
+    l.stream = stream;
+    l.pdl = g_pdl != 0;
+    return nvk::launch(l, kern, p, g);
 }
 
 // Common entry: validates, then picks the tensor-core route or the generic one.
@@ -407,12 +406,151 @@ int w4a16_linear(cudaStream_t stream, const uint8_t* wq_a, const uint8_t* sc_a, 
         return pro ? dispatch_mma<false, 1>(stream, p) : dispatch_mma<false, 0>(stream, p);
     }
     const int total = dual ? 2 * N : N;
-    dim3 grid((unsigned)nvk::ceil_div(total, 8));
-    if (pro)
-        w4a16_rowwarp_kernel<1><<<grid, 256, 0, stream>>>(p);
-    else
-        w4a16_rowwarp_kernel<0><<<grid, 256, 0, stream>>>(p);
-    return (int)cudaGetLastError();
+    const nvk::Launch l = nvk::launch_1d(stream, (unsigned)nvk::ceil_div(total, 8), 256);
+    return pro ? nvk::launch(l, w4a16_rowwarp_kernel<1>, p) : nvk::launch(l, w4a16_rowwarp_kernel<0>, p);
+}
+
+// ------------------------------------------------------------------------------------------
+// W4A4 at M = 1: an NVFP4 activation row against NVFP4 weights.  The activation is dequantized
+// exactly while it is staged (tile prologues 2 and 3), so this is the W4A16 tile with another
+// prologue: weights stream once with 16-byte copies, a 128-row x k-tile scale tile is read as
+// contiguous bytes, and the sum over K is taken in the tile's fixed order (bit-stable run to run).
+int w4a4_gemv(cudaStream_t stream, const uint8_t* W_packed, const uint8_t* W_scales, const uint8_t* x_packed,
+              const uint8_t* x_scales, uint16_t* y, float alpha, int N, int K) {
+    GemmParams p = {};
+    p.wq[0] = W_packed;
+    p.sc[0] = W_scales;
+    p.x = reinterpret_cast<const uint16_t*>(x_packed);
+    p.x2 = reinterpret_cast<const uint16_t*>(x_scales);
+    p.y[0] = y;
+    p.alpha[0] = alpha;
+    p.M = 1; p.N = N; p.K = K;
+    p.tiles_per_arm = nvk::ceil_div(N, kRowsPerCta);
+    p.k_tiles = nvk::ceil_div(K, 64);
+    p.nsc = nvk::ceil_div(K, kSuper);
+    const bool fast = (K & 31) == 0 && aligned16(W_packed) && aligned16(W_scales) &&
+                      (reinterpret_cast<uintptr_t>(x_packed) & 3u) == 0 && p.tiles_per_arm <= 65535;
+    if (fast) return launch_mma<1, false, 3, 8, 1>(stream, p);
+    return nvk::launch(nvk::launch_1d(stream, (unsigned)nvk::ceil_div(N, 8), 256), w4a16_rowwarp_kernel<3>, p);
+}
+
+// Grouped form: group g is one (token, expert) pair -- expert ids[g], activation = row 0 of the
+// g-th activation tile, output row g.  A group whose id is outside [0, num_experts) gets a zero row.
+struct W4a4GroupArgs {
+    const uint8_t* a_packed;
+    const uint8_t* a_scales;
+    const float* alphas;
+    const int32_t* ids;
+    int num_experts;
+    size_t a_group_bytes;      // packed bytes between the activation tiles of consecutive groups
+    size_t a_sf_group_bytes;   // scale bytes between them
+    size_t w_stride, sc_stride;
+    long long d_group_stride;  // output elements between groups
+};
+
+__global__ void __launch_bounds__(256, 3) w4a4_m1_grouped_kernel(const GemmParams p, const W4a4GroupArgs g) {
+    // ids and activations come from the kernels just before this one.
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
+    const int grp = blockIdx.z, tile = blockIdx.y;
+    const int e = g.ids[grp];
+    uint16_t* y = p.y[0] + (size_t)grp * (size_t)g.d_group_stride;
+    if (e < 0 || e >= g.num_experts) {   // the same for every CTA of a K-split cluster
+        if (blockIdx.x == 0)
+            for (int r = threadIdx.x; r < kRowsPerCta; r += 256)
+                if (tile * kRowsPerCta + r < p.N) y[tile * kRowsPerCta + r] = 0;
+        return;
+    }
+    TileView t;
+    t.wq = p.wq[0] + (size_t)e * g.w_stride;
+    t.sc = p.sc[0] + (size_t)e * g.sc_stride;
+    t.x = reinterpret_cast<const uint16_t*>(g.a_packed + (size_t)grp * g.a_group_bytes);
+    t.x2 = reinterpret_cast<const uint16_t*>(g.a_scales + (size_t)grp * g.a_sf_group_bytes);
+    t.xrows = nullptr;
+    t.x_rows = 0;
+    t.status = nullptr;
+    t.y = y;
+    t.alpha = g.alphas[e];
+    t.xrow0 = 0;
+    t.M = 1;
+    t.sub = tile;
+    t.pdl = false;
+    t.ws = nullptr;
+    w4a16_tile<1, 2, 8, 1>(p, t);
+}
+
+// Shapes the tile does not take (K % 32 != 0, unaligned banks): one warp per (row, group), fp32 FMAs.
+__global__ void __launch_bounds__(256) w4a4_m1_grouped_rowwarp_kernel(const GemmParams p, const W4a4GroupArgs g) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int grp = blockIdx.y;
+    if (n >= p.N) return;
+    uint16_t* y = p.y[0] + (size_t)grp * (size_t)g.d_group_stride;
+    const int e = g.ids[grp];
+    if (e < 0 || e >= g.num_experts) {
+        if (lane == 0) y[n] = 0;
+        return;
+    }
+    const int kb_total = p.K >> 4;
+    const uint8_t* wrow = p.wq[0] + (size_t)e * g.w_stride + (size_t)n * (p.K >> 1);
+    const uint8_t* wsc = p.sc[0] + (size_t)e * g.sc_stride;
+    const uint8_t* xa = g.a_packed + (size_t)grp * g.a_group_bytes;
+    const uint8_t* xs = g.a_scales + (size_t)grp * g.a_sf_group_bytes;
+    float acc = 0.f;
+    for (int kb = lane; kb < kb_total; kb += 32) {
+        const float ws = nvk::ue4m3_to_f32(wsc[nvk::swz_offset(n, kb, kb_total)]);
+        const float as = nvk::ue4m3_to_f32(xs[(size_t)(kb >> 2) * 512 + (kb & 3)]);
+        float bd = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t w2 = nvk::ptx::e2m1x2_to_f16x2(wrow[kb * 8 + i]), a2 = nvk::ptx::e2m1x2_to_f16x2(xa[kb * 8 + i]);
+            const float2 wf = __half22float2(*reinterpret_cast<__half2*>(&w2));
+            const float2 af = __half22float2(*reinterpret_cast<__half2*>(&a2));
+            bd = fmaf(wf.x, af.x, bd);   // exact: multiples of 1/4, at most 16 * 36
+            bd = fmaf(wf.y, af.y, bd);
+        }
+        acc = fmaf(ws * as, bd, acc);
+    }
+    acc = nvk::warp_sum(acc);
+    if (lane == 0) y[n] = nvk::f32_to_bf16_bits(acc * g.alphas[e]);
+}
+
+int w4a4_grouped(cudaStream_t stream, GemmParams& p, const W4a4GroupArgs& g, int num_groups, bool fast) {
+    if (!fast) {
+        nvk::Launch l;
+        l.grid = dim3((unsigned)nvk::ceil_div(p.N, 8), (unsigned)num_groups, 1);
+        l.block = dim3(256, 1, 1);
+        l.stream = stream;
+        return nvk::launch(l, w4a4_m1_grouped_rowwarp_kernel, p, g);
+    }
+    constexpr int MT = 8, RS = 128 + 4, KW = 1;
+    p.M = 1;
+    p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta);
+    int ksplit = 1;
+    if (g_force_ksplit > 0) {
+        ksplit = g_force_ksplit;
+    } else {
+        const long long ctas = (long long)p.tiles_per_arm * num_groups;
+        while (ksplit < 8 && ctas * ksplit < 148 && nvk::ceil_div(p.nsc, ksplit * 2) >= 2) ksplit *= 2;
+    }
+    p.spc = nvk::ceil_div(p.nsc, ksplit);
+    p.ph = min(96, p.spc);
+    p.x_stride = p.ph * 512 + 64;
+    const size_t smem_x = (size_t)p.x_stride;
+    const size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
+    p.ring_off = (int)((max(smem_x, smem_red) + 127) / 128 * 128);
+    const size_t smem = (size_t)p.ring_off + (size_t)8 * kDepth * kSlotBytes;
+    static nvk::SmemOptin optin;
+    if (int rc = optin.ensure((const void*)w4a4_m1_grouped_kernel, smem)) return rc;
+    if (p.tiles_per_arm > 65535 || num_groups > 65535) return NVK_ERR_GRID_AXIS;
+    nvk::Launch l;
+    l.grid = dim3((unsigned)ksplit, (unsigned)p.tiles_per_arm, (unsigned)num_groups);
+    l.block = dim3(256, 1, 1);
+    l.smem = smem;
+    l.stream = stream;
+    l.cluster_x = (unsigned)ksplit;
+    l.pdl = g_pdl != 0;
+    return nvk::launch(l, w4a4_m1_grouped_kernel, p, g);
 }
 
 }  // namespace
@@ -491,12 +629,24 @@ int nvk_b200_linear_nvfp4_w4a16(void* stream, const uint8_t* wq_a, const uint8_t
 
 // Grouped-expert W4A16 linear for routed MoE tokens (no counterpart in the reference, whose grouped
 // decode path quantizes activations to NVFP4 and gives every (token, expert) pair its own tile).
+// Expert e works on the sorted slots [expert_offsets[e], expert_offsets[e + 1]); slot s reads row
+// row_index[s] of x (row s when row_index is NULL) and writes row s of the outputs.  With
+// `active_experts` / `n_active` (device; as nvk_b200_moe_route_permute writes them) the launch covers
+// min(num_experts, num_slots) experts instead of all of them -- at batch 1 with top-8 routing that is 8
+// CTAs per row tile instead of 128.  `num_slots` is
+// the number of rows the outputs (and row_index) hold, `x_rows` the number of rows of x: offsets and
+// row indices outside them are never followed -- the slots are skipped or read as zeros and, when
+// `status` (one device int, zeroed by the caller) is given, bit 0 (offset) or bit 1 (row) is set in it.
 int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uint8_t* sc_bank_a,
                                const uint8_t* wq_bank_b, const uint8_t* sc_bank_b, const float* alphas_a,
                                const float* alphas_b, const uint16_t* x, const uint16_t* x2,
-                               const int32_t* row_index, const int32_t* expert_offsets, uint16_t* y_a,
-                               uint16_t* y_b, int num_experts, int N, int K) {
+                               const int32_t* row_index, const int32_t* expert_offsets,
+                               const int32_t* active_experts, const int32_t* n_active, uint16_t* y_a,
+                               uint16_t* y_b, int num_experts, int N, int K, int num_slots, int x_rows,
+                               int* status) {
     if (num_experts <= 0 || N <= 0 || K <= 0) return 0;
+    if (num_slots < 0 || x_rows < 0) return NVK_ERR_ARG;
+    if ((active_experts == nullptr) != (n_active == nullptr)) return NVK_ERR_ARG;
     if ((K & 31) != 0) return NVK_ERR_SHAPE;
     if ((wq_bank_b == nullptr) != (y_b == nullptr) || (wq_bank_b == nullptr) != (sc_bank_b == nullptr) ||
         (wq_bank_b == nullptr) != (alphas_b == nullptr))
@@ -521,6 +671,12 @@ int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uin
     g.xrows = row_index;
     g.w_stride = w_stride;
     g.sc_stride = sc_stride;
+    g.active = active_experts;
+    g.n_active = n_active;
+    g.n_experts = num_experts;
+    g.n_slots = num_slots;
+    g.x_rows = row_index ? x_rows : num_slots;
+    g.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     const bool dual = wq_bank_b != nullptr;
     if (dual) return x2 ? launch_grouped<true, 1>(s, p, g, num_experts) : launch_grouped<true, 0>(s, p, g, num_experts);
@@ -579,6 +735,52 @@ int nvk_b200_linear_nvfp4_w4a16_ws(void* stream, const uint8_t* wq_a, const uint
     if (M <= 16) return launch_mma_ws<2, false>(s, p, ws);
     if (M <= 32) return launch_mma_ws<4, false>(s, p, ws);
     return launch_mma_ws<8, false>(s, p, ws);
+}
+
+// W4A4 at M = 1 (the reference's test/shader-mirror pair with the flat row quantizer): packed e2m1
+// activation row with a flat [K/16] ue4m3 scale array against swizzled NVFP4 weights.
+int nv_kernels_nvfp4_gemv_bf16(void* stream, const uint8_t* W_packed, const uint8_t* W_scales, const uint8_t* x_packed,
+                               const uint8_t* x_scales, uint16_t* y, float alpha, int N, int K) {
+    if (N <= 0 || K <= 0) return 0;
+    if ((K & 15) != 0) return NVK_ERR_SHAPE;
+    if (nvk::any_null(W_packed, W_scales, x_packed, x_scales, y)) return NVK_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(W_packed) & 7) != 0 || (reinterpret_cast<uintptr_t>(x_packed) & 7) != 0)
+        return NVK_ERR_ARG;
+    return w4a4_gemv((cudaStream_t)stream, W_packed, W_scales, x_packed, x_scales, y, alpha, N, K);
+}
+
+// Grouped M = 1 expert GEMV with NVFP4 activations: d[g, :] = bf16(alphas[e] * W_e a_g), e = ids[g],
+// a_g = row 0 of the g-th activation tile (tiles are a_tile_stride_rows rows apart).
+int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packed, const uint8_t* a_scales,
+                                            const uint8_t* b_packed, const uint8_t* b_scales, const float* alphas,
+                                            uint16_t* d_bf16, const int32_t* group_expert_ids, int num_groups,
+                                            int num_experts_total, int n, int k, int a_tile_stride_rows,
+                                            long long d_group_stride_elems) {
+    if (num_groups <= 0 || num_experts_total <= 0 || n <= 0 || k <= 0) return NVK_ERR_SHAPE;
+    if ((k & 15) != 0) return NVK_ERR_SHAPE;
+    if (a_tile_stride_rows <= 0 || (a_tile_stride_rows & 127) != 0) return NVK_ERR_SHAPE;
+    if (d_group_stride_elems < (long long)n) return NVK_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(a_packed) & 7) != 0 || (reinterpret_cast<uintptr_t>(b_packed) & 7) != 0)
+        return NVK_ERR_ARG;
+    if (num_groups > 65535) return NVK_ERR_GRID_AXIS;
+    if (nvk::any_null(a_packed, a_scales, b_packed, b_scales, alphas, d_bf16, group_expert_ids)) return NVK_ERR_ARG;
+    GemmParams p = {};
+    p.wq[0] = b_packed;
+    p.sc[0] = b_scales;
+    p.y[0] = d_bf16;
+    p.N = n; p.K = k;
+    p.k_tiles = nvk::ceil_div(k, 64);
+    p.nsc = nvk::ceil_div(k, kSuper);
+    W4a4GroupArgs g = {};
+    g.a_packed = a_packed; g.a_scales = a_scales; g.alphas = alphas; g.ids = group_expert_ids;
+    g.num_experts = num_experts_total;
+    g.a_group_bytes = (size_t)a_tile_stride_rows * (size_t)(k >> 1);
+    g.a_sf_group_bytes = (size_t)(a_tile_stride_rows / 128) * (size_t)p.k_tiles * 512;
+    g.w_stride = (size_t)n * (size_t)(k >> 1);
+    g.sc_stride = (size_t)nvk::ceil_div(n, 128) * 128 * (size_t)p.k_tiles * 4;
+    g.d_group_stride = d_group_stride_elems;
+    const bool fast = (k & 31) == 0 && aligned16(b_packed) && aligned16(b_scales) && (g.w_stride & 15) == 0;
+    return w4a4_grouped((cudaStream_t)stream, p, g, num_groups, fast);
 }
 
 }  // extern "C"

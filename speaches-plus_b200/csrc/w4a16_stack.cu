@@ -40,11 +40,7 @@ struct StackOp {
     int k_tiles, nsc, ph, x_stride, ring_off;
 };
 
-__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+using nvk::ptx::ld_acquire_gpu;
 
 // Tiles inside the persistent launch: no cluster (an item owns all of K for its rows), activations
 // written earlier in the SAME launch -- so they are read from L2 (another SM wrote them; this SM's L1
@@ -94,6 +90,8 @@ __device__ __forceinline__ void run_item(const StackOp& op, int item, int M, con
     t.x = op.x;
     t.x2 = op.x2;
     t.xrows = nullptr;
+    t.x_rows = 0;
+    t.status = nullptr;
     t.y = op.y[arm];
     t.alpha = op.alpha[arm];
     t.xrow0 = 0;
@@ -269,18 +267,10 @@ int nvk_b200_stack_run(void* stream, void* plan_dev, int n_ops, int M, int grid,
     unsigned* done = reinterpret_cast<unsigned*>(base + ops_b + ctr_b);
     cudaError_t e = cudaMemsetAsync(next_item, 0, 2 * ctr_b, s);
     if (e != cudaSuccess) return (int)e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3(kStackThreads, 1, 1);
-    cfg.dynamicSmemBytes = (size_t)smem_bytes;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    nvk::Launch l = nvk::launch_1d(s, (unsigned)grid, kStackThreads, (size_t)smem_bytes);
+    l.cooperative = true;
     const StackOp* ops = reinterpret_cast<const StackOp*>(base);
-    return (int)cudaLaunchKernelEx(&cfg, w4a16_stack_kernel, ops, n_ops, M, next_item, done, err);
+    return nvk::launch(l, w4a16_stack_kernel, ops, n_ops, M, next_item, done, err);
 }
 
 }  // extern "C"

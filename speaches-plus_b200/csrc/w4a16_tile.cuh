@@ -31,11 +31,7 @@ struct GemmParams {
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    nvk::ptx::mma_m16n8k16_f16(d, a0, a1, a2, a3, b0, b1);
 }
 
 constexpr int kDepth = 4;           // cp.async groups in flight per thread
@@ -43,22 +39,16 @@ constexpr int kSlotBytes = 2560;    // one warp, one iteration: 4 x 512 B of wei
 
 // 16-byte (weights) and 8-byte (scales) asynchronous global -> shared copies; src_bytes == 0 writes
 // zeros without touching global memory.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+using nvk::ptx::cp_async16;
+using nvk::ptx::cp_async8;
+using nvk::ptx::cp_async_commit;
+using nvk::ptx::cp_async_wait;
 
 // Two ue4m3 scale bytes (the low half of `w`, bit 7 of each byte already cleared) -> f16x2.
 // ue4m3 is the non-negative half of e4m3, so the hardware e4m3 convert is exact for 0x00..0x7E;
 // 0x7F (never produced by an NVFP4 encoder, NaN in e4m3) converts to NaN.
 __device__ __forceinline__ __half2 scales2_f16(uint32_t w) {
-    uint32_t d;
-    asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo;}" : "=r"(d) : "r"(w));
+    uint32_t d = nvk::ptx::e4m3x2_to_f16x2(w);
     return *reinterpret_cast<__half2*>(&d);
 }
 
@@ -85,9 +75,11 @@ __device__ __forceinline__ void silu_mul_bf16x8(uint32_t (&ws)[4], const uint4 u
 struct TileView {
     const uint8_t* wq;
     const uint8_t* sc;
-    const uint16_t* x;       // activation rows (gate when PRO == 1)
-    const uint16_t* x2;      // up rows when PRO == 1
+    const uint16_t* x;       // activation rows (gate when PRO == 1; packed e2m1 rows when PRO >= 2)
+    const uint16_t* x2;      // up rows when PRO == 1; the activation's ue4m3 scales when PRO >= 2
     const int32_t* xrows;    // optional gather: token m reads row xrows[xrow0 + m]; else row xrow0 + m
+    int x_rows;              // rows of x a gathered index may name (others read as zeros and are reported)
+    int* status;             // optional word, bit 1 set when a gathered row index was out of range
     uint16_t* y;             // output row of token m is y + m * N
     float alpha;
     int xrow0;
@@ -110,6 +102,8 @@ struct LaunchHooks {
     __device__ static __forceinline__ uint4 load_x(const uint16_t* q) { return *reinterpret_cast<const uint4*>(q); }
 };
 
+// PRO: 0 = bf16 activations; 1 = bf16(SiLU(x) * x2); 2 = an NVFP4 activation row whose scales are row 0
+// of a 128x4 swizzled tile; 3 = an NVFP4 activation row with a flat [K/16] scale array.
 // XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
 // in a caller-supplied workspace; the CTA streams them through a shared ring next to the weights
 // instead of converting its whole K range itself.  Needs KW == 1 (all warps walk K together).
@@ -120,7 +114,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     constexpr int MT = 8 * NT;      // token columns
     constexpr int ROWS = 16 * UG;   // weight rows per CTA
     constexpr int SUB = 8 / UG;     // CTAs per 128-row scale tile
-    extern __shared__ __align__(16) uint8_t smem[];
+    NVK_DYN_SMEM_AS(uint8_t, smem);
     __shared__ uint32_t s_amax[MT];   // slice maximum (bf16 magnitude bits), then f32 bits of 2^-pw
     __shared__ int s_pw[MT];          // power of two currently folded into the accumulators
     __shared__ float s_rescale[MT];   // 2^(pw_old - pw_new) at a phase boundary
@@ -148,7 +142,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
         sc + (size_t)mt * p.k_tiles * 512 + (size_t)(8 * h + gid) * 16 + pair * 8 + (size_t)(tg >> 1) * 512;
 
     // shared memory: [activations / reduction scratch | weight ring]
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)p.ring_off +
+    const uint32_t ring = nvk::ptx::smem_addr(smem) + (uint32_t)p.ring_off +
                           (uint32_t)(warp * kDepth * kSlotBytes) + (uint32_t)lane * 16;
     const uint8_t* ring_g = smem + p.ring_off + warp * kDepth * kSlotBytes + lane * 16;
 
@@ -168,7 +162,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             if (XWS) {
                 // this stage's activations: M rows of 512 bytes, row stride 576 in shared memory
                 const uint8_t* xsrc = t.ws + 256 + (size_t)s * M * 512;
-                const uint32_t xdst = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)(slot * M * 576);
+                const uint32_t xdst = nvk::ptx::smem_addr(smem) + (uint32_t)(slot * M * 576);
                 for (int idx = threadIdx.x; idx < M * 32; idx += THREADS)
                     cp_async16(xdst + (idx >> 5) * 576 + (idx & 31) * 16, xsrc + (size_t)idx * 16, 16);
             }
@@ -236,11 +230,11 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     // Programmatic dependent launch: let the next kernel in the stream start its own weight
     // prefetch while this one runs, and prefetch our weights (which no earlier kernel writes) before
     // waiting for the previous kernel, whose output may be our activations.
-    if (t.pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    if (t.pdl) nvk::ptx::pdl_launch_dependents();
     int s_issue = sc_begin + kw, n_issued = 0, n_done = 0;
     if (XWS) {
         // The prepared activations come from the kernel just before this one.
-        if (t.pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        if (t.pdl) nvk::ptx::pdl_wait();
         if (threadIdx.x < MT) s_pw[threadIdx.x] = reinterpret_cast<const int*>(t.ws)[min((int)threadIdx.x, M - 1)];
 #pragma unroll
         for (int d = 0; d < kDepth - 1; ++d) {
@@ -265,7 +259,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
         s_issue += KW;
         ++n_issued;
     }
-    if (t.pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (t.pdl) nvk::ptx::pdl_wait();
     HK::before_activations(t);
 
     for (int p0 = sc_begin; p0 < sc_end; p0 += p.ph) {
@@ -288,7 +282,34 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             const int rem = idx - m * pieces_per_tok;
             const int k = (p0 + (rem >> 5)) * kSuper + (rem & 31) * 8;
             if (k >= K) return false;
-            const size_t xr0 = (size_t)(t.xrows ? t.xrows[t.xrow0 + m] : t.xrow0 + m) * K + k;
+            int xrow = t.xrow0 + m;
+            if (t.xrows != nullptr) {
+                xrow = t.xrows[t.xrow0 + m];
+                if ((unsigned)xrow >= (unsigned)t.x_rows) {   // a routing table must not steer a load
+                    if (t.status != nullptr) atomicOr(t.status, 2);
+                    return false;
+                }
+            }
+            if (PRO >= 2) {
+                // NVFP4 activation row: eight e2m1 values times their block's ue4m3 scale.  The product
+                // has at most six significand bits, so it is exact as bf16 and the W4A4 contraction
+                // sum (w*ws)*(a*as) is this tile's ordinary W4A16 sum over an exactly dequantized row.
+                const uint8_t* xa = reinterpret_cast<const uint8_t*>(t.x) + (size_t)xrow * (size_t)(K >> 1);
+                const uint8_t* xs = reinterpret_cast<const uint8_t*>(t.x2);
+                const int kb = k >> 4;
+                const uint32_t sb = PRO == 2 ? xs[(size_t)(kb >> 2) * 512 + (kb & 3)]   // row 0 of a swizzled tile
+                                             : xs[kb];                                  // flat [K/16]
+                const float sf = nvk::ue4m3_to_f32(sb);
+                uint32_t h[4];
+                nvk::e2m1x8_to_f16x2x4(*reinterpret_cast<const uint32_t*>(xa + (k >> 1)), h[0], h[1], h[2], h[3]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+                    ws[i] = (uint32_t)nvk::f32_to_bf16_bits(f.x * sf) | ((uint32_t)nvk::f32_to_bf16_bits(f.y * sf) << 16);
+                }
+                return true;
+            }
+            const size_t xr0 = (size_t)xrow * K + k;
             const uint4 v = HK::load_x(t.x + xr0);
             ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
             if (PRO == 1) silu_mul_bf16x8(ws, HK::load_x(t.x2 + xr0));

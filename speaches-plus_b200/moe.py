@@ -99,6 +99,20 @@ class GroupedDecodeContext:
         self.up_out = torch.zeros((slots, w.inter), dtype=torch.bfloat16, device=device)
         self.down_out = torch.zeros((slots, w.hidden), dtype=torch.bfloat16, device=device)
         self.y_acc = torch.zeros((max_tokens, w.hidden), dtype=torch.float32, device=device)
+        # experts that received slots (written by the fused router; lets the expert launches cover
+        # only those) and the word in which the kernels report a routing table they refused to follow
+        self.active = torch.zeros(max(1, min(w.total_experts, slots)), **i32)
+        self.n_active = torch.zeros(1, **i32)
+        self.status = torch.zeros(1, **i32)
+
+    def check_status(self) -> None:
+        """Raise if a kernel met an offset or row index outside its buffers since the last check
+        (bit 0: expert offset, bit 1: gathered row, bit 2: combine row).  Reads one int back."""
+        v = int(self.status.item())
+        if v:
+            self.status.zero_()
+            raise RuntimeError(f"MoE decode step: a routing table pointed outside its buffers (status {v:#x}); "
+                               "the affected slots were skipped")
 
 
 def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: torch.Tensor,
@@ -115,11 +129,13 @@ def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: t
     assert router_logits.dtype == torch.float32 and router_logits.is_contiguous()
     s = _stream()
     bias_p = bias.data_ptr() if bias is not None else None
-    if E <= 256 and n * k <= 4096:
-        # decode-sized: router and permutation in one launch
+    fused = E <= 256 and n * k <= 4096
+    if fused:
+        # decode-sized: router, slot sort and the list of active experts in one launch
         _ffi.check("nvk_b200_moe_route_permute", s, router_logits.data_ptr(), bias_p, ctx.topk_ids.data_ptr(),
                    ctx.topk_weights.data_ptr(), ctx.perm_token.data_ptr(), ctx.offsets.data_ptr(),
-                   ctx.inv_perm.data_ptr(), n, E, k, mode, float(softcap), int(norm_topk), float(routed_scaling))
+                   ctx.inv_perm.data_ptr(), ctx.active.data_ptr(), ctx.n_active.data_ptr(), n, E, k, mode,
+                   float(softcap), int(norm_topk), float(routed_scaling))
     else:
         _ffi.check("nv_kernels_moe_route_topk", s, router_logits.data_ptr(), bias_p, ctx.topk_ids.data_ptr(),
                    ctx.topk_weights.data_ptr(), n, E, k, mode, float(softcap), int(norm_topk), float(routed_scaling))
@@ -127,18 +143,24 @@ def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: t
                    ctx.offsets.data_ptr(), ctx.inv_perm.data_ptr(), ctx.counts.data_ptr(), n, k, E)
     g, u, d = w.gate, w.up, w.down
     # Local expert i owns the sorted slots [offsets[first + i], offsets[first + i + 1]): the same offsets
-    # array, entered at this rank's first expert.  Slot positions stay global.
+    # array, entered at this rank's first expert.  Slot positions stay global.  The active-expert list
+    # holds layer-wide ids, so it is used only when this object holds the whole layer.
     offsets = ctx.offsets.data_ptr() + 4 * w.first_expert
+    use_active = fused and not w.sharded
+    act = ctx.active.data_ptr() if use_active else None
+    n_act = ctx.n_active.data_ptr() if use_active else None
+    slots = n * k
     if w.sharded:
-        ctx.down_out[: n * k].zero_()   # rows of slots routed to other ranks' experts contribute nothing
+        ctx.down_out[:slots].zero_()   # rows of slots routed to other ranks' experts contribute nothing
     _ffi.check("nvk_b200_moe_grouped_w4a16", s, g[0].data_ptr(), g[1].data_ptr(), u[0].data_ptr(), u[1].data_ptr(),
-               g[2].data_ptr(), u[2].data_ptr(), x.data_ptr(), None, ctx.perm_token.data_ptr(), offsets,
-               ctx.gate_out.data_ptr(), ctx.up_out.data_ptr(), w.num_experts, w.inter, w.hidden)
+               g[2].data_ptr(), u[2].data_ptr(), x.data_ptr(), None, ctx.perm_token.data_ptr(), offsets, act, n_act,
+               ctx.gate_out.data_ptr(), ctx.up_out.data_ptr(), w.num_experts, w.inter, w.hidden, slots, n,
+               ctx.status.data_ptr())
     _ffi.check("nvk_b200_moe_grouped_w4a16", s, d[0].data_ptr(), d[1].data_ptr(), None, None, d[2].data_ptr(), None,
-               ctx.gate_out.data_ptr(), ctx.up_out.data_ptr(), None, offsets, ctx.down_out.data_ptr(),
-               None, w.num_experts, w.hidden, w.inter)
-    _ffi.check("nv_kernels_moe_unpermute_scatter", s, ctx.down_out.data_ptr(), ctx.topk_weights.data_ptr(),
-               ctx.inv_perm.data_ptr(), ctx.y_acc.data_ptr(), n, k, w.hidden, w.hidden)
+               ctx.gate_out.data_ptr(), ctx.up_out.data_ptr(), None, offsets, act, n_act, ctx.down_out.data_ptr(),
+               None, w.num_experts, w.hidden, w.inter, slots, slots, ctx.status.data_ptr())
+    _ffi.check("nvk_b200_moe_combine", s, ctx.down_out.data_ptr(), ctx.topk_weights.data_ptr(),
+               ctx.inv_perm.data_ptr(), ctx.y_acc.data_ptr(), n, k, w.hidden, w.hidden, slots, ctx.status.data_ptr())
     if w.sharded:
         import torch.distributed as dist
         dist.all_reduce(ctx.y_acc[:n], group=group)

@@ -1,0 +1,56 @@
+"""Build the host emulation of the CUDA library: the product's own .cu sources compiled as C++ with
+-DNVK_EMU against tests/emu (see cuda_emu.h).  Output: tests/emu/build/libnvk_b200_emu.so, loaded
+only by the tests.
+
+    python tests/emu/build_emu.py [--force]
+"""
+from __future__ import annotations
+
+import pathlib
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = pathlib.Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+CSRC = ROOT / "speaches-plus_b200" / "csrc"
+OUT_DIR = HERE / "build"
+LIB = OUT_DIR / "libnvk_b200_emu.so"
+# -O1: fast enough to run, quick to compile; no fast-math and no FMA contraction, so float
+# expressions round the way the kernels' source says (nvcc is likewise given no fast-math).
+CXX_FLAGS = ["-std=c++17", "-O1", "-g", "-fPIC", "-fno-fast-math", "-ffp-contract=off", "-DNVK_EMU", "-Wall",
+             "-Wno-unknown-pragmas", "-Wno-unused-function", "-Wno-unused-variable", "-Wno-sign-compare",
+             f"-I{HERE / 'shim'}", f"-I{HERE}", f"-I{CSRC}"]
+
+
+def _deps_mtime() -> float:
+    files = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(HERE.glob("*.h")) + list(HERE.glob("*.cpp"))
+    return max(f.stat().st_mtime for f in files)
+
+
+def build(force: bool = False) -> pathlib.Path:
+    if not force and LIB.exists() and LIB.stat().st_mtime >= _deps_mtime():
+        return LIB
+    OUT_DIR.mkdir(exist_ok=True)
+    newest_header = max(f.stat().st_mtime for f in list(CSRC.glob("*.cuh")) + list(HERE.glob("*.h")))
+
+    def compile_one(src: pathlib.Path) -> pathlib.Path:
+        obj = OUT_DIR / (src.stem + ".emu.o")
+        if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, newest_header):
+            return obj
+        lang = ["-x", "c++"] if src.suffix == ".cu" else []
+        r = subprocess.run(["g++", *CXX_FLAGS, *lang, "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError(f"emulation build failed on {src.name}")
+        return obj
+
+    srcs = sorted(CSRC.glob("*.cu")) + [HERE / "emu_rt.cpp"]
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(compile_one, srcs))
+    subprocess.run(["g++", "-shared", "-o", str(LIB), *map(str, objs), "-lpthread"], check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

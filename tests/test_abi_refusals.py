@@ -28,7 +28,7 @@ def test_shape_refusals():
     assert f("nv_kernels_gemm_nvfp4_w4a16_mk_dual", S, P, P, None, None, P, P, None, 1.0, 1.0, 4, 48, 64) == -1   # N % 32
     assert f("nvk_b200_linear_nvfp4_w4a16", S, P, P, None, None, P, None, P, None, 1.0, 0.0, 65, 128, 128) == -1  # M > 64
     assert f("nv_kernels_quantize_nvfp4_bf16", S, P, P, P, 1.0, 4, 4, 40) == -1
-    assert f("nvk_b200_moe_grouped_w4a16", S, P, P, None, None, P, None, P, None, None, P, P, None, 4, 64, 48) == -1
+    assert f("nvk_b200_moe_grouped_w4a16", S, P, P, None, None, P, None, P, None, None, P, None, None, P, None, 4, 64, 48, 8, 8, None) == -1
     assert f("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", S, P, P, P, P, P, P, P, 4, 8, 64, 64, 100, 64) == -1    # tile stride
 
 
@@ -45,7 +45,7 @@ def test_argument_refusals():
     assert f("nv_kernels_moe_permute", S, 0, 0, 0, 0, 0, 4, 2, 8) == -2
     assert f("nv_kernels_moe_unpermute_scatter", S, P, P, P, P, 4, 2, 64, 32) == -2           # row stride < hidden
     assert f("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", S, 4, P, P, P, P, P, P, 4, 8, 64, 64, 128, 64) == -2     # alignment
-    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
+    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, None, None, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
     assert f("nvk_b200_set_tuning", 3, 0) == -2 and f("nvk_b200_set_tuning", 0, 48) == -2
     assert f("nvk_b200_set_tuning", 0, 0) == 0
     assert f("nvk_b200_tp_allreduce_bf16", S, P, 2, 2, P, P, 8, 64, P, P) == -2               # rank outside the world
@@ -54,8 +54,8 @@ def test_argument_refusals():
 
 
 def test_resource_and_grid_refusals():
-    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, 4, 257, 4, 0, 0.0, 1, 1.0) == -3   # > 256 experts
-    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, 2000, 8, 4, 0, 0.0, 1, 1.0) == -3  # > 4096 slots
+    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, None, None, 4, 257, 4, 0, 0.0, 1, 1.0) == -3   # > 256 experts
+    assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, None, None, 2000, 8, 4, 0, 0.0, 1, 1.0) == -3  # > 4096 slots
     assert f("nvk_b200_moe_permute_static", S, P, P, P, P, 4, 2, 4097) == -3
     assert f("nv_kernels_rmsnorm_quantize_nvfp4_bf16", S, P, P, P, P, 1.0, 1e-6, 1, 1, 32768) == -3  # row > 48 KiB
     assert f("nv_kernels_gather_rows_bf16_strided", S, P, P, P, 9, 64, 4, 4) == -3

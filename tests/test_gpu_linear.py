@@ -272,6 +272,7 @@ def test_mk_dual_reference_symbol(m):
     assert np.array_equal(U.host_u16(yc), U.host_u16(ya))
 
 
+@pytest.mark.big
 @pytest.mark.parametrize("m", [3, 8, 9, 16, 24, 33, 64])
 @pytest.mark.parametrize("n,k", [(8192, 4096), (6200, 5408), (20480, 5120)])
 def test_workspace_path_is_bit_identical(m, n, k):
@@ -363,6 +364,7 @@ def test_bf16_lm_head_gemv():
         assert U.bf16_ulp_diff(U.host_u16(y), cpu[0]).max() <= 2
 
 
+@pytest.mark.big
 @pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)])
 @pytest.mark.parametrize("m", [1, 4, 16, 64])
 def test_configs1_full_size_sweep(k, n, m):
@@ -464,6 +466,8 @@ def test_persistent_step_equals_the_standalone_launches(m, rows):
         torch.cuda.synchronize()
         step.check()
         assert same()
+    if getattr(U.ffi, "EMULATED", False):
+        return   # graph capture needs the real CUDA runtime
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
         step.run()

@@ -14,7 +14,7 @@ import torch
 from oracle import ref
 from tests import _util as U
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.needs_cuda_runtime]   # the CUTLASS library runs on a GPU only
 
 
 def run_gemm(ap, asw, bp, bsw, alpha, m, n, k, entry="nv_kernels_cutlass_fp4_gemm_sm120_bf16"):

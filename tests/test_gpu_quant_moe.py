@@ -429,16 +429,34 @@ def test_fused_route_permute_equals_the_two_kernels(E, K, mode, n):
                       a[4].data_ptr(), scr.data_ptr(), n, K, E) == 0
     b = bufs()
     assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), dl.data_ptr(), db.data_ptr() if db is not None else None,
-                      b[0].data_ptr(), b[1].data_ptr(), b[2].data_ptr(), b[3].data_ptr(), b[4].data_ptr(), n, E, K, mode,
-                      0.0, 1, scaling) == 0
+                      b[0].data_ptr(), b[1].data_ptr(), b[2].data_ptr(), b[3].data_ptr(), b[4].data_ptr(), None, None, n, E,
+                      K, mode, 0.0, 1, scaling) == 0
     torch.cuda.synchronize()
     for x, y in zip(a, b):
         assert np.array_equal(x.cpu().numpy().view(np.int32), y.cpu().numpy().view(np.int32))
-    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 4, 257, 4, 0, 0.0, 1, 1.0) == -3
-    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
+    # with the list of active experts: same outputs, plus the experts that received slots, ascending
+    c = bufs()
+    act = torch.full((min(E, n * K),), -5, dtype=torch.int32, device="cuda")
+    n_act = torch.full((1,), -5, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), dl.data_ptr(), db.data_ptr() if db is not None else None,
+                      c[0].data_ptr(), c[1].data_ptr(), c[2].data_ptr(), c[3].data_ptr(), c[4].data_ptr(),
+                      act.data_ptr(), n_act.data_ptr(), n, E, K, mode, 0.0, 1, scaling) == 0
+    torch.cuda.synchronize()
+    for x, y in zip(a, c):
+        assert np.array_equal(x.cpu().numpy().view(np.int32), y.cpu().numpy().view(np.int32))
+    want_active = np.unique(a[0].cpu().numpy())
+    assert int(n_act.cpu().numpy()[0]) == want_active.size
+    assert np.array_equal(act.cpu().numpy()[:want_active.size], want_active)
+    # the permutation is the stable sort of the slots by expert
+    flat = a[0].cpu().numpy().ravel()
+    order = np.argsort(flat, kind="stable")
+    assert np.array_equal(a[2].cpu().numpy(), (order // K).astype(np.int32))
+    assert np.array_equal(a[4].cpu().numpy()[order], np.arange(n * K, dtype=np.int32))
+    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 0, 0, 4, 257, 4, 0, 0.0, 1, 1.0) == -3
+    assert U.ffi.call("nvk_b200_moe_route_permute", U.stream(), 0, 0, 0, 0, 0, 0, 0, 0, 0, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
 
 
-@pytest.mark.parametrize("n_tok", [3, 200])
+@pytest.mark.parametrize("n_tok", [3, pytest.param(200, marks=pytest.mark.needs_cuda_runtime)])
 def test_moe_block_matches_the_mixture_formula(n_tok):
     """MoeBlock.forward == sum_j softmax(top-k logits)_j * expert_j(x) + sigmoid(x . w_g) * shared(x)
     (rust/crates/nv-layers/src/moe.rs:1035-1133 checks the same closed form on the Cpu backend).
