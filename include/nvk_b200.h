@@ -110,6 +110,13 @@ int nvk_b200_set_pdl(int enabled);
  * (rust/crates/nv-kernels/cuda/gemv_bf16.cu:22-76,467-533) */
 int nv_kernels_gemv_bf16(void* stream, const uint16_t* W, const uint16_t* x, uint16_t* y, int N, int K);
 
+/* No counterpart with this signature in the reference, which sends a bf16 linear with several rows to
+ * a library GEMM (rust/crates/nv-layers/src/linear.rs:717-804): y [M, N] = bf16(x [M, K] W^T), bf16 W
+ * [N, K], fp32 accumulate, 1 <= M <= 64 (-1 otherwise), in ONE pass over W for all M rows (the lm_head
+ * of a batched decode step).  Needs K % 8 == 0 and 16-byte aligned W and x for that; other shapes and
+ * M == 1 run nv_kernels_gemv_bf16 once per row. */
+int nvk_b200_linear_bf16(void* stream, const uint16_t* W, const uint16_t* x, uint16_t* y, int M, int N, int K);
+
 /* ---- bf16 -> NVFP4 quantizers (byte-exact with nv_quant::nvfp4::quantize_block_with_global,
  *      rust/crates/nv-quant/src/nvfp4.rs:91-129) -------------------------------------------------- */
 

@@ -479,7 +479,8 @@ int nvo_moe_route_topk(const float* logits, const float* bias, int32_t* ids, flo
 /* ---- combine: rust/crates/nv-kernels/cuda/moe_unpermute_scatter.cu:6-32 ----
  * y_acc[n,h] = sum_s w[n,s] * bf16(y_sorted[inv_perm[n,s], h]), f32, s in order.  The reference
  * statement `acc += w * v` is device code, which nvcc contracts to one fused multiply-add; fmaf
- * states that rounding explicitly. */
+ * states that rounding explicitly.  A negative row (a slot the slot sort left out because its
+ * expert id was outside [0, E); the reference has no such rule and would index with it) adds nothing. */
 void nvo_moe_unpermute_scatter(const uint16_t* y_sorted, const float* w, const int32_t* inv_perm,
                                float* y_acc, int n_tokens, int k, int H, int row_stride) {
     for (int n = 0; n < n_tokens; ++n)
@@ -487,6 +488,7 @@ void nvo_moe_unpermute_scatter(const uint16_t* y_sorted, const float* w, const i
             float acc = 0.0f;
             for (int s = 0; s < k; ++s) {
                 int row = inv_perm[n * k + s];
+                if (row < 0) continue;
                 acc = fmaf(w[n * k + s], nvo_bf16_to_f32(y_sorted[(size_t)row * row_stride + h]), acc);
             }
             y_acc[(size_t)n * H + h] = acc;

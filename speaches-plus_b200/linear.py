@@ -292,7 +292,8 @@ class Nvfp4Linear:
 
 
 class Bf16Linear:
-    """bf16 linear used for the lm_head at M=1 (nv_kernels_gemv_bf16); rows loop for M > 1."""
+    """bf16 linear (lm_head, router gate): nv_kernels_gemv_bf16 at M = 1, nvk_b200_linear_bf16 -- one pass
+    over the weight for all rows -- for up to 64 rows, row chunks of 64 beyond that."""
 
     def __init__(self, weight: torch.Tensor):
         assert weight.dtype == torch.bfloat16 and weight.dim() == 2
@@ -310,11 +311,21 @@ class Bf16Linear:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, self.in_features).contiguous()
         y = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
-        s = _stream()
-        for r in range(x2.shape[0]):
-            _ffi.check("nv_kernels_gemv_bf16", s, self.weight.data_ptr(), x2[r].data_ptr(), y[r].data_ptr(),
-                       self.out_features, self.in_features)
+        self.forward_into(x2, y)
         return y.reshape(*x.shape[:-1], self.out_features)
+
+    def forward_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
+        """x2 [M, in] bf16 contiguous -> y [M, out] (contiguous), allocating nothing."""
+        s = _stream()
+        m = x2.shape[0]
+        if m == 1:
+            _ffi.check("nv_kernels_gemv_bf16", s, self.weight.data_ptr(), x2.data_ptr(), y.data_ptr(), self.out_features,
+                       self.in_features)
+            return
+        for r0 in range(0, m, MAX_DECODE_M):
+            mm = min(MAX_DECODE_M, m - r0)
+            _ffi.check("nvk_b200_linear_bf16", s, self.weight.data_ptr(), x2[r0:].data_ptr(), y[r0:].data_ptr(), mm,
+                       self.out_features, self.in_features)
 
     __call__ = forward
 

@@ -364,6 +364,49 @@ def test_bf16_lm_head_gemv():
         assert U.bf16_ulp_diff(U.host_u16(y), cpu[0]).max() <= 2
 
 
+@pytest.mark.parametrize("m", [2, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(1000, 1024), (37, 200), (20000, 264), (128, 2048), (19008, 512)])
+def test_bf16_linear_for_a_few_rows(m, n, k):
+    """nvk_b200_linear_bf16: one pass over W for all rows of x.  Oracle: the reference's Cpu-backend
+    linear (bf16 -> f32 both sides, f32 matmul, bf16 out; rust/crates/nv-layers/src/linear.rs:1148-1161)
+    with its test's bound (linear.rs:2612-2660: relative error below 1e-2), here in the floored form, and
+    an f64 dot.  N = 20000 and 19008 take the warp-per-16-rows kernel, the others split K over a CTA."""
+    U.require_gpu()
+    rng = np.random.default_rng(m * 1000 + n + k)
+    w = U.gauss_bf16(rng, (n, k), 0.02)
+    x = U.gauss_bf16(rng, (m, k))
+    dw, dx = U.dev(w), U.dev(x)
+    y = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nvk_b200_linear_bf16", U.stream(), dw.data_ptr(), dx.data_ptr(), y.data_ptr(), m, n, k) == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[m * n:] == 0x7FC0)
+    got = ref.bf16_to_f32(out[:m * n]).reshape(m, n)
+    want = ref.bf16_to_f32(x).astype(np.float64) @ ref.bf16_to_f32(w).astype(np.float64).T
+    assert U.rel_err_floor(got, want) < 1e-2
+    cpu = ref.linear_cpu_backend(w, x)
+    assert U.rel_err_floor(got, ref.bf16_to_f32(cpu)) < 1e-2
+    # element by element: within 2 bf16 ulp of the sequential f32 dot, or (near a cancellation) within
+    # the f32 summation-order noise of a sum of this size
+    ulp = U.bf16_ulp_diff(out[:m * n].reshape(m, n), cpu)
+    absd = np.abs(got - ref.bf16_to_f32(cpu))
+    rms = float(np.sqrt(np.mean(want ** 2)))
+    assert np.all((ulp <= 2) | (absd <= 2e-3 * rms))
+    assert U.ffi.call("nvk_b200_linear_bf16", U.stream(), dw.data_ptr(), dx.data_ptr(), y.data_ptr(), 65, n, k) == -1
+    assert U.ffi.call("nvk_b200_linear_bf16", U.stream(), dw.data_ptr(), dx.data_ptr(), y.data_ptr(), 0, n, k) == -1
+
+
+def test_bf16_linear_odd_shapes_take_the_row_loop():
+    U.require_gpu()
+    rng = np.random.default_rng(77)
+    m, n, k = 3, 50, 100   # K % 8 != 0
+    w, x = U.gauss_bf16(rng, (n, k), 0.02), U.gauss_bf16(rng, (m, k))
+    y = torch.zeros(m * n, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nvk_b200_linear_bf16", U.stream(), U.dev(w).data_ptr(), U.dev(x).data_ptr(), y.data_ptr(), m, n, k) == 0
+    torch.cuda.synchronize()
+    assert U.bf16_ulp_diff(U.host_u16(y).reshape(m, n), ref.linear_cpu_backend(w, x)).max() <= 2
+
+
 @pytest.mark.big
 @pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)])
 @pytest.mark.parametrize("m", [1, 4, 16, 64])

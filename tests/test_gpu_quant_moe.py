@@ -629,3 +629,124 @@ def test_rmsnorm_bf16_and_the_prenorm_decode_route():
     assert torch.equal(out.view(torch.int16), direct.view(torch.int16))
     want = ref.linear_w4a16_f64(packed, sw, got, alpha, n, k)
     assert U.rel_err_floor(out.float().cpu().numpy(), want) < 1e-4 + 1e-2
+
+
+# ---- routing tables are data, not trusted: nothing may index with an id, offset or row that is out of range ----
+
+def test_router_rows_with_too_few_usable_scores():
+    """NaN never wins, an expert wins at most once, missing winners are id -1 / weight 0 and still take
+    part in the softmax like a padded loop over K entries would."""
+    U.require_gpu()
+    E, K = 16, 4
+    lg = np.zeros((5, E), np.float32)
+    lg[0] = np.nan                                    # nothing usable
+    lg[1] = np.nan; lg[1, [3, 9]] = [1.0, 2.0]        # two usable
+    lg[2] = -np.inf; lg[2, 7] = 0.5                   # -inf is an ordinary (lowest) score: lowest ids first
+    lg[3] = np.arange(E, dtype=np.float32); lg[3, 5] = np.nan
+    lg[4] = 1.0                                       # all tied: lowest ids
+    ids = torch.full((5, K), -9, dtype=torch.int32, device="cuda")
+    w = torch.full((5, K), -9.0, dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_route_topk", U.stream(), U.dev(lg).data_ptr(), None, ids.data_ptr(), w.data_ptr(),
+                      5, E, K, 0, 0.0, 1, 1.0) == 0
+    torch.cuda.synchronize()
+    got, gw = ids.cpu().numpy(), w.cpu().numpy()
+    assert got[0].tolist() == [-1, -1, -1, -1]
+    assert got[1].tolist() == [9, 3, -1, -1]
+    assert got[2].tolist() == [7, 0, 1, 2]
+    assert got[3].tolist() == [15, 14, 13, 12]
+    assert got[4].tolist() == [0, 1, 2, 3]
+    # row 1: softmax over (2, 1, 0, 0), the two padded entries with raw score 0
+    e = np.exp(np.array([2, 1, 0, 0], np.float32) - np.float32(2))
+    np.testing.assert_allclose(gw[1], e / e.sum(), rtol=1e-6)
+    np.testing.assert_allclose(gw[4], 0.25, rtol=1e-6)
+    # rows without degenerate scores equal the oracle exactly
+    wi, ww = ref.moe_route_topk(lg[3:5].copy(), K)
+    assert np.array_equal(got[4], wi[1])
+
+
+def test_slot_sort_and_combine_skip_ids_outside_the_expert_range():
+    U.require_gpu()
+    rng = np.random.default_rng(11)
+    n_tok, k, E, H = 7, 4, 6, 64
+    topk = rng.integers(0, E, (n_tok, k)).astype(np.int32)
+    topk[0, 1] = -1
+    topk[3, 0] = E          # one past the last expert
+    topk[5, 3] = 1 << 20
+    flat = topk.ravel()
+    valid = (flat >= 0) & (flat < E)
+    for entry, with_scratch in (("nv_kernels_moe_permute", True), ("nvk_b200_moe_permute_static", False)):
+        dt = U.dev(topk)
+        perm = torch.full((n_tok * k + 8,), -7, dtype=torch.int32, device="cuda")
+        offs = torch.full((E + 1 + 8,), -7, dtype=torch.int32, device="cuda")
+        inv = torch.full((n_tok * k + 8,), -7, dtype=torch.int32, device="cuda")
+        args = [U.stream(), dt.data_ptr(), perm.data_ptr(), offs.data_ptr(), inv.data_ptr()]
+        scr = None
+        if with_scratch:
+            scr = torch.full((E + 8,), 12345, dtype=torch.int32, device="cuda")   # stale contents, canary tail
+            args.append(scr.data_ptr())
+        assert U.ffi.call(entry, *args, n_tok, k, E) == 0
+        torch.cuda.synchronize()
+        perm_h, offs_h, inv_h = perm.cpu().numpy(), offs.cpu().numpy(), inv.cpu().numpy()
+        assert np.all(perm_h[n_tok * k:] == -7) and np.all(offs_h[E + 1:] == -7) and np.all(inv_h[n_tok * k:] == -7)
+        if scr is not None:
+            assert np.all(scr.cpu().numpy()[E:] == 12345)   # nothing written in front of or behind the counters
+        counts = np.bincount(flat[valid], minlength=E)
+        assert np.array_equal(offs_h[:E + 1], np.concatenate([[0], np.cumsum(counts)]))
+        order = np.argsort(np.where(valid, flat, E), kind="stable")[:valid.sum()]   # stable sort of the valid slots
+        assert np.array_equal(perm_h[:valid.sum()], (order // k).astype(np.int32))
+        assert np.array_equal(inv_h[:n_tok * k][order], np.arange(valid.sum(), dtype=np.int32))
+        assert np.all(inv_h[:n_tok * k][~valid] == -1)
+    # combine: slots with inv_perm -1 add nothing; a row past the sorted buffer is skipped and reported
+    ys = U.gauss_bf16(rng, (n_tok * k, H))
+    wts = rng.random((n_tok, k)).astype(np.float32)
+    inv_c = inv_h[:n_tok * k].copy()
+    want = ref.moe_unpermute_scatter(ys, wts, inv_c.reshape(n_tok, k), H, H)
+    dy, dw, di = U.dev(ys), U.dev(wts), U.dev(inv_c)
+    acc = torch.zeros((n_tok, H), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_unpermute_scatter", U.stream(), dy.data_ptr(), dw.data_ptr(), di.data_ptr(),
+                      acc.data_ptr(), n_tok, k, H, H) == 0
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(acc.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+    inv_bad = inv_c.copy()
+    bad_slot = int(np.flatnonzero(valid)[2])
+    inv_bad[bad_slot] = n_tok * k + 1000
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nvk_b200_moe_combine", U.stream(), dy.data_ptr(), dw.data_ptr(), U.dev(inv_bad).data_ptr(),
+                      acc.data_ptr(), n_tok, k, H, H, n_tok * k, status.data_ptr()) == 0
+    torch.cuda.synchronize()
+    assert int(status.cpu().numpy()[0]) == 4
+    inv_skip = inv_c.copy()
+    inv_skip[bad_slot] = -1
+    want2 = ref.moe_unpermute_scatter(ys, wts, inv_skip.reshape(n_tok, k), H, H)
+    np.testing.assert_allclose(acc.cpu().numpy(), want2, rtol=1e-6, atol=1e-7)
+
+
+def test_grouped_linear_does_not_follow_offsets_or_rows_outside_its_buffers():
+    U.require_gpu()
+    rng = np.random.default_rng(12)
+    E, n, k, slots, x_rows = 3, 128, 64, 6, 4
+    packed = np.zeros((E, n, k // 2), np.uint8)
+    scales = np.zeros((E, ref.swizzled_len(n, k // 16)), np.uint8)
+    alphas = np.zeros(E, np.float32)
+    host = []
+    for e in range(E):
+        p_, s_, a_, _ = U.make_weight(rng, n, k, 0.05)
+        packed[e], scales[e], alphas[e] = p_, s_, a_
+        host.append((p_, s_, a_))
+    x = U.gauss_bf16(rng, (x_rows, k))
+    offsets = np.array([0, 2, 9, 2000], np.int32)            # expert 1 and 2 run past the 6 slots
+    rows = np.array([1, 3, 0, -4, 7, 2], np.int32)            # slots 3 and 4 name rows that do not exist
+    y = torch.full((slots + 4, n), 0x7FC0, dtype=torch.int16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dev = [U.dev(a) for a in (packed, scales, alphas, x, rows, offsets)]
+    assert U.ffi.call("nvk_b200_moe_grouped_w4a16", U.stream(), dev[0].data_ptr(), dev[1].data_ptr(), None, None,
+                      dev[2].data_ptr(), None, dev[3].data_ptr(), None, dev[4].data_ptr(), dev[5].data_ptr(), None,
+                      None, y.data_ptr(), None, E, n, k, slots, x_rows, status.data_ptr()) == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[slots:] == 0x7FC0)                      # nothing past the last slot
+    assert int(status.cpu().numpy()[0]) == 3                  # both kinds of violation reported
+    for slot, e in ((0, 0), (1, 0), (2, 1), (5, 1)):
+        want = ref.linear_w4a16_f64(host[e][0], host[e][1], x[rows[slot]:rows[slot] + 1], host[e][2], n, k)
+        assert U.rel_err_floor(ref.bf16_to_f32(out[slot]), want[0]) < 1e-2
+    assert np.all(out[3] == 0) and np.all(out[4] == 0)        # rows that do not exist read as zeros

@@ -3,9 +3,8 @@
 Hosts that have no device memory left to allocate (a server whose KV-cache pool took all of it), that
 cannot pay for an allocation's device-wide synchronisation inside the decode loop, or whose FFI rule is
 that the C side never allocates, call this entry point instead of nv_kernels_moe_permute: it needs no
-scratch argument because its counters live in a fixed array inside the library.  This file is
-collected last so that a run stopping at the first failure has already run every other test; the
-test also passes on its own in a fresh process (its first call does the one-time address look-up).
+scratch argument because its counters live in a fixed array inside the library.  The test also
+passes on its own in a fresh process (its first call does the one-time address look-up).
 """
 import numpy as np
 import pytest
@@ -47,6 +46,10 @@ def test_static_permute_matches_the_scratch_version_twice_in_a_row():
         counts = np.bincount(topk.ravel(), minlength=E)
         assert np.array_equal(offs, np.concatenate([[0], np.cumsum(counts)]))
         assert sorted(inv) == list(range(n_tok * k))
+        # checked on its own too, not only against the other entry point: the stable sort by expert
+        order = np.argsort(topk.ravel(), kind="stable")
+        assert np.array_equal(perm, (order // k).astype(np.int32))
+        assert np.array_equal(inv[order], np.arange(n_tok * k, dtype=np.int32))
 
 
 def test_static_permute_refuses_more_experts_than_the_array_holds():
