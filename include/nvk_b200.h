@@ -170,6 +170,65 @@ int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16,
                                            uint8_t* packed_out, uint8_t* scales_out_swizzled, float stored_global,
                                            float eps, int m_padded, int m_logical, int K);
 
+/* ---- W4A8 decode MLP: NVFP4 weights x int8 activation rows (one dequant scale per row) -----------
+ *   y[m, n] = bf16( fma( sum_k W[n, k] * q[m, k],  alpha * scale[m],  residual[m, n] ) )
+ * W = e2m1 x ue4m3 block scale, q int8 in [-127, 127], fp32 accumulate, one rounding.  N, K > 0 and
+ * K % 32 == 0 (-1 otherwise, nothing launched); weights and scales 16-byte aligned, x_q8 8-byte
+ * aligned, no NULL operand except residual (-2).  The reference refuses K > 98304 (its shared-memory
+ * staging); this library has no such limit.
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:627-715, 746-776
+ * (rust/crates/nv-kernels/cuda/gemv_nvfp4_w4a8_decode.cu) */
+int nv_kernels_gemv_nvfp4_w4a8_dual_m1(void* stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
+                                       const uint8_t* sc_b, const int8_t* x_q8, const float* x_dequant_scale,
+                                       uint16_t* y_a, uint16_t* y_b, float alpha_a, float alpha_b, int N, int K);
+int nv_kernels_gemv_nvfp4_w4a8_dual_mk(void* stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
+                                       const uint8_t* sc_b, const int8_t* x_q8, const float* x_dequant_scales,
+                                       uint16_t* y_a, uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K);
+int nv_kernels_gemv_nvfp4_w4a8_down_residual_m1(void* stream, const uint8_t* wq, const uint8_t* sc, const int8_t* x_q8,
+                                                const float* x_dequant_scale, const uint16_t* residual, uint16_t* y,
+                                                float alpha, int N, int K);
+int nv_kernels_gemv_nvfp4_w4a8_down_residual_mk(void* stream, const uint8_t* wq, const uint8_t* sc, const int8_t* x_q8,
+                                                const float* x_dequant_scales, const uint16_t* residual, uint16_t* y,
+                                                float alpha, int M, int N, int K);
+/* ... and leaves 1/rms of the new row for the next RMSNorm: rstd_ssq_count_pack = {rstd, running sum
+ * of squares, arrival count} (three 32-bit words the caller zeroes once); after the launch word 0 is
+ * rsqrt(sum(y^2) / N + rstd_eps) and words 1, 2 are zero again.  The CTAs' partial sums are added in
+ * arrival order (as in the reference), so word 0 may differ in its last bits between runs. */
+int nv_kernels_gemv_nvfp4_w4a8_down_residual_m1_rstd_emit(void* stream, const uint8_t* wq, const uint8_t* sc,
+                                                          const int8_t* x_q8, const float* x_dequant_scale,
+                                                          const uint16_t* residual, uint16_t* y, float alpha,
+                                                          float* rstd_ssq_count_pack, float rstd_eps, int N, int K);
+/* The down projection reading the staged bf16 activation of nv_kernels_silu_mul_stage_partial_absmax_m1
+ * and quantizing it to int8 while it stages it: bit-identical to nv_kernels_silu_mul_rowquant_i8_m1
+ * followed by nv_kernels_gemv_nvfp4_w4a8_down_residual_m1.  num_partials > 0 (-1 otherwise). */
+int nv_kernels_gemv_nvfp4_w4a8_down_residual_quant_prologue_m1(void* stream, const uint8_t* wq, const uint8_t* sc,
+                                                               const uint16_t* act_staged_bf16,
+                                                               const float* partial_absmax, int num_partials,
+                                                               const uint16_t* residual, uint16_t* y, float alpha, int N,
+                                                               int K);
+/* act = bf16(SiLU(gate) * up); scale = max|act| / 127; q = clamp(rn(act / scale), +-127) (ties to even).
+ * _m1: one row, K % 4 == 0 and K * 2 bytes <= 96 KiB (-1 otherwise).  _mk: M rows in two passes --
+ * act_staged_bf16 [M, K] and partial_absmax [nv_kernels_silu_mul_rowquant_i8_mk_partials_len(M, K)]
+ * are caller buffers; K % 16 == 0.  _stage_partial_absmax_m1 is the first pass alone for one row. */
+int nv_kernels_silu_mul_rowquant_i8_m1(void* stream, const uint16_t* gate, const uint16_t* up, int8_t* act_q8,
+                                       float* act_dequant_scale, int K);
+int nv_kernels_silu_mul_rowquant_i8_mk_partials_len(int M, int K);
+int nv_kernels_silu_mul_rowquant_i8_mk(void* stream, const uint16_t* gate, const uint16_t* up, uint16_t* act_staged_bf16,
+                                       float* partial_absmax, int8_t* act_q8, float* act_dequant_scales, int M, int K);
+int nv_kernels_silu_mul_stage_partial_absmax_m1(void* stream, const uint16_t* gate, const uint16_t* up,
+                                                uint16_t* act_staged_bf16, float* partial_absmax, int K);
+/* res_out = bf16(x + res_in); v = bf16(res_out * rsqrt(mean((x + res_in)^2) + eps) * weight).
+ * _rowquant_i8_m1 (one row, hidden <= 24576 else -1) quantizes v to int8 like the kernels above;
+ * _bf16 writes v for `batch` rows.
+ * replace rust/crates/nv-kernels/include/nv_kernels.h:717-727 (cuda/gemv_nvfp4_w4a8_decode.cu:323-386)
+ * and :1195-1205 (cuda/rmsnorm_residual_writeout.cu) */
+int nv_kernels_rmsnorm_residual_writeout_rowquant_i8_m1(void* stream, const uint16_t* x, const uint16_t* res_in,
+                                                        const uint16_t* weight, uint16_t* res_out, int8_t* out_q8,
+                                                        float* out_dequant_scale, int hidden, float eps);
+int nv_kernels_rmsnorm_residual_writeout_bf16(void* stream, const uint16_t* x, const uint16_t* res_in,
+                                              const uint16_t* weight, uint16_t* res_out, uint16_t* out, size_t batch,
+                                              size_t hidden, float eps);
+
 /* ---- MoE decode ------------------------------------------------------------------------------ */
 
 /* mode 0: top-K of the (optionally tanh soft-capped) logits, softmax over the K winners;

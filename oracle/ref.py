@@ -289,5 +289,39 @@ def moe_unpermute_scatter(y_sorted_bits, weights, inv_perm, hidden: int, row_str
     return out
 
 
+def rowquant_i8(x_f32):
+    """Per-row int8 quantizer of the W4A8 route: scale = max|x| / 127 (f32), q = clamp(rn(x * (1 / scale)), +-127),
+    ties to even -- the host statement in rust/crates/nv-kernels/tests/gemv_nvfp4_w4a8_decode_parity.rs:19-29
+    (and cuda/gemv_nvfp4_w4a8_decode.cu:146-183).  x [rows, K] f32 -> (q int8 [rows, K], scales f32 [rows])."""
+    x = np.atleast_2d(_c(x_f32, np.float32))
+    amax = np.max(np.abs(x), axis=1).astype(np.float32)
+    scale = (amax / np.float32(127.0)).astype(np.float32)
+    inv = np.where(scale > 0, np.float32(1.0) / np.where(scale > 0, scale, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+    q = np.clip(np.rint((x * inv[:, None]).astype(np.float32)), -127, 127).astype(np.int8)   # rint: ties to even
+    return q, scale
+
+
+def linear_w4a8_f64(packed, scales_sw, q_i8, x_scales, alpha: float, n: int, k: int, residual_bits=None) -> np.ndarray:
+    """y = residual + alpha * scale[m] * sum_k W[n,k] q[m,k] in f64 (integer-exact block dots): the
+    "int8 mechanics oracle" of gemv_nvfp4_w4a8_decode_parity.rs:130-190."""
+    w = dequantize_packed_swizzled(packed, scales_sw, n, k, 1.0).astype(np.float64).reshape(n, k)
+    q = np.atleast_2d(np.asarray(q_i8)).astype(np.float64)
+    y = (q @ w.T) * (np.float64(np.float32(alpha)) * np.asarray(x_scales, np.float32).astype(np.float64))[:, None]
+    if residual_bits is not None:
+        y = y + bf16_to_f32(residual_bits).astype(np.float64).reshape(y.shape)
+    return y
+
+
+def rmsnorm_residual(x_bits, res_bits, w_bits, eps: float):
+    """s = x + res (f32), res_out = bf16(s), rstd = 1 / sqrt(mean(s^2) + eps) with s unrounded, v =
+    bf16(res_out * rstd * w): rust/crates/nv-kernels/cuda/rmsnorm_residual_writeout.cu:6-52.  Returns
+    (res_out bits, v bits), the mean taken in f64 (the device sums in f32 in its own order)."""
+    s = bf16_to_f32(x_bits) + bf16_to_f32(res_bits)
+    res_out = f32_to_bf16(s)
+    rstd = np.float32(1.0 / np.sqrt(np.mean(s.astype(np.float64) ** 2, axis=-1, keepdims=True) + np.float64(np.float32(eps))))
+    v = f32_to_bf16((bf16_to_f32(res_out) * rstd).astype(np.float32) * bf16_to_f32(w_bits))
+    return res_out, v
+
+
 def num_threads() -> int:
     return int(lib().nvo_num_threads())

@@ -62,6 +62,18 @@ SIGNATURES = {
     "nvk_b200_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "nv_kernels_moe_route_gather_quant_m1": [_vp] * 12 + [_i, _i, _i, _f, _i, _f, _i, _i, _i],
     "nv_kernels_prof_timestamp": [_vp, _vp],
+    "nv_kernels_gemv_nvfp4_w4a8_dual_m1": [_vp] * 9 + [_f, _f, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a8_dual_mk": [_vp] * 9 + [_f, _f, _i, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a8_down_residual_m1": [_vp] * 7 + [_f, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a8_down_residual_m1_rstd_emit": [_vp] * 7 + [_f, _vp, _f, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a8_down_residual_mk": [_vp] * 7 + [_f, _i, _i, _i],
+    "nv_kernels_gemv_nvfp4_w4a8_down_residual_quant_prologue_m1": [_vp] * 5 + [_i, _vp, _vp, _f, _i, _i],
+    "nv_kernels_silu_mul_rowquant_i8_m1": [_vp] * 5 + [_i],
+    "nv_kernels_silu_mul_rowquant_i8_mk_partials_len": [_i, _i],
+    "nv_kernels_silu_mul_rowquant_i8_mk": [_vp] * 7 + [_i, _i],
+    "nv_kernels_silu_mul_stage_partial_absmax_m1": [_vp] * 5 + [_i],
+    "nv_kernels_rmsnorm_residual_writeout_rowquant_i8_m1": [_vp] * 7 + [_i, _f],
+    "nv_kernels_rmsnorm_residual_writeout_bf16": [_vp] * 6 + [C.c_size_t, C.c_size_t, _f],
     "nvk_b200_moe_permute_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_moe_grouped_fp4_gemv_m1_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll],
 }

@@ -25,7 +25,7 @@ template <int NT, bool DUAL, int PRO, int UG, int KW>
 __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
-    TileView t;
+    TileView t = {};
     t.wq = p.wq[arm];
     t.sc = p.sc[arm];
     t.x = p.x;
@@ -47,7 +47,7 @@ template <int NT, bool DUAL>
 __global__ void __launch_bounds__(256, NT >= 4 ? 1 : 2) w4a16_mma_ws_kernel(const GemmParams p, const uint8_t* ws) {
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
-    TileView t;
+    TileView t = {};
     t.wq = p.wq[arm];
     t.sc = p.sc[arm];
     t.x = nullptr;
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(256, 3) w4a16_grouped_kernel(const GemmParams 
     if (end <= begin) return;
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
-    TileView t;
+    TileView t = {};
     t.wq = p.wq[arm] + (size_t)e * g.w_stride;
     t.sc = p.sc[arm] + (size_t)e * g.sc_stride;
     t.x = p.x;
@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(256, 3) w4a4_m1_grouped_kernel(const GemmParam
                 if (tile * kRowsPerCta + r < p.N) y[tile * kRowsPerCta + r] = 0;
         return;
     }
-    TileView t;
+    TileView t = {};
     t.wq = p.wq[0] + (size_t)e * g.w_stride;
     t.sc = p.sc[0] + (size_t)e * g.sc_stride;
     t.x = reinterpret_cast<const uint16_t*>(g.a_packed + (size_t)grp * g.a_group_bytes);

@@ -84,7 +84,7 @@ __device__ __forceinline__ void run_item(const StackOp& op, int item, int M, con
     p.x_stride = op.x_stride;
     p.ring_off = op.ring_off;
     const int arm = item >= op.tiles_per_arm ? 1 : 0;
-    TileView t;
+    TileView t = {};
     t.wq = op.wq[arm];
     t.sc = op.sc[arm];
     t.x = op.x;

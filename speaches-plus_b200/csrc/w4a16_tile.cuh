@@ -91,7 +91,32 @@ struct TileView {
     const unsigned* gate;    // arrival counter of the operation that produces x (null: nothing to wait for)
     unsigned gate_target;    // arrivals that mean "complete"
     int* gate_err;           // set to 1 when the wait gives up
+    // Used only when EPI == 1 (the output is a residual update and/or carries a per-token multiplier):
+    const uint16_t* residual;   // [M, N] bf16 added to the product before the single rounding, or null
+    const float* row_scale;     // [M] per-token multiplier (an int8 row's dequant scale), or null
+    float* rstd_pack;           // {rstd, sum of squares, arrival count}: see emit_rstd; or null
+    float rstd_eps;
+    unsigned rstd_blocks;       // CTAs of the launch (each arrives once)
+    // Used only when PRO == 5 (the int8 scale is derived here from partial maxima):
+    const float* absmax_partials;
+    int n_partials;
 };
+
+// The last CTA of a launch to arrive turns the launch's sum of squared outputs into the next
+// RMSNorm's 1/rms: pack[0] = rsqrt(pack[1] / n + eps), then pack[1] and the arrival count return to
+// zero for the next launch.  The float additions of the CTAs' partial sums arrive in no fixed order.
+__device__ __forceinline__ void emit_rstd(float* pack, float block_ssq, unsigned blocks, int n, float eps) {
+    atomicAdd(&pack[1], block_ssq);
+    __threadfence();
+    unsigned* count = reinterpret_cast<unsigned*>(pack) + 2;
+    const unsigned prev = atomicInc(count, blocks - 1u);
+    if (prev == blocks - 1u) {
+        __threadfence();
+        const float ssq = *reinterpret_cast<volatile float*>(&pack[1]);
+        pack[0] = rsqrtf(ssq / (float)n + eps);
+        pack[1] = 0.f;
+    }
+}
 
 // How a tile sits in its launch.  LaunchHooks: one tile per CTA, K split over the CTAs along
 // gridDim.x (a cluster when there is more than one), activations written by an earlier kernel.
@@ -103,11 +128,15 @@ struct LaunchHooks {
 };
 
 // PRO: 0 = bf16 activations; 1 = bf16(SiLU(x) * x2); 2 = an NVFP4 activation row whose scales are row 0
-// of a 128x4 swizzled tile; 3 = an NVFP4 activation row with a flat [K/16] scale array.
+// of a 128x4 swizzled tile; 3 = an NVFP4 activation row with a flat [K/16] scale array; 4 = int8
+// activation rows (their dequant scales are applied in the epilogue through row_scale); 5 = one bf16
+// activation row quantized to int8 here, scale = max(absmax_partials) / 127.
+// EPI: 0 = y = bf16(alpha * sum); 1 = y = bf16(fma(sum, alpha * row_scale, residual)), optionally
+// followed by emit_rstd over the launch's outputs.
 // XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
 // in a caller-supplied workspace; the CTA streams them through a shared ring next to the weights
 // instead of converting its whole K range itself.  Needs KW == 1 (all warps walk K together).
-template <int NT, int PRO, int UG, int KW, bool XWS = false, class HK = LaunchHooks>
+template <int NT, int PRO, int UG, int KW, bool XWS = false, class HK = LaunchHooks, int EPI = 0>
 __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& t) {
     static_assert(!XWS || KW == 1, "the shared activation ring needs every warp on the same K step");
     constexpr int THREADS = 32 * UG * KW;
@@ -118,6 +147,8 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     __shared__ uint32_t s_amax[MT];   // slice maximum (bf16 magnitude bits), then f32 bits of 2^-pw
     __shared__ int s_pw[MT];          // power of two currently folded into the accumulators
     __shared__ float s_rescale[MT];   // 2^(pw_old - pw_new) at a phase boundary
+    __shared__ float s_q8[2];         // PRO == 5: the int8 row's dequant scale and its reciprocal
+    __shared__ float s_ssq[32];       // EPI == 1: per-warp sums of squared outputs
 
     cg::cluster_group cluster = cg::this_cluster();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -261,6 +292,21 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     }
     if (t.pdl) nvk::ptx::pdl_wait();
     HK::before_activations(t);
+    if (PRO == 5) {
+        // row maximum = the largest partial maximum (first warp), then scale = max / 127
+        if (warp == 0) {
+            float a = 0.f;
+            for (int i = lane; i < t.n_partials; i += 32) a = fmaxf(a, t.absmax_partials[i]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            if (lane == 0) {
+                const float scale = a / 127.0f;
+                s_q8[0] = scale;
+                s_q8[1] = scale > 0.f ? 1.0f / scale : 0.f;
+            }
+        }
+        __syncthreads();
+    }
 
     for (int p0 = sc_begin; p0 < sc_end; p0 += p.ph) {
         const int pend = min(sc_end, p0 + p.ph);
@@ -289,6 +335,31 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
                     if (t.status != nullptr) atomicOr(t.status, 2);
                     return false;
                 }
+            }
+            if (PRO == 4) {
+                // int8 row: the integers (at most 7 bits) are exact as bf16
+                const uint2 q8 = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(t.x) + (size_t)xrow * K + k);
+                const uint32_t qs[2] = {q8.x, q8.y};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float lo = (float)(int)(int8_t)((qs[i >> 1] >> (16 * (i & 1))) & 0xFFu);
+                    const float hi = (float)(int)(int8_t)((qs[i >> 1] >> (16 * (i & 1) + 8)) & 0xFFu);
+                    ws[i] = (uint32_t)nvk::f32_to_bf16_bits(lo) | ((uint32_t)nvk::f32_to_bf16_bits(hi) << 16);
+                }
+                return true;
+            }
+            if (PRO == 5) {
+                // bf16 row -> int8 with the row scale derived above: q = clamp(rn(v / scale), +-127)
+                const uint4 v = HK::load_x(t.x + (size_t)xrow * K + k);
+                const uint32_t vs[4] = {v.x, v.y, v.z, v.w};
+                const float inv = s_q8[1];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int q0 = max(-127, min(127, __float2int_rn(nvk::bf16_bits_to_f32(vs[i] & 0xFFFFu) * inv)));
+                    const int q1 = max(-127, min(127, __float2int_rn(nvk::bf16_bits_to_f32(vs[i] >> 16) * inv)));
+                    ws[i] = (uint32_t)nvk::f32_to_bf16_bits((float)q0) | ((uint32_t)nvk::f32_to_bf16_bits((float)q1) << 16);
+                }
+                return true;
             }
             if (PRO >= 2) {
                 // NVFP4 activation row: eight e2m1 values times their block's ue4m3 scale.  The product
@@ -409,6 +480,24 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     if (sc_begin >= sc_end && threadIdx.x < MT) s_pw[threadIdx.x] = 0;  // empty slice: acc is zero
     }  // !XWS
 
+    // y for (token m, row r) from the finished sum v (the activation power of two already undone)
+    float ssq = 0.f;   // EPI == 1 with rstd_pack: this thread's sum of squared (rounded) outputs
+    auto finish = [&](float v, int m, int r, uint16_t* __restrict__ y, float alpha) {
+        uint16_t out;
+        if (EPI == 0) {
+            out = nvk::f32_to_bf16_bits(v * alpha);
+        } else {
+            float mult = alpha;
+            if (PRO == 5) mult *= s_q8[0];
+            if (t.row_scale != nullptr) mult *= t.row_scale[m];
+            const float base = t.residual != nullptr ? nvk::bf16_bits_to_f32(t.residual[(size_t)m * N + r]) : 0.f;
+            out = nvk::f32_to_bf16_bits(fmaf(v, mult, base));
+            const float o = nvk::bf16_bits_to_f32(out);
+            ssq = fmaf(o, o, ssq);
+        }
+        y[(size_t)m * N + r] = out;
+    };
+
     if (KW == 1 && nranks == 1) {
         // One warp saw the whole of K for its rows: the accumulator fragment is the result.
         const float alpha1 = t.alpha;
@@ -421,13 +510,11 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
                 const int r = row0 + 32 * (j >> 1);
                 if (m < M && r < N) {
                     const float d = __uint_as_float((uint32_t)(127 + s_pw[m]) << 23);
-                    y1[(size_t)m * N + r] = nvk::f32_to_bf16_bits((acc[n][j] * d) * alpha1);
+                    finish(acc[n][j] * d, m, r, y1, alpha1);
                 }
             }
         }
-        return;
-    }
-
+    } else {
     // ---- sum the K-warps of this CTA: red[kw][token][row] ----
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem);
@@ -476,9 +563,47 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
         // undo the local row numbering: rl = ul*16 + i*8 + g, unit = (sub % SUB)*UG + ul
         const int uu = (sub % SUB) * UG + (rl >> 4);
         const int n_out = mt * kRowsPerCta + 32 * (2 * (uu & 1) + ((rl >> 3) & 1)) + 8 * (uu >> 1) + (rl & 7);
-        if (n_out < N) y[(size_t)m * N + n_out] = nvk::f32_to_bf16_bits(v * alpha);
+        if (n_out < N) finish(v, m, n_out, y, alpha);
     }
     if (nranks > 1) cluster.sync();  // peers may still be reading this CTA's partial
+    }
+
+    if (EPI == 1 && t.rstd_pack != nullptr) {
+        // CTA's sum of squares: lanes, then warps in order, then one arrival for the whole CTA
+        ssq = nvk::warp_sum(ssq);
+        if (lane == 0) s_ssq[warp] = ssq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float blk = 0.f;
+            for (int w = 0; w < THREADS / 32; ++w) blk += s_ssq[w];
+            emit_rstd(t.rstd_pack, blk, t.rstd_blocks, N, t.rstd_eps);
+        }
+    }
+}
+
+// Host side: lays out one launch's dynamic shared memory ([staged activations or reduction scratch |
+// weight ring]) for a CTA of 8 warps owning one 128-row scale tile (UG = 8, KW = 1) with K split over
+// `ksplit` CTAs, and returns its size.  M tokens, MT = 8 * NT token columns.
+inline size_t tile_layout_rows128(GemmParams& p, int M, int MT, int ksplit) {
+    constexpr int RS = 128 + 4;
+    int ph_cap = (48 * 1024) / ((M > 1 ? M : 1) * 512);
+    if (ph_cap < 1) ph_cap = 1;
+    p.spc = nvk::ceil_div(p.nsc, ksplit);
+    p.ph = ph_cap < p.spc ? ph_cap : p.spc;
+    if (p.ph < 1) p.ph = 1;
+    p.x_stride = p.ph * 512 + 64;
+    const size_t smem_x = (size_t)M * p.x_stride;
+    const size_t smem_red = (size_t)2 * MT * RS * sizeof(float);
+    p.ring_off = (int)(((smem_x > smem_red ? smem_x : smem_red) + 127) / 128 * 128);
+    return (size_t)p.ring_off + (size_t)8 * kDepth * kSlotBytes;
+}
+
+// K split for a launch of `ctas` row-tile CTAs: over a cluster, only while the row tiles alone leave
+// SMs idle and every CTA keeps at least two super-chunks.
+inline int tile_ksplit(int ctas, int nsc) {
+    int ksplit = 1;
+    while (ksplit < 8 && ctas * ksplit < 148 && nvk::ceil_div(nsc, ksplit * 2) >= 2) ksplit *= 2;
+    return ksplit;
 }
 
 }  // namespace

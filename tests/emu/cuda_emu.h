@@ -205,6 +205,7 @@ static inline uint32_t __float_as_uint(float f) { uint32_t u; memcpy(&u, &f, 4);
 static inline int __float_as_int(float f) { int u; memcpy(&u, &f, 4); return u; }
 static inline float __int_as_float(int u) { float f; memcpy(&f, &u, 4); return f; }
 static inline float rsqrtf(float x) { return 1.0f / sqrtf(x); }
+static inline int __float2int_rn(float x) { return (int)nearbyintf(x); }   // round to nearest even (default mode)
 static inline int __popc(unsigned v) { return __builtin_popcount(v); }
 static inline int __ffs(int v) { return __builtin_ffs(v); }
 static inline int __clz(int v) { return v == 0 ? 32 : __builtin_clz((unsigned)v); }
@@ -260,6 +261,11 @@ static inline unsigned atomicMax(unsigned* p, unsigned v) {
 static inline int atomicMax(int* p, int v) {
     int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
     while (old < v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {}
+    return old;
+}
+static inline unsigned atomicInc(unsigned* p, unsigned limit) {   // old >= limit ? 0 : old + 1
+    unsigned old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+    while (!__atomic_compare_exchange_n(p, &old, old >= limit ? 0u : old + 1u, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {}
     return old;
 }
 static inline int atomicExch(int* p, int v) { return __atomic_exchange_n(p, v, __ATOMIC_SEQ_CST); }
