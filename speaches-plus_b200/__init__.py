@@ -7,6 +7,6 @@ library is missing or a launcher refuses the call.
 from . import _ffi as ffi  # noqa: F401
 from .linear import Nvfp4Linear, Bf16Linear, Nvfp4Mlp, quantize_weight_nvfp4, swizzled_scale_bytes  # noqa: F401
 from .moe import (MoeGroupedWeights, GroupedDecodeContext, forward_grouped_decode, forward_grouped,  # noqa: F401
-                  plan_routing, MoeBlock, MoeConfig)
+                  plan_routing, MoeBlock, MoeConfig, TiledDecodeContext, forward_grouped_decode_into)
 from . import weights  # noqa: F401,E402
 from .stack import DecodeStep  # noqa: F401,E402

@@ -35,8 +35,15 @@ class MoeGroupedWeights:
     [E, sc_bytes], alphas [E] for gate, up ([inter, hidden]) and down ([hidden, inter])."""
 
     def __init__(self, gate, up, down, hidden: int, inter: int, num_experts: int, first_expert: int = 0,
-                 total_experts: int | None = None):
+                 total_experts: int | None = None, input_globals_gate_up=None, input_globals_down=None):
         self.gate, self.up, self.down = gate, up, down  # each: (packed, scales, alphas)
+        # stored activation globals per expert for the route that quantizes activations (f32 [E] on the
+        # banks' device; ones when a checkpoint carries none) -- moe_grouped.rs `input_globals_*`
+        dev = gate[0].device
+        self.folded_shared = gate[0].shape[0] == num_experts + 1   # a shared expert stored as bank entry E
+        ones = lambda: torch.ones(gate[0].shape[0], dtype=torch.float32, device=dev)   # noqa: E731
+        self.input_globals_gate_up = ones() if input_globals_gate_up is None else input_globals_gate_up
+        self.input_globals_down = ones() if input_globals_down is None else input_globals_down
         self.hidden, self.inter, self.num_experts = hidden, inter, num_experts
         # expert parallelism: this object holds experts [first_expert, first_expert + num_experts) of
         # a layer with total_experts routed experts
@@ -62,8 +69,13 @@ class MoeGroupedWeights:
                                  self.num_experts)
 
     @classmethod
-    def build_from_experts(cls, experts):
-        """experts: list of (gate, up, down) Nvfp4Linear triples."""
+    def build_from_experts(cls, experts, shared=None):
+        """experts: list of (gate, up, down) Nvfp4Linear triples; `shared`: one more triple of the same
+        shapes stored after them as bank entry E (the shared expert folded into the routed step,
+        moe_grouped.rs `folded_shared`)."""
+        n_routed = len(experts)
+        if shared is not None:
+            experts = list(experts) + [shared]
         e0 = experts[0]
         hidden, inter = e0[0].in_features, e0[0].out_features
 
@@ -75,7 +87,7 @@ class MoeGroupedWeights:
             alphas = torch.tensor([l.alpha_w4a16 for l in lins], dtype=torch.float32, device=packed.device)
             return packed, scales, alphas
 
-        return cls(bank(0), bank(1), bank(2), hidden, inter, len(experts))
+        return cls(bank(0), bank(1), bank(2), hidden, inter, n_routed)
 
     def per_expert_bytes(self) -> int:
         """Packed + scale bytes of one expert (rust/crates/nv-layers/src/moe_grouped.rs `per_expert_bytes`)."""
@@ -165,6 +177,124 @@ def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: t
         import torch.distributed as dist
         dist.all_reduce(ctx.y_acc[:n], group=group)
     return ctx.y_acc[:n]
+
+
+# ------------------------------------------------------------------------------------------------
+# decode on the route that quantizes activations (FP4 x FP4), every (token, winner) pair a tile
+class TiledDecodeContext:
+    """Buffers of `forward_grouped_decode_into` (rust/crates/nv-layers/src/moe_grouped.rs:575-782): every
+    (token, winner) pair -- plus one pair per token for a shared expert folded in as expert id E --
+    owns a 128-row tile of which row 0 is live.  Everything is allocated here, once; the step itself
+    allocates nothing.  Inputs are written into `x_in` / `logits_f32`, the result is read from `y_acc`."""
+
+    def __init__(self, w: MoeGroupedWeights, n_tokens: int, top_k: int, device, folded_shared: bool = False):
+        if top_k <= 0 or n_tokens <= 0:
+            raise ValueError("TiledDecodeContext: k and n_tokens must be > 0")
+        self.k, self.n_tokens, self.folded_shared = top_k, n_tokens, folded_shared
+        self.tiles_per_token = top_k + (1 if folded_shared else 0)
+        tiles = n_tokens * self.tiles_per_token
+        m_total = tiles * MIN_TILE
+        self.hidden, self.inter, self.num_experts = w.hidden, w.inter, w.total_experts
+        i32 = dict(dtype=torch.int32, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        u8 = dict(dtype=torch.uint8, device=device)
+        bf = dict(dtype=torch.bfloat16, device=device)
+        src = torch.full((m_total,), -1, dtype=torch.int32)
+        src[::MIN_TILE] = torch.arange(tiles, dtype=torch.int32) // self.tiles_per_token
+        self.src_idx = src.to(device)                                       # tile row 0 <- its token
+        self.inv_perm = (torch.arange(tiles, dtype=torch.int32) * MIN_TILE).to(device)
+        self.topk_ids = torch.zeros(tiles, **i32)
+        self.topk_weights = torch.zeros(tiles, **f32)
+        self.input_gu_mini = torch.zeros(tiles, **f32)
+        self.input_dn_mini = torch.zeros(tiles, **f32)
+        self.x_sorted = torch.zeros((m_total, w.hidden), **bf)
+        self.x_fp4 = torch.zeros((m_total, w.hidden // 2), **u8)
+        self.x_sf = torch.zeros(L.swizzled_scale_bytes(m_total, w.hidden), **u8)
+        self.y_gate = torch.zeros((m_total, w.inter), **bf)
+        self.y_up = torch.zeros((m_total, w.inter), **bf)
+        self.y_act_fp4 = torch.zeros((m_total, w.inter // 2), **u8)
+        self.y_act_sf = torch.zeros(L.swizzled_scale_bytes(m_total, w.inter), **u8)
+        self.y_down = torch.zeros((m_total, w.hidden), **bf)
+        self.x_in = torch.zeros((n_tokens, w.hidden), **bf)
+        self.logits_f32 = torch.zeros((n_tokens, w.total_experts), **f32)
+        self.y_acc = torch.zeros((n_tokens, w.hidden), **f32)
+        # FP4 x FP4 multipliers: the reciprocal of the weight global times the reciprocal of the
+        # activation global the tile was quantized with
+        self.alphas = tuple((bank[2] / g).contiguous() for bank, g in
+                            ((w.gate, w.input_globals_gate_up), (w.up, w.input_globals_gate_up),
+                             (w.down, w.input_globals_down)))
+
+
+def forward_grouped_decode_into(w: MoeGroupedWeights, ctx: TiledDecodeContext, bias=None, mode: int = 0,
+                                softcap: float = 0.0, norm_topk: bool = True, routed_scaling: float = 1.0,
+                                run_scatter: bool = True, prof_base: int | None = None) -> None:
+    """One decode step over the context's own buffers (moe_grouped.rs:1137-1495): route; each tile's
+    activation globals; quantize the token's row per tile; gate and up as grouped M = 1 FP4 GEMVs;
+    SiLU(gate) * up quantized per tile; down; f32 weighted combine into ctx.y_acc.  A single token with
+    at most 256 experts routes, gathers and quantizes in one launch.  `prof_base`: device address of
+    u64 slots that receive GPU timestamps after the route, the quantize, gate/up, activation, down."""
+    if w.sharded:
+        raise ValueError("forward_grouped_decode_into: expert-parallel shards use forward_grouped_decode")
+    if (ctx.hidden, ctx.inter, ctx.num_experts) != (w.hidden, w.inter, w.num_experts):
+        raise ValueError("TiledDecodeContext shape mismatch")
+    if ctx.folded_shared and not w.folded_shared:
+        raise ValueError("TiledDecodeContext folds the shared expert but the grouped weights were built without it")
+    s = _stream()
+    E, k, n, tpt = w.num_experts, ctx.k, ctx.n_tokens, ctx.tiles_per_token
+    tiles = n * tpt
+    m_total = tiles * MIN_TILE
+    hidden, inter = w.hidden, w.inter
+    tail = E if ctx.folded_shared else -1
+    bias_p = bias.data_ptr() if bias is not None else None
+
+    def mark(slot):
+        if prof_base is not None:
+            _ffi.check("nv_kernels_prof_timestamp", s, prof_base + 8 * slot)
+
+    if n == 1 and E <= 256:
+        _ffi.check("nv_kernels_moe_route_gather_quant_m1", s, ctx.logits_f32.data_ptr(), bias_p, ctx.x_in.data_ptr(),
+                   w.input_globals_gate_up.data_ptr(), w.input_globals_down.data_ptr(), ctx.topk_ids.data_ptr(),
+                   ctx.topk_weights.data_ptr(), ctx.input_gu_mini.data_ptr(), ctx.input_dn_mini.data_ptr(),
+                   ctx.x_fp4.data_ptr(), ctx.x_sf.data_ptr(), E, k, mode, float(softcap), int(norm_topk),
+                   float(routed_scaling), tail, hidden, MIN_TILE)
+        mark(0)
+        mark(1)
+    else:
+        if ctx.folded_shared:
+            _ffi.check("nv_kernels_moe_route_topk_shared_tail", s, ctx.logits_f32.data_ptr(), bias_p,
+                       ctx.topk_ids.data_ptr(), ctx.topk_weights.data_ptr(), n, E, k, mode, float(softcap),
+                       int(norm_topk), float(routed_scaling), tail)
+        else:
+            _ffi.check("nv_kernels_moe_route_topk", s, ctx.logits_f32.data_ptr(), bias_p, ctx.topk_ids.data_ptr(),
+                       ctx.topk_weights.data_ptr(), n, E, k, mode, float(softcap), int(norm_topk),
+                       float(routed_scaling))
+        mark(0)
+        for src, dst in ((w.input_globals_gate_up, ctx.input_gu_mini), (w.input_globals_down, ctx.input_dn_mini)):
+            _ffi.check("nv_kernels_gather_f32_by_ids", s, src.data_ptr(), ctx.topk_ids.data_ptr(), dst.data_ptr(), tiles)
+        _ffi.check("nv_kernels_gather_rows_bf16_strided", s, ctx.x_in.data_ptr(), ctx.src_idx.data_ptr(),
+                   ctx.x_sorted.data_ptr(), m_total, hidden, n, MIN_TILE)
+        _ffi.check("nv_kernels_quantize_nvfp4_bf16_per_expert_strided", s, ctx.x_sorted.data_ptr(), ctx.x_fp4.data_ptr(),
+                   ctx.x_sf.data_ptr(), ctx.input_gu_mini.data_ptr(), MIN_TILE, m_total, hidden)
+        mark(1)
+    n_ids = E + (1 if ctx.folded_shared else 0)   # a folded shared expert is bank entry E
+
+    def gemv(a_fp4, a_sf, bank, alphas, out, n_out, k_in):
+        _ffi.check("nv_kernels_moe_grouped_fp4_gemv_m1_bf16", s, a_fp4.data_ptr(), a_sf.data_ptr(), bank[0].data_ptr(),
+                   bank[1].data_ptr(), alphas.data_ptr(), out.data_ptr(), ctx.topk_ids.data_ptr(), tiles, n_ids, n_out,
+                   k_in, MIN_TILE, MIN_TILE * n_out)
+
+    gemv(ctx.x_fp4, ctx.x_sf, w.gate, ctx.alphas[0], ctx.y_gate, inter, hidden)
+    gemv(ctx.x_fp4, ctx.x_sf, w.up, ctx.alphas[1], ctx.y_up, inter, hidden)
+    mark(2)
+    _ffi.check("nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert_strided", s, ctx.y_gate.data_ptr(),
+               ctx.y_up.data_ptr(), ctx.y_act_fp4.data_ptr(), ctx.y_act_sf.data_ptr(), ctx.input_dn_mini.data_ptr(),
+               MIN_TILE, m_total, inter)
+    mark(3)
+    gemv(ctx.y_act_fp4, ctx.y_act_sf, w.down, ctx.alphas[2], ctx.y_down, hidden, inter)
+    mark(4)
+    if run_scatter:
+        _ffi.check("nv_kernels_moe_unpermute_scatter", s, ctx.y_down.data_ptr(), ctx.topk_weights.data_ptr(),
+                   ctx.inv_perm.data_ptr(), ctx.y_acc.data_ptr(), n, tpt, hidden, hidden)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -750,3 +750,63 @@ def test_grouped_linear_does_not_follow_offsets_or_rows_outside_its_buffers():
         want = ref.linear_w4a16_f64(host[e][0], host[e][1], x[rows[slot]:rows[slot] + 1], host[e][2], n, k)
         assert U.rel_err_floor(ref.bf16_to_f32(out[slot]), want[0]) < 1e-2
     assert np.all(out[3] == 0) and np.all(out[4] == 0)        # rows that do not exist read as zeros
+
+
+@pytest.mark.parametrize("n_tok,folded", [(1, False), (1, True), (3, False), (2, True)])
+def test_tiled_w4a4_decode_step_matches_the_per_pair_oracle(n_tok, folded):
+    """forward_grouped_decode_into: every (token, winner) pair a 128-row tile with row 0 live, activations
+    quantized to NVFP4 with the winner's stored global, FP4 x FP4 expert GEMVs.  One token routes, gathers
+    and quantizes in one launch (nv_kernels_moe_route_gather_quant_m1); several tokens take the separate
+    kernels.  Oracle: the W4A4 statement per pair (rust/crates/nv-quant/src/nvfp4.rs:1086-1106)."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(500 + 10 * n_tok + folded)
+    E, top_k, hidden, inter = 12, 3, 256, 128
+    n_bank = E + (1 if folded else 0)
+    experts, host = [], []
+    for e in range(n_bank):
+        trip, htrip = [], []
+        for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter)):
+            wf = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+            g = ref.weight_global(wf)
+            packed, lin = ref.quantize_rows(wf, g)
+            alpha = float(np.float32(1.0) / np.float32(g))
+            trip.append(sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(ref.swizzle_scales(lin)), alpha, k, n))
+            htrip.append((packed, lin, alpha))
+        experts.append(tuple(trip))
+        host.append(htrip)
+    w = sp.MoeGroupedWeights.build_from_experts(experts[:E], shared=experts[E] if folded else None)
+    gu = (0.5 + rng.random(n_bank)).astype(np.float32)
+    dn = (0.5 + rng.random(n_bank)).astype(np.float32)
+    w.input_globals_gate_up, w.input_globals_down = U.dev(gu), U.dev(dn)
+    ctx = sp.TiledDecodeContext(w, n_tok, top_k, "cuda", folded_shared=folded)
+    x = U.gauss_bf16(rng, (n_tok, hidden))
+    logits = rng.standard_normal((n_tok, E)).astype(np.float32)
+    ctx.x_in.copy_(U.dev(x).view(torch.bfloat16))
+    ctx.logits_f32.copy_(U.dev(logits))
+    stamps = torch.zeros(5, dtype=torch.int64, device="cuda")
+    sp.forward_grouped_decode_into(w, ctx, prof_base=stamps.data_ptr())
+    torch.cuda.synchronize()
+    got = ctx.y_acc.cpu().numpy()
+    ids, wts = ref.moe_route_topk(logits, top_k)
+    tpt = top_k + (1 if folded else 0)
+    got_ids = ctx.topk_ids.cpu().numpy().reshape(n_tok, tpt)
+    assert np.array_equal(got_ids[:, :top_k], ids)
+    if folded:
+        assert np.all(got_ids[:, top_k] == E) and np.all(ctx.topk_weights.cpu().numpy().reshape(n_tok, tpt)[:, top_k] == 1.0)
+    st = stamps.cpu().numpy()
+    assert np.all(st > 0) and np.all(np.diff(st) >= 0)   # timestamps were written, in stream order
+    want = np.zeros((n_tok, hidden), np.float64)
+    for t in range(n_tok):
+        pairs = [(int(ids[t, j]), float(wts[t, j])) for j in range(top_k)] + ([(E, 1.0)] if folded else [])
+        for e, wt in pairs:
+            (pg, lg_, ag), (pu, lu, au), (pd, ld, ad) = host[e]
+            xq, xlin = ref.quantize_rows_bf16(x[t:t + 1], float(gu[e]))
+            a_gu = float(np.float32(ag) / gu[e])
+            gate = ref.matmul_w4a4(xq, xlin, pg, lg_, 1, inter, hidden, a_gu)
+            up = ref.matmul_w4a4(xq, xlin, pu, lu, 1, inter, hidden, float(np.float32(au) / gu[e]))
+            act = ref.silu_mul(gate, up, round_bf16=False)                 # f32, not rounded before the quantizer
+            aq, alin = ref.quantize_rows(act, float(dn[e]))
+            down = ref.matmul_w4a4(aq, alin, pd, ld, 1, hidden, inter, float(np.float32(ad) / dn[e]))
+            want[t] += np.float64(np.float32(wt)) * ref.bf16_to_f32(down)[0].astype(np.float64)
+    assert U.rel_err_floor(got, want) < 1e-2
