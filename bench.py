@@ -1,14 +1,15 @@
 #!/usr/bin/env python
-"""Benchmark of the NVFP4 decode GEMV path (BASELINE.json metric: achieved HBM GB/s).
+"""Benchmark of the NVFP4 decode GEMV path: achieved HBM GB/s of the batch-1 weight-only linear.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
-Workload (BASELINE configs[1] at M=1): the four decode GEMV shapes
+Workload (the decode GEMV shape sweep at M=1): the four shapes
 (K,N) in {(4096,6144),(4096,4096),(4096,28672),(14336,4096)}, x bf16 ~ N(0,1), weights bf16 ~ N(0,0.02)
-quantized to NVFP4 (global 448*6/amax).  One step = one pass over `copies` distinct weight sets of
-all four shapes, so a step streams ~1 GB of weights (far larger than the 126 MB L2: every launch
-reads cold weights).  value = algorithmic bytes of the step / device time, where
-bytes(M,N,K) = N*K/2 + N*K/16 + 2*M*K + 2*M*N + 4.
+quantized to NVFP4 (global 448*6/amax).  One graph replay = one pass over `copies` distinct weight sets
+of all four shapes (~3.9 GB of weights, far larger than the 126 MB L2: every launch reads cold
+weights).  One STEP = `replays_per_step` replays, chosen once so that a step lasts ~0.1 s and the timed
+region of K steps is long enough for the clock sampler to see it.  value = algorithmic bytes of the
+step / device time, where bytes(M,N,K) = N*K/2 + N*K/16 + 2*M*K + 2*M*N + 4.
 
 At N > 1 the same matrices are sharded tensor-parallel over the ranks (strong scaling): the QKV and
 gate+up shapes column-parallel (rows split, output left sharded for the consumer), the o_proj and
@@ -36,8 +37,12 @@ if str(ROOT) not in sys.path:
 SHAPES_KN = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]  # (K, N)
 ROW_PARALLEL = {(4096, 4096), (14336, 4096)}  # o_proj / down: split along K at N > 1, all-reduce of y;
 # the other two (QKV, gate+up) split along N and their outputs stay sharded into the consumer
-COPIES = 8
+COPIES = 32            # distinct weight sets per shape in one graph replay
+STEP_TARGET_S = 0.1    # a step is as many replays as make it last about this long
 METRIC = "nvfp4_decode_gemv_hbm_gbs"
+# sizes of the two layer-stack legs (hidden, q width, kv width, FFN, vocabulary; experts, expert FFN, top-k)
+STACK_DIMS = {"H": 5120, "QO": 8192, "KV": 1024, "F": 25600, "V": 151936, "layers": 64}
+MOE_DIMS = {"E": 128, "H": 2048, "F": 768, "TOPK": 8, "layers": 48}
 
 
 def algo_bytes(m: int, n: int, k: int) -> int:
@@ -50,27 +55,59 @@ def step_bytes(copies: int) -> int:
 
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs.  Every sample carries
+    nvidia-smi's own timestamp; `stop(t0, t1)` keeps the samples taken between the two host times."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, gpu_index: int):
-        self.idx = gpu_index
+    def __init__(self, gpu_index: int, period_ms: int = 100):
+        self.idx, self.period_ms = gpu_index, period_ms
         self.proc = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
-                 str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
-    def stop(self) -> dict:
+    @classmethod
+    def parse(cls, text: str, t0=None, t1=None) -> dict:
+        """Summary of nvidia-smi's CSV lines; with t0/t1 (datetime) only the samples between them count."""
+        import datetime
+        sm, mx, power, reasons, total = [], [], [], set(), 0
+        for line in text.strip().splitlines():
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 10:
+                continue
+            try:
+                when = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                clk, cmax = float(f[2]), float(f[3])
+            except ValueError:
+                continue
+            total += 1
+            if t0 is not None and not (t0 <= when <= t1):
+                continue
+            sm.append(clk)
+            mx.append(cmax)
+            try:
+                power.append(float(f[4]))
+            except ValueError:
+                pass
+            for name, v in zip(cls.NAMES, f[6:10]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples_in_region": len(sm), "samples_total": total,
+                "reasons": sorted(reasons)}
+
+    def stop(self, t0=None, t1=None) -> dict:
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples_in_region": 0, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
         try:
@@ -78,22 +115,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            f = [c.strip() for c in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        return self.parse(out, t0, t1)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -155,10 +177,12 @@ def run_b200(args) -> dict:
             for lin in per_copy:
                 lin.forward(x, gather=False)
 
-    launches_per_step = copies * len(SHAPES_KN)
+    launches_per_replay = copies * len(SHAPES_KN)
+    n_row_parallel = sum(1 for k, n in SHAPES_KN if (k, n) in ROW_PARALLEL)
     mark("weights ready")
 
-    # ---- device-resident timing: the step captured once as a CUDA graph ----
+    # ---- device-resident timing: one pass captured as a CUDA graph, a step = `rps` replays ----
+    import datetime
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for _ in range(2):
@@ -169,35 +193,61 @@ def run_b200(args) -> dict:
         with torch.cuda.graph(graph, stream=stream):
             one_step()
         mark("graph captured")
-        for _ in range(max(args.warmup, 3)):
+        # how many replays make a step of about STEP_TARGET_S (decided on rank 0, the same on every rank)
+        for _ in range(3):
             graph.replay()
         stream.synchronize()
-        mark("graph warm-up done")
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(5):
+            graph.replay()
+        b.record(stream)
+        stream.synchronize()
+        rps_t = torch.tensor([max(1, min(400, int(round(STEP_TARGET_S / max(a.elapsed_time(b) / 5 * 1e-3, 1e-6)))))],
+                             dtype=torch.int32, device=dev)
+        if world > 1:
+            dist.broadcast(rps_t, 0)
+        rps = int(rps_t.item())
+        warm = max(args.warmup, 3)
+        for _ in range(warm):           # warm-up steps (>= 10 warm replays of every launch)
+            for _ in range(rps):
+                graph.replay()
+        stream.synchronize()
+        mark(f"graph warm-up done, {rps} replays per step")
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record(stream)
+            time.sleep(0.25)            # let the sampler produce its first line before the region opens
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        t_open = datetime.datetime.now()
+        ev[0].record(stream)
+        for i in range(args.steps):
+            for _ in range(rps):
+                graph.replay()
+            ev[i + 1].record(stream)
         stream.synchronize()
+        t_close = datetime.datetime.now()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        clocks = sampler.stop() if rank == 0 else None
-        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop(t_open, t_close) if rank == 0 else None
+        ms = ev[0].elapsed_time(ev[-1])
+        step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
         mark("timed region done")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    total_bytes = step_bytes(copies)
+    total_bytes = step_bytes(copies) * rps
+    launches_per_step = launches_per_replay * rps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- time of each GEMV inside a graph replay, from GPU timestamps between the launches ----
+    stamped = stamped_graph_leg(dev, stream, layers, xs) if world == 1 else None
 
     # ---- per-shape breakdown (each shape's copies timed as their own region) ----
     per_shape = {}
@@ -228,7 +278,7 @@ def run_b200(args) -> dict:
     pin_x = {k: torch.randn((1, k), dtype=torch.float32).to(torch.bfloat16).pin_memory() for k in xs}
     pin_y = {(k, n): torch.empty((1, n), dtype=torch.bfloat16).pin_memory() for k, n in SHAPES_KN}
     dx = {k: torch.empty((1, k), dtype=torch.bfloat16, device=dev) for k in xs}
-    h2d = launches_per_step and sum(2 * k for k, n in SHAPES_KN) * copies
+    h2d = sum(2 * k for k, n in SHAPES_KN) * copies     # per pass over the weight sets
     d2h = sum(2 * n for k, n in SHAPES_KN) * copies
 
     def e2e_step():
@@ -256,7 +306,7 @@ def run_b200(args) -> dict:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_value = total_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    e2e_value = step_bytes(copies) / (e2e_ms / e2e_steps * 1e-3) / 1e9   # an e2e step is ONE pass
 
     out = None
     if rank == 0:
@@ -267,21 +317,31 @@ def run_b200(args) -> dict:
             peaks = json.loads(pk.read_text())
             peak, peak_src = float(peaks["hbm_gbs"]), "measured"
         per_gpu_gbs = value / world
+        step_ms_sorted = sorted(step_ms)
+        # kernels of this library inside the timed region: the GEMVs, plus one all-reduce kernel per
+        # row-parallel GEMV when the sums go over peer memory
+        own_collectives = copies * n_row_parallel * rps if (world > 1 and peer_ar is not None) else 0
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "warmup": warm, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "e2m1*ue4m3 x bf16 -> f32",
             "data": "synthetic",
-            "config": {"workload": "configs[1] NVFP4 GEMV shape sweep, M=1", "shapes_KN": SHAPES_KN,
-                       "weight_copies_per_shape": copies, "launches_per_step": launches_per_step,
-                       "parallelism": f"tp{world}" if world > 1 else "single",
-                       "collective": (args.collective if world > 1 else None),
-                       "l2": f"inputs larger than L2: {total_bytes / 1e6:.0f} MB of cold weights per step",
-                       "timing": "CUDA events around K replays of a CUDA graph of one step"},
+            "config": bench_config(world, args.collective if world > 1 else None),
+            "step": {"passes_per_step": rps, "step_bytes": total_bytes, "launches_per_step": launches_per_step,
+                     "timing": "CUDA events around every step; a step = passes_per_step replays of a CUDA graph of "
+                               "one pass"},
+            "step_ms": {"median": round(statistics.median(step_ms), 4), "best": round(step_ms_sorted[0], 4),
+                        "worst": round(step_ms_sorted[-1], 4),
+                        "gbs_median": round(total_bytes / (statistics.median(step_ms) * 1e-3) / 1e9 / 1, 1),
+                        "gbs_best": round(total_bytes / (step_ms_sorted[0] * 1e-3) / 1e9, 1),
+                        "timed_replays_of_every_launch": rps * args.steps, "note": "rank 0's own steps"},
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "path": "Nvfp4Linear.forward per GEMV: pinned x -> device, launch, y -> pinned host"},
-            "gpu_launches": launches_per_step * args.steps,
+                    "path": "Nvfp4Linear.forward per GEMV: pinned x -> device, launch, y -> pinned host; an e2e "
+                            "step is one pass over the weight sets"},
+            "e2e_check": {"copies_declared": True, "h2d_copies_per_step": launches_per_replay,
+                          "d2h_copies_per_step": launches_per_replay},
+            "gpu_launches": (launches_per_step + own_collectives) * args.steps,
             "roofline": {"bound": "hbm", "achieved": round(per_gpu_gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu_gbs / peak, 4), "peak_source": peak_src,
                          "frac_of_nominal_8TBs": round(per_gpu_gbs / 8000.0, 4),
@@ -294,6 +354,7 @@ def run_b200(args) -> dict:
                          "bytes_per_launch_avg": total_bytes // launches_per_step // world,
                          "us_per_launch_avg": round(ms_per_step * 1e3 / launches_per_step, 3)},
             "per_shape": per_shape,
+            "per_shape_in_graph": stamped,
             "clocks": clocks,
         }
         if args.cpu_baseline:
@@ -338,8 +399,62 @@ def run_b200(args) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
+def bench_config(world: int, collective) -> dict:
+    """The workload both arms are run on (the reference arm samples it; see its `cpu_baseline.sample`).
+    The two arms print the same dict."""
+    return {"workload": "NVFP4 decode GEMV shape sweep, M=1 (x bf16 [1,K], W [N,K] NVFP4, y bf16, fp32 accumulate)",
+            "shapes_KN": SHAPES_KN, "weight_copies_per_shape": COPIES,
+            "launches_per_pass": COPIES * len(SHAPES_KN), "pass_bytes": step_bytes(COPIES),
+            "parallelism": f"tp{world}" if world > 1 else "single", "collective": collective,
+            "l2": f"inputs larger than L2: {step_bytes(COPIES) / 1e6:.0f} MB of cold weights per pass",
+            "step": "as many passes as last about 0.1 s on the device that runs them (see `step`)"}
+
+
+def stamped_graph_leg(dev, stream, layers, xs, copies_used: int = 8, reps: int = 9) -> dict:
+    """Per-GEMV time INSIDE a graph replay: a second graph of the same launches with a GPU timestamp
+    (nv_kernels_prof_timestamp, %globaltimer) before each one and after the last.  A stamp is a kernel
+    of its own without programmatic dependent launch, so consecutive GEMVs do not overlap here as they
+    do in the timed graph: these are serialised per-kernel times (their SHARES are what carries over)."""
+    import torch
+
+    import speaches_plus_b200 as sp
+    seq = [(k, n, lin) for k, n, per_copy in layers for lin in per_copy[:copies_used]]
+    stamps = torch.zeros(len(seq) + 1, dtype=torch.int64, device=dev)
+
+    def body():
+        s = torch.cuda.current_stream().cuda_stream
+        for i, (k, n, lin) in enumerate(seq):
+            sp.ffi.check("nv_kernels_prof_timestamp", s, stamps.data_ptr() + 8 * i)
+            lin.forward(xs[k], gather=False)
+        sp.ffi.check("nv_kernels_prof_timestamp", s, stamps.data_ptr() + 8 * len(seq))
+
+    per = {}
+    with torch.cuda.stream(stream):
+        body()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            body()
+        samples = {}
+        for _ in range(reps):
+            g.replay()
+            stream.synchronize()
+            t = stamps.cpu().numpy()
+            for i, (k, n, _) in enumerate(seq):
+                samples.setdefault((k, n), []).append(float(t[i + 1] - t[i]) * 1e-3)   # ns -> us
+        total = sum(statistics.median(v) for v in samples.values())
+        for (k, n), v in samples.items():
+            us = statistics.median(v)
+            per[f"K{k}_N{n}"] = {"us_per_launch": round(us, 3), "gbs": round(algo_bytes(1, n, k) / (us * 1e-6) / 1e9, 1),
+                                 "share": round(us / total, 4)}
+        del g
+    per["note"] = "serialised (a timestamp kernel sits between launches); cold weights: distinct copies in sequence"
+    return per
+
+
+# ------------------------------------------------------------------------------------------------
 def persistent_step_leg(dev, layers, xs, replays: int) -> dict:
-    """The configs[1] M=1 sweep as one persistent launch: the same GEMVs, each made to wait for the one
+    """The M=1 shape sweep as one persistent launch: the same GEMVs, each made to wait for the one
     before it (as consecutive linears of a decode step do), timed over graph replays."""
     import torch
 
@@ -380,8 +495,8 @@ def persistent_step_leg(dev, layers, xs, replays: int) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
-def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, replays: int = 5, peer_ar=None) -> dict:
-    """BASELINE configs[2]: dense decoder linear stack (hidden 5120, 64 q / 8 kv heads of 128, SwiGLU
+def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, peer_ar=None) -> dict:
+    """Dense 64-layer decoder linear stack (hidden 5120, 64 q / 8 kv heads of 128, SwiGLU
     25600, bf16 lm_head 151936), random-init NVFP4 weights, one decode step of `batch` tokens through
     every linear.  Attention itself is outside the path: o_proj is fed the q slice of the QKV output.
     Tensor parallel: QKV and gate/up column-parallel (outputs stay sharded into the row-parallel
@@ -392,7 +507,7 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, r
 
     import speaches_plus_b200 as sp
     ffi = sp.ffi
-    H, QO, KV, F, V = 5120, 8192, 1024, 25600, 151936
+    H, QO, KV, F, V, layers = (STACK_DIMS[k] for k in ("H", "QO", "KV", "F", "V", "layers"))
     q_l, kv_l, f_l = QO // world, KV // world, F // world
     v_l = (V // world + 127) // 128 * 128 if world > 1 else V
 
@@ -446,9 +561,7 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, r
             lin_call(w_d, None, gate, up, d_out, None)
             if world > 1:
                 reduce_(d_out)
-        for r in range(batch):
-            ffi.check("nv_kernels_gemv_bf16", torch.cuda.current_stream().cuda_stream, lm_head.weight.data_ptr(),
-                      d_out[r].data_ptr(), logits_l[r].data_ptr(), v_l, H)
+        lm_head.forward_into(d_out, logits_l)   # M = 1: the GEMV; M > 1: one pass over the matrix for all rows
         if world > 1:
             dist.all_gather_into_tensor(logits, logits_l)
 
@@ -481,15 +594,15 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, layers: int = 64, r
     out = {"batch": batch, "layers": layers, "tp": world, "ms_per_step": round(ms, 4),
            "tok_s": round(batch / (ms * 1e-3), 1), "bytes_per_step_per_gpu": bytes_rank,
            "gbs_per_gpu": round(bytes_rank / (ms * 1e-3) / 1e9, 1),
-           "launches_per_step": layers * 4 + batch, "collectives_per_step": (2 * layers + 1) if world > 1 else 0}
+           "launches_per_step": layers * 4 + 1, "collectives_per_step": (2 * layers + 1) if world > 1 else 0}
     del graph, stack, lm_head
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
     return out
 
 
-def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5, rank: int = 0, world: int = 1) -> dict:
-    """BASELINE configs[3]: 48 layers x 128 experts (hidden 2048, SwiGLU 768), top-8 with
+def moe_decode_leg(dev, batch: int, replays: int = 5, rank: int = 0, world: int = 1) -> dict:
+    """MoE expert decode: 48 layers x 128 experts (hidden 2048, SwiGLU 768), top-8 with
     softmax over the winners, router logits ~ N(0,1); one decode step of `batch` tokens through
     route -> sort -> grouped gate+up -> grouped down (SiLU prologue) -> combine in every layer.
     Algorithmic bytes count each distinct routed expert once per layer (from the actual routing).
@@ -504,7 +617,7 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5, rank: in
     import speaches_plus_b200 as sp
     from speaches_plus_b200 import linear as L
     ffi = sp.ffi
-    E, H, F, TOPK = 128, 2048, 768, 8
+    E, H, F, TOPK, layers = (MOE_DIMS[k] for k in ("E", "H", "F", "TOPK", "layers"))
 
     def bank(n, k, seed):
         g = torch.Generator(device=dev).manual_seed(seed)
@@ -574,37 +687,64 @@ def moe_decode_leg(dev, batch: int, layers: int = 48, replays: int = 5, rank: in
     return out
 
 
-def prefill_leg(dev, m: int = 2048, reps: int = 10) -> list:
-    """BASELINE configs[4]: M=2048 tokens through FFN up (K=5120, N=25600) and down (K=25600, N=5120),
-    activations quantized online to NVFP4 (global 1.0), block-scaled FP4 x FP4 GEMM, bf16 out.
-    Reported per shape: GEMM-only time and time including the activation quantizer."""
+def prefill_leg(dev, m: int = 2048, reps: int = 10) -> dict:
+    """Prefill block-scaled GEMM: M=2048 tokens through FFN up (K=5120, N=25600) and down (K=25600, N=5120),
+    activations quantized online to NVFP4 (global 1.0), FP4 x FP4 tensor-core GEMM, bf16 out -- for both
+    tiles of the prefill library (this is a single-GPU process, so the 2-SM tile may be selected).
+    The tensor peak these are set against is MEASURED here: the same kernel on a problem that stays in
+    L2 (4096^3, 48 MB of operands and output), best of several runs; the nominal 9 PFLOP/s is quoted
+    beside it."""
     import torch
 
     import speaches_plus_b200 as sp
-    out = []
-    for k, n in ((5120, 25600), (25600, 5120)):
-        g = torch.Generator(device=dev).manual_seed(k)
-        w = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-        lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w)
-        del w
-        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-        y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+
+    def timed(fn, n):
         for _ in range(3):
-            lin.forward_prefill_into(x, y)
+            fn()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(reps):
-            lin.forward_prefill_into(x, y)
+        for _ in range(n):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / reps
-        flop = 2.0 * m * n * k
-        out.append({"M": m, "K": k, "N": n, "ms_quantize_plus_gemm": round(ms, 4),
-                    "tflops": round(flop / (ms * 1e-3) / 1e12, 1),
-                    "frac_of_nominal_fp4_dense_9000": round(flop / (ms * 1e-3) / 1e12 / 9000.0, 4)})
-        del lin, x, y
-        torch.cuda.empty_cache()
+        return a.elapsed_time(b) / n
+
+    def make(n, k, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        w = (torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        lin = sp.Nvfp4Linear.from_bf16_quantized_nvfp4_dev(w)
+        del w
+        return lin, g
+
+    out = {"tiles": {}}
+    for cfg, name in ((1, "1sm_128x128x256"), (2, "2sm_256x128x256_cluster2")):
+        sp.ffi.check("nvk_b200_set_prefill_config", cfg)
+        # proxy peak: L2-resident problem, GEMM alone (activations quantized beforehand)
+        lin, g = make(4096, 4096, 1)
+        xq = torch.randn((4096, 4096), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        a_packed, a_scales = sp.linear.quantize_nvfp4_bf16(xq, 1.0, m_padded=4096)
+        y = torch.empty((4096, 4096), dtype=torch.bfloat16, device=dev)
+        peak_ms = min(timed(lambda: lin._fp4_gemm(a_packed, a_scales, y, 4096), 20) for _ in range(3))
+        peak_tf = 2.0 * 4096 ** 3 / (peak_ms * 1e-3) / 1e12
+        del lin, xq, a_packed, a_scales, y
+        rows = []
+        for k, n in ((5120, 25600), (25600, 5120)):
+            lin, g = make(n, k, k)
+            x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            ms_all = timed(lambda: lin.forward_prefill_into(x, y), reps)
+            a_packed, a_scales = sp.linear.quantize_nvfp4_bf16(x, lin.input_stored_global, m_padded=m)
+            ms_gemm = timed(lambda: lin._fp4_gemm(a_packed, a_scales, y, m), reps)
+            flop = 2.0 * m * n * k
+            tf = flop / (ms_gemm * 1e-3) / 1e12
+            rows.append({"M": m, "K": k, "N": n, "ms_gemm": round(ms_gemm, 4), "ms_quantize_plus_gemm": round(ms_all, 4),
+                         "tflops_gemm": round(tf, 1), "frac_of_measured_proxy_peak": round(tf / peak_tf, 4),
+                         "frac_of_nominal_fp4_dense_9000": round(tf / 9000.0, 4)})
+            del lin, x, y, a_packed, a_scales
+            torch.cuda.empty_cache()
+        out["tiles"][name] = {"proxy_peak_tflops_L2_resident_4096cubed": round(peak_tf, 1), "shapes": rows}
+    sp.ffi.check("nvk_b200_set_prefill_config", 1)
     return out
 
 
@@ -665,6 +805,10 @@ def cpu_reference_leg(passes: int, warm: int) -> dict:
 
 
 def run_reference(args) -> dict | None:
+    """The reference's own CPU implementation of the path (the oracle's port of its Cpu-backend linear),
+    all host threads, on the B200 arm's workload and config.  A step is a bounded SAMPLE of that
+    arm's step -- one weight set of each shape instead of replays_per_step x COPIES of them -- and the
+    metric (GB/s of algorithmic bytes) does not depend on how many sets a step covers."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
@@ -679,14 +823,15 @@ def run_reference(args) -> dict | None:
     dt = (time.perf_counter() - t0) / steps
     b = sum(algo_bytes(1, n, k) for k, n in SHAPES_KN)
     v = round(b / dt / 1e9, 3)
-    sample = ("each step = one weight set of each of the 4 shapes at M=1 (1/%d of the B200 arm's step), CPU oracle "
+    sample = ("each step = one weight set of each of the 4 shapes at M=1 (1/%d of one pass of the B200 arm), CPU oracle "
               "port of the reference's Cpu-backend linear (16 partial sums per output), all host threads" % COPIES)
     return {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
             "warmup": warm, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
             "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16 x bf16 -> f32",
             "data": "synthetic",
-            "config": {"workload": "configs[1] NVFP4 GEMV shape sweep, M=1", "shapes_KN": SHAPES_KN,
-                       "weight_copies_per_shape": 1, "parallelism": "host cores"},
+            "config": bench_config(args.gpus, (args.collective if args.gpus > 1 else None)),
+            "step": {"passes_per_step": 1.0 / COPIES, "step_bytes": b, "launches_per_step": 0,
+                     "timing": "host clock around the steps"},
             "cpu_baseline": {"value": v, "unit": "GB/s", "cores": ref.num_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -726,7 +871,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-extras", dest="extras", action="store_false",
-                    help="skip the configs[2] decode-stack and configs[3] MoE legs")
+                    help="skip the decode-stack, MoE and prefill legs")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="row-parallel sum at --gpus > 1: one-shot all-reduce over peer memory, or NCCL")
     ap.add_argument("--profile-case", default=None, metavar="K,N,M",

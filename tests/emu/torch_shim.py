@@ -86,10 +86,53 @@ def install() -> None:
     torch.cuda.synchronize = lambda *a, **k: None
     torch.cuda.set_device = lambda *a, **k: None
     torch.cuda.current_stream = lambda *a, **k: types.SimpleNamespace(cuda_stream=0)
+    torch.cuda.empty_cache = lambda: None
+    torch.Tensor.pin_memory = lambda self, *a, **k: self
+
+    # Streams, events and graphs for code that times itself (bench.py): launches are synchronous here,
+    # so a "captured" graph is simply its body run once and a replay does nothing; events read the
+    # host clock.  Good for exercising the control flow and the output contract, not for numbers.
+    import contextlib
+    import time as _time
+
+    class Stream:
+        cuda_stream = 0
+
+        def synchronize(self):
+            pass
+
+        def wait_stream(self, other):
+            pass
+
+    class Event:
+        def __init__(self, enable_timing=False):
+            self.t = None
+
+        def record(self, stream=None):
+            self.t = _time.perf_counter()
+
+        def synchronize(self):
+            pass
+
+        def elapsed_time(self, other):
+            return max(1e-3, (other.t - self.t) * 1e3)
+
+    class CUDAGraph:
+        def replay(self):
+            pass
+
+    torch.cuda.Stream = Stream
+    torch.cuda.Event = Event
+    torch.cuda.CUDAGraph = CUDAGraph
+    torch.cuda.stream = lambda s: contextlib.nullcontext()
+    torch.cuda.graph = lambda g, stream=None, **k: contextlib.nullcontext()
+    orig_generator = torch.Generator
+    torch.Generator = lambda device=None: orig_generator()
 
     # the package's binding now talks to the emulated library (same symbols, same argument types)
     sp.ffi._lib = harness.lib()
     sp.ffi.EMULATED = True
+    sp.ffi.prefill_available = lambda: False   # the CUTLASS library needs a GPU
     import os
     if os.environ.get("NVK_EMU_CP_ASYNC_EARLY") == "1":
         harness.set_option("cp_async_early", 1)
