@@ -104,6 +104,11 @@ int nvk_b200_set_tuning(int force_ksplit, int force_rows_per_cta);
  * for that kernel only before it reads activations or writes outputs.  enabled = 0 turns this off
  * (plain stream order); the default is on. */
 int nvk_b200_set_pdl(int enabled);
+/* Polls a kernel of this library spends in ONE wait on another CTA or another GPU (the peer
+ * all-reduce's flags, a persistent step's dependency counters) before it gives up, sets its error
+ * word and returns -- no wait is unbounded.  0 restores the default (2,000,000 polls, about a second).
+ * Applies to later calls made by the calling thread.  No counterpart in the reference. */
+int nvk_b200_set_wait_limit(unsigned polls);
 
 /* bf16 weights, M = 1 (lm_head): y[n] = bf16(sum_k W[n,k] x[k]).
  * replaces rust/crates/nv-kernels/include/nv_kernels.h:116-123
@@ -427,7 +432,10 @@ int nv_kernels_mul_sigmoid_rowgate_f32(void* stream, const float* x, const float
  *   nvk_b200_stack_run(...)            enqueue one step: clears the plan's counters on the stream and
  *                                      launches; allocates nothing, never synchronises.  `err` is a
  *                                      device int owned and zeroed by the caller, set to 1 if a wait
- *                                      inside the kernel ran out (about a second). */
+ *                                      inside the kernel ran out (nvk_b200_set_wait_limit).  n_ops, M and
+ *                                      smem_bytes must be the values the plan was built with and grid at
+ *                                      most the CTAs nvk_b200_stack_build returned, else -2 (a plan that
+ *                                      this process did not build is refused the same way). */
 typedef struct NvkStackOp {
     const uint8_t* wq_a;   /* packed weights [N, K/2] and swizzled scales of the (first) matrix */
     const uint8_t* sc_a;

@@ -30,6 +30,7 @@ SIGNATURES = {
     "nvk_b200_stack_run": [_vp, _vp, _i, _i, _i, _i, _vp],
     "nvk_b200_set_tuning": [_i, _i],
     "nvk_b200_set_pdl": [_i],
+    "nvk_b200_set_wait_limit": [C.c_uint],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],
     "nvk_b200_linear_bf16": [_vp, _vp, _vp, _vp, _i, _i, _i],
     "nv_kernels_quantize_nvfp4_bf16": [_vp, _vp, _vp, _vp, _f, _i, _i, _i],

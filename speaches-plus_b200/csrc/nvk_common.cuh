@@ -98,6 +98,22 @@ __device__ __forceinline__ uint32_t encode_ue4m3(float s) {
     return byte == 0x7Fu ? 0x7Eu : byte;
 }
 
+// Polls *p (acquire, system scope) until it is >= target or `limit` polls have passed; false = gave up.
+// Every wait on another CTA or GPU in this library goes through here: none of them is unbounded.
+__device__ __forceinline__ bool bounded_wait_ge(const uint32_t* p, uint32_t target, uint32_t limit) {
+    for (uint32_t polls = 0; ptx::ld_acquire_sys(p) < target;)
+        if (++polls > limit) return false;
+    return true;
+}
+
+// Polls per wait before a kernel gives up (about a second on the device); nvk_b200_set_wait_limit
+// changes it for later calls of the calling thread.
+constexpr uint32_t kDefaultWaitLimit = 2000000u;
+inline uint32_t& wait_limit_setting() {
+    static thread_local uint32_t polls = kDefaultWaitLimit;
+    return polls;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

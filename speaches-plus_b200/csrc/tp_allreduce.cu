@@ -15,8 +15,8 @@
 // alternates between two halves, which is enough because a rank can only be one call ahead of any
 // peer (it needs that peer's flag to finish a call).
 //
-// Every wait is bounded: after kSpinLimit polls the kernel records an error and returns, leaving the
-// context usable.  The caller must run the same sequence of calls on every rank.
+// Every wait is bounded: after the wait limit (nvk_b200_set_wait_limit; about a second by default) the
+// kernel records an error and returns, leaving the context usable.  The caller must run the same sequence of calls on every rank.
 #include <string.h>
 
 #include "nvk_common.cuh"
@@ -27,7 +27,6 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxCtas = 32;
 constexpr int kFlagBytes = 4096;           // kMaxCtas * kMaxRanks * 4 = 1024 used
 constexpr int kElemsPerCta = 8192;          // 16 KB of bf16 per CTA
-constexpr unsigned kSpinLimit = 2000000u;   // about a second of polling
 
 struct ArParams {
     uint8_t* peer[kMaxRanks];   // base of every rank's symmetric buffer (peer[rank] is our own)
@@ -36,9 +35,9 @@ struct ArParams {
     uint32_t* epoch;            // [kMaxCtas] call counters in local memory
     int* err;                   // set to 1 + peer index on a wait that gave up
     int rank, world, n, max_elems;
+    uint32_t wait_limit;        // polls per peer before the wait gives up
 };
 
-using nvk::ptx::ld_acquire_sys;
 using nvk::ptx::st_release_sys;
 
 __global__ void __launch_bounds__(512) tp_allreduce_kernel(const ArParams p) {
@@ -69,13 +68,9 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const ArParams p) {
         const int r = threadIdx.x;
         st_release_sys(reinterpret_cast<uint32_t*>(p.peer[r]) + cta * kMaxRanks + p.rank, epoch);
         const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.peer[p.rank]) + cta * kMaxRanks + r;
-        unsigned spins = 0;
-        while (ld_acquire_sys(mine) < epoch) {
-            if (++spins > kSpinLimit) {
-                atomicExch(p.err, 1 + r);
-                s_ok = 0;
-                break;
-            }
+        if (!nvk::bounded_wait_ge(mine, epoch, p.wait_limit)) {
+            atomicExch(p.err, 1 + r);
+            s_ok = 0;
         }
     }
     __syncthreads();
@@ -107,6 +102,14 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const ArParams p) {
 }  // namespace
 
 extern "C" {
+
+// Polls a kernel of this library spends in one wait on another CTA or GPU before it gives up and
+// reports through its error word; 0 restores the default (about a second).  Applies to later calls
+// made by the calling thread.
+int nvk_b200_set_wait_limit(unsigned polls) {
+    nvk::wait_limit_setting() = polls ? polls : nvk::kDefaultWaitLimit;
+    return 0;
+}
 
 // ---- set-up helpers (host side, not on the launch path) ------------------------------------------
 // The exchange buffer is plain device memory shared between the ranks of one node with CUDA IPC
@@ -168,6 +171,7 @@ int nvk_b200_tp_allreduce_bf16(void* stream, const void* const* peer_bufs, int r
     }
     p.x = x; p.y = y; p.epoch = epoch; p.err = err;
     p.rank = rank; p.world = world; p.n = n; p.max_elems = max_elems;
+    p.wait_limit = nvk::wait_limit_setting();
     return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)ctas, 512, 0, true), tp_allreduce_kernel, p);
 }
 

@@ -13,14 +13,15 @@
 //   * the per-tile arithmetic is w4a16_tile (w4a16_tile.cuh), unchanged: an item computes exactly
 //     what the stand-alone launch with the same rows-per-CTA and no K split computes, bit for bit.
 //
-// Every wait is bounded: after kGateSpinLimit polls the CTA records an error and goes on (its
+// Every wait is bounded: after the wait limit (nvk_b200_set_wait_limit) the CTA records an error and goes on (its
 // results are then meaningless, the launch still ends).  The launch is cooperative, so all CTAs are
 // resident together and a CTA never waits for one that is not running.
+#include <map>
+
 #include "w4a16_tile.cuh"
 
 namespace {
 
-constexpr unsigned kGateSpinLimit = 1000000u;   // roughly a second of polling
 constexpr int kStackThreads = 256;
 constexpr int kMaxOps = 1024;
 
@@ -40,8 +41,6 @@ struct StackOp {
     int k_tiles, nsc, ph, x_stride, ring_off;
 };
 
-using nvk::ptx::ld_acquire_gpu;
-
 // Tiles inside the persistent launch: no cluster (an item owns all of K for its rows), activations
 // written earlier in the SAME launch -- so they are read from L2 (another SM wrote them; this SM's L1
 // may hold a stale line from an earlier operation) after the producer's arrival counter says so.
@@ -50,15 +49,7 @@ struct StackHooks {
     __device__ static __forceinline__ int nranks() { return 1; }
     __device__ static __forceinline__ void before_activations(const TileView& t) {
         if (t.gate == nullptr) return;   // uniform over the CTA
-        if (threadIdx.x == 0) {
-            unsigned spins = 0;
-            while (ld_acquire_gpu(t.gate) < t.gate_target) {
-                if (++spins > kGateSpinLimit) {
-                    atomicExch(t.gate_err, 1);
-                    break;
-                }
-            }
-        }
+        if (threadIdx.x == 0 && !nvk::bounded_wait_ge(t.gate, t.gate_target, t.gate_limit)) atomicExch(t.gate_err, 1);
         __syncthreads();
     }
     __device__ static __forceinline__ uint4 load_x(const uint16_t* q) {
@@ -68,7 +59,7 @@ struct StackHooks {
 
 template <int UG, int KW>
 __device__ __forceinline__ void run_item(const StackOp& op, int item, int M, const unsigned* done, const StackOp* ops,
-                                         int* err) {
+                                         int* err, unsigned wait_limit) {
     GemmParams p = {};
     p.wq[0] = op.wq[0]; p.wq[1] = op.wq[1];
     p.sc[0] = op.sc[0]; p.sc[1] = op.sc[1];
@@ -102,6 +93,7 @@ __device__ __forceinline__ void run_item(const StackOp& op, int item, int M, con
     t.gate = op.dep >= 0 ? done + op.dep : nullptr;
     t.gate_target = op.dep >= 0 ? (unsigned)ops[op.dep].items : 0u;
     t.gate_err = err;
+    t.gate_limit = wait_limit;
     if (op.x2 != nullptr)
         w4a16_tile<1, 1, UG, KW, false, StackHooks>(p, t);
     else
@@ -111,7 +103,8 @@ __device__ __forceinline__ void run_item(const StackOp& op, int item, int M, con
 // next_item[o]: the next unclaimed item of operation o; done[o]: items of operation o completed.
 // Both start at zero (the launcher clears them on the stream before every launch).
 __global__ void __launch_bounds__(kStackThreads, 2) w4a16_stack_kernel(const StackOp* __restrict__ ops, int n_ops, int M,
-                                                                       unsigned* next_item, unsigned* done, int* err) {
+                                                                       unsigned* next_item, unsigned* done, int* err,
+                                                                       unsigned wait_limit) {
     __shared__ int s_item;
     for (int o = 0; o < n_ops; ++o) {
         const StackOp op = ops[o];
@@ -122,9 +115,9 @@ __global__ void __launch_bounds__(kStackThreads, 2) w4a16_stack_kernel(const Sta
             const int item = s_item;
             if (item >= op.items) break;
             if (op.ug == 8)
-                run_item<8, 1>(op, item, M, done, ops, err);
+                run_item<8, 1>(op, item, M, done, ops, err, wait_limit);
             else
-                run_item<1, 8>(op, item, M, done, ops, err);
+                run_item<1, 8>(op, item, M, done, ops, err, wait_limit);
             __syncthreads();   // every thread's outputs of this item are written ...
             if (threadIdx.x == 0) {
                 __threadfence();            // ... and visible device-wide before the arrival is counted
@@ -135,6 +128,15 @@ __global__ void __launch_bounds__(kStackThreads, 2) w4a16_stack_kernel(const Sta
 }
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
+
+// What nvk_b200_stack_build laid a plan out for.  nvk_b200_stack_run checks its arguments against
+// this record: a step run with more tokens than the plan's shared-memory layout was sized for, or
+// with another operation count, would compute garbage without any error.
+struct PlanRecord {
+    int n_ops, M, grid, smem;
+};
+std::mutex g_plans_mu;
+std::map<const void*, PlanRecord> g_plans;
 
 size_t plan_bytes(int n_ops) {
     // [StackOp x n_ops | next_item x n_ops | done x n_ops], each part 256-byte aligned
@@ -249,6 +251,8 @@ int nvk_b200_stack_build(const NvkStackOp* ops, int n_ops, int M, void* plan_dev
     if (rc == 0) {
         launch_out[0] = (per_sm > 2 ? 2 : per_sm) * sms;   // all of them resident together
         launch_out[1] = (int)smem_max;
+        std::lock_guard<std::mutex> lock(g_plans_mu);
+        g_plans[plan_dev] = PlanRecord{n_ops, M, launch_out[0], launch_out[1]};
     }
     return rc;
 }
@@ -259,6 +263,15 @@ int nvk_b200_stack_build(const NvkStackOp* ops, int n_ops, int M, void* plan_dev
 int nvk_b200_stack_run(void* stream, void* plan_dev, int n_ops, int M, int grid, int smem_bytes, int* err) {
     if (plan_dev == nullptr || err == nullptr) return NVK_ERR_ARG;
     if (n_ops <= 0 || n_ops > kMaxOps || M <= 0 || M > 8 || grid <= 0 || smem_bytes <= 0) return NVK_ERR_ARG;
+    {
+        // the plan must be one this process built, run with the shape it was built for (a smaller
+        // grid is allowed: the work items are drawn from counters)
+        std::lock_guard<std::mutex> lock(g_plans_mu);
+        auto it = g_plans.find(plan_dev);
+        if (it == g_plans.end()) return NVK_ERR_ARG;
+        const PlanRecord& r = it->second;
+        if (n_ops != r.n_ops || M != r.M || smem_bytes != r.smem || grid > r.grid) return NVK_ERR_ARG;
+    }
     cudaStream_t s = (cudaStream_t)stream;
     uint8_t* base = static_cast<uint8_t*>(plan_dev);
     const size_t ops_b = ((size_t)n_ops * sizeof(StackOp) + 255) / 256 * 256;
@@ -270,7 +283,7 @@ int nvk_b200_stack_run(void* stream, void* plan_dev, int n_ops, int M, int grid,
     nvk::Launch l = nvk::launch_1d(s, (unsigned)grid, kStackThreads, (size_t)smem_bytes);
     l.cooperative = true;
     const StackOp* ops = reinterpret_cast<const StackOp*>(base);
-    return nvk::launch(l, w4a16_stack_kernel, ops, n_ops, M, next_item, done, err);
+    return nvk::launch(l, w4a16_stack_kernel, ops, n_ops, M, next_item, done, err, nvk::wait_limit_setting());
 }
 
 }  // extern "C"

@@ -91,6 +91,7 @@ struct TileView {
     const unsigned* gate;    // arrival counter of the operation that produces x (null: nothing to wait for)
     unsigned gate_target;    // arrivals that mean "complete"
     int* gate_err;           // set to 1 when the wait gives up
+    unsigned gate_limit;     // polls before it does
     // Used only when EPI == 1 (the output is a residual update and/or carries a per-token multiplier):
     const uint16_t* residual;   // [M, N] bf16 added to the product before the single rounding, or null
     const float* row_scale;     // [M] per-token multiplier (an int8 row's dequant scale), or null

@@ -509,6 +509,13 @@ def test_persistent_step_equals_the_standalone_launches(m, rows):
         torch.cuda.synchronize()
         step.check()
         assert same()
+    # the run call checks its arguments against what the plan was built for
+    n_ops, (grid, smem) = len(step._ops), step._launch
+    bad = [(n_ops + 1, m, grid, smem), (n_ops, m + 1 if m < 8 else m - 1, grid, smem), (n_ops, m, grid + 1, smem),
+           (n_ops, m, grid, smem + 16)]
+    for a_ops, a_m, a_grid, a_smem in bad:
+        assert U.ffi.call("nvk_b200_stack_run", U.stream(), step._plan.data_ptr(), a_ops, a_m, a_grid, a_smem,
+                          step.err.data_ptr()) == -2
     if getattr(U.ffi, "EMULATED", False):
         return   # graph capture needs the real CUDA runtime
     s = torch.cuda.Stream()
@@ -526,3 +533,68 @@ def test_persistent_step_equals_the_standalone_launches(m, rows):
     step.check()
     assert same()
     del graph
+
+
+def test_a_wait_on_a_peer_that_never_arrives_runs_out_and_reports():
+    """The peer all-reduce's wait is bounded: with a peer whose flag nobody raises the kernel gives up
+    after the configured number of polls, sets err = 1 + that peer, leaves y alone and returns; the
+    context stays usable and the next call works.  One GPU, both "ranks'" buffers local; nothing
+    faults, traps or hangs."""
+    U.require_gpu()
+    import ctypes as C
+    n, max_elems, world = 256, 256, 2
+    nbytes = U.ffi.lib().nvk_b200_tp_allreduce_buffer_bytes(world, max_elems)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    rng = np.random.default_rng(4)
+    x = U.dev(U.gauss_bf16(rng, (n,)))
+    y = torch.full((n,), 0x7FC0, dtype=torch.int16, device="cuda")
+    epoch = torch.zeros(32, dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nvk_b200_set_wait_limit", 1000) == 0
+    try:
+        assert U.ffi.call("nvk_b200_tp_allreduce_bf16", U.stream(), C.addressof(ptrs), 0, world, x.data_ptr(), y.data_ptr(), n,
+                          max_elems, epoch.data_ptr(), err.data_ptr()) == 0
+        torch.cuda.synchronize()                       # returns: the wait ran out
+        assert int(err.cpu().numpy()[0]) == 2          # 1 + the peer that never arrived
+        assert np.all(U.host_u16(y) == 0x7FC0)         # no sum was written
+        assert int(epoch.cpu().numpy()[0]) == 1        # the call still counted: ranks stay in step
+    finally:
+        assert U.ffi.call("nvk_b200_set_wait_limit", 0) == 0
+    # the next call (a world of one) works
+    err.zero_()
+    one = (C.c_void_p * 1)(bufs[0].data_ptr())
+    assert U.ffi.call("nvk_b200_tp_allreduce_bf16", U.stream(), C.addressof(one), 0, 1, x.data_ptr(), y.data_ptr(), n, max_elems,
+                      epoch.data_ptr(), err.data_ptr()) == 0
+    torch.cuda.synchronize()
+    assert int(err.cpu().numpy()[0]) == 0 and np.array_equal(U.host_u16(y), U.host_u16(x))
+
+
+def test_two_ranks_of_the_peer_all_reduce_on_one_device_buffer_pair():
+    """Both ranks' kernels of one exchange, run one after the other on ONE GPU with a short wait limit,
+    is NOT how the kernel is meant to run (ranks are processes on different GPUs and wait for each other);
+    what can be checked on one device is the data path: rank 1 first (its wait for rank 0 runs out, its
+    push has landed), then rank 0 finds rank 1's slot and flag and produces the sum in rank order."""
+    U.require_gpu()
+    import ctypes as C
+    n, max_elems, world = 512, 512, 2
+    nbytes = U.ffi.lib().nvk_b200_tp_allreduce_buffer_bytes(world, max_elems)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    rng = np.random.default_rng(8)
+    xs = [U.gauss_bf16(rng, (n,)) for _ in range(world)]
+    dx = [U.dev(v) for v in xs]
+    ys = [torch.zeros(n, dtype=torch.int16, device="cuda") for _ in range(world)]
+    epochs = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
+    errs = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    assert U.ffi.call("nvk_b200_set_wait_limit", 1000) == 0
+    try:
+        for r in (1, 0):
+            assert U.ffi.call("nvk_b200_tp_allreduce_bf16", U.stream(), C.addressof(ptrs), r, world, dx[r].data_ptr(),
+                              ys[r].data_ptr(), n, max_elems, epochs[r].data_ptr(), errs[r].data_ptr()) == 0
+            torch.cuda.synchronize()
+    finally:
+        U.ffi.call("nvk_b200_set_wait_limit", 0)
+    assert int(errs[1].cpu().numpy()[0]) == 1 and int(errs[0].cpu().numpy()[0]) == 0
+    want = ref.f32_to_bf16(ref.bf16_to_f32(xs[0]) + ref.bf16_to_f32(xs[1]))   # fp32 sum in rank order, one rounding
+    assert np.array_equal(U.host_u16(ys[0]), want)
