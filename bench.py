@@ -13,8 +13,8 @@ step / device time, where bytes(M,N,K) = N*K/2 + N*K/16 + 2*M*K + 2*M*N + 4.
 
 At N > 1 the same matrices are sharded tensor-parallel over the ranks (strong scaling): the QKV and
 gate+up shapes column-parallel (rows split, output left sharded for the consumer), the o_proj and
-down shapes row-parallel (K split, all-reduce of the partial y over peer memory, or NCCL with
---collective nccl), one process per GPU.
+down shapes row-parallel (K split, all-reduce of the partial y with NCCL, or over peer memory with
+--collective peer), one process per GPU.
 
 `--impl reference` times the reference's CPU path for the same linears (weights dequantized to
 bf16 once, then bf16 x bf16 -> f32 -> bf16, all host cores) through the CPU oracle.
@@ -872,8 +872,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="skip the decode-stack, MoE and prefill legs")
-    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
-                    help="row-parallel sum at --gpus > 1: one-shot all-reduce over peer memory, or NCCL")
+    ap.add_argument("--collective", default="nccl", choices=["peer", "nccl"],
+                    help="row-parallel sum at --gpus > 1: NCCL (default; in-switch multicast off), or this "
+                         "library's one-shot all-reduce over CUDA-IPC peer memory")
     ap.add_argument("--profile-case", default=None, metavar="K,N,M",
                     help="run a few eager launches of one case and exit (for profiler captures)")
     ap.add_argument("--copies", type=int, default=4)
