@@ -19,6 +19,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "../csrc/nvk_common.cuh"
 
 #ifdef NVK_HAVE_CUTLASS
@@ -46,7 +48,7 @@ using LayoutD = cutlass::layout::RowMajor;
 constexpr int kAlignAB = 32;                    // elements: 16 bytes of packed e2m1
 constexpr int kAlignD = 128 / cutlass::sizeof_bits<ElementD>::value;
 
-template <class TileShape, class ClusterShape>
+template <class TileShape, class ClusterShape, class Scheduler = void>
 struct GemmConfig {
     using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassBlockScaledTensorOp, TileShape, ClusterShape,
@@ -57,7 +59,7 @@ struct GemmConfig {
         LayoutB, kAlignAB, ElementAcc, TileShape, ClusterShape,
         cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
         cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
-    using GemmKernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, void>;
+    using GemmKernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue, Scheduler>;
     using Gemm = cutlass::gemm::device::GemmUniversalAdapter<GemmKernel>;
     using SfConfig = typename GemmKernel::CollectiveMainloop::Sm1xxBlkScaledConfig;
 };
@@ -69,12 +71,17 @@ using Cfg1 = GemmConfig<Shape<_128, _128, _256>, Shape<_1, _1, _1>>;
 // every operand this GPU's own memory.
 using Cfg2 = GemmConfig<Shape<_256, _128, _256>, Shape<_2, _1, _1>>;
 
+// The 1-SM tile under the stream-K scheduler: output tiles that do not fill the last wave are split
+// along K over the idle SMs and reduced through the workspace (K = 25600 with 320 output tiles on 148
+// SMs is the case it exists for).
+using Cfg1SK = GemmConfig<Shape<_128, _128, _256>, Shape<_1, _1, _1>, cutlass::gemm::StreamKScheduler>;
+
 // The tile choice is per calling thread (the entry points may be called from any thread).
 thread_local int g_prefill_cfg = 1;
 
 template <class Cfg>
 typename Cfg::Gemm::Arguments make_args(const void* a, const void* a_sf, const void* b, const void* b_sf,
-                                   const float* alpha_dev, void* d, int m, int n, int k) {
+                                   const float* alpha_dev, void* d, int m, int n, int k, int splits = 0) {
     using Gemm = typename Cfg::Gemm;
     using GemmKernel = typename Cfg::GemmKernel;
     using SfConfig = typename Cfg::SfConfig;
@@ -102,18 +109,21 @@ typename Cfg::Gemm::Arguments make_args(const void* a, const void* a_sf, const v
     args.epilogue.dC = cutlass::make_cute_packed_stride(StrideD{}, {m, n, 1});
     args.epilogue.ptr_D = static_cast<ElementD*>(d);
     args.epilogue.dD = cutlass::make_cute_packed_stride(StrideD{}, {m, n, 1});
+    if constexpr (std::is_same_v<Cfg, Cfg1SK>) {
+        if (splits >= 2) args.scheduler.splits = splits;   // forced split of every tile; else the heuristic
+    }
     return args;
 }
 
 template <class Cfg>
 int run_gemm_cfg(cudaStream_t stream, const void* a, const void* a_sf, const void* b, const void* b_sf,
                  const float* alpha_dev, void* d, int m, int n, int k, void* workspace, size_t workspace_bytes,
-                 size_t* required_workspace) {
+                 size_t* required_workspace, int splits = 0) {
     using Gemm = typename Cfg::Gemm;
     if (m <= 0 || n <= 0 || k <= 0) return NVK_ERR_SHAPE;
     if ((k % 32) != 0 || (n % 8) != 0) return NVK_ERR_SHAPE;  // 16-byte rows of packed operands and of D
     try {
-        auto args = make_args<Cfg>(a, a_sf, b, b_sf, alpha_dev, d, m, n, k);
+        auto args = make_args<Cfg>(a, a_sf, b, b_sf, alpha_dev, d, m, n, k, splits);
         const size_t need = Gemm::get_workspace_size(args);
         if (required_workspace) *required_workspace = need;
         // all data pointers null: a pure workspace query, nothing is launched
@@ -140,12 +150,24 @@ int run_gemm(cudaStream_t stream, const void* a, const void* a_sf, const void* b
                               required_workspace);
 }
 
+int run_gemm_streamk(cudaStream_t stream, const void* a, const void* a_sf, const void* b, const void* b_sf,
+                     const float* alpha_dev, void* d, int m, int n, int k, void* workspace, size_t workspace_bytes,
+                     size_t* required_workspace, int splits) {
+    return run_gemm_cfg<Cfg1SK>(stream, a, a_sf, b, b_sf, alpha_dev, d, m, n, k, workspace, workspace_bytes,
+                                required_workspace, splits);
+}
+
 }  // namespace
 #else   // !NVK_HAVE_CUTLASS
 namespace { thread_local int g_prefill_cfg = 1; }
 namespace {
 int run_gemm(cudaStream_t, const void*, const void*, const void*, const void*, const float*, void*, int, int, int,
              void*, size_t, size_t* required_workspace) {
+    if (required_workspace) *required_workspace = 0;
+    return NVK_ERR_SHAPE;
+}
+int run_gemm_streamk(cudaStream_t, const void*, const void*, const void*, const void*, const float*, void*, int, int, int,
+                     void*, size_t, size_t* required_workspace, int) {
     if (required_workspace) *required_workspace = 0;
     return NVK_ERR_SHAPE;
 }
@@ -164,9 +186,14 @@ int nvk_b200_set_prefill_config(int cfg) {
 }
 
 // The reference names these after the architecture of its own tensor-core kernels; the symbols are
-// kept so that its call sites bind unchanged.  All three run the same sm_100a kernel: the tile and
-// stream-K knobs of the reference's variants select among its sm_120 configurations and have no
-// meaning here.
+// kept so that its call sites bind unchanged.
+//   ..._bf16          the data-parallel kernel with the tile nvk_b200_set_prefill_config selected;
+//   ..._bf16_streamk  the 1-SM tile under the stream-K scheduler (its own, larger workspace: query it
+//                     through this symbol);
+//   ..._bf16_tiled    `tile` 0..2 names one of the reference's sm_120 tile shapes -- all three map to
+//                     the one 1-SM 128x128x256 tile here, any other value is -3 as in the reference --
+//                     and `stream_k` keeps its meaning: 0 data-parallel, 1 stream-K, >= 2 that many
+//                     forced splits of every output tile along K.
 int nv_kernels_cutlass_fp4_gemm_sm120_bf16(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
                                            const void* b_sf, const float* global_sf, void* d_bf16, int m, int n, int k,
                                            void* workspace, size_t workspace_bytes, size_t* required_workspace) {
@@ -178,18 +205,25 @@ int nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk(void* stream, const void* a_f
                                                    const void* b_fp4, const void* b_sf, const float* global_sf,
                                                    void* d_bf16, int m, int n, int k, void* workspace,
                                                    size_t workspace_bytes, size_t* required_workspace) {
-    return run_gemm((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
-                    workspace_bytes, required_workspace);
+    return run_gemm_streamk((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
+                            workspace_bytes, required_workspace, 0);
 }
 
 int nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
                                                  const void* b_sf, const float* global_sf, void* d_bf16, int m, int n,
                                                  int k, int tile, int stream_k, void* workspace,
                                                  size_t workspace_bytes, size_t* required_workspace) {
-    (void)tile;
-    (void)stream_k;
+    if (tile < 0 || tile > 2 || stream_k < 0) return NVK_ERR_RESOURCE;
+    if (stream_k >= 1)
+        return run_gemm_streamk((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
+                                workspace_bytes, required_workspace, stream_k >= 2 ? stream_k : 0);
+#ifdef NVK_HAVE_CUTLASS
+    return run_gemm_cfg<Cfg1>((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
+                              workspace_bytes, required_workspace);
+#else
     return run_gemm((cudaStream_t)stream, a_fp4, a_sf, b_fp4, b_sf, global_sf, d_bf16, m, n, k, workspace,
                     workspace_bytes, required_workspace);
+#endif
 }
 
 }  // extern "C"

@@ -17,12 +17,12 @@ from tests import _util as U
 pytestmark = [pytest.mark.gpu, pytest.mark.needs_cuda_runtime]   # the CUTLASS library runs on a GPU only
 
 
-def run_gemm(ap, asw, bp, bsw, alpha, m, n, k, entry="nv_kernels_cutlass_fp4_gemm_sm120_bf16"):
+def run_gemm(ap, asw, bp, bsw, alpha, m, n, k, entry="nv_kernels_cutlass_fp4_gemm_sm120_bf16", tile=0, stream_k=0):
     d = [U.dev(a) for a in (ap, asw, bp, bsw)]
     al = torch.tensor([alpha], dtype=torch.float32, device="cuda")
     out = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
     need = ctypes.c_size_t(0)
-    extra = [0, 0] if entry.endswith("_tiled") else []
+    extra = [tile, stream_k] if entry.endswith("_tiled") else []
     assert U.ffi.call(entry, U.stream(), None, None, None, None, None, None, m, n, k, *extra, None, 0,
                       ctypes.addressof(need)) == 0  # size query
     ws = torch.zeros(max(need.value, 16), dtype=torch.uint8, device="cuda")
@@ -63,9 +63,56 @@ def test_block_scaled_gemm_matches_w4a4_oracle(m, n, k, tile_config):
     absd = np.abs(ref.bf16_to_f32(got) - ref.bf16_to_f32(want))
     assert np.all((ulp <= 2) | (absd <= 1e-3)), f"max ulp {ulp.max()}"
     assert U.rel_err_floor(ref.bf16_to_f32(got), ref.bf16_to_f32(want).astype(np.float64)) < 1e-2
-    if (m, n, k) == (256, 384, 512):
-        for entry in ("nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk", "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled"):
-            assert np.array_equal(run_gemm(ap, asw, bp, bsw, alpha, m, n, k, entry), got)
+    if (m, n, k) == (256, 384, 512) and tile_config == 1:
+        # the data-parallel form of the tiled symbol is the same kernel: same bits, whatever tile id
+        for tile in (0, 1, 2):
+            assert np.array_equal(run_gemm(ap, asw, bp, bsw, alpha, m, n, k,
+                                           "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled", tile, 0), got)
+
+
+@pytest.mark.parametrize("m,n,k,stream_k", [(256, 384, 512, 1), (256, 256, 4096, 1), (256, 256, 4096, 4), (130, 264, 1056, 2),
+                                            (2048, 640, 3200, 1)])
+def test_stream_k_forms_match_the_oracle(m, n, k, stream_k):
+    """Stream-K splits output tiles along K and reduces the parts through the workspace, so the
+    summation order differs from the data-parallel kernel: same bound against the W4A4 oracle
+    (2 bf16 ulp or 1e-3 absolute), bit-stable run to run."""
+    U.require_gpu()
+    rng = np.random.default_rng(m + n + k + stream_k)
+    ap, alin, asw, _ = quantized_operand(rng, m, k, 1.0, 1.0)
+    bp, blin, bsw, gb = quantized_operand(rng, n, k, 0.02)
+    alpha = float(np.float32(1.0) / np.float32(gb))
+    want = ref.matmul_w4a4(ap, alin, bp, blin, m, n, k, alpha)
+    runs = [run_gemm(ap, asw, bp, bsw, alpha, m, n, k, "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled", 1, stream_k)
+            for _ in range(2)]
+    if stream_k == 1:
+        runs.append(run_gemm(ap, asw, bp, bsw, alpha, m, n, k, "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk"))
+    for got in runs:
+        ulp = U.bf16_ulp_diff(got, want)
+        absd = np.abs(ref.bf16_to_f32(got) - ref.bf16_to_f32(want))
+        assert np.all((ulp <= 2) | (absd <= 1e-3)), f"max ulp {ulp.max()}"
+    assert np.array_equal(runs[0], runs[1])
+    need = ctypes.c_size_t(0)
+    assert U.ffi.call("nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled", U.stream(), None, None, None, None, None, None, m, n, k,
+                      3, 0, None, 0, ctypes.addressof(need)) == -3     # no such tile
+
+
+def test_true_m_equals_padded_m_bitwise():
+    """rust/crates/nv-quant/tests/nvfp4_true_m.rs: a GEMM told the true row count gives the same bits
+    for those rows as one told the 128-padded count (pad rows are zeros and are not part of the result)."""
+    U.require_gpu()
+    rng = np.random.default_rng(31)
+    n, k = 384, 1024
+    bp, blin, bsw, gb = quantized_operand(rng, n, k, 0.02)
+    alpha = float(np.float32(1.0) / np.float32(gb))
+    for m in (1, 64, 130, 200):
+        m_pad = -(-m // 128) * 128
+        x = U.gauss_bf16(rng, (m, k))
+        ap, alin = ref.quantize_rows_bf16(x, 1.0, m_padded=m_pad)      # pad rows quantize to zeros
+        asw = ref.swizzle_scales(alin)
+        true_m = run_gemm(ap, asw, bp, bsw, alpha, m, n, k)
+        padded = run_gemm(ap, asw, bp, bsw, alpha, m_pad, n, k)
+        assert np.array_equal(true_m, padded[:m])
+        assert np.all(padded[m:] == 0)
 
 
 def test_linear_prefill_route_and_chunk_invariance(tile_config):
