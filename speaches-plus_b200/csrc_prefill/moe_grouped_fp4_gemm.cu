@@ -16,8 +16,13 @@
 //
 // The contraction is the CUTLASS sm100 pointer-array block-scaled collective (tcgen05.mma
 // kind::mxf4nvf4, scale factors in tensor memory, TMA operand loads with per-group descriptors,
-// accumulators in TMEM) with a 1-SM 128x128x256 tile and no cluster.  A small kernel turns the
-// offsets into the per-group pointer / stride / scale-layout arrays that collective reads.
+// accumulators in TMEM) with a 1-SM 128x128x256 tile and no cluster: library templates instantiated
+// here, not a hand-written kernel.  What this file adds is the planning step in front of it: one
+// kernel turns the routing tables into the per-group argument arrays the collective reads (their
+// structure-of-arrays form is the collective's interface) AND checks them -- the tables are data
+// written by earlier kernels, so a group whose sizes disagree with the launch's (N, K), whose row
+// count or offsets are negative, or whose expert id is negative is given zero rows in a private copy
+// of the problem sizes instead of being followed.
 //
 // Built only when CUTLASS headers are found (NVK_HAVE_CUTLASS); otherwise the entry points refuse.
 #include <cuda_runtime.h>
@@ -94,6 +99,7 @@ struct GroupArrays {
     StrideD* dd;
     LayoutSFA* lsfa;
     LayoutSFB* lsfb;
+    int32_t* sizes;   // checked copy of the caller's (m, n, k) triples: what the GEMM actually reads
 };
 
 struct Carver {
@@ -122,22 +128,34 @@ GroupArrays carve(uint8_t* scratch, int groups, size_t* bytes) {
     g.dd = c.take<StrideD>(groups);
     g.lsfa = c.take<LayoutSFA>(groups);
     g.lsfb = c.take<LayoutSFB>(groups);
+    g.sizes = c.take<int32_t>(3 * groups);
     *bytes = c.off;
     return g;
 }
 
-// One thread per group: offsets -> pointers, strides and scale layouts.
-__global__ void group_args_kernel(GroupArrays g, const uint8_t* a_packed, const uint8_t* a_scales,
-                                  const uint8_t* b_packed, const uint8_t* b_scales, const float* alphas,
-                                  uint16_t* d_bf16, const int32_t* expert_offsets, const int32_t* sf_offsets,
-                                  const int32_t* problem_sizes, const int32_t* active_expert_indices, int groups,
-                                  int64_t a_row_stride, int64_t b_row_stride, int64_t d_row_stride) {
+// One thread per group: routing tables -> checked problem size, pointers, strides and scale layouts.
+__global__ void plan_groups_kernel(GroupArrays g, const uint8_t* a_packed, const uint8_t* a_scales,
+                                   const uint8_t* b_packed, const uint8_t* b_scales, const float* alphas,
+                                   uint16_t* d_bf16, const int32_t* expert_offsets, const int32_t* sf_offsets,
+                                   const int32_t* problem_sizes, const int32_t* active_expert_indices, int groups,
+                                   int launch_n, int launch_k, int64_t a_row_stride, int64_t b_row_stride,
+                                   int64_t d_row_stride) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= groups) return;
-    const int m = problem_sizes[3 * i], n = problem_sizes[3 * i + 1], k = problem_sizes[3 * i + 2];
-    const int64_t row0 = expert_offsets[i];
-    const int64_t sf_row0 = sf_offsets[i];
-    const int64_t e = active_expert_indices ? active_expert_indices[i] : i;
+    int m = problem_sizes[3 * i];
+    const int n = launch_n, k = launch_k;
+    int64_t row0 = expert_offsets[i];
+    int64_t sf_row0 = sf_offsets[i];
+    int64_t e = active_expert_indices ? active_expert_indices[i] : i;
+    const bool sane = m >= 0 && problem_sizes[3 * i + 1] == n && problem_sizes[3 * i + 2] == k && row0 >= 0 &&
+                      sf_row0 >= 0 && (sf_row0 & 127) == 0 && e >= 0;
+    if (!sane) {   // an empty group at the start of the buffers: nothing is read or written for it
+        m = 0;
+        row0 = sf_row0 = e = 0;
+    }
+    g.sizes[3 * i] = m;
+    g.sizes[3 * i + 1] = n;
+    g.sizes[3 * i + 2] = k;
     const int64_t k_bytes = k / 2;                                   // packed bytes per row
     const int64_t sf_cols = (int64_t)((k / 16 + 3) / 4) * 4;          // scale bytes per row, padded to k-tiles
     const int64_t n_pad = (int64_t)((n + 127) / 128) * 128;
@@ -177,9 +195,8 @@ int run_grouped(void* stream, const void* a_packed, const void* a_scales, const 
 
         typename Gemm::Arguments args{};
         args.mode = cutlass::gemm::GemmUniversalMode::kGrouped;
-        args.problem_shape = {num_groups,
-                              reinterpret_cast<typename GroupShape::UnderlyingProblemShape*>(
-                                  const_cast<int32_t*>(problem_sizes)),
+        // the GEMM reads the checked copy of the sizes that plan_groups_kernel writes, not the caller's
+        args.problem_shape = {num_groups, reinterpret_cast<typename GroupShape::UnderlyingProblemShape*>(g.sizes),
                               nullptr};
         args.mainloop.ptr_A = g.a;
         args.mainloop.dA = g.da;
@@ -213,12 +230,13 @@ int run_grouped(void* stream, const void* a_packed, const void* a_scales, const 
         if (need > gemm_workspace_bytes || (need > 0 && !gemm_workspace)) return -12;
 
         cudaStream_t s = (cudaStream_t)stream;
-        group_args_kernel<<<(unsigned)((num_groups + 127) / 128), 128, 0, s>>>(
-            g, static_cast<const uint8_t*>(a_packed), static_cast<const uint8_t*>(a_scales),
-            static_cast<const uint8_t*>(b_packed), static_cast<const uint8_t*>(b_scales), alphas,
-            static_cast<uint16_t*>(d_bf16), expert_offsets, sf_offsets, problem_sizes, active_expert_indices,
-            num_groups, a_row_stride_elems, b_row_stride_elems, c_row_stride_elems);
-        if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return (int)e;
+        if (int rc = nvk::launch(nvk::launch_1d(s, (unsigned)((num_groups + 127) / 128), 128), plan_groups_kernel, g,
+                                 static_cast<const uint8_t*>(a_packed), static_cast<const uint8_t*>(a_scales),
+                                 static_cast<const uint8_t*>(b_packed), static_cast<const uint8_t*>(b_scales), alphas,
+                                 static_cast<uint16_t*>(d_bf16), expert_offsets, sf_offsets, problem_sizes,
+                                 active_expert_indices, num_groups, N, K, a_row_stride_elems, b_row_stride_elems,
+                                 c_row_stride_elems))
+            return rc;
 
         Gemm gemm;
         if (gemm.can_implement(args) != cutlass::Status::kSuccess) return -13;

@@ -264,31 +264,53 @@ class Nvfp4Linear:
             y += self.bias
         return y.reshape(*lead, self.out_features)
 
+    def prepare_prefill(self, max_m: int, device=None) -> None:
+        """Create everything the prefill route needs for up to `max_m` rows -- the quantized-activation
+        buffers, the GEMM workspace and the device copy of alpha -- so that later calls allocate nothing
+        (the reference creates its runner's workspace ahead of time for the same reason,
+        rust/crates/nv-quant/src/nvfp4.rs:391-409).  Called on first use if not before."""
+        dev = self.weight_u8.device if device is None else torch.device(device)
+        k, n = self.in_features, self.out_features
+        m_pad = -(-max_m // 128) * 128
+        need = C.c_size_t(0)
+        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", _stream(), None, None, None, None, None, None, m_pad, n, k,
+                   None, 0, C.addressof(need))
+        self._prefill = {
+            "m_pad": m_pad,
+            "a_packed": torch.empty((m_pad, k // 2), dtype=torch.uint8, device=dev),
+            "a_scales": torch.zeros(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=dev),
+            "ws": torch.empty(max(int(need.value), 16), dtype=torch.uint8, device=dev),
+            "alpha": torch.tensor([self.weight_alpha], dtype=torch.float32, device=dev),
+        }
+
+    def _prefill_buffers(self, m: int, device):
+        st = getattr(self, "_prefill", None)
+        if st is None or st["m_pad"] < m or st["ws"].device != device:
+            self.prepare_prefill(m, device)
+            st = self._prefill
+        return st
+
     def forward_prefill_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
         """Prefill-sized M: the reference's default route (rust/crates/nv-layers/src/linear.rs:1590-1795) --
         quantize the activations to NVFP4 (global 1.0, rows padded to a multiple of 128 with zeros), then one
-        block-scaled FP4 x FP4 tensor-core GEMM with alpha = weight_alpha in device memory."""
-        m = x2.shape[0]
+        block-scaled FP4 x FP4 tensor-core GEMM with alpha = weight_alpha in device memory.  Uses the
+        buffers of `prepare_prefill` (created on the first call that needs them)."""
+        m, k = x2.shape
+        st = self._prefill_buffers(m, x2.device)
         m_pad = -(-m // 128) * 128
-        a_packed, a_scales = quantize_nvfp4_bf16(x2, self.input_stored_global, m_padded=m_pad)
+        a_packed, a_scales = st["a_packed"][:m_pad], st["a_scales"][:swizzled_scale_bytes(m_pad, k)]
+        _ffi.check("nv_kernels_quantize_nvfp4_bf16", _stream(), x2.data_ptr(), a_packed.data_ptr(), a_scales.data_ptr(),
+                   float(self.input_stored_global), m_pad, m, k)
         self._fp4_gemm(a_packed, a_scales, y, m)
 
     def _fp4_gemm(self, a_packed: torch.Tensor, a_scales: torch.Tensor, y: torch.Tensor, m: int) -> None:
         """y [m, out] = alpha * A W^T for activations already quantized (rows padded to 128)."""
         k, n = self.in_features, self.out_features
-        dev = a_packed.device
-        if getattr(self, "_alpha_dev", None) is None or self._alpha_dev.device != dev:
-            self._alpha_dev = torch.tensor([self.weight_alpha], dtype=torch.float32, device=dev)
+        st = self._prefill_buffers(m, a_packed.device)
         need = C.c_size_t(0)
-        s = _stream()
-        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", s, None, None, None, None, None, None, m, n, k, None, 0,
-                   C.addressof(need))
-        ws = linear_workspace(dev, 1, 16)
-        if ws.numel() < need.value:
-            ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
-        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", s, a_packed.data_ptr(), a_scales.data_ptr(),
-                   self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), self._alpha_dev.data_ptr(), y.data_ptr(),
-                   m, n, k, ws.data_ptr(), ws.numel(), C.addressof(need))
+        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", _stream(), a_packed.data_ptr(), a_scales.data_ptr(),
+                   self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), st["alpha"].data_ptr(), y.data_ptr(),
+                   m, n, k, st["ws"].data_ptr(), st["ws"].numel(), C.addressof(need))
 
 
 class Bf16Linear:
