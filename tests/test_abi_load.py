@@ -73,7 +73,7 @@ def declared_prototypes():
                 kinds.append("size_t")
             elif re.match(r"(const\s+)?float\b", prm):
                 kinds.append("float")
-            elif re.match(r"(const\s+)?(int|int32_t)\b", prm):
+            elif re.match(r"(const\s+)?(int|int32_t|unsigned)\b", prm):
                 kinds.append("int")
             else:
                 raise AssertionError(f"{name}: parameter type not understood: {prm!r}")
@@ -84,8 +84,8 @@ def declared_prototypes():
 def test_binding_argument_types_match_the_header():
     """Every ctypes signature has the header's parameter count and kinds, in order: a drifted binding
     would pass garbage through the C ABI without any error."""
-    kind = {ctypes.c_void_p: "ptr", ctypes.c_int: "int", ctypes.c_float: "float", ctypes.c_size_t: "size_t",
-            ctypes.c_longlong: "i64"}
+    kind = {ctypes.c_void_p: "ptr", ctypes.c_int: "int", ctypes.c_uint: "int", ctypes.c_float: "float",
+            ctypes.c_size_t: "size_t", ctypes.c_longlong: "i64"}
     protos = declared_prototypes()
     sigs = dict(sp.ffi.SIGNATURES)
     sigs.update(sp.ffi.PREFILL_SIGNATURES)
