@@ -2,7 +2,12 @@
 -DNVK_EMU against tests/emu (see cuda_emu.h).  Output: tests/emu/build/libnvk_b200_emu.so, loaded
 only by the tests.
 
-    python tests/emu/build_emu.py [--force]
+    python tests/emu/build_emu.py [--force] [--sanitize]
+
+--sanitize builds tests/emu/build/libnvk_b200_emu_san.so with -fsanitize=alignment,shift,
+signed-integer-overflow,bounds (no recovery): a misaligned vector load or store in a kernel -- a fault on
+the GPU -- aborts the run.  Use it with
+    NVK_EMU_LIB=tests/emu/build/libnvk_b200_emu_san.so python -m pytest tests -m gpu --emu
 """
 from __future__ import annotations
 
@@ -28,18 +33,23 @@ def _deps_mtime() -> float:
     return max(f.stat().st_mtime for f in files)
 
 
-def build(force: bool = False) -> pathlib.Path:
-    if not force and LIB.exists() and LIB.stat().st_mtime >= _deps_mtime():
-        return LIB
+SAN_FLAGS = ["-fsanitize=alignment,shift,signed-integer-overflow,bounds", "-fno-sanitize-recover=all"]
+
+
+def build(force: bool = False, sanitize: bool = False) -> pathlib.Path:
+    lib = OUT_DIR / "libnvk_b200_emu_san.so" if sanitize else LIB
+    if not force and lib.exists() and lib.stat().st_mtime >= _deps_mtime():
+        return lib
     OUT_DIR.mkdir(exist_ok=True)
     newest_header = max(f.stat().st_mtime for f in list(CSRC.glob("*.cuh")) + list(HERE.glob("*.h")))
 
     def compile_one(src: pathlib.Path) -> pathlib.Path:
-        obj = OUT_DIR / (src.stem + ".emu.o")
+        obj = OUT_DIR / (src.stem + (".san.o" if sanitize else ".emu.o"))
         if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, newest_header):
             return obj
         lang = ["-x", "c++"] if src.suffix == ".cu" else []
-        r = subprocess.run(["g++", *CXX_FLAGS, *lang, "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+        r = subprocess.run(["g++", *CXX_FLAGS, *(SAN_FLAGS if sanitize else []), *lang, "-c", str(src), "-o", str(obj)],
+                           capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError(f"emulation build failed on {src.name}")
@@ -48,9 +58,10 @@ def build(force: bool = False) -> pathlib.Path:
     srcs = sorted(CSRC.glob("*.cu")) + [HERE / "emu_rt.cpp"]
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, srcs))
-    subprocess.run(["g++", "-shared", "-o", str(LIB), *map(str, objs), "-lpthread"], check=True)
-    return LIB
+    subprocess.run(["g++", "-shared", "-o", str(lib), *map(str, objs), "-lpthread", *(["-lubsan"] if sanitize else [])],
+                   check=True)
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, sanitize="--sanitize" in sys.argv))

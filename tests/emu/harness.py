@@ -26,7 +26,9 @@ def _build_module():
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        path = _build_module().build()
+        import os
+        # NVK_EMU_LIB: a prebuilt emulation library to use instead (e.g. one built with -fsanitize=...)
+        path = os.environ.get("NVK_EMU_LIB") or _build_module().build()
         L = C.CDLL(str(path))
         for name, args in sp.ffi.SIGNATURES.items():
             fn = getattr(L, name)   # the emulated library must export every symbol of the product's
