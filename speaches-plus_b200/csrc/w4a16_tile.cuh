@@ -46,10 +46,23 @@ using nvk::ptx::cp_async_wait;
 
 // Two ue4m3 scale bytes (the low half of `w`, bit 7 of each byte already cleared) -> f16x2.
 // ue4m3 is the non-negative half of e4m3, so the hardware e4m3 convert is exact for 0x00..0x7E;
-// 0x7F (never produced by an NVFP4 encoder, NaN in e4m3) converts to NaN.
+// 0x7F (never produced by an NVFP4 encoder, NaN in e4m3) converts to NaN and is repaired by
+// fix_scale_7f below: the decode rule gives (1 + 7/8) * 2^8 = 480 for that byte.
 __device__ __forceinline__ __half2 scales2_f16(uint32_t w) {
     uint32_t d = nvk::ptx::e4m3x2_to_f16x2(w);
     return *reinterpret_cast<__half2*>(&d);
+}
+
+// Non-zero if either half is NaN (only a 0x7F scale byte can make one).
+__device__ __forceinline__ uint32_t scale_nan_bits(__half2 s) {
+    const __half2 f = __hisnan2(s);   // 1.0 where NaN, else 0.0
+    return *reinterpret_cast<const uint32_t*>(&f);
+}
+// Each NaN half becomes 480.0 (0x5F80); the other half is kept.  Off the hot path.
+__device__ __noinline__ uint32_t fix_scale_7f(uint32_t bits) {
+    if ((bits & 0x7FFFu) > 0x7C00u) bits = (bits & 0xFFFF0000u) | 0x5F80u;
+    if ((bits & 0x7FFF0000u) > 0x7C000000u) bits = (bits & 0x0000FFFFu) | 0x5F800000u;
+    return bits;
 }
 
 // In place: eight bf16 gate values (as 4 words) -> bf16(SiLU(gate) * up), fp32 math, one rounding.
@@ -233,6 +246,16 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             const uint2 sw = *reinterpret_cast<const uint2*>(src - lane * 8 + 2048 + pc * 256);
             sp[0][pc] = scales2_f16((sw.x & 0x7F7F7F7Fu) >> (16 * (tg & 1)));
             sp[1][pc] = scales2_f16((sw.y & 0x7F7F7F7Fu) >> (16 * (tg & 1)));
+        }
+        // a 0x7F scale byte (NaN after the hardware convert) decodes to 480 like every other route
+        if (scale_nan_bits(sp[0][0]) | scale_nan_bits(sp[0][1]) | scale_nan_bits(sp[1][0]) | scale_nan_bits(sp[1][1])) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int pc = 0; pc < 2; ++pc) {
+                    const uint32_t b = fix_scale_7f(*reinterpret_cast<const uint32_t*>(&sp[i][pc]));
+                    sp[i][pc] = *reinterpret_cast<const __half2*>(&b);
+                }
         }
 #pragma unroll
         for (int wi = 0; wi < 8; ++wi) {

@@ -295,6 +295,10 @@ static inline __half __float2half_rn(float f) { _Float16 v = (_Float16)f; __half
 static inline __half __double2half_rn_emu(double f) { _Float16 v = (_Float16)f; __half h; memcpy(&h.bits, &v, 2); return h; }
 static inline __half2 __floats2half2_rn(float a, float b) { return __half2{__float2half_rn(a), __float2half_rn(b)}; }
 static inline float2 __half22float2(__half2 h) { return float2{__half2float(h.x), __half2float(h.y)}; }
+static inline __half2 __hisnan2(__half2 h) {
+    const float a = __half2float(h.x), b = __half2float(h.y);
+    return __half2{__float2half_rn(a != a ? 1.f : 0.f), __float2half_rn(b != b ? 1.f : 0.f)};
+}
 static inline __half2 __high2half2(__half2 h) { return __half2{h.y, h.y}; }
 static inline __half2 __low2half2(__half2 h) { return __half2{h.x, h.x}; }
 // f16 x f16 is exact in f32 (11 + 11 significand bits), so one rounding to f16 is the IEEE result

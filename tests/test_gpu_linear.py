@@ -202,19 +202,33 @@ def test_wide_dynamic_range_and_special_values():
 
 
 def test_every_scale_byte_and_code_decodes_like_the_oracle():
-    """Random nibbles and random scale bytes over the whole 0..0x7E range, plus bytes with bit 7 set
-    (the reference's decode formula ignores that bit).  0x7F is left out: no NVFP4 encoder emits it
-    (it is NaN in e4m3) and the kernel's hardware convert yields NaN where the formula gives 480."""
+    """Random nibbles and random scale bytes over the whole 0..0x7F range, plus bytes with bit 7 set
+    (the reference's decode formula ignores that bit).  0x7F -- which no NVFP4 encoder emits and which is
+    NaN to the hardware's e4m3 convert -- decodes to 480 as the formula says (rust/crates/nv-quant/src/nvfp4.rs:76-85),
+    on the tensor-core route and on the generic one."""
     U.require_gpu()
     rng = np.random.default_rng(11)
     n, k = 128, 512
     packed = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
-    lin = rng.integers(0, 0x7F, size=(n, k // 16), dtype=np.uint8)
-    lin[0, :8] = [0x80, 0xFE, 0x81, 0x00, 0x01, 0x07, 0x08, 0x7E]
+    lin = rng.integers(0, 0x80, size=(n, k // 16), dtype=np.uint8)
+    lin[0, :10] = [0x80, 0xFE, 0x81, 0x00, 0x01, 0x07, 0x08, 0x7E, 0x7F, 0xFF]
+    lin[5:9, :] = 0x7F
+    assert (lin == 0x7F).sum() > 100
     sw = ref.swizzle_scales(lin)
     x = U.gauss_bf16(rng, (1, k))
     got = run_gemv(packed, sw, x, 2.0 ** -12, n, k)
+    assert not np.any(np.isnan(ref.bf16_to_f32(got)))
     check_against_oracle(got, packed, sw, x, 2.0 ** -12, n, k, cpu_backend=False)
+    # the generic route (K % 32 != 0) and several tokens decode the same way
+    k2 = 48
+    lin2 = np.full((n, k2 // 16), 0x7F, np.uint8)
+    packed2 = rng.integers(0, 256, size=(n, k2 // 2), dtype=np.uint8)
+    x2 = U.gauss_bf16(rng, (1, k2))
+    got2 = run_gemv(packed2, ref.swizzle_scales(lin2), x2, 2.0 ** -12, n, k2)
+    check_against_oracle(got2, packed2, ref.swizzle_scales(lin2), x2, 2.0 ** -12, n, k2, cpu_backend=False)
+    x5 = U.gauss_bf16(rng, (5, k))
+    got5 = run_linear(packed, sw, x5, 2.0 ** -12, 5, n, k)
+    check_against_oracle(got5, packed, sw, x5, 2.0 ** -12, n, k, cpu_backend=False)
 
 
 def test_dual_and_silu_prologue_m1():
