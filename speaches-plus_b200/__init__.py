@@ -9,4 +9,5 @@ from .linear import Nvfp4Linear, Bf16Linear, Nvfp4Mlp, quantize_weight_nvfp4, sw
 from .moe import (MoeGroupedWeights, GroupedDecodeContext, forward_grouped_decode, forward_grouped,  # noqa: F401
                   plan_routing, MoeBlock, MoeConfig, TiledDecodeContext, forward_grouped_decode_into)
 from . import weights  # noqa: F401,E402
+from . import runner  # noqa: F401,E402
 from .stack import DecodeStep  # noqa: F401,E402

@@ -307,6 +307,11 @@ class Nvfp4Linear:
         """y [m, out] = alpha * A W^T for activations already quantized (rows padded to 128)."""
         k, n = self.in_features, self.out_features
         st = self._prefill_buffers(m, a_packed.device)
+        runner = getattr(self, "runner", None)
+        if runner is not None:
+            # an Nvfp4GemmRunner (runner.py) picks the scheduler for the shape and owns the workspace
+            runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, st["alpha"], y, m, n, k)
+            return
         need = C.c_size_t(0)
         _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", _stream(), a_packed.data_ptr(), a_scales.data_ptr(),
                    self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), st["alpha"].data_ptr(), y.data_ptr(),

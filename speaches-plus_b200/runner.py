@@ -1,0 +1,166 @@
+"""Host-side mirror of the reference's `Nvfp4GemmRunner` (rust/crates/nv-quant/src/nvfp4.rs:359-1084) for
+the prefill-sized FP4 x FP4 GEMM: which scheduler a shape gets, the per-stream workspace created ahead of
+graph capture, and the environment knobs, over this library's three GEMM entry points.
+
+One backend exists here (the block-scaled tensor-core GEMM of libnvk_b200_prefill.so); asking for the
+reference's cuBLASLt backend is an error, not a silent switch.  Single-GPU processes only (the prefill
+library refuses to load in a rank of several).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import os
+
+import torch
+
+from . import _ffi
+
+WORKSPACE_BYTES = 64 * 1024 * 1024      # per stream (nvfp4.rs:377)
+TILE_M = TILE_N = 128                   # the tile the scheduler rule counts in (nvfp4.rs:365-367)
+SM_COUNT = 148                          # B200
+
+
+# ---- environment knobs: the reference's parsers, name for name (nvfp4.rs:213-229, 424-463) ------------
+def skinny_lt_from(raw):
+    return raw != "0"
+
+
+def k256_from(raw):
+    return raw != "0"
+
+
+def streamk_k256_from(raw):
+    return raw is not None and raw != "" and raw != "0"
+
+
+def streamk_down_splits_from(raw) -> int:
+    try:
+        s = int(raw.strip()) if raw is not None else 0
+    except ValueError:
+        return 0
+    return s if s >= 2 else 0
+
+
+class StreamkMode(enum.Enum):
+    NEVER = 0
+    ALWAYS = 1
+    AUTO = 2
+
+
+def streamk_mode_from(raw) -> StreamkMode:
+    return {"0": StreamkMode.NEVER, "1": StreamkMode.ALWAYS}.get(raw, StreamkMode.AUTO)
+
+
+class Nvfp4Backend(enum.Enum):
+    CUBLASLT = "cublaslt"
+    CUTLASS = "cutlass"
+    AUTO = "auto"
+
+    @classmethod
+    def from_env(cls, raw=None) -> "Nvfp4Backend":
+        raw = os.environ.get("SPEACHES_NVFP4_BACKEND") if raw is None else raw
+        v = (raw or "auto").strip().lower()
+        if v in ("cublaslt", "cublas"):
+            return cls.CUBLASLT
+        if v == "cutlass":
+            return cls.CUTLASS
+        return cls.AUTO      # unrecognised values fall back to auto, as the reference does
+
+
+# ---- scheduler rule ---------------------------------------------------------------------------------------
+def skinny_tiles(m: int, n: int) -> bool:
+    """The reference's rule (nvfp4.rs:667-671): few enough output tiles that a data-parallel launch
+    leaves SMs idle."""
+    return -(-m // TILE_M) * -(-n // TILE_N) <= 192
+
+
+def ragged_last_wave(m: int, n: int, sms: int = SM_COUNT) -> bool:
+    """This library's addition for a 148-SM part: at most eight waves of output tiles of which the last
+    is at most half full (M = 2048, N = 5120: 640 tiles = 4 waves + 48 tiles)."""
+    tiles = -(-m // TILE_M) * -(-n // TILE_N)
+    full, rest = divmod(tiles, sms)
+    return 0 < rest <= sms // 2 and full < 8
+
+
+# ---- per-stream workspaces ----------------------------------------------------------------------------------
+_WORKSPACES: dict = {}
+
+
+def _stream_key() -> tuple:
+    return (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+
+
+def ensure_workspace_for_stream() -> torch.Tensor:
+    """The current stream's 64 MiB workspace, created on first use -- which must not be inside a graph
+    capture (nvfp4.rs:391-409): call this on the capture stream before capturing."""
+    key = _stream_key()
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"nvfp4 workspace for stream {key[1]:#x} must be created before graph capture "
+                               "(call ensure_workspace_for_stream on the capture stream first)")
+        ws = torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=f"cuda:{key[0]}")
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def release_stream_workspace(device_index: int, cu_stream: int) -> None:
+    _WORKSPACES.pop((device_index, cu_stream), None)
+
+
+# ---- the runner -------------------------------------------------------------------------------------------
+class Nvfp4GemmRunner:
+    """d [m, n] bf16 = alpha * A [m, k] * B [n, k]^T for NVFP4 operands with swizzled block scales."""
+
+    def __init__(self, backend: Nvfp4Backend | None = None, env=None):
+        env = os.environ if env is None else env
+        self.backend = Nvfp4Backend.from_env(env.get("SPEACHES_NVFP4_BACKEND")) if backend is None else backend
+        if self.backend is Nvfp4Backend.CUBLASLT:
+            raise NotImplementedError("the cuBLASLt NVFP4 backend of the reference is not part of this library; "
+                                      "unset SPEACHES_NVFP4_BACKEND or set it to cutlass/auto")
+        self.streamk_mode = streamk_mode_from(env.get("NV_NVFP4_STREAMK"))
+        self.k256 = k256_from(env.get("NV_NVFP4_K256"))
+        self.streamk_k256 = streamk_k256_from(env.get("NV_NVFP4_STREAMK_K256"))
+        self.streamk_down_splits = streamk_down_splits_from(env.get("NV_NVFP4_STREAMK_DOWN_SPLITS"))
+        self.streamk_failed = False     # a stream-K launch that fails switches it off for good (nvfp4.rs:719-727)
+
+    def streamk_wanted(self, m: int, n: int) -> bool:
+        if self.streamk_failed or self.streamk_mode is StreamkMode.NEVER:
+            return False
+        if self.streamk_mode is StreamkMode.ALWAYS:
+            return True
+        return skinny_tiles(m, n) or ragged_last_wave(m, n)
+
+    def plan(self, m: int, n: int, k: int, stream_k: bool):
+        """(entry point, extra integer arguments) for one launch -- the reference's choice tree
+        (nvfp4.rs:767-854) over this library's symbols."""
+        tiled = "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled"
+        if stream_k and self.streamk_down_splits >= 2:
+            return tiled, (0, self.streamk_down_splits)
+        if stream_k:
+            if k % 256 == 0 and self.streamk_k256:
+                return tiled, (1, 1)
+            return "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk", ()
+        if k % 256 == 0 and self.k256:
+            return tiled, (1, 0)
+        return "nv_kernels_cutlass_fp4_gemm_sm120_bf16", ()
+
+    def _launch(self, entry, extra, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m, n, k, ws) -> int:
+        need = C.c_size_t(0)
+        return _ffi.call(entry, torch.cuda.current_stream().cuda_stream, a_packed.data_ptr(), a_scales.data_ptr(),
+                         b_packed.data_ptr(), b_scales.data_ptr(), alpha_dev.data_ptr(), d.data_ptr(), m, n, k, *extra,
+                         ws.data_ptr(), ws.numel(), C.addressof(need))
+
+    def matmul(self, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m: int, n: int, k: int) -> None:
+        ws = ensure_workspace_for_stream()
+        if self.streamk_wanted(m, n):
+            entry, extra = self.plan(m, n, k, True)
+            rc = self._launch(entry, extra, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m, n, k, ws)
+            if rc == 0:
+                return
+            self.streamk_failed = True   # fall back to the data-parallel scheduler, permanently
+        entry, extra = self.plan(m, n, k, False)
+        rc = self._launch(entry, extra, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m, n, k, ws)
+        if rc != 0:
+            raise _ffi.NvkError(entry, rc)

@@ -133,3 +133,64 @@ def test_persistent_step_protocol_cannot_deadlock():
             done[o] += 1
             state[c][1] = None
         assert all(all(v == 1 for v in r) for r in ran) and done == items
+
+
+# ---- the GEMM runner's host logic (rust/crates/nv-quant/src/nvfp4.rs:359-1084) ----
+
+def test_runner_knob_parsers_follow_the_reference_pins():
+    from speaches_plus_b200 import runner as R
+    # nvfp4.rs:1133-1170 (streamk_k256_gate_tests and the sibling gates)
+    assert not R.streamk_k256_from(None) and not R.streamk_k256_from("") and not R.streamk_k256_from("0")
+    assert R.streamk_k256_from("1") and R.streamk_k256_from("yes")
+    assert R.k256_from(None) and R.k256_from("1") and not R.k256_from("0")
+    assert R.skinny_lt_from(None) and not R.skinny_lt_from("0")
+    assert R.streamk_down_splits_from(None) == 0 and R.streamk_down_splits_from("1") == 0
+    assert R.streamk_down_splits_from(" 4 ") == 4 and R.streamk_down_splits_from("x") == 0
+    assert R.streamk_mode_from("0") is R.StreamkMode.NEVER and R.streamk_mode_from("1") is R.StreamkMode.ALWAYS
+    assert R.streamk_mode_from(None) is R.StreamkMode.AUTO
+    assert R.Nvfp4Backend.from_env("CUBLAS ") is R.Nvfp4Backend.CUBLASLT
+    assert R.Nvfp4Backend.from_env("bogus") is R.Nvfp4Backend.AUTO
+
+
+def test_runner_scheduler_rule():
+    from speaches_plus_b200 import runner as R
+    # nvfp4.rs:1116-1124 skinny_tiles_covers_verify_shapes_not_prefill
+    assert R.skinny_tiles(128, 5376) and R.skinny_tiles(128, 5376 * 2) and R.skinny_tiles(128, 20480)
+    assert not R.skinny_tiles(128, 43008) and not R.skinny_tiles(2048, 5376) and not R.skinny_tiles(1024, 43008)
+    # the 148-SM addition: 640 tiles leave a last wave of 48; 3200 tiles are 21 waves and a bit
+    assert R.ragged_last_wave(2048, 5120) and not R.ragged_last_wave(2048, 25600)
+    assert not R.ragged_last_wave(128 * 148, 128)          # exactly one wave
+    r = R.Nvfp4GemmRunner(env={})
+    assert r.streamk_wanted(2048, 5120) and not r.streamk_wanted(2048, 25600)
+    assert not R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK": "0"}).streamk_wanted(128, 128)
+    assert R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK": "1"}).streamk_wanted(8192, 8192)
+    with __import__("pytest").raises(NotImplementedError):
+        R.Nvfp4GemmRunner(env={"SPEACHES_NVFP4_BACKEND": "cublaslt"})
+
+
+def test_runner_choice_tree_and_permanent_fallback(monkeypatch):
+    from speaches_plus_b200 import runner as R
+    tiled, sk, dp = ("nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled", "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk",
+                     "nv_kernels_cutlass_fp4_gemm_sm120_bf16")
+    r = R.Nvfp4GemmRunner(env={})
+    assert r.plan(256, 256, 512, False) == (tiled, (1, 0))          # K % 256 == 0: the K256 tile id
+    assert r.plan(256, 256, 384, False) == (dp, ())
+    assert r.plan(256, 256, 512, True) == (sk, ())                   # stream-K K256 ships off
+    assert R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK_K256": "1"}).plan(256, 256, 512, True) == (tiled, (1, 1))
+    assert R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK_DOWN_SPLITS": "4"}).plan(256, 256, 512, True) == (tiled, (0, 4))
+    assert R.Nvfp4GemmRunner(env={"NV_NVFP4_K256": "0"}).plan(256, 256, 512, False) == (dp, ())
+    # a failing stream-K launch falls back to the data-parallel scheduler and stays there
+    calls = []
+
+    def fake_launch(self, entry, extra, *a):
+        calls.append(entry)
+        return -1 if "streamk" in entry else 0
+
+    monkeypatch.setattr(R.Nvfp4GemmRunner, "_launch", fake_launch)
+    monkeypatch.setattr(R, "ensure_workspace_for_stream", lambda: None)
+    r = R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK": "1", "NV_NVFP4_K256": "0"})
+    r.matmul(None, None, None, None, None, None, 128, 128, 384)
+    assert calls == [sk, dp] and r.streamk_failed
+    calls.clear()
+    r.matmul(None, None, None, None, None, None, 128, 128, 384)
+    assert calls == [dp]
