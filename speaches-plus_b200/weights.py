@@ -500,6 +500,104 @@ def dequantize_packed_to_bf16_bits(packed: np.ndarray, scales_linear: np.ndarray
     return _f32_to_bf16_bits(vals.reshape(rows, cols))
 
 
+# ---- host-side NVFP4 container and quantizer (load-time tools; the decode path quantizes on the GPU) ----
+def encode_e2m1_host(x: np.ndarray) -> np.ndarray:
+    """f32 -> 4-bit e2m1 codes (sign in bit 3): nearest codebook value, the FIRST minimum winning, i.e.
+    ties go to the lower code (rust/crates/nv-quant/src/nvfp4.rs:6-22).  Midpoints with strict `>`."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.abs(x)
+    code = np.zeros(x.shape, dtype=np.uint8)
+    for mid in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0):
+        code += (a > np.float32(mid)).astype(np.uint8)
+    return code | (np.signbit(x).astype(np.uint8) << 3)
+
+
+def encode_ue4m3_host(s: np.ndarray) -> np.ndarray:
+    """f32 scale -> ue4m3 byte (nvfp4.rs:38-74): <= 0 / NaN / Inf -> 0; clamp to 448; below 2^-6 the
+    subnormal grid m * 2^-9; else mantissa rounded half away from zero with carry; 0x7F -> 0x7E."""
+    s = np.asarray(s, dtype=np.float32)
+    ok = np.isfinite(s) & (s > 0)
+    c = np.minimum(np.where(ok, s, np.float32(1.0)), np.float32(448.0)).astype(np.float32)
+    half_away = lambda v: np.floor(v + np.float32(0.5))   # noqa: E731  (arguments are non-negative)
+    sub_m = half_away((c / np.float32(2.0 ** -9)).astype(np.float32))
+    sub = np.where(sub_m <= 0, 0, np.where(sub_m <= 7, sub_m, 8)).astype(np.int64)
+    _, e2 = np.frexp(c)
+    ex = e2.astype(np.int64) - 1
+    mf = (np.ldexp(c, -ex.astype(np.int32)) - np.float32(1.0)).astype(np.float32)
+    mant = half_away((mf * np.float32(8.0)).astype(np.float32)).astype(np.int64)
+    mant = np.maximum(mant, 0)
+    carry = mant > 7
+    mant = np.where(carry, 0, mant)
+    ex = ex + carry
+    biased = np.clip(ex + 7, 1, 15)
+    byte = (biased << 3) | mant
+    byte = np.where(byte == 0x7F, 0x7E, byte)
+    out = np.where(c < np.float32(2.0 ** -6), sub, byte)
+    return np.where(ok, out, 0).astype(np.uint8)
+
+
+def quantize_rows_host(x: np.ndarray, stored_global: float = 1.0):
+    """f32 [rows, cols] -> (packed [rows, cols/2], row-major scales [rows, cols/16]) by the block rule of
+    nvfp4.rs:91-120: local = amax/6 (1 for an all-zero block); byte = ue4m3(G * local); inv = G / decode(byte)
+    (1 when that is 0); code = e2m1(clamp(v * inv, +-6)); G in {0, NaN, Inf} counts as 1.  All in f32."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    if cols % BLOCK_SIZE != 0:
+        raise WeightError(f"cols must be a multiple of {BLOCK_SIZE}")
+    g = np.float32(stored_global)
+    if g == 0 or not np.isfinite(g):
+        g = np.float32(1.0)
+    b = x.reshape(rows, cols // BLOCK_SIZE, BLOCK_SIZE)
+    amax = np.max(np.abs(b), axis=2).astype(np.float32)
+    local = np.where(amax == 0, np.float32(1.0), (amax / np.float32(6.0)).astype(np.float32)).astype(np.float32)
+    scales = encode_ue4m3_host((g * local).astype(np.float32))
+    dec = _UE4M3[scales]
+    inv = np.where(dec == 0, np.float32(1.0), (g / np.where(dec == 0, np.float32(1.0), dec)).astype(np.float32))
+    q = np.clip((b * inv[:, :, None].astype(np.float32)).astype(np.float32), np.float32(-6.0), np.float32(6.0))
+    codes = encode_e2m1_host(q)
+    packed = (codes[:, :, 0::2] | (codes[:, :, 1::2] << 4)).astype(np.uint8).reshape(rows, cols // 2)
+    return packed, scales.astype(np.uint8)
+
+
+@dataclasses.dataclass
+class Nvfp4Tensor:
+    """Row-major NVFP4 container on the host (nvfp4.rs:131-210): `data` [rows, cols/2] packed e2m1 (even
+    element in the low nibble), `scales` [rows, cols/16] ue4m3, row-major."""
+    data: np.ndarray
+    scales: np.ndarray
+    rows: int
+    cols: int
+
+    @classmethod
+    def quantize_rows(cls, rows) -> "Nvfp4Tensor":
+        return cls.quantize_rows_with_global(rows, 1.0)
+
+    @classmethod
+    def quantize_rows_with_global(cls, rows, stored_global: float) -> "Nvfp4Tensor":
+        x = np.asarray(rows, dtype=np.float32)
+        packed, scales = quantize_rows_host(x, stored_global)
+        return cls(packed, scales, x.shape[0], x.shape[1])
+
+    def scales_swizzled(self) -> np.ndarray:
+        return swizzle_scales(self.scales, self.rows, self.cols // BLOCK_SIZE)
+
+    def scales_column_major(self) -> np.ndarray:
+        return np.ascontiguousarray(self.scales.reshape(self.rows, self.cols // BLOCK_SIZE).T).reshape(-1)
+
+    def dequantize(self) -> np.ndarray:
+        return self.dequantize_scaled(1.0)
+
+    def dequantize_scaled(self, weight_mult: float) -> np.ndarray:
+        """f32 [rows, cols]: (e2m1 * ue4m3) then * weight_mult, as nvfp4.rs:178-209 multiplies."""
+        kb = self.cols // BLOCK_SIZE
+        block = _UE4M3[self.scales.reshape(self.rows, kb)].reshape(self.rows, kb, 1)
+        p = self.data.reshape(self.rows, kb, BLOCK_SIZE // 2)
+        vals = np.empty((self.rows, kb, BLOCK_SIZE), dtype=np.float32)
+        vals[:, :, 0::2] = _E2M1[p & 0xF] * block
+        vals[:, :, 1::2] = _E2M1[p >> 4] * block
+        return (vals.reshape(self.rows, self.cols) * np.float32(weight_mult)).astype(np.float32)
+
+
 def dequantize_nvfp4_to_bf16(weights: WeightLoader, module: str, out_features: int, in_features: int) -> np.ndarray:
     """A module too small for the NVFP4 kernels, expanded to bf16 bits on the host
     (moe.rs:955-992), with 1/stored_global as the multiplier.  Reads the compressed-tensors names, as

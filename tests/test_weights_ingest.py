@@ -334,3 +334,37 @@ def test_interoperates_with_the_safetensors_library(tmp_path):
                                                              "b": ("U8", b.shape, b.tobytes())})
     back = st.load_file(str(mine))
     assert np.array_equal(back["a"], a) and np.array_equal(back["b"], b)
+
+
+def test_host_nvfp4_tensor_is_byte_exact_with_the_oracle():
+    """The host container and its quantizer (rust/crates/nv-quant/src/nvfp4.rs:91-210) against the C
+    oracle: codes, scale bytes, swizzle, column-major scales and dequantization, on random data, ties,
+    zeros, huge and tiny magnitudes and odd globals."""
+    import numpy as np
+
+    from oracle import ref
+    from speaches_plus_b200 import weights as W
+    rng = np.random.default_rng(21)
+    rows, cols = 37, 256
+    x = (rng.standard_normal((rows, cols)) * np.exp(rng.uniform(-12, 12, (rows, 1)))).astype(np.float32)
+    x[0, :16] = 0.0
+    x[1, :16] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0]  # ties at unit scale
+    x[2, :16] = 1e30
+    x[3, :16] = 1e-30
+    for g in (1.0, 3.7, 2688.0 / 0.31, 0.0, float("nan"), float("inf")):
+        t = W.Nvfp4Tensor.quantize_rows_with_global(x, g)
+        packed, lin = ref.quantize_rows(x, g if np.isfinite(g) and g != 0 else 1.0)
+        assert np.array_equal(t.data, packed), g
+        assert np.array_equal(t.scales, lin), g
+        assert np.array_equal(t.scales_swizzled(), ref.swizzle_scales(lin))
+        assert np.array_equal(t.scales_column_major().reshape(cols // 16, rows), lin.T)
+        want = ref.dequantize_packed_linear(packed, lin, rows, cols, 0.5).reshape(rows, cols)
+        assert np.array_equal(t.dequantize_scaled(0.5), want)
+    assert W.Nvfp4Tensor.quantize_rows(x).scales.shape == (rows, cols // 16)
+    # every scale the encoder can meet: a dense sweep against the oracle's scalar encoder
+    s = np.concatenate([np.float32(2.0) ** rng.uniform(-12, 10, 4000).astype(np.float32),
+                        np.array([0, -1, np.nan, np.inf, 448, 449, 1e9, 2 ** -6, 2 ** -9, 2 ** -10], np.float32)])
+    assert np.array_equal(W.encode_ue4m3_host(s), np.array([ref.encode_ue4m3(float(v)) for v in s], np.uint8))
+    v = np.concatenate([rng.uniform(-7, 7, 4000).astype(np.float32),
+                        np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.0, 0.0], np.float32)])
+    assert np.array_equal(W.encode_e2m1_host(v), np.array([ref.encode_e2m1(float(q)) for q in v], np.uint8))
