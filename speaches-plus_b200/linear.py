@@ -111,6 +111,7 @@ class Nvfp4Linear:
         self.input_stored_global = float(input_stored_global)
         self.in_features, self.out_features = in_features, out_features
         self.bias = bias
+        self._lora = None   # adapter hook, see set_lora_hook
 
     # -- constructors (names follow the reference) --
     @classmethod
@@ -169,6 +170,16 @@ class Nvfp4Linear:
         sites do (rust/crates/nv-models/src/qwen3_5_moe.rs:718-727)."""
         return float(np.float32(self.weight_alpha) * np.float32(self.input_stored_global))
 
+    # -- adapter hook (rust/crates/nv-layers/src/linear.rs:591-606) --
+    def set_lora_hook(self, hook) -> None:
+        """`hook(x2, y2, window)` runs after the base matmul on the flattened [rows, in] input and
+        [rows, out] output (window is None for a whole linear) and returns a replacement for y2, or None
+        to keep it -- the adapter's low-rank delta is its business.  None removes the hook."""
+        self._lora = hook
+
+    def has_lora(self) -> bool:
+        return self._lora is not None
+
     # -- forward --
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] != self.in_features:
@@ -177,6 +188,10 @@ class Nvfp4Linear:
         x2 = x.reshape(-1, self.in_features)
         y = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
         self.forward_into(x2, y)
+        if self._lora is not None:
+            replaced = self._lora(x2, y, None)
+            if replaced is not None:
+                y = replaced
         if self.bias is not None:
             y += self.bias
         return y.reshape(*lead, self.out_features)
@@ -217,8 +232,8 @@ class Nvfp4Linear:
         return "decode"
 
     def prenorm_nvfp4_eligible(self) -> bool:
-        """linear.rs:648-651: an NVFP4 projection without bias (and without an adapter)."""
-        return self.bias is None
+        """linear.rs:648-651: an NVFP4 projection without bias and without an adapter."""
+        return self.bias is None and not self.has_lora()
 
     def forward_prenorm_nvfp4(self, x_pre: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
         """RMSNorm fused into the activation quantizer, then the FP4 x FP4 GEMM (linear.rs:653-689 with

@@ -612,3 +612,41 @@ def test_two_ranks_of_the_peer_all_reduce_on_one_device_buffer_pair():
     assert int(errs[1].cpu().numpy()[0]) == 1 and int(errs[0].cpu().numpy()[0]) == 0
     want = ref.f32_to_bf16(ref.bf16_to_f32(xs[0]) + ref.bf16_to_f32(xs[1]))   # fp32 sum in rank order, one rounding
     assert np.array_equal(U.host_u16(ys[0]), want)
+
+
+def test_lora_hook_runs_after_the_base_matmul_and_before_the_bias():
+    """rust/crates/nv-layers/src/linear.rs:624-645: matmul, adapter hook (may replace the output), bias."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(2)
+    n, k, m, r = 256, 512, 3, 8
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    bias = U.dev(U.gauss_bf16(rng, (n,))).view(torch.bfloat16)
+    lin = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n, bias)
+    x = U.dev(U.gauss_bf16(rng, (m, k))).view(torch.bfloat16)
+    base = lin(x).float().cpu()
+    a = sp.Bf16Linear(U.dev(U.gauss_bf16(rng, (r, k), 0.05)).view(torch.bfloat16))     # down-projection [r, k]
+    b = sp.Bf16Linear(U.dev(U.gauss_bf16(rng, (n, r), 0.05)).view(torch.bfloat16))     # up-projection [n, r]
+    seen = []
+
+    def hook(x2, y2, window):
+        seen.append((tuple(x2.shape), tuple(y2.shape), window))
+        return y2 + 2.0 * b(a(x2))
+
+    assert lin.prenorm_nvfp4_eligible() is False            # it has a bias
+    lin.set_lora_hook(hook)
+    assert lin.has_lora()
+    got = lin(x).float().cpu()
+    torch.cuda.synchronize()
+    assert seen == [((m, k), (m, n), None)]
+    delta = (2.0 * b(a(x))).float().cpu()
+    want = ((base - bias.float().cpu()).to(torch.bfloat16).float() + delta).to(torch.bfloat16).float() + bias.float().cpu()
+    assert torch.allclose(got, want.to(torch.bfloat16).float(), atol=0.05, rtol=0.02)
+    lin.set_lora_hook(lambda x2, y2, w: None)                # a hook may decline
+    assert torch.equal(lin(x).float().cpu(), base)
+    lin.set_lora_hook(None)
+    assert not lin.has_lora()
+    nb = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+    assert nb.prenorm_nvfp4_eligible()
+    nb.set_lora_hook(hook)
+    assert not nb.prenorm_nvfp4_eligible()
