@@ -10,5 +10,6 @@ from .moe import (MoeGroupedWeights, GroupedDecodeContext, forward_grouped_decod
                   plan_routing, MoeBlock, MoeConfig, TiledDecodeContext, forward_grouped_decode_into)
 from . import weights  # noqa: F401,E402
 from . import runner  # noqa: F401,E402
+from . import backend  # noqa: F401,E402
 from .weights import Nvfp4Tensor  # noqa: F401,E402
 from .stack import DecodeStep  # noqa: F401,E402

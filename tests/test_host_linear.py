@@ -194,3 +194,27 @@ def test_runner_choice_tree_and_permanent_fallback(monkeypatch):
     calls.clear()
     r.matmul(None, None, None, None, None, None, 128, 128, 384)
     assert calls == [dp]
+
+
+def test_backend_registry_knows_one_backend():
+    """rust/crates/nv-layers/src/backend.rs:16-233: the selection values parse as in the reference; only
+    cuda resolves, and it serves every kernel id of the path."""
+    import pytest
+
+    from speaches_plus_b200 import backend as B
+    assert B.BackendSel.parse(" AUTO ") is B.BackendSel.AUTO and B.BackendSel.parse("") is B.BackendSel.AUTO
+    assert B.BackendSel.parse("wgpu") is B.BackendSel.WGPU and B.BackendSel.parse("metal") is None
+    assert B.BackendSel.from_env({}) is B.BackendSel.AUTO
+    assert B.BackendSel.from_env({B.BACKEND_ENV: "Cuda"}) is B.BackendSel.CUDA
+    with pytest.raises(B.BackendError, match="not one of auto"):
+        B.BackendSel.from_env({B.BACKEND_ENV: "vulkan"})
+    assert B.resolve(B.BackendSel.AUTO) is B.BackendKind.CUDA and B.resolve(B.BackendSel.CUDA) is B.BackendKind.CUDA
+    for sel in (B.BackendSel.CPU, B.BackendSel.WGPU):
+        with pytest.raises(B.BackendError, match="no CPU or wgpu fallback"):
+            B.resolve(sel)
+    assert all(B.kind_supports(B.BackendKind.CUDA, k) for k in B.KernelId)
+    assert B.missing_on(B.BackendKind.CPU, list(B.KernelId)) == list(B.KernelId)
+    assert B.supporting_backends(B.KernelId.GEMV_NVFP4) == [B.BackendKind.CUDA]
+    assert B.library_for(B.KernelId.GEMM_NVFP4) == "libnvk_b200_prefill.so"
+    assert B.library_for(B.KernelId.GEMV_NVFP4) == "libnvk_b200.so"
+    assert str(B.BackendKind.CUDA) == "cuda"
