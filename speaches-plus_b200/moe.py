@@ -388,35 +388,53 @@ def forward_grouped(w: MoeGroupedWeights, x: torch.Tensor, topk_ids, topk_weight
     inv_perm = torch.from_numpy(np.ascontiguousarray(plan["inv_perm"])).to(dev)
     wts = topk_weights.to(device=dev, dtype=torch.float32).contiguous()
     s = _stream()
-    u8 = dict(dtype=torch.uint8, device=dev)
-    bf = dict(dtype=torch.bfloat16, device=dev)
-
-    x_sorted = torch.empty((m_total, hidden), **bf)
+    b = _grouped_buffers(w, m_total, n, dev)
+    x_sorted, x_fp4, x_sf, meta, ws = b["x_sorted"], b["x_fp4"], b["x_sf"], b["meta"], b["ws"]
+    y_gate, y_up, act_fp4, act_sf, y_down = b["y_gate"], b["y_up"], b["act_fp4"], b["act_sf"], b["y_down"]
     _ffi.check("nv_kernels_gather_rows_bf16", s, x.data_ptr(), src_idx.data_ptr(), x_sorted.data_ptr(), m_total,
                hidden, n)
-    x_fp4 = torch.empty((m_total, hidden // 2), **u8)
-    x_sf = torch.zeros(L.swizzled_scale_bytes(m_total, hidden), **u8)
     _ffi.check("nv_kernels_quantize_nvfp4_bf16_per_expert", s, x_sorted.data_ptr(), x_fp4.data_ptr(), x_sf.data_ptr(),
                gu_dev.data_ptr(), MIN_TILE, m_total, hidden)
-    meta = torch.empty(128 * 1024, **u8)
-    ws = torch.empty(16 * 1024 * 1024, **u8)
     gu_all, dn_all = torch.from_numpy(gu).to(dev), torch.from_numpy(dn).to(dev)
-    y_gate = torch.empty((m_total, inter), **bf)
-    y_up = torch.empty((m_total, inter), **bf)
     grouped_gemm_chunked(x_fp4, x_sf, w.gate, (w.gate[2] / gu_all).contiguous(), y_gate, active_ids, inter, hidden,
                          meta, ws)
     grouped_gemm_chunked(x_fp4, x_sf, w.up, (w.up[2] / gu_all).contiguous(), y_up, active_ids, inter, hidden, meta, ws)
-    act_fp4 = torch.empty((m_total, inter // 2), **u8)
-    act_sf = torch.zeros(L.swizzled_scale_bytes(m_total, inter), **u8)
     _ffi.check("nv_kernels_silu_mul_quantize_nvfp4_bf16_per_expert", s, y_gate.data_ptr(), y_up.data_ptr(),
                act_fp4.data_ptr(), act_sf.data_ptr(), dn_dev.data_ptr(), MIN_TILE, m_total, inter)
-    y_down = torch.empty((m_total, hidden), **bf)
     grouped_gemm_chunked(act_fp4, act_sf, w.down, (w.down[2] / dn_all).contiguous(), y_down, active_ids, hidden,
                          inter, meta, ws)
     y_acc = torch.empty((n, hidden), dtype=torch.float32, device=dev)
     _ffi.check("nv_kernels_moe_unpermute_scatter", s, y_down.data_ptr(), wts.data_ptr(), inv_perm.data_ptr(),
                y_acc.data_ptr(), n, k, hidden, hidden)
     return y_acc
+
+
+def _grouped_buffers(w: MoeGroupedWeights, m_total: int, n: int, dev) -> dict:
+    """The intermediates of a prefill-shaped step, kept on the weights object and grown on demand: a
+    step of a size seen before allocates only its result (moe_grouped.rs keeps them in its context for
+    the same reason)."""
+    cache = w.__dict__.setdefault("_grouped_bufs", {})
+    st = cache.get("b")
+    if st is None or st["rows"] < m_total or st["x_sorted"].device != torch.device(dev):
+        hidden, inter = w.hidden, w.inter
+        u8 = dict(dtype=torch.uint8, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        st = {"rows": m_total,
+              "x_sorted": torch.empty((m_total, hidden), **bf), "x_fp4": torch.empty((m_total, hidden // 2), **u8),
+              "x_sf": torch.zeros(L.swizzled_scale_bytes(m_total, hidden), **u8),
+              "y_gate": torch.empty((m_total, inter), **bf), "y_up": torch.empty((m_total, inter), **bf),
+              "act_fp4": torch.empty((m_total, inter // 2), **u8),
+              "act_sf": torch.zeros(L.swizzled_scale_bytes(m_total, inter), **u8),
+              "y_down": torch.empty((m_total, hidden), **bf),
+              "meta": torch.empty(256 * 1024, **u8), "ws": torch.empty(16 * 1024 * 1024, **u8)}
+        cache["b"] = st
+    # views of exactly this step's size (the scale buffers' size depends on the row count)
+    hidden, inter = w.hidden, w.inter
+    return {"x_sorted": st["x_sorted"][:m_total], "x_fp4": st["x_fp4"][:m_total],
+            "x_sf": st["x_sf"][:L.swizzled_scale_bytes(m_total, hidden)],
+            "y_gate": st["y_gate"][:m_total], "y_up": st["y_up"][:m_total], "act_fp4": st["act_fp4"][:m_total],
+            "act_sf": st["act_sf"][:L.swizzled_scale_bytes(m_total, inter)], "y_down": st["y_down"][:m_total],
+            "meta": st["meta"], "ws": st["ws"]}
 
 
 # ------------------------------------------------------------------------------------------------

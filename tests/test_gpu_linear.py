@@ -5,7 +5,7 @@ Tolerances (written here, as the contract asks):
     reference's own GEMV bound (rust/crates/nv-quant/tests/nvfp4_m1_gemv_ab.rs:103-118), i.e.
     fp32-accumulate noise plus bf16 output rounding; in practice the worst case is ~2^-9.
   * vs the reference's Cpu-backend linear (weights dequantized to bf16, f32 matmul, bf16 out):
-    max relative error < 1e-2 with the same floored denominator for K >= 1024 (every BASELINE
+    max relative error < 1e-2 with the same floored denominator for K >= 1024 (every benchmark
     shape).  That path rounds every weight to bf16 (2^-9 relative each) and both sides round the
     output to bf16, so for short rows the two roundings plus the weight noise can by themselves
     reach 1e-2; below K = 1024 the bound used is 1.5e-2 (the f64 bound above still applies).
@@ -75,7 +75,7 @@ def test_capability_is_sm100():
 
 
 def test_config0_single_linear_seed0():
-    """BASELINE configs[0]: x [1,4096] ~ N(0,1), W [4096,4096] ~ N(0,0.02), seed 0."""
+    """The single-linear case the reference's Cpu backend can run: x [1,4096] ~ N(0,1), W [4096,4096] ~ N(0,0.02), seed 0."""
     U.require_gpu()
     rng = np.random.default_rng(0)
     x = U.gauss_bf16(rng, (1, 4096))
@@ -425,7 +425,7 @@ def test_bf16_linear_odd_shapes_take_the_row_loop():
 @pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)])
 @pytest.mark.parametrize("m", [1, 4, 16, 64])
 def test_configs1_full_size_sweep(k, n, m):
-    """BASELINE configs[1] at full size: every (K, N) x M against the f64 oracle on a seeded subset of
+    """The decode GEMV shape sweep at full size: every (K, N) x M against the f64 oracle on a seeded subset of
     rows (all tokens; 512 output rows spread over the matrix, so every launch path is exercised while
     the CPU side stays at seconds), plus a size-independent property on the whole output: with the
     split of K pinned (it is otherwise chosen from the number of row tiles), rows computed as part of
