@@ -426,7 +426,7 @@ def _grouped_buffers(w: MoeGroupedWeights, m_total: int, n: int, dev) -> dict:
               "act_fp4": torch.empty((m_total, inter // 2), **u8),
               "act_sf": torch.zeros(L.swizzled_scale_bytes(m_total, inter), **u8),
               "y_down": torch.empty((m_total, hidden), **bf),
-              "meta": torch.empty(256 * 1024, **u8), "ws": torch.empty(16 * 1024 * 1024, **u8)}
+              "meta": torch.empty(512 * 1024, **u8), "ws": torch.empty(16 * 1024 * 1024, **u8)}
         cache["b"] = st
     # views of exactly this step's size (the scale buffers' size depends on the row count)
     hidden, inter = w.hidden, w.inter
