@@ -11,6 +11,8 @@ if str(ROOT) not in sys.path:
 def pytest_addoption(parser):
     parser.addoption("--emu", action="store_true", default=False,
                      help="run the tests marked gpu on the host emulation of the CUDA library (tests/emu)")
+    parser.addoption("--emu-big", action="store_true", default=False,
+                     help="with --emu: also run the full-size shapes (slow: minutes per case)")
 
 
 def pytest_configure(config):
@@ -34,5 +36,5 @@ def pytest_collection_modifyitems(config, items):
         for item in items:
             if "needs_cuda_runtime" in item.keywords:
                 item.add_marker(skip_rt)
-            elif "big" in item.keywords:
+            elif "big" in item.keywords and not config.getoption("--emu-big"):
                 item.add_marker(skip_big)

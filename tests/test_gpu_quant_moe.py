@@ -381,7 +381,11 @@ def test_grouped_w4a16_moe_decode_matches_the_per_pair_oracle(n_tok):
     xt = U.dev(x).view(torch.bfloat16)
     y = sp.forward_grouped_decode(w, ctx, xt, U.dev(logits))
     torch.cuda.synchronize()
+    ctx.check_status()   # no kernel met a routing table it had to refuse
     got = y.cpu().numpy()
+    # the fused router's list of active experts: ascending, exactly the experts that won a slot
+    n_act = int(ctx.n_active.cpu().numpy()[0])
+    assert np.array_equal(ctx.active.cpu().numpy()[:n_act], np.unique(ctx.topk_ids[:n_tok].cpu().numpy()))
     ids, wts = ref.moe_route_topk(logits, top_k)
     assert np.array_equal(ctx.topk_ids[:n_tok].cpu().numpy(), ids)
     want = np.zeros((n_tok, hidden), np.float64)
