@@ -252,12 +252,20 @@ __device__ __forceinline__ void place_slots_stable(const int32_t* ids, int32_t* 
 }
 
 // Exclusive scan of counts[0..E) by one CTA of 256 threads: offsets[0..E] and, in place, the cursors.
+// GLOBAL: `counts` is global memory that other threads of the CTA updated with atomics; those live in
+// L2, so the counts are read with L1 bypassed.
+template <bool GLOBAL>
+__device__ __forceinline__ int read_count(const int32_t* p) {
+    return GLOBAL ? __ldcg(p) : *p;
+}
+
+template <bool GLOBAL>
 __device__ __forceinline__ void scan_counts_cta(int32_t* counts, int32_t* offsets, int E, int32_t* s_part /*[257]*/) {
     const int tid = threadIdx.x;
     const int per = nvk::ceil_div(E, 256);
     const int e0 = min(E, tid * per), e1 = min(E, e0 + per);
     int sum = 0;
-    for (int e = e0; e < e1; ++e) sum += counts[e];
+    for (int e = e0; e < e1; ++e) sum += read_count<GLOBAL>(counts + e);
     s_part[tid + 1] = sum;
     if (tid == 0) s_part[0] = 0;
     __syncthreads();
@@ -284,7 +292,7 @@ __device__ __forceinline__ void scan_counts_cta(int32_t* counts, int32_t* offset
     __syncthreads();
     int acc = s_part[tid];
     for (int e = e0; e < e1; ++e) {
-        const int c = counts[e];
+        const int c = read_count<GLOBAL>(counts + e);
         offsets[e] = acc;
         counts[e] = acc;   // becomes the cursor
         acc += c;
@@ -309,7 +317,7 @@ __global__ void __launch_bounds__(256) slot_sort_kernel(const int32_t* __restric
         if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
     }
     __syncthreads();
-    scan_counts_cta(counts, offsets, E, s_part);
+    scan_counts_cta<true>(counts, offsets, E, s_part);
     if (tid < 32) place_slots_stable(topk_ids, counts, perm_token, inv_perm, total, k, E, tid);
 }
 
@@ -363,7 +371,7 @@ __global__ void __launch_bounds__(256) route_sort_kernel(const RouteSortArgs a) 
         if (lane == 0 && a.n_active != nullptr) *a.n_active = n_act;
     }
     __syncthreads();
-    scan_counts_cta(s_counts, s_offsets, E, s_part);
+    scan_counts_cta<false>(s_counts, s_offsets, E, s_part);
     for (int e = tid; e <= E; e += 256) a.offsets[e] = s_offsets[e];
     if (warp == 0) place_slots_stable(s_ids, s_counts, a.perm_token, a.inv_perm, total, K, E, lane);
 }

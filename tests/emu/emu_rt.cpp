@@ -14,6 +14,30 @@
 
 #include "cuda_emu.h"
 
+// Race checking (build_emu.py --tsan): the kernels are compiled with -fsanitize=thread and every
+// emulated CUDA thread is a ThreadSanitizer fiber.  Switching fibers establishes NO ordering; the only
+// happens-before edges are the ones CUDA gives -- block, warp and cluster barriers, launch boundaries --
+// so two threads of a block that touch the same shared or global bytes without a barrier between them
+// are reported, although the fibers here always run one after the other.  This file itself is compiled
+// without instrumentation: the emulation's own bookkeeping is not part of the check.
+#ifdef NVK_EMU_TSAN
+extern "C" {
+void* __tsan_get_current_fiber(void);
+void* __tsan_create_fiber(unsigned flags);
+void __tsan_destroy_fiber(void* fiber);
+void __tsan_switch_to_fiber(void* fiber, unsigned flags);
+void __tsan_acquire(void* addr);
+void __tsan_release(void* addr);
+}
+#define TSAN_ACQUIRE(p) __tsan_acquire((void*)(p))
+#define TSAN_RELEASE(p) __tsan_release((void*)(p))
+#define TSAN_SWITCH(f) __tsan_switch_to_fiber((f), 1u /* no synchronisation */)
+#else
+#define TSAN_ACQUIRE(p) ((void)0)
+#define TSAN_RELEASE(p) ((void)0)
+#define TSAN_SWITCH(f) ((void)0)
+#endif
+
 namespace emu {
 
 namespace {
@@ -33,6 +57,7 @@ struct Warp {
     uint32_t tab[2][32][8];
     int arrived = 0, alive = 0;
     unsigned gen = 0;
+    char sync_w[2] = {0, 0};   // race-checker edges of the warp barrier, by generation parity
 };
 }  // namespace
 
@@ -40,6 +65,7 @@ struct Cluster {
     unsigned size = 1;
     Block* blocks[16] = {};
     pthread_barrier_t bar;
+    char sync_all[2] = {0, 0};   // by barrier generation parity, like Block::sync_block
 };
 
 struct Copy {
@@ -55,6 +81,7 @@ struct Fiber {
     bool done = false;
     std::vector<Copy> pending;
     unsigned groups = 0;
+    void* tsan = nullptr;
 };
 
 struct Block {
@@ -71,6 +98,13 @@ struct Block {
     unsigned long progress = 0;
     bool external_wait = false;
     const std::function<void()>* body = nullptr;
+    void* tsan_sched = nullptr;
+    // Addresses that the race checker's happens-before edges hang on.  A barrier uses two, by the parity
+    // of its generation: a thread that has left barrier g and already arrived at barrier g + 1 must not
+    // pass what it wrote in between to a thread that has yet to leave g.
+    char sync_block[2] = {0, 0};
+    char sync_start = 0, sync_end = 0;   // scheduler -> threads at block start, threads -> scheduler at its end
+    char* sync_worker = nullptr;         // orders successive blocks on one arena (its shared memory, its stacks)
 };
 
 thread_local Block* g_block = nullptr;
@@ -91,12 +125,20 @@ namespace {
     _exit(97);
 }
 
-inline void yield() { swapcontext(&g_fiber->ctx, &g_block->sched); }
+// launch boundaries: what ran before a launch -> its threads (begin); its threads -> what comes next (end).
+// Two addresses, so that the blocks of ONE launch are not ordered with each other through them.
+char g_launch_begin = 0, g_launch_end = 0;
+
+inline void yield() {
+    TSAN_SWITCH(g_block->tsan_sched);
+    swapcontext(&g_fiber->ctx, &g_block->sched);
+}
 
 // ---- per-OS-thread resources: fiber stacks and the dynamic shared memory window ----------------
 struct Arena {
     uint8_t* stacks = nullptr;   // 1024 x (guard page + stack)
     uint8_t* smem = nullptr;     // guard | kSmemMax (+ slack) | guard
+    char sync = 0;               // orders the blocks that use this arena one after the other
     Arena() {
         const size_t per = kStackBytes + kPage;
         stacks = (uint8_t*)mmap(nullptr, 1024 * per, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE,
@@ -158,15 +200,24 @@ void fiber_exit_bookkeeping(Block* b, Fiber* f) {
 void trampoline(unsigned lo, unsigned hi) {
     Fiber* f = reinterpret_cast<Fiber*>(((uintptr_t)hi << 32) | (uintptr_t)lo);
     Block* b = g_block;
+    // a thread starts knowing what preceded the launch and the block's set-up, and nothing that another
+    // thread of the launch has done: threads only ever release to sync_end / g_launch_end
+    TSAN_ACQUIRE(&g_launch_begin);
+    TSAN_ACQUIRE(&b->sync_start);
     (*b->body)();
+    TSAN_RELEASE(&b->sync_end);
+    TSAN_RELEASE(&g_launch_end);
     f->done = true;
     fiber_exit_bookkeeping(b, f);
+    TSAN_SWITCH(b->tsan_sched);
     swapcontext(&f->ctx, &b->sched);
     die("a finished fiber was resumed");
 }
 
 void run_block(Block& b, Arena* arena) {
     g_block = &b;
+    b.sync_worker = &arena->sync;
+    TSAN_ACQUIRE(b.sync_worker);   // the block that used this arena's shared memory before us is over
     b.pub.dyn_smem = arena->smem_for(b.pub.dyn_bytes);
     const unsigned n = (unsigned)b.nthreads;
     b.fibers.clear();
@@ -182,6 +233,9 @@ void run_block(Block& b, Arena* arena) {
         f.pub.lane = (int)(t & 31);
         f.pub.warp = (int)(t >> 5);
         b.warps[t >> 5].alive++;
+#ifdef NVK_EMU_TSAN
+        f.tsan = __tsan_create_fiber(0);
+#endif
         getcontext(&f.ctx);
         f.ctx.uc_stack.ss_sp = arena->stack((int)t);
         f.ctx.uc_stack.ss_size = kStackBytes;
@@ -189,6 +243,10 @@ void run_block(Block& b, Arena* arena) {
         const uintptr_t p = reinterpret_cast<uintptr_t>(&f);
         makecontext(&f.ctx, (void (*)())trampoline, 2, (unsigned)(p & 0xFFFFFFFFu), (unsigned)(p >> 32));
     }
+#ifdef NVK_EMU_TSAN
+    b.tsan_sched = __tsan_get_current_fiber();
+#endif
+    TSAN_RELEASE(&b.sync_start);
     unsigned remaining = n;
     unsigned idle_passes = 0;
     while (remaining) {
@@ -198,6 +256,7 @@ void run_block(Block& b, Arena* arena) {
             Fiber& f = b.fibers[t];
             if (f.done) continue;
             g_fiber = &f;
+            TSAN_SWITCH(f.tsan);
             swapcontext(&b.sched, &f.ctx);
             if (f.done) --remaining;
         }
@@ -207,6 +266,11 @@ void run_block(Block& b, Arena* arena) {
             idle_passes = 0;
         }
     }
+    TSAN_ACQUIRE(&b.sync_end);     // the threads are done: the worker may reuse or free what they used
+    TSAN_RELEASE(b.sync_worker);
+#ifdef NVK_EMU_TSAN
+    for (unsigned t = 0; t < n; ++t) __tsan_destroy_fiber(b.fibers[t].tsan);
+#endif
     g_fiber = nullptr;
     g_block = nullptr;
 }
@@ -220,26 +284,34 @@ std::map<const void*, size_t> g_func_smem;
 void syncthreads() {
     Block* b = g_block;
     const unsigned gen = b->bar_gen;
+    char* const edge = &b->sync_block[gen & 1u];
+    TSAN_RELEASE(edge);
     if (++b->bar_arrived == b->alive) {
         b->bar_arrived = 0;
         b->bar_gen++;
         on_barrier_release(b);
+        TSAN_ACQUIRE(edge);
         return;
     }
     while (b->bar_gen == gen) yield();
+    TSAN_ACQUIRE(edge);
 }
 
 void syncwarp() {
     Block* b = g_block;
     Warp& w = b->warps[g_fiber->pub.warp];
     const unsigned gen = w.gen;
+    char* const edge = &w.sync_w[gen & 1u];
+    TSAN_RELEASE(edge);
     if (++w.arrived == w.alive) {
         w.arrived = 0;
         w.gen++;
         on_barrier_release(b);
+        TSAN_ACQUIRE(edge);
         return;
     }
     while (w.gen == gen) yield();
+    TSAN_ACQUIRE(edge);
 }
 
 const uint32_t (*warp_publish(const uint32_t* words, int n_words))[8] {
@@ -259,14 +331,18 @@ void cluster_sync() {
         return;
     }
     const unsigned gen = b->cbar_gen;
+    char* const edge = &b->cluster->sync_all[gen & 1u];
+    TSAN_RELEASE(edge);
     if (++b->cbar_arrived == b->alive) {
         pthread_barrier_wait(&b->cluster->bar);   // every fiber of this block is parked: block the OS thread
         b->cbar_arrived = 0;
         b->cbar_gen++;
         on_barrier_release(b);
+        TSAN_ACQUIRE(edge);
         return;
     }
     while (b->cbar_gen == gen) yield();
+    TSAN_ACQUIRE(edge);
 }
 
 void* cluster_map(void* p, unsigned rank) {
@@ -386,6 +462,12 @@ int run_grid(const LaunchCfg& c, const void* func, const std::function<void()>& 
     int hw = g_opt.threads.load();
     if (hw <= 0) hw = (int)std::thread::hardware_concurrency();
     if (hw <= 0) hw = 4;
+    TSAN_RELEASE(&g_launch_begin);   // stream order: what ran before this launch is visible to its threads
+    struct AfterLaunch {
+        ~AfterLaunch() {   // ... and what they did, to whatever comes next (the next launch included)
+            TSAN_ACQUIRE(&g_launch_end);
+        }
+    } after_launch;
 
     if (c.cooperative) {
         // every block resident at once, as a cooperative launch guarantees

@@ -44,3 +44,44 @@ def test_front_and_back_guarded_buffers_give_the_same_result():
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
     packed, lin = ref.quantize_rows_bf16(x, 2.0)
     assert np.array_equal(outs[0][0], packed) and np.array_equal(outs[0][1], ref.swizzle_scales(lin))
+
+
+_RACE = r"""
+import sys
+sys.path.insert(0, {root!r})
+import ctypes as C
+import numpy as np
+from tests.emu import harness as H
+L = H.lib()
+L.emu_selftest_rotate.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+a = H.Buf(np.arange(64, dtype=np.int32))
+o = H.Buf(np.zeros(64, np.int32))
+rc = L.emu_selftest_rotate(a.ptr, o.ptr, {synced})
+print("returned", rc, int(np.array_equal(o.read(), (np.arange(64) + 33) % 64)))
+"""
+
+
+def _run_under_race_checker(synced: int):
+    import os
+    import shutil
+    import pytest
+    tsan_rt = subprocess.run(["gcc", "-print-file-name=libtsan.so"], capture_output=True, text=True).stdout.strip()
+    if not shutil.which("gcc") or not os.path.isabs(tsan_rt):
+        pytest.skip("no ThreadSanitizer runtime on this machine")
+    from tests.emu import harness as H
+    lib = H._build_module().build(tsan=True)
+    env = dict(os.environ, LD_PRELOAD=tsan_rt, NVK_EMU_LIB=str(lib),
+               TSAN_OPTIONS="halt_on_error=1 exitcode=66 report_signal_unsafe=0")
+    return subprocess.run([sys.executable, "-c", _RACE.format(root=str(ROOT), synced=synced)], capture_output=True,
+                          text=True, timeout=600, env=env)
+
+
+def test_the_race_checker_passes_a_kernel_with_its_barrier():
+    r = _run_under_race_checker(1)
+    assert r.returncode == 0 and "returned 0 1" in r.stdout, (r.returncode, r.stdout, r.stderr[-2000:])
+
+
+def test_the_race_checker_reports_a_missing_barrier():
+    r = _run_under_race_checker(0)
+    assert r.returncode == 66, (r.returncode, r.stdout, r.stderr[-2000:])
+    assert "data race" in r.stderr and "rotate_kernel<false>" in r.stderr
