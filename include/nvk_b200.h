@@ -99,6 +99,20 @@ int nvk_b200_linear_nvfp4_w4a16_ws(void* stream, const uint8_t* wq_a, const uint
  * 64, 128} fixes the rows one CTA owns (M <= 16 only). */
 int nvk_b200_set_tuning(int force_ksplit, int force_rows_per_cta);
 
+/* No counterpart in the reference: tuning/test hook for the calling thread.  When the 128-row tiles of
+ * a W4A16 launch (M <= 64, no K split) fit the GPU at once but not evenly -- more CTAs than SMs, fewer
+ * than a whole number of CTAs per SM -- the launch instead starts the same number of CTAs on every SM
+ * and deals the 16-row units round-robin over all of them, so that no SM carries a whole CTA more than
+ * another.  A row's result does not depend on which warp computes it.  mode 0 = decide per launch
+ * (default), 1 = deal whenever the route allows it, 2 = never.  -2 for another value. */
+int nvk_b200_set_row_balance(int mode);
+
+/* The rule behind mode 0, as a host-only query (no GPU needed): for a launch of tile_ctas 128-row-tile
+ * CTAs that each need smem_bytes of shared memory and of which registers allow max_ctas_per_sm per SM,
+ * the number of CTAs the dealt launch starts instead (a multiple of 148), or 0 when the per-tile launch
+ * is kept: tile_ctas <= 148, more CTAs than are resident at once, or no SM would carry fewer warps. */
+int nvk_b200_row_balance_grid(int tile_ctas, size_t smem_bytes, int max_ctas_per_sm);
+
 /* No counterpart in the reference.  The W4A16 launches use programmatic dependent launch: a kernel
  * starts prefetching its weights while the previous kernel of the stream is still running and waits
  * for that kernel only before it reads activations or writes outputs.  enabled = 0 turns this off

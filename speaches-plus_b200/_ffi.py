@@ -29,6 +29,8 @@ SIGNATURES = {
     "nvk_b200_stack_build": [_vp, _i, _i, _vp, C.c_size_t, _vp],
     "nvk_b200_stack_run": [_vp, _vp, _i, _i, _i, _i, _vp],
     "nvk_b200_set_tuning": [_i, _i],
+    "nvk_b200_set_row_balance": [_i],
+    "nvk_b200_row_balance_grid": [_i, C.c_size_t, _i],
     "nvk_b200_set_pdl": [_i],
     "nvk_b200_set_wait_limit": [C.c_uint],
     "nv_kernels_gemv_bf16": [_vp, _vp, _vp, _vp, _i, _i],

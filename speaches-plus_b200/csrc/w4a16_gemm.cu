@@ -24,8 +24,20 @@ namespace {
 template <int NT, bool DUAL, int PRO, int UG, int KW>
 __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
     const int tile = blockIdx.y;
-    const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
+    int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
+    int unit_p1 = 0;
+    if (UG == 8 && KW == 1 && p.bal_ctas > 0) {
+        // Units dealt round-robin: warp w of CTA c takes unit w * bal_ctas + c of the launch (both arms
+        // counted through), so that the CTAs -- all resident at once -- carry equal numbers of busy warps.
+        // Units past the end name rows >= N and idle.
+        const int units_per_arm = p.tiles_per_arm * 8;
+        int gu = (int)(threadIdx.x >> 5) * p.bal_ctas + tile;
+        arm = DUAL && gu >= units_per_arm ? 1 : 0;
+        gu -= arm * units_per_arm;
+        unit_p1 = gu + 1;
+    }
     TileView t = {};
+    t.unit_p1 = unit_p1;
     t.wq = p.wq[arm];
     t.sc = p.sc[arm];
     t.x = p.x;
@@ -246,6 +258,28 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
 // must not change another thread's launches.
 thread_local int g_force_ksplit = 0, g_force_ug = 0;
 thread_local int g_pdl = 1;  // programmatic dependent launch on every tensor-core-route launch
+thread_local int g_balance = 0;  // unit dealing over a full-GPU grid: 0 = where it evens the SMs' load, 1 = wherever possible, 2 = never
+
+constexpr int kSmCount = 148;                 // B200
+constexpr size_t kSmemPerSm = 227 * 1024;     // usable by CTAs; each CTA also reserves 1 KiB
+
+// Grid size (CTAs) for dealing `units` 16-row units round-robin, or 0 to keep one 128-row tile per CTA.
+// `ctas` tile CTAs of `smem` bytes, at most `max_per_sm` of them resident per SM by registers.
+// Dealing pays when the tile CTAs fit the GPU at once but not evenly: some SMs would hold one CTA more
+// than others and the launch lasts as long as those.  With r CTAs on every SM and the units dealt over
+// all of them, an SM carries about units / 148 busy warps instead of 8 * ceil(ctas / 148).
+inline int balanced_grid(long ctas, size_t smem, int max_per_sm, int mode) {
+    if (mode == 2 || ctas <= 0) return 0;
+    const int r = (int)((ctas + kSmCount - 1) / kSmCount);
+    const long grid = (long)r * kSmCount;
+    if (grid > 65535) return 0;
+    if (mode == 1) return (int)grid;
+    const int per_sm = (int)std::min<size_t>((size_t)max_per_sm, kSmemPerSm / (smem + 1024));
+    if (ctas <= kSmCount || r > per_sm) return 0;   // fewer tiles than SMs, or more than one wave
+    const long units = ctas * 8;
+    const long dealt_max = (long)r * ((units + grid - 1) / grid);
+    return dealt_max < 8L * r ? (int)grid : 0;
+}
 
 template <int NT, bool DUAL, int PRO, int UG, int KW>
 int launch_mma(cudaStream_t stream, GemmParams& p) {
@@ -275,8 +309,13 @@ int launch_mma(cudaStream_t stream, GemmParams& p) {
     static nvk::SmemOptin optin;
     auto* kern = w4a16_mma_kernel<NT, DUAL, PRO, UG, KW>;
     if (int rc = optin.ensure((const void*)kern, smem)) return rc;
-    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
+    size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
     if (ctas > 65535) return NVK_ERR_GRID_AXIS;
+    p.bal_ctas = 0;
+    if (UG == 8 && KW == 1 && ksplit == 1) {
+        p.bal_ctas = balanced_grid((long)ctas, smem, NT >= 4 ? 2 : 3, g_balance);
+        if (p.bal_ctas > 0) ctas = (size_t)p.bal_ctas;
+    }
 
     nvk::Launch l;
     l.grid = dim3((unsigned)ksplit, (unsigned)ctas, 1);
@@ -562,6 +601,16 @@ extern "C" {
 int nvk_b200_set_pdl(int enabled) {
     g_pdl = enabled ? 1 : 0;
     return 0;
+}
+
+int nvk_b200_set_row_balance(int mode) {
+    if (mode < 0 || mode > 2) return NVK_ERR_ARG;
+    g_balance = mode;
+    return 0;
+}
+
+int nvk_b200_row_balance_grid(int tile_ctas, size_t smem_bytes, int max_ctas_per_sm) {
+    return balanced_grid((long)tile_ctas, smem_bytes, max_ctas_per_sm, 0);
 }
 
 int nvk_b200_set_tuning(int force_ksplit, int force_rows_per_cta) {

@@ -23,6 +23,7 @@ struct GemmParams {
     int tiles_per_arm;  // ceil(N / 128)
     int k_tiles;        // ceil(K / 64): scale tiles along K
     int nsc;            // ceil(K / 256)
+    int bal_ctas;       // > 0: 16-row units are dealt round-robin over this many CTAs (see TileView::unit_p1)
     int spc;            // super-chunks per CTA (the CTA's K slice)
     int ph;             // super-chunks staged per phase
     int x_stride;       // bytes between token rows of the staged activations
@@ -98,6 +99,8 @@ struct TileView {
     int xrow0;
     int M;                   // tokens (<= 8 * NT)
     int sub;                 // CTA index within the arm
+    int unit_p1;             // 0: this warp's 16-row unit follows from `sub`; else 1 + its unit index within the
+                             // arm, chosen by the caller (only where a warp sums all of K itself: KW == 1, no cluster)
     bool pdl;                // signal/await the neighbouring kernels of the stream here
     const uint8_t* ws;       // prepared activations (XWS only): 256-byte header of int pw[], then f16 stages
     // Used only by hooks that wait inside the kernel for an earlier operation of the same launch:
@@ -169,8 +172,9 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     const int ul = warp % UG, kw = warp / UG;  // local unit, K-warp
     const int gid = lane >> 2, tg = lane & 3;
     const int sub = t.sub;
-    const int mt = sub / SUB;               // 128-row scale tile
-    const int u = (sub % SUB) * UG + ul;    // unit inside it
+    const int gu = t.unit_p1 > 0 ? t.unit_p1 - 1 : sub * UG + ul;   // 16-row unit within the arm
+    const int mt = gu >> 3;                 // 128-row scale tile (== sub / SUB when derived from sub)
+    const int u = gu & 7;                   // unit inside it
     const int h = u >> 1, pair = u & 1;
     const int crank = HK::crank();
     const int nranks = HK::nranks();
@@ -181,6 +185,8 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     const int row0 = mt * kRowsPerCta + 64 * pair + 8 * h + gid;  // second row is 32 further
     const size_t half_k = (size_t)(K >> 1);
     const bool rv0 = row0 < N, rv1 = row0 + 32 < N;
+    // every row of the unit lies past N: the warp copies and multiplies nothing, it only keeps the barriers
+    const bool idle = mt * kRowsPerCta + 64 * pair + 8 * h >= N;
     const uint8_t* w_row0 = rv0 ? wq + (size_t)row0 * half_k + tg * 16 : wq;
     const uint8_t* w_row1 = rv1 ? wq + (size_t)(row0 + 32) * half_k + tg * 16 : wq;
     const uint8_t* sc_thread =
@@ -211,6 +217,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
                 for (int idx = threadIdx.x; idx < M * 32; idx += THREADS)
                     cp_async16(xdst + (idx >> 5) * 576 + (idx & 31) * 16, xsrc + (size_t)idx * 16, 16);
             }
+            if (!idle) {
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
                 const int kk = s * kSuper + 128 * pc + 32 * tg;   // first K value of this piece
@@ -220,6 +227,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
                 cp_async16(dst + (1 * 2 + pc) * 512, w_row1 + off, rv1 ? okk : 0);
                 cp_async8(dst - (uint32_t)lane * 8 + 2048 + pc * 256, sc_thread + (size_t)(4 * s + 2 * pc) * 512,
                           okk ? 8 : 0);
+            }
             }
         }
         cp_async_commit();
@@ -303,7 +311,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             issue(s_issue, n_issued % kDepth);  // refills the slot of step s - 1
             s_issue += KW;
             ++n_issued;
-            compute(n_done % kDepth, (n_done % kDepth) * M * 576);
+            if (!idle) compute(n_done % kDepth, (n_done % kDepth) * M * 576);
             ++n_done;
         }
         cp_async_wait<0>();
@@ -491,6 +499,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
         }
         __syncthreads();
         // ---- stream this phase's weights through the ring ----
+        if (!idle)
         for (int s = p0 + kw; s < pend; s += KW) {
             issue(s_issue, n_issued % kDepth);
             s_issue += KW;

@@ -48,6 +48,8 @@ def test_argument_refusals():
     assert f("nvk_b200_moe_route_permute", S, P, 0, P, P, P, P, P, None, None, 4, 8, 9, 0, 0.0, 1, 1.0) == -2
     assert f("nvk_b200_set_tuning", 3, 0) == -2 and f("nvk_b200_set_tuning", 0, 48) == -2
     assert f("nvk_b200_set_tuning", 0, 0) == 0
+    assert f("nvk_b200_set_row_balance", 3) == -2 and f("nvk_b200_set_row_balance", -1) == -2
+    assert f("nvk_b200_set_row_balance", 0) == 0
     assert f("nvk_b200_tp_allreduce_bf16", S, P, 2, 2, P, P, 8, 64, P, P) == -2               # rank outside the world
     assert f("nvk_b200_tp_allreduce_bf16", S, P, 0, 2, P, P, 12, 64, P, P) == -2              # n % 8
     assert f("nvk_b200_tp_allreduce_bf16", S, P, 0, 9, P, P, 8, 64, P, P) == -2               # more than 8 ranks
@@ -148,3 +150,17 @@ def test_rowgate_refusals():
 def test_rmsnorm_refusals():
     assert f("nv_kernels_rmsnorm_bf16", S, P, P, P, 0, 64, 1e-6) == 0
     assert f("nv_kernels_rmsnorm_bf16", S, P, 0, P, 2, 64, 1e-6) == -2
+
+
+def test_row_balance_rule():
+    """The dealt launch is chosen exactly when the 128-row tile CTAs fit the GPU at once but unevenly."""
+    g = lambda ctas, smem=90 * 1024, per_sm=3: f("nvk_b200_row_balance_grid", ctas, smem, per_sm)
+    assert g(224) == 296          # 224 tiles, two 90 KiB CTAs per SM: 76 SMs would hold two tiles, 72 one
+    assert g(150) == 296          # two SMs would do double work
+    assert g(148) == 0 and g(100) == 0 and g(0) == 0      # at most one tile per SM: nothing to even out
+    assert g(296) == 0            # two tiles on every SM already
+    assert g(290) == 0            # ceil(2320 / 296) = 8 units per CTA: dealing would not lower the maximum
+    assert g(297) == 0            # more than one wave at two CTAs per SM
+    assert g(300, 60 * 1024) == 444   # three 60 KiB CTAs per SM are resident: one wave again
+    assert g(224, 120 * 1024) == 0    # one 120 KiB CTA per SM: 224 tiles take two waves
+    assert g(224, 90 * 1024, 1) == 0  # registers allow one CTA per SM

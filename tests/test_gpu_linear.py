@@ -163,6 +163,52 @@ def test_rows_per_cta_variants_agree(rows, m):
     check_against_oracle(got, packed, sw, x, alpha, n, k)
 
 
+@pytest.mark.parametrize("m", [1, 5, 16])
+@pytest.mark.parametrize("dual", [False, True])
+def test_units_dealt_over_a_full_grid_give_the_same_bits(m, dual):
+    """The launch that deals 16-row units round-robin over 148 * r CTAs (forced here on a small matrix
+    whose last 128-row tile is ragged, so most warps idle) gives bit for bit what one CTA per 128-row
+    tile gives, for one and for two arms, and both give the oracle's answer."""
+    U.require_gpu()
+    rng = np.random.default_rng(90 + m)
+    n, k = 3 * 128 + 40, 768
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    packed_b, sw_b, alpha_b, _ = U.make_weight(rng, n, k) if dual else (None, None, 0.0, None)
+    x = U.gauss_bf16(rng, (m, k))
+    outs = []
+    for mode in (2, 1):
+        assert U.ffi.call("nvk_b200_set_row_balance", mode) == 0
+        try:
+            outs.append(run_linear(packed, sw, x, alpha, m, n, k, packed_b, sw_b, alpha_b))
+        finally:
+            U.ffi.call("nvk_b200_set_row_balance", 0)
+    if dual:
+        assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+        check_against_oracle(outs[1][0], packed, sw, x, alpha, n, k)
+        check_against_oracle(outs[1][1], packed_b, sw_b, x, alpha_b, n, k)
+    else:
+        assert np.array_equal(outs[0], outs[1])
+        check_against_oracle(outs[1], packed, sw, x, alpha, n, k)
+
+
+def test_row_balance_is_chosen_for_a_one_and_a_half_wave_launch():
+    """150 row tiles on 148 SMs: the automatic choice deals the 1200 units over 296 CTAs (five warps busy in
+    most of them); the result equals the per-tile launch bit for bit."""
+    U.require_gpu()
+    rng = np.random.default_rng(17)
+    n, k, m = 150 * 128, 256, 2
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    auto = run_linear(packed, sw, x, alpha, m, n, k)
+    assert U.ffi.call("nvk_b200_set_row_balance", 2) == 0
+    try:
+        per_tile = run_linear(packed, sw, x, alpha, m, n, k)
+    finally:
+        U.ffi.call("nvk_b200_set_row_balance", 0)
+    assert np.array_equal(auto, per_tile)
+    check_against_oracle(auto, packed, sw, x, alpha, n, k, cpu_backend=False)
+
+
 def test_multi_phase_activation_staging():
     """K large enough at M=64 that the activations are staged in several phases, with magnitudes
     that change by 2^40 along K so the per-phase power-of-two rescale is exercised."""
