@@ -371,8 +371,13 @@ int nv_kernels_moe_grouped_fp4_gemv_m1_bf16(void* stream, const uint8_t* a_packe
  * Runs tcgen05 kind::mxf4nvf4 block-scaled MMA on sm_100a.  Workspace protocol as in the reference:
  * *required_workspace is always written; all five data pointers NULL is a pure size query (returns 0,
  * launches nothing); a workspace that is too small returns -10.  k % 32 != 0 or n % 8 != 0 returns -1.
- * The `_streamk` / `_tiled` forms select among the reference's sm_120 tile configurations, which
- * have no counterpart here: all three symbols run the same kernel.
+ *   ..._bf16          data-parallel scheduler, the tile nvk_b200_set_prefill_config selected;
+ *   ..._bf16_streamk  the 1-SM tile under the stream-K scheduler (its own, larger workspace: query it
+ *                     through this symbol);
+ *   ..._bf16_tiled    `tile` 0..2 names one of the reference's sm_120 tile shapes -- all three map to the
+ *                     1-SM 128x128x256 tile here, any other value is -3 as in the reference -- and
+ *                     `stream_k` keeps its meaning: 0 data-parallel, 1 stream-K, >= 2 that many forced
+ *                     splits of every output tile along K.
  * replace rust/crates/nv-kernels/include/nv_kernels.h:1037-1049,1924-1955
  * (rust/crates/nv-kernels/cuda_sm120/cutlass_fp4_gemm.cu:14-221) */
 int nv_kernels_cutlass_fp4_gemm_sm120_bf16(void* stream, const void* a_fp4, const void* a_sf, const void* b_fp4,
@@ -411,9 +416,25 @@ int nv_kernels_cutlass_moe_grouped_fp4_gemm_sm120_bf16_decode(
     int64_t a_row_stride_elems, int64_t b_row_stride_elems, int64_t c_row_stride_elems, void* meta_scratch,
     size_t meta_scratch_bytes, void* gemm_workspace, size_t gemm_workspace_bytes, size_t* required_workspace);
 
-/* No counterpart in the reference: tuning hook for the prefill GEMM.  1 = 1-SM 128x128x256 tile,
- * 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster (default). */
+/* No counterpart in the reference: tuning hook for the prefill GEMM, per calling thread.  1 = 1-SM
+ * 128x128x256 tile (default), 2 = 2-SM (cta_group::2) 256x128x256 tile with a 2x1x1 cluster, whose
+ * operand loads use cluster multicast: single-GPU processes and this GPU's own memory only. */
 int nvk_b200_set_prefill_config(int cfg);
+
+/* The library route of the same contraction: d [m, n] = bf16(alpha * a [m, k] * b [n, k]^T) through
+ * cuBLASLt (CUDA_R_4F_E2M1 operands, VEC16_UE4M3 block scaling, TN, weights as the library's A), what
+ * the reference's runner does with SPEACHES_NVFP4_BACKEND=cublaslt
+ * (rust/crates/nv-quant/src/nvfp4.rs:866-1067; the reference binds cuBLASLt from Rust, so there is no
+ * nv_kernels symbol to keep).  alpha is a host value.  cuBLASLt is opened at run time.  0 for an empty
+ * problem; -1 unless k % 16 == 0 and m, n, k >= 128 (the reference's rule for this route,
+ * nvfp4.rs:564-590); -2 null or not 16-byte aligned operands; -3 cuBLASLt cannot be opened or gives no
+ * handle; -100 - s for a cuBLASLt status s (-115: no algorithm for the shape).  The first call for a
+ * shape makes its plan and must not be inside a graph capture; later calls are capturable.
+ * nvk_b200_cublaslt_fp4_workspace_bytes() = the 64 MiB the reference gives this route per stream. */
+int nvk_b200_cublaslt_fp4_gemm_bf16(void* stream, const uint8_t* a_packed, const uint8_t* a_scales,
+                                    const uint8_t* b_packed, const uint8_t* b_scales, uint16_t* d, int m, int n,
+                                    int k, float alpha, void* workspace, size_t workspace_bytes);
+size_t nvk_b200_cublaslt_fp4_workspace_bytes(void);
 
 /* RMSNorm over bf16 rows, y = bf16(x * rsqrt(mean(x^2) + eps) * weight): the launch the reference's
  * M = 1 GEMV route puts in front of nv_kernels_nvfp4_gemv_bf16act when a norm precedes the linear

@@ -84,6 +84,8 @@ SIGNATURES = {
 # symbols exported by the prefill library
 PREFILL_SIGNATURES = {
     "nvk_b200_set_prefill_config": [_i],
+    "nvk_b200_cublaslt_fp4_gemm_bf16": [_vp] * 6 + [_i, _i, _i, _f, _vp, C.c_size_t],
+    "nvk_b200_cublaslt_fp4_workspace_bytes": [],
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16_streamk": [_vp] * 7 + [_i, _i, _i, _vp, C.c_size_t, _vp],
     "nv_kernels_cutlass_fp4_gemm_sm120_bf16_tiled": [_vp] * 7 + [_i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
@@ -181,7 +183,7 @@ def prefill_lib() -> C.CDLL:
         for name, args in PREFILL_SIGNATURES.items():
             fn = getattr(L, name)
             fn.argtypes = args
-            fn.restype = C.c_int
+            fn.restype = C.c_size_t if name.endswith("_bytes") else C.c_int
         _prefill_lib = L
     return _prefill_lib
 

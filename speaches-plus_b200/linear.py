@@ -325,6 +325,17 @@ class Nvfp4Linear:
         runner = getattr(self, "runner", None)
         if runner is not None:
             # an Nvfp4GemmRunner (runner.py) picks the scheduler for the shape and owns the workspace
+            if runner.backend.value == "cublaslt":
+                # the library route computes every padded row: into a padded buffer, then trimmed
+                # (pad -> quantize -> GEMM -> trim, rust/crates/nv-layers/src/linear.rs:1590-1795)
+                m_pad = a_packed.shape[0]
+                yp = st.get("y_pad")
+                if yp is None or yp.shape[0] < m_pad:
+                    yp = st["y_pad"] = torch.empty((st["m_pad"], n), dtype=torch.bfloat16, device=a_packed.device)
+                runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, st["alpha"], yp[:m_pad], m_pad,
+                              n, k, alpha_host=self.weight_alpha)
+                y.copy_(yp[:m])
+                return
             runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, st["alpha"], y, m, n, k)
             return
         need = C.c_size_t(0)

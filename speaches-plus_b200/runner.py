@@ -2,9 +2,10 @@
 the prefill-sized FP4 x FP4 GEMM: which scheduler a shape gets, the per-stream workspace created ahead of
 graph capture, and the environment knobs, over this library's three GEMM entry points.
 
-One backend exists here (the block-scaled tensor-core GEMM of libnvk_b200_prefill.so); asking for the
-reference's cuBLASLt backend is an error, not a silent switch.  Single-GPU processes only (the prefill
-library refuses to load in a rank of several).
+Two backends, as in the reference: this library's block-scaled tensor-core GEMM (`cutlass`, and what
+`auto` picks for every shape) and cuBLASLt's FP4 matmul (`cublaslt`, only when asked for: the reference's
+automatic reroute of skinny shapes to it is answered by the stream-K scheduler here).  Single-GPU
+processes only (the prefill library refuses to load in a rank of several).
 """
 from __future__ import annotations
 
@@ -18,6 +19,7 @@ from . import _ffi
 
 WORKSPACE_BYTES = 64 * 1024 * 1024      # per stream (nvfp4.rs:377)
 TILE_M = TILE_N = 128                   # the tile the scheduler rule counts in (nvfp4.rs:365-367)
+MIN_TILE = 128                          # smallest n, k of any route and smallest m of the library route
 SM_COUNT = 148                          # B200
 
 
@@ -116,9 +118,6 @@ class Nvfp4GemmRunner:
     def __init__(self, backend: Nvfp4Backend | None = None, env=None):
         env = os.environ if env is None else env
         self.backend = Nvfp4Backend.from_env(env.get("SPEACHES_NVFP4_BACKEND")) if backend is None else backend
-        if self.backend is Nvfp4Backend.CUBLASLT:
-            raise NotImplementedError("the cuBLASLt NVFP4 backend of the reference is not part of this library; "
-                                      "unset SPEACHES_NVFP4_BACKEND or set it to cutlass/auto")
         self.streamk_mode = streamk_mode_from(env.get("NV_NVFP4_STREAMK"))
         self.k256 = k256_from(env.get("NV_NVFP4_K256"))
         self.streamk_k256 = streamk_k256_from(env.get("NV_NVFP4_STREAMK_K256"))
@@ -152,8 +151,31 @@ class Nvfp4GemmRunner:
                          b_packed.data_ptr(), b_scales.data_ptr(), alpha_dev.data_ptr(), d.data_ptr(), m, n, k, *extra,
                          ws.data_ptr(), ws.numel(), C.addressof(need))
 
-    def matmul(self, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m: int, n: int, k: int) -> None:
+    def matmul_cublaslt(self, a_packed, a_scales, b_packed, b_scales, alpha_host: float, d, m, n, k, ws) -> None:
+        """The library route (nvfp4.rs:866-1067): needs m >= 128 -- pad the activation -- and a host alpha."""
+        if m < MIN_TILE:
+            raise ValueError(f"NVFP4 cuBLASLt path requires m >= {MIN_TILE} (got m={m}); pad the activation "
+                             "or use the cutlass backend")
+        entry = "nvk_b200_cublaslt_fp4_gemm_bf16"
+        rc = _ffi.call(entry, torch.cuda.current_stream().cuda_stream, a_packed.data_ptr(), a_scales.data_ptr(),
+                       b_packed.data_ptr(), b_scales.data_ptr(), d.data_ptr(), m, n, k, float(alpha_host),
+                       ws.data_ptr(), ws.numel())
+        if rc != 0:
+            raise _ffi.NvkError(entry, rc)
+
+    def matmul(self, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m: int, n: int, k: int,
+               alpha_host: float | None = None) -> None:
+        """`alpha_host` is the host copy of `alpha_dev` the reference's callers keep beside it
+        (nvfp4.rs:556-563); only the cuBLASLt backend reads it, and reads nothing else."""
+        if k % 16 != 0:
+            raise ValueError(f"k={k} must be a multiple of 16")
+        if m == 0 or n < MIN_TILE or k < MIN_TILE:
+            raise ValueError(f"NVFP4 GEMM requires m >= 1 and n,k >= {MIN_TILE}; got m={m} n={n} k={k}")
         ws = ensure_workspace_for_stream()
+        if self.backend is Nvfp4Backend.CUBLASLT:
+            if alpha_host is None:
+                raise ValueError("the cublaslt backend takes alpha from the host: pass alpha_host")
+            return self.matmul_cublaslt(a_packed, a_scales, b_packed, b_scales, alpha_host, d, m, n, k, ws)
         if self.streamk_wanted(m, n):
             entry, extra = self.plan(m, n, k, True)
             rc = self._launch(entry, extra, a_packed, a_scales, b_packed, b_scales, alpha_dev, d, m, n, k, ws)

@@ -164,3 +164,18 @@ def test_row_balance_rule():
     assert g(300, 60 * 1024) == 444   # three 60 KiB CTAs per SM are resident: one wave again
     assert g(224, 120 * 1024) == 0    # one 120 KiB CTA per SM: 224 tiles take two waves
     assert g(224, 90 * 1024, 1) == 0  # registers allow one CTA per SM
+
+
+def test_library_route_refusals():
+    """The cuBLASLt route refuses before it opens the library: empty problems are no-ops, the reference's
+    shape rule for this route (k % 16, every dimension at least 128), null and misaligned operands."""
+    g = lambda *a: f("nvk_b200_cublaslt_fp4_gemm_bf16", S, *a)
+    assert g(0, 0, 0, 0, 0, 0, 128, 128, 1.0, 0, 0) == 0
+    assert g(P, P, P, P, P, 128, 128, 136, 1.0, P, 1024) == -1      # k % 16
+    assert g(P, P, P, P, P, 64, 128, 128, 1.0, P, 1024) == -1       # m < 128: pad the activation
+    assert g(P, P, P, P, P, 128, 96, 128, 1.0, P, 1024) == -1
+    assert g(P, P, P, P, P, 128, 128, 64, 1.0, P, 1024) == -1
+    assert g(P, P, 0, P, P, 128, 128, 128, 1.0, P, 1024) == -2      # null weights
+    assert g(P + 8, P, P, P, P, 128, 128, 128, 1.0, P, 1024) == -2  # misaligned activations
+    assert g(P, P, P, P, P, 128, 128, 128, 1.0, 0, 1024) == -2      # workspace size without a workspace
+    assert sp.ffi.prefill_lib().nvk_b200_cublaslt_fp4_workspace_bytes() == 64 << 20

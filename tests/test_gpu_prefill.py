@@ -96,6 +96,58 @@ def test_stream_k_forms_match_the_oracle(m, n, k, stream_k):
                       3, 0, None, 0, ctypes.addressof(need)) == -3     # no such tile
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (384, 640, 1056)])
+def test_library_route_matches_the_oracle_and_the_tensor_core_route(m, n, k):
+    """The cuBLASLt route (the reference's `cublaslt` backend, nvfp4.rs:866-1067) against the W4A4 oracle
+    with the bound of the other routes, and against this library's own GEMM within the 4 bf16 ulp the
+    reference allows between its two backends (nv-quant/tests/nvfp4_default_routing_split.rs)."""
+    U.require_gpu()
+    rng = np.random.default_rng(3 * m + n + k)
+    ap, alin, asw, _ = quantized_operand(rng, m, k, 1.0, 1.0)
+    bp, blin, bsw, gb = quantized_operand(rng, n, k, 0.02)
+    alpha = float(np.float32(1.0) / np.float32(gb))
+    d = [U.dev(a) for a in (ap, asw, bp, bsw)]
+    out = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    ws = torch.zeros(U.ffi.prefill_lib().nvk_b200_cublaslt_fp4_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    for _ in range(2):   # the second call reuses the shape's plan
+        rc = U.ffi.call("nvk_b200_cublaslt_fp4_gemm_bf16", U.stream(), d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(),
+                        d[3].data_ptr(), out.data_ptr(), m, n, k, alpha, ws.data_ptr(), ws.numel())
+        assert rc == 0, rc
+    torch.cuda.synchronize()
+    o = U.host_u16(out)
+    assert np.all(o[m * n:] == 0x7FC0)
+    got = o[:m * n].reshape(m, n)
+    want = ref.matmul_w4a4(ap, alin, bp, blin, m, n, k, alpha)
+    ulp = U.bf16_ulp_diff(got, want)
+    absd = np.abs(ref.bf16_to_f32(got) - ref.bf16_to_f32(want))
+    assert np.all((ulp <= 2) | (absd <= 1e-3)), f"max ulp {ulp.max()}"
+    ours = run_gemm(ap, asw, bp, bsw, alpha, m, n, k)
+    ulp2 = U.bf16_ulp_diff(got, ours)
+    absd2 = np.abs(ref.bf16_to_f32(got) - ref.bf16_to_f32(ours))
+    assert np.all((ulp2 <= 4) | (absd2 <= 1e-3)), f"max ulp between the routes {ulp2.max()}"
+
+
+def test_runner_with_the_library_backend_pads_and_trims():
+    """Nvfp4Linear with an Nvfp4GemmRunner whose backend is cublaslt: 200 rows are padded to 256, computed by
+    the library route and trimmed; same bound against the linear's oracle as the default route."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    from speaches_plus_b200 import runner as R
+    rng = np.random.default_rng(77)
+    n, k, m = 256, 512, 200
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    lin = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+    xt = U.dev(x).view(torch.bfloat16)
+    base = lin(xt)
+    lin.runner = R.Nvfp4GemmRunner(env={"SPEACHES_NVFP4_BACKEND": "cublaslt"})
+    got = lin(xt)
+    torch.cuda.synchronize()
+    a = ref.bf16_to_f32(U.host_u16(got).reshape(m, n))
+    b = ref.bf16_to_f32(U.host_u16(base).reshape(m, n))
+    assert U.rel_err_floor(a, b.astype(np.float64)) < 1e-2
+
+
 def test_true_m_equals_padded_m_bitwise():
     """rust/crates/nv-quant/tests/nvfp4_true_m.rs: a GEMM told the true row count gives the same bits
     for those rows as one told the 128-padded count (pad rows are zeros and are not part of the result)."""

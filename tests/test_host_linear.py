@@ -164,8 +164,28 @@ def test_runner_scheduler_rule():
     assert r.streamk_wanted(2048, 5120) and not r.streamk_wanted(2048, 25600)
     assert not R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK": "0"}).streamk_wanted(128, 128)
     assert R.Nvfp4GemmRunner(env={"NV_NVFP4_STREAMK": "1"}).streamk_wanted(8192, 8192)
-    with __import__("pytest").raises(NotImplementedError):
-        R.Nvfp4GemmRunner(env={"SPEACHES_NVFP4_BACKEND": "cublaslt"})
+    assert R.Nvfp4GemmRunner(env={"SPEACHES_NVFP4_BACKEND": "cublaslt"}).backend is R.Nvfp4Backend.CUBLASLT
+    assert R.Nvfp4GemmRunner(env={"SPEACHES_NVFP4_BACKEND": "nonsense"}).backend is R.Nvfp4Backend.AUTO
+
+
+def test_runner_library_backend_and_shape_refusals(monkeypatch):
+    """nvfp4.rs:564-590: k % 16, n and k at least 128 for every backend, m at least 128 for the library
+    route, which is given the host copy of alpha and the stream's workspace."""
+    import pytest
+    from speaches_plus_b200 import runner as R
+    monkeypatch.setattr(R, "ensure_workspace_for_stream", lambda: None)
+    r = R.Nvfp4GemmRunner(env={})
+    with pytest.raises(ValueError, match="multiple of 16"):
+        r.matmul(None, None, None, None, None, None, 128, 128, 136)
+    with pytest.raises(ValueError, match="n,k >= 128"):
+        r.matmul(None, None, None, None, None, None, 128, 64, 128)
+    with pytest.raises(ValueError, match="m >= 1"):
+        r.matmul(None, None, None, None, None, None, 0, 128, 128)
+    lt = R.Nvfp4GemmRunner(env={"SPEACHES_NVFP4_BACKEND": "cublaslt"})
+    with pytest.raises(ValueError, match="alpha_host"):
+        lt.matmul(None, None, None, None, None, None, 128, 128, 128)
+    with pytest.raises(ValueError, match="requires m >= 128"):
+        lt.matmul(None, None, None, None, None, None, 64, 128, 128, alpha_host=1.0)
 
 
 def test_runner_choice_tree_and_permanent_fallback(monkeypatch):
