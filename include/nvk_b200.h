@@ -113,10 +113,11 @@ int nvk_b200_set_row_balance(int mode);
  * is kept: tile_ctas <= 148, more CTAs than are resident at once, or no SM would carry fewer warps. */
 int nvk_b200_row_balance_grid(int tile_ctas, size_t smem_bytes, int max_ctas_per_sm);
 
-/* No counterpart in the reference.  The W4A16 launches use programmatic dependent launch: a kernel
- * starts prefetching its weights while the previous kernel of the stream is still running and waits
- * for that kernel only before it reads activations or writes outputs.  enabled = 0 turns this off
- * (plain stream order); the default is on. */
+/* No counterpart in the reference.  The decode-path launches use programmatic dependent launch: a
+ * kernel may be scheduled while the previous kernel of the stream is still running and waits for that
+ * kernel (griddepcontrol.wait) before it reads anything that kernel may have written or writes
+ * anything -- the W4A16 kernels fill their weight ring first, every other kernel waits first of all.
+ * enabled = 0 turns this off for the calling thread's launches (plain stream order); default on. */
 int nvk_b200_set_pdl(int enabled);
 /* Polls a kernel of this library spends in ONE wait on another CTA or another GPU (the peer
  * all-reduce's flags, a persistent step's dependency counters) before it gives up, sets its error

@@ -20,6 +20,9 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc)
 template <bool VEC>
 __global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ x,
                                                         uint16_t* __restrict__ y, int N, int K) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (n >= N) return;
@@ -54,7 +57,7 @@ extern "C" int nv_kernels_gemv_bf16(void* stream, const uint16_t* W, const uint1
     if (nvk::any_null(W, x, y)) return NVK_ERR_ARG;
     const unsigned grid = (unsigned)((N + 7) / 8);
     const bool vec = (K & 7) == 0 && ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15u) == 0;
-    const nvk::Launch l = nvk::launch_1d((cudaStream_t)stream, grid, 256);
+    const nvk::Launch l = nvk::launch_1d((cudaStream_t)stream, grid, 256, 0, true);
     return vec ? nvk::launch(l, gemv_bf16_kernel<true>, W, x, y, N, K) : nvk::launch(l, gemv_bf16_kernel<false>, W, x, y, N, K);
 }
 

@@ -28,6 +28,9 @@ __device__ __forceinline__ uint4 zero4() { return make_uint4(0u, 0u, 0u, 0u); }
 // NT: 8-token column tiles.  KW: warps of the CTA along K (1: a warp sums all of K for its 16 rows).
 template <int NT, int KW>
 __global__ void __launch_bounds__(256) linear_bf16_kernel(const Bf16LinearArgs a) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     constexpr int UNITS = 8 / KW;   // 16-row units per CTA
     __shared__ float s_red[KW > 1 ? KW * UNITS * 16 * 8 * NT : 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -109,7 +112,7 @@ int launch_nt(cudaStream_t stream, const Bf16LinearArgs& a) {
     // a warp per 16 rows when that alone fills the GPU, else the eight warps of a CTA share 16 rows
     const bool split = nvk::ceil_div(a.N, 128) < 148;
     const unsigned grid = (unsigned)nvk::ceil_div(a.N, split ? 16 : 128);
-    const nvk::Launch l = nvk::launch_1d(stream, grid, 256);
+    const nvk::Launch l = nvk::launch_1d(stream, grid, 256, 0, true);
     return split ? nvk::launch(l, linear_bf16_kernel<NT, 8>, a) : nvk::launch(l, linear_bf16_kernel<NT, 1>, a);
 }
 

@@ -135,6 +135,9 @@ __device__ __forceinline__ void store_winner(const RouteArgs& a, int n, int lane
 // Router for E <= 256: eight tokens per CTA, one per warp, no shared memory, no barrier.
 template <int R>
 __global__ void __launch_bounds__(256) route_warp_kernel(const RouteArgs a) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (n >= a.n_tokens) return;   // whole warps leave together
@@ -150,6 +153,9 @@ __global__ void __launch_bounds__(256) route_warp_kernel(const RouteArgs a) {
 // warps' candidates, done redundantly by every warp from shared memory.
 template <int R>
 __global__ void __launch_bounds__(256) route_cta_kernel(const RouteArgs a) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     __shared__ uint32_t s_top[8], s_win[8];
     __shared__ float s_raw[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -212,13 +218,13 @@ __global__ void __launch_bounds__(256) route_cta_kernel(const RouteArgs a) {
 
 int launch_router(cudaStream_t stream, const RouteArgs& a) {
     if (a.E <= 256) {
-        const nvk::Launch l = nvk::launch_1d(stream, (unsigned)nvk::ceil_div(a.n_tokens, 8), 256);
+        const nvk::Launch l = nvk::launch_1d(stream, (unsigned)nvk::ceil_div(a.n_tokens, 8), 256, 0, true);
         if (a.E <= 32) return nvk::launch(l, route_warp_kernel<1>, a);
         if (a.E <= 64) return nvk::launch(l, route_warp_kernel<2>, a);
         if (a.E <= 128) return nvk::launch(l, route_warp_kernel<4>, a);
         return nvk::launch(l, route_warp_kernel<8>, a);
     }
-    const nvk::Launch l = nvk::launch_1d(stream, (unsigned)a.n_tokens, 256);
+    const nvk::Launch l = nvk::launch_1d(stream, (unsigned)a.n_tokens, 256, 0, true);
     if (a.E <= 512) return nvk::launch(l, route_cta_kernel<2>, a);
     if (a.E <= 1024) return nvk::launch(l, route_cta_kernel<4>, a);
     if (a.E <= 2048) return nvk::launch(l, route_cta_kernel<8>, a);
@@ -382,6 +388,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __rest
                                                           const int32_t* __restrict__ src_idx,
                                                           uint16_t* __restrict__ out, int rows, int hidden,
                                                           int n_tokens, int row_step) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int r = blockIdx.x * row_step;
     if (r >= rows) return;
     const int s = src_idx[r];
@@ -398,6 +407,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __rest
 
 __global__ void __launch_bounds__(128) gather_f32_kernel(const float* __restrict__ src, const int32_t* __restrict__ ids,
                                                          float* __restrict__ dst, int n) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int e = ids[i];
@@ -425,6 +437,9 @@ struct CombineArgs {
 
 template <bool TAIL, bool VEC>
 __global__ void __launch_bounds__(128) combine_kernel(const CombineArgs a) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     constexpr int W = VEC ? 8 : 1;
     const int n = blockIdx.y;
     const int h0 = (blockIdx.x * 128 + threadIdx.x) * W;
@@ -473,6 +488,7 @@ int launch_combine(cudaStream_t stream, const CombineArgs& a) {
     l.grid = dim3((unsigned)nvk::ceil_div(a.hidden, 128 * (vec ? 8 : 1)), (unsigned)a.n_tokens, 1);
     l.block = dim3(128, 1, 1);
     l.stream = stream;
+    l.pdl = true;
     if (a.n_tokens > 65535) return NVK_ERR_GRID_AXIS;
     return vec ? nvk::launch(l, combine_kernel<TAIL, true>, a) : nvk::launch(l, combine_kernel<TAIL, false>, a);
 }
@@ -480,6 +496,9 @@ int launch_combine(cudaStream_t stream, const CombineArgs& a) {
 // y[r, h] = x[r, h] * sigmoid(gate_logits[r]): the shared expert's gate (one logit per token).
 __global__ void __launch_bounds__(256) rowgate_kernel(const float* __restrict__ x, const float* __restrict__ gate_logits,
                                                       float* __restrict__ y, int rows, int hidden) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * hidden) return;
     const float g = 1.f / (1.f + expf(-gate_logits[(int)(i / hidden)]));
@@ -572,7 +591,7 @@ int gather_rows(void* stream, const uint16_t* x, const int32_t* src_idx, uint16_
                 int n_tokens, int row_step) {
     const int block = hidden >= 2048 ? 256 : (hidden >= 512 ? 64 : 32);
     const unsigned grid = (unsigned)(rows / row_step);
-    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, grid, (unsigned)block), gather_rows_kernel, x, src_idx, out,
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, grid, (unsigned)block, 0, true), gather_rows_kernel, x, src_idx, out,
                        rows, hidden, n_tokens, row_step);
 }
 
@@ -594,7 +613,7 @@ int nv_kernels_mul_sigmoid_rowgate_f32(void* stream, const float* x, const float
     if (nvk::any_null(x, gate_logits, y)) return NVK_ERR_ARG;
     const long long grid = ((long long)rows * hidden + 255) / 256;
     if (grid > 0x7FFFFFFFLL) return NVK_ERR_GRID_AXIS;
-    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)grid, 256), rowgate_kernel, x, gate_logits, y, rows,
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)grid, 256, 0, true), rowgate_kernel, x, gate_logits, y, rows,
                        hidden);
 }
 
@@ -662,7 +681,7 @@ int nv_kernels_gather_rows_bf16_strided(void* stream, const uint16_t* x_bf16, co
 int nv_kernels_gather_f32_by_ids(void* stream, const float* src, const int32_t* ids, float* dst, int n) {
     if (n <= 0) return 0;
     if (nvk::any_null(src, ids, dst)) return NVK_ERR_ARG;
-    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)((n + 127) / 128), 128), gather_f32_kernel, src, ids,
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)((n + 127) / 128), 128, 0, true), gather_f32_kernel, src, ids,
                        dst, n);
 }
 

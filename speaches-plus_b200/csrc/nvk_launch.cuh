@@ -15,6 +15,10 @@ struct Launch {
     bool cooperative = false;  // all CTAs resident together
 };
 
+// Programmatic dependent launch for the calling thread's launches (nvk_b200_set_pdl): when 0, a launch
+// that asks for it is an ordinary stream-ordered launch (the kernels' waits are then no-ops).
+inline thread_local int g_pdl_enabled = 1;
+
 inline Launch launch_1d(cudaStream_t stream, unsigned grid, unsigned block, size_t smem = 0, bool pdl = false) {
     Launch l;
     l.grid = dim3(grid, 1, 1);
@@ -50,7 +54,7 @@ inline int launch(const Launch& l, void (*kernel)(P...), A&&... args) {
         attr[na].val.clusterDim.z = 1;
         ++na;
     }
-    if (l.pdl) {
+    if (l.pdl && g_pdl_enabled != 0) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;

@@ -46,6 +46,9 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], float store
 // SRC 0: plain bf16; SRC 1: SiLU(gate)*up evaluated in f32 (not rounded to bf16 first).
 template <int SRC>
 __global__ void __launch_bounds__(256) quantize_blocks_kernel(const QuantParams p) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     const int bpr = p.K >> 4;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)p.rows * bpr;
@@ -94,6 +97,9 @@ __global__ void __launch_bounds__(256) quantize_blocks_kernel(const QuantParams 
 // The quantized value is bf16(x * rsqrt(mean(x^2) + eps) * w): one rounding to bf16, then the
 // plain block quantizer.
 __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const QuantParams p) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     NVK_DYN_SMEM_AS(uint16_t, row_s);
     __shared__ float red[8];
     const int row = blockIdx.x;
@@ -141,6 +147,9 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const QuantParams
 __global__ void __launch_bounds__(256) rmsnorm_bf16_kernel(const uint16_t* __restrict__ x,
                                                            const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
                                                            size_t hidden, float eps) {
+    // stream order through programmatic dependent launch: nothing of the predecessor's is read before this
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
     __shared__ float red[8];
     const uint16_t* xr = x + (size_t)blockIdx.x * hidden;
     uint16_t* yr = y + (size_t)blockIdx.x * hidden;
@@ -165,7 +174,7 @@ int launch_blocks(cudaStream_t s, const QuantParams& p) {
     const long long total = (long long)p.rows * (p.K >> 4);
     const long long grid = (total + 255) / 256;
     if (grid > 0x7FFFFFFFLL) return NVK_ERR_GRID_AXIS;
-    return nvk::launch(nvk::launch_1d(s, (unsigned)grid, 256), quantize_blocks_kernel<SRC>, p);
+    return nvk::launch(nvk::launch_1d(s, (unsigned)grid, 256, 0, true), quantize_blocks_kernel<SRC>, p);
 }
 
 bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
@@ -263,7 +272,7 @@ int nv_kernels_rmsnorm_bf16(void* stream, const uint16_t* x, const uint16_t* wei
     if (batch == 0 || hidden == 0) return 0;
     if (nvk::any_null(x, weight, y)) return NVK_ERR_ARG;
     if (batch > 0x7FFFFFFFull) return NVK_ERR_GRID_AXIS;
-    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)batch, 256), rmsnorm_bf16_kernel, x, weight, y,
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)batch, 256, 0, true), rmsnorm_bf16_kernel, x, weight, y,
                        hidden, eps);
 }
 
@@ -282,7 +291,7 @@ int nv_kernels_rmsnorm_quantize_nvfp4_bf16(void* stream, const uint16_t* x_bf16,
     p.x = x_bf16; p.norm_w = weight_bf16; p.packed = packed_out; p.scales = scales_out_swizzled;
     p.global = stored_global; p.eps = eps; p.rows = m_padded; p.rows_logical = m_logical; p.K = K;
     p.row_mul = 1; p.m_per_expert = 1;
-    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)m_padded, 256, smem), rmsnorm_quantize_kernel, p);
+    return nvk::launch(nvk::launch_1d((cudaStream_t)stream, (unsigned)m_padded, 256, smem, true), rmsnorm_quantize_kernel, p);
 }
 
 }  // extern "C"

@@ -257,7 +257,6 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
 // per calling thread: the entry points may be called from any thread, and one thread's experiment
 // must not change another thread's launches.
 thread_local int g_force_ksplit = 0, g_force_ug = 0;
-thread_local int g_pdl = 1;  // programmatic dependent launch on every tensor-core-route launch
 thread_local int g_balance = 0;  // unit dealing over a full-GPU grid: 0 = where it evens the SMs' load, 1 = wherever possible, 2 = never
 
 constexpr int kSmCount = 148;                 // B200
@@ -323,7 +322,7 @@ int launch_mma(cudaStream_t stream, GemmParams& p) {
     l.smem = smem;
     l.stream = stream;
     l.cluster_x = (unsigned)ksplit;
-    l.pdl = g_pdl != 0;
+    l.pdl = true;
     return nvk::launch(l, kern, p);
 }
 
@@ -381,12 +380,12 @@ int launch_mma_ws(cudaStream_t stream, GemmParams& p, const uint8_t* ws) {
     l.smem = smem;
     l.stream = stream;
     l.cluster_x = (unsigned)ksplit;
-    l.pdl = g_pdl != 0;
+    l.pdl = true;
     return nvk::launch(l, kern, p, ws);
 }
 
 int launch_prepare(cudaStream_t stream, const uint16_t* x, const uint16_t* x2, uint8_t* ws, int M, int K, int nsc) {
-    const nvk::Launch l = nvk::launch_1d(stream, (unsigned)M, 256, 0, g_pdl != 0);
+    const nvk::Launch l = nvk::launch_1d(stream, (unsigned)M, 256, 0, true);
     if (x2) return nvk::launch(l, x_prepare_kernel<1>, x, x2, ws, M, K, nsc);
     return nvk::launch(l, x_prepare_kernel<0>, x, x2, ws, M, K, nsc);
 }
@@ -415,7 +414,7 @@ int launch_grouped(cudaStream_t stream, GemmParams& p, const GroupedParams& g, i
     l.block = dim3(256, 1, 1);
     l.smem = smem;
     l.stream = stream;
-    l.pdl = g_pdl != 0;
+    l.pdl = true;
     return nvk::launch(l, kern, p, g);
 }
 
@@ -588,7 +587,7 @@ int w4a4_grouped(cudaStream_t stream, GemmParams& p, const W4a4GroupArgs& g, int
     l.smem = smem;
     l.stream = stream;
     l.cluster_x = (unsigned)ksplit;
-    l.pdl = g_pdl != 0;
+    l.pdl = true;
     return nvk::launch(l, w4a4_m1_grouped_kernel, p, g);
 }
 
@@ -599,7 +598,7 @@ int w4a4_grouped(cudaStream_t stream, GemmParams& p, const W4a4GroupArgs& g, int
 extern "C" {
 
 int nvk_b200_set_pdl(int enabled) {
-    g_pdl = enabled ? 1 : 0;
+    nvk::g_pdl_enabled = enabled ? 1 : 0;
     return 0;
 }
 
