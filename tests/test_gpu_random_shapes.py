@@ -1,0 +1,146 @@
+"""Seeded random shapes through the C ABI: sizes nobody picked by hand (ragged last tiles, K that is a
+multiple of 16 but not of 32 or 256, token counts between the template steps, expert counts around the
+router's warp/CTA switch), each checked against the oracle with the bound of the hand-picked tests.
+Every output buffer has a canary tail; on the host emulation every buffer also ends at a guard page, so
+an index that leaves its buffer on any of these shapes ends the run."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from tests import _util as U
+from tests.test_gpu_linear import check_against_oracle, run_linear
+from tests.test_gpu_quant_moe import gpu_quantize
+
+pytestmark = pytest.mark.gpu
+
+
+def _linear_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        m = int(rng.choice([1, 1, 2, 3, 5, 8, 9, 15, 16, 17, 31, 33, 48, 64]))
+        n = int(rng.integers(1, 700))
+        k = 16 * int(rng.integers(1, 90))
+        if i % 3 == 0:
+            k = (k + 31) // 32 * 32          # the tensor-core route's K rule
+        form = int(rng.integers(0, 3))       # 0 plain, 1 two arms, 2 SiLU(x) * x2 prologue
+        out.append((m, n, k, form, seed * 1000 + i))
+    return out
+
+
+@pytest.mark.parametrize("m,n,k,form,seed", _linear_cases(11, 36))
+def test_random_linear_shapes(m, n, k, form, seed):
+    U.require_gpu()
+    rng = np.random.default_rng(seed)
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    if form == 1:
+        packed_b, sw_b, alpha_b, _ = U.make_weight(rng, n, k)
+        ya, yb = run_linear(packed, sw, x, alpha, m, n, k, packed_b, sw_b, alpha_b)
+        check_against_oracle(ya, packed, sw, x, alpha, n, k, cpu_backend=False)
+        check_against_oracle(yb, packed_b, sw_b, x, alpha_b, n, k, cpu_backend=False)
+    elif form == 2:
+        up = U.gauss_bf16(rng, (m, k))
+        got = run_linear(packed, sw, x, alpha, m, n, k, up_bits=up)
+        g, u = ref.bf16_to_f32(x), ref.bf16_to_f32(up)
+        act = ref.f32_to_bf16((g / (np.float32(1.0) + np.exp(-g))).astype(np.float32) * u)
+        want = ref.linear_w4a16_f64(packed, sw, act, alpha, n, k)
+        # expf on the device and numpy's exp may round an activation to neighbouring bf16 values
+        assert U.rel_err_floor(ref.bf16_to_f32(got).reshape(-1, n), want) < 2e-2
+    else:
+        got = run_linear(packed, sw, x, alpha, m, n, k)
+        check_against_oracle(got, packed, sw, x, alpha, n, k, cpu_backend=False)
+
+
+def _quant_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(1, 300)), 16 * int(rng.integers(1, 70)), float(rng.choice([1.0, 0.37, 96.0, 2688.0])),
+             int(rng.integers(0, 2)), seed * 1000 + i) for i in range(count)]
+
+
+@pytest.mark.parametrize("m,k,g,pad,seed", _quant_cases(12, 16))
+def test_random_quantizer_shapes_are_byte_exact(m, k, g, pad, seed):
+    U.require_gpu()
+    rng = np.random.default_rng(seed)
+    mags = np.exp(rng.uniform(np.log(1e-3), np.log(300.0), size=(m, 1))).astype(np.float32)
+    x = ref.f32_to_bf16(rng.standard_normal((m, k)).astype(np.float32) * mags)
+    m_pad = -(-m // 128) * 128 if pad else None
+    p, s = gpu_quantize(x, g, m_pad)
+    pw, lw = ref.quantize_rows_bf16(x, g, m_padded=m_pad) if pad else ref.quantize_rows_bf16(x, g)
+    assert np.array_equal(p, pw)
+    assert np.array_equal(s, ref.swizzle_scales(lw))
+
+
+def _router_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        E = int(rng.choice([2, 7, 31, 32, 33, 64, 100, 128, 255, 256, 257, 384, 600]))
+        K = int(rng.integers(1, min(E, 16) + 1))
+        out.append((int(rng.integers(1, 70)), E, K, int(rng.integers(0, 2)), seed * 1000 + i))
+    return out
+
+
+@pytest.mark.parametrize("n,E,K,mode,seed", _router_cases(13, 16))
+def test_random_router_shapes(n, E, K, mode, seed):
+    """Ids bit-exact, weights to the last float operation's rounding, for every (tokens, experts, winners)
+    drawn; then the slot sort of those ids against numpy's stable sort."""
+    U.require_gpu()
+    rng = np.random.default_rng(seed)
+    lg = rng.standard_normal((n, E)).astype(np.float32)
+    bias = (rng.standard_normal(E) * 0.1).astype(np.float32) if mode == 1 else None
+    dl = U.dev(lg)
+    db = U.dev(bias) if bias is not None else None
+    ids = torch.full((n * K + 16,), -7, dtype=torch.int32, device="cuda")
+    w = torch.full((n * K + 16,), -7.0, dtype=torch.float32, device="cuda")
+    scaling = 2.5 if mode == 1 else 1.0
+    assert U.ffi.call("nv_kernels_moe_route_topk", U.stream(), dl.data_ptr(), db.data_ptr() if db is not None else None,
+                      ids.data_ptr(), w.data_ptr(), n, E, K, mode, 0.0, 1, scaling) == 0
+    torch.cuda.synchronize()
+    wi, ww = ref.moe_route_topk(lg, K, bias=bias, mode=mode, norm_topk=True, routed_scaling=scaling)
+    got_ids, got_w = ids.cpu().numpy(), w.cpu().numpy()
+    assert np.all(got_ids[n * K:] == -7) and np.all(got_w[n * K:] == -7.0)
+    assert np.array_equal(got_ids[:n * K].reshape(n, K), wi)
+    np.testing.assert_allclose(got_w[:n * K].reshape(n, K), ww, rtol=2e-6, atol=1e-7)
+
+    total = n * K
+    perm = torch.full((total + 8,), -7, dtype=torch.int32, device="cuda")
+    offs = torch.full((E + 1 + 8,), -7, dtype=torch.int32, device="cuda")
+    inv = torch.full((total + 8,), -7, dtype=torch.int32, device="cuda")
+    scr = torch.zeros(E, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_permute", U.stream(), ids.data_ptr(), perm.data_ptr(), offs.data_ptr(),
+                      inv.data_ptr(), scr.data_ptr(), n, K, E) == 0
+    torch.cuda.synchronize()
+    flat = wi.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    p, o, iv = perm.cpu().numpy(), offs.cpu().numpy(), inv.cpu().numpy()
+    assert np.all(p[total:] == -7) and np.all(o[E + 1:] == -7) and np.all(iv[total:] == -7)
+    assert np.array_equal(o[:E + 1], np.concatenate([[0], np.cumsum(np.bincount(flat, minlength=E))]))
+    assert np.array_equal(p[:total], (order // K).astype(np.int32))     # sorted slot -> its token
+    want_inv = np.empty(total, np.int32)
+    want_inv[order] = np.arange(total, dtype=np.int32)
+    assert np.array_equal(iv[:total], want_inv)
+
+
+def _bf16_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(1, 65)), int(rng.integers(1, 900)), 8 * int(rng.integers(1, 120)), seed * 1000 + i)
+            for i in range(count)]
+
+
+@pytest.mark.parametrize("m,n,k,seed", _bf16_cases(14, 12))
+def test_random_bf16_linear_shapes(m, n, k, seed):
+    U.require_gpu()
+    rng = np.random.default_rng(seed)
+    w = U.gauss_bf16(rng, (n, k), 0.05)
+    x = U.gauss_bf16(rng, (m, k))
+    dw, dx = U.dev(w), U.dev(x)
+    y = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nvk_b200_linear_bf16", U.stream(), dw.data_ptr(), dx.data_ptr(), y.data_ptr(), m, n, k) == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[m * n:] == 0x7FC0)
+    want = ref.bf16_to_f32(w).astype(np.float64) @ ref.bf16_to_f32(x).astype(np.float64).T   # [n, m]
+    got = ref.bf16_to_f32(out[:m * n].reshape(m, n))
+    assert U.rel_err_floor(got, want.T) < 1e-2
