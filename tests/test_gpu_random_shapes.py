@@ -144,3 +144,53 @@ def test_random_bf16_linear_shapes(m, n, k, seed):
     want = ref.bf16_to_f32(w).astype(np.float64) @ ref.bf16_to_f32(x).astype(np.float64).T   # [n, m]
     got = ref.bf16_to_f32(out[:m * n].reshape(m, n))
     assert U.rel_err_floor(got, want.T) < 1e-2
+
+
+def _moe_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        E = int(rng.choice([2, 5, 8, 24, 40]))
+        out.append((int(rng.choice([1, 2, 7, 9, 20, 33])), E, int(rng.integers(1, min(E, 6) + 1)),
+                    32 * int(rng.integers(4, 14)), 32 * int(rng.integers(4, 14)), seed * 1000 + i))   # >= 128, the host rule
+    return out
+
+
+@pytest.mark.parametrize("n_tok,E,top_k,hidden,inter,seed", _moe_cases(15, 8))
+def test_random_moe_decode_shapes(n_tok, E, top_k, hidden, inter, seed):
+    """The grouped decode step (router + slot sort + active list, gate/up, SiLU prologue + down, f32
+    combine) on drawn (tokens, experts, winners, hidden, expert width), against the per-(token, expert)
+    oracle; status word clean."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(seed)
+    experts, host = [], []
+    for e in range(E):
+        trip, htrip = [], []
+        for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter)):
+            w = U.gauss_bf16(rng, (n, k), 0.05)
+            packed, sw, alpha = ref.quantize_weight_bf16(w)
+            trip.append(sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n))
+            htrip.append((packed, sw, alpha))
+        experts.append(tuple(trip))
+        host.append(htrip)
+    w = sp.MoeGroupedWeights.build_from_experts(experts)
+    ctx = sp.GroupedDecodeContext(w, max(n_tok, 4), top_k, "cuda")
+    x = U.gauss_bf16(rng, (n_tok, hidden))
+    logits = rng.standard_normal((n_tok, E)).astype(np.float32)
+    y = sp.forward_grouped_decode(w, ctx, U.dev(x).view(torch.bfloat16), U.dev(logits))
+    torch.cuda.synchronize()
+    ctx.check_status()
+    got = y.cpu().numpy()
+    ids, wts = ref.moe_route_topk(logits, top_k)
+    assert np.array_equal(ctx.topk_ids[:n_tok].cpu().numpy(), ids)
+    want = np.zeros((n_tok, hidden), np.float64)
+    for t in range(n_tok):
+        for j in range(top_k):
+            (pg, sg, ag), (pu, su, au), (pd, sd, ad) = host[ids[t, j]]
+            gate = ref.f32_to_bf16(ref.linear_w4a16_f64(pg, sg, x[t:t + 1], ag, inter, hidden).astype(np.float32))
+            up = ref.f32_to_bf16(ref.linear_w4a16_f64(pu, su, x[t:t + 1], au, inter, hidden).astype(np.float32))
+            act = ref.f32_to_bf16(ref.silu_mul(gate, up, round_bf16=True))
+            down = ref.f32_to_bf16(ref.linear_w4a16_f64(pd, sd, act, ad, hidden, inter).astype(np.float32))
+            want[t] += np.float64(wts[t, j]) * ref.bf16_to_f32(down)[0].astype(np.float64)
+    assert U.rel_err_floor(got, want) < 1e-2
