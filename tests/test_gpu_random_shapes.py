@@ -194,3 +194,61 @@ def test_random_moe_decode_shapes(n_tok, E, top_k, hidden, inter, seed):
             down = ref.f32_to_bf16(ref.linear_w4a16_f64(pd, sd, act, ad, hidden, inter).astype(np.float32))
             want[t] += np.float64(wts[t, j]) * ref.bf16_to_f32(down)[0].astype(np.float64)
     assert U.rel_err_floor(got, want) < 1e-2
+
+
+def _w4a8_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(1, 80)), int(rng.integers(1, 500)), 32 * int(rng.integers(1, 60)), seed * 1000 + i)
+            for i in range(count)]
+
+
+@pytest.mark.parametrize("m,n,k,seed", _w4a8_cases(16, 12))
+def test_random_w4a8_shapes(m, n, k, seed):
+    """int8 rows x NVFP4 weights, two arms and the residual form, M rows per call (chunks of 64 beyond):
+    the W4A8 parity bound against integer-exact f64 dots."""
+    U.require_gpu()
+    from tests.test_gpu_w4a8 import TOL, rel_quarter, w4a8
+    rng = np.random.default_rng(seed)
+    wa, wb = U.make_weight(rng, n, k)[:3], U.make_weight(rng, n, k)[:3]
+    x = (rng.standard_normal((m, k)) * np.linspace(0.2, 3.0, m)[:, None]).astype(np.float32)
+    q, sc = ref.rowquant_i8(x)
+    ya, yb = w4a8("nv_kernels_gemv_nvfp4_w4a8_dual_mk", wa, q, sc, m, n, k, second=wb)
+    assert rel_quarter(ya, ref.linear_w4a8_f64(wa[0], wa[1], q, sc, wa[2], n, k)) < TOL
+    assert rel_quarter(yb, ref.linear_w4a8_f64(wb[0], wb[1], q, sc, wb[2], n, k)) < TOL
+    resid = U.gauss_bf16(rng, (m, n))
+    yd = w4a8("nv_kernels_gemv_nvfp4_w4a8_down_residual_mk", wa, q, sc, m, n, k, residual=resid)
+    assert rel_quarter(yd, ref.linear_w4a8_f64(wa[0], wa[1], q, sc, wa[2], n, k, resid)) < TOL
+
+
+def _w4a4_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(1, 600)), 16 * int(rng.integers(1, 150)), seed * 1000 + i) for i in range(count)]
+
+
+@pytest.mark.parametrize("n,k,seed", _w4a4_cases(17, 12))
+def test_random_w4a4_gemv_shapes(n, k, seed):
+    """Row quantizer (flat scales) + the M = 1 FP4 x FP4 GEMV on drawn (N, K): quantizer bytes exact, the
+    product within 2 bf16 ulp of the W4A4 host oracle."""
+    U.require_gpu()
+    rng = np.random.default_rng(seed)
+    w = U.gauss_bf16(rng, (n, k), 0.02)
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    x = U.gauss_bf16(rng, (1, k))
+    dx = U.dev(x)
+    xp = torch.zeros(k // 2, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(k // 16, dtype=torch.uint8, device="cuda")
+    assert U.ffi.call("nv_kernels_nvfp4_quantize_row_bf16", U.stream(), dx.data_ptr(), xp.data_ptr(), xs.data_ptr(),
+                      1.0, k) == 0
+    y = torch.full((n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    dw, ds = U.dev(packed), U.dev(sw)
+    assert U.ffi.call("nv_kernels_nvfp4_gemv_bf16", U.stream(), dw.data_ptr(), ds.data_ptr(), xp.data_ptr(),
+                      xs.data_ptr(), y.data_ptr(), alpha, n, k) == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[n:] == 0x7FC0)
+    ap, alin = ref.quantize_rows_bf16(x, 1.0)
+    assert np.array_equal(xp.cpu().numpy(), ap[0]) and np.array_equal(xs.cpu().numpy(), alin[0])
+    want = ref.matmul_w4a4(ap, alin, packed, ref.unswizzle_scales(sw, n, k // 16), 1, n, k, alpha)[0]
+    ulp = U.bf16_ulp_diff(out[:n], want)
+    absd = np.abs(ref.bf16_to_f32(out[:n]) - ref.bf16_to_f32(want))
+    assert np.all((ulp <= 2) | (absd <= 1e-3))
