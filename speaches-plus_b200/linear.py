@@ -250,12 +250,18 @@ class Nvfp4Linear:
         assert x2.is_cuda and x2.dtype == torch.bfloat16 and norm_weight.dtype == torch.bfloat16
         m, k = x2.shape
         m_pad = -(-m // 128) * 128
-        a_packed = torch.empty((m_pad, k // 2), dtype=torch.uint8, device=x2.device)
-        a_scales = torch.zeros(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=x2.device)
+        entry = self._acquire_staging(m, x2.device)
+        if entry is not None:
+            # live rows only: the rest of the staging entry is zero (linear.rs:1713)
+            a_packed, a_scales, rows = entry.packed, entry.scales, m
+        else:
+            a_packed = torch.empty((m_pad, k // 2), dtype=torch.uint8, device=x2.device)
+            a_scales = torch.zeros(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=x2.device)
+            rows = m_pad
         _ffi.check("nv_kernels_rmsnorm_quantize_nvfp4_bf16", _stream(), x2.data_ptr(), norm_weight.data_ptr(),
-                   a_packed.data_ptr(), a_scales.data_ptr(), float(self.input_stored_global), float(eps), m_pad, m, k)
+                   a_packed.data_ptr(), a_scales.data_ptr(), float(self.input_stored_global), float(eps), rows, m, k)
         y = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=x2.device)
-        self._fp4_gemm(a_packed, a_scales, y, m)
+        self._fp4_gemm(a_packed, a_scales, y, m, entry)
         return y.reshape(*lead, self.out_features)
 
     def forward_prenorm_decode(self, x_pre: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -279,69 +285,120 @@ class Nvfp4Linear:
             y += self.bias
         return y.reshape(*lead, self.out_features)
 
-    def prepare_prefill(self, max_m: int, device=None) -> None:
-        """Create everything the prefill route needs for up to `max_m` rows -- the quantized-activation
-        buffers, the GEMM workspace and the device copy of alpha -- so that later calls allocate nothing
-        (the reference creates its runner's workspace ahead of time for the same reason,
-        rust/crates/nv-quant/src/nvfp4.rs:391-409).  Called on first use if not before."""
-        dev = self.weight_u8.device if device is None else torch.device(device)
-        k, n = self.in_features, self.out_features
-        m_pad = -(-max_m // 128) * 128
-        need = C.c_size_t(0)
-        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", _stream(), None, None, None, None, None, None, m_pad, n, k,
-                   None, 0, C.addressof(need))
-        self._prefill = {
-            "m_pad": m_pad,
-            "a_packed": torch.empty((m_pad, k // 2), dtype=torch.uint8, device=dev),
-            "a_scales": torch.zeros(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=dev),
-            "ws": torch.empty(max(int(need.value), 16), dtype=torch.uint8, device=dev),
-            "alpha": torch.tensor([self.weight_alpha], dtype=torch.float32, device=dev),
-        }
+    # -- prefill-sized rows: activation staging per (stream, padded rows), as the reference keeps it --
+    def _staging_cache(self):
+        from .runner import StagingCache
+        c = getattr(self, "_staging", None)
+        if c is None:
+            c = self._staging = StagingCache()
+        return c
 
-    def _prefill_buffers(self, m: int, device):
-        st = getattr(self, "_prefill", None)
-        if st is None or st["m_pad"] < m or st["ws"].device != device:
-            self.prepare_prefill(m, device)
-            st = self._prefill
-        return st
+    def _alpha_on(self, device) -> torch.Tensor:
+        """weight_alpha as one f32 in device memory (`weight_alpha_dev`, linear.rs:314).  Made on first use,
+        which must not be inside a graph capture: `prepare_prefill` makes it ahead of time."""
+        cache = self.__dict__.setdefault("_alpha_dev", {})
+        t = cache.get(device)
+        if t is None:
+            if device.type == "cuda" and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("nvfp4 linear: the device copy of alpha must exist before graph capture "
+                                   "(call prepare_prefill first)")
+            t = cache[device] = torch.tensor([self.weight_alpha], dtype=torch.float32, device=device)
+        return t
+
+    def _workspace_for(self, m_pad: int, device, entry) -> torch.Tensor:
+        """The data-parallel GEMM's workspace for `m_pad` rows: kept with the staging entry, or made for
+        this call when there is none."""
+        if entry is not None and "ws" in entry.extra:
+            return entry.extra["ws"]
+        need = C.c_size_t(0)
+        _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", _stream(), None, None, None, None, None, None, m_pad,
+                   self.out_features, self.in_features, None, 0, C.addressof(need))
+        ws = torch.empty(max(int(need.value), 16), dtype=torch.uint8, device=device)
+        if entry is not None:
+            entry.extra["ws"] = ws
+        return ws
+
+    def _acquire_staging(self, m: int, device):
+        """The current stream's staging entry for ceil(m / 128) * 128 rows (made on first use outside a
+        capture, evicted when the stream's epoch has moved, zeroed when fewer rows arrive than last time:
+        linear.rs:1620-1660), or None inside a capture that finds none."""
+        from .runner import stream_cache_key
+        k = self.in_features
+        m_pad = -(-m // 128) * 128
+        capturing = device.type == "cuda" and torch.cuda.is_current_stream_capturing()
+
+        def alloc_zeros():
+            return (torch.zeros((m_pad, k // 2), dtype=torch.uint8, device=device),
+                    torch.zeros(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=device))
+
+        return self._staging_cache().acquire(stream_cache_key(), m_pad, m, capturing, alloc_zeros,
+                                             lambda buf: buf.zero_())
+
+    def prepare_prefill(self, max_m: int, device=None) -> None:
+        """Create, on the current stream, everything a later call with ceil(max_m / 128) * 128 padded rows
+        needs -- the staging entry, the GEMM workspace and the device copy of alpha -- so that such a call
+        allocates nothing and can be captured (the reference creates its runner's workspace ahead of
+        time for the same reason, rust/crates/nv-quant/src/nvfp4.rs:391-409).  Other row counts get their
+        entry on first use."""
+        dev = self.weight_u8.device if device is None else torch.device(device)
+        self._alpha_on(dev)
+        entry = self._acquire_staging(max_m, dev)
+        entry.hwm_rows = 0   # nothing has been written yet
+        self._workspace_for(-(-max_m // 128) * 128, dev, entry)
+
+    def nvfp4_staging_diag(self, stream_key: int, m_padded: int):
+        """(epoch, high-water mark) of a staging entry, or None (linear.rs:1802-1808)."""
+        return self._staging_cache().diag(stream_key, m_padded)
 
     def forward_prefill_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
         """Prefill-sized M: the reference's default route (rust/crates/nv-layers/src/linear.rs:1590-1795) --
         quantize the activations to NVFP4 (global 1.0, rows padded to a multiple of 128 with zeros), then one
-        block-scaled FP4 x FP4 tensor-core GEMM with alpha = weight_alpha in device memory.  Uses the
-        buffers of `prepare_prefill` (created on the first call that needs them)."""
+        block-scaled FP4 x FP4 tensor-core GEMM with alpha = weight_alpha in device memory.  With a
+        staging entry the quantizer writes the live rows only (the rest of the entry is zero); without
+        one -- a capture that was not prepared for this row count -- buffers of this call and the
+        quantizer that writes the pad rows too."""
         m, k = x2.shape
-        st = self._prefill_buffers(m, x2.device)
         m_pad = -(-m // 128) * 128
-        a_packed, a_scales = st["a_packed"][:m_pad], st["a_scales"][:swizzled_scale_bytes(m_pad, k)]
-        _ffi.check("nv_kernels_quantize_nvfp4_bf16", _stream(), x2.data_ptr(), a_packed.data_ptr(), a_scales.data_ptr(),
-                   float(self.input_stored_global), m_pad, m, k)
-        self._fp4_gemm(a_packed, a_scales, y, m)
+        entry = self._acquire_staging(m, x2.device)
+        if entry is not None:
+            a_packed, a_scales = entry.packed, entry.scales
+            _ffi.check("nv_kernels_quantize_nvfp4_bf16_rows", _stream(), x2.data_ptr(), a_packed.data_ptr(),
+                       a_scales.data_ptr(), float(self.input_stored_global), m, k)
+        else:
+            a_packed = torch.empty((m_pad, k // 2), dtype=torch.uint8, device=x2.device)
+            a_scales = torch.empty(swizzled_scale_bytes(m_pad, k), dtype=torch.uint8, device=x2.device)
+            _ffi.check("nv_kernels_quantize_nvfp4_bf16", _stream(), x2.data_ptr(), a_packed.data_ptr(),
+                       a_scales.data_ptr(), float(self.input_stored_global), m_pad, m, k)
+        self._fp4_gemm(a_packed, a_scales, y, m, entry)
 
-    def _fp4_gemm(self, a_packed: torch.Tensor, a_scales: torch.Tensor, y: torch.Tensor, m: int) -> None:
+    def _fp4_gemm(self, a_packed: torch.Tensor, a_scales: torch.Tensor, y: torch.Tensor, m: int, entry=None) -> None:
         """y [m, out] = alpha * A W^T for activations already quantized (rows padded to 128)."""
         k, n = self.in_features, self.out_features
-        st = self._prefill_buffers(m, a_packed.device)
+        dev = a_packed.device
+        m_pad = a_packed.shape[0]
+        alpha = self._alpha_on(dev)
         runner = getattr(self, "runner", None)
         if runner is not None:
             # an Nvfp4GemmRunner (runner.py) picks the scheduler for the shape and owns the workspace
             if runner.backend.value == "cublaslt":
                 # the library route computes every padded row: into a padded buffer, then trimmed
                 # (pad -> quantize -> GEMM -> trim, rust/crates/nv-layers/src/linear.rs:1590-1795)
-                m_pad = a_packed.shape[0]
-                yp = st.get("y_pad")
-                if yp is None or yp.shape[0] < m_pad:
-                    yp = st["y_pad"] = torch.empty((st["m_pad"], n), dtype=torch.bfloat16, device=a_packed.device)
-                runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, st["alpha"], yp[:m_pad], m_pad,
-                              n, k, alpha_host=self.weight_alpha)
+                yp = entry.extra.get("y_pad") if entry is not None else None
+                if yp is None:
+                    yp = torch.empty((m_pad, n), dtype=torch.bfloat16, device=dev)
+                    if entry is not None:
+                        entry.extra["y_pad"] = yp
+                runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, alpha, yp, m_pad, n, k,
+                              alpha_host=self.weight_alpha)
                 y.copy_(yp[:m])
                 return
-            runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, st["alpha"], y, m, n, k)
+            runner.matmul(a_packed, a_scales, self.weight_u8, self.weight_scales, alpha, y, m, n, k)
             return
+        ws = self._workspace_for(m_pad, dev, entry)
         need = C.c_size_t(0)
         _ffi.check("nv_kernels_cutlass_fp4_gemm_sm120_bf16", _stream(), a_packed.data_ptr(), a_scales.data_ptr(),
-                   self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), st["alpha"].data_ptr(), y.data_ptr(),
-                   m, n, k, st["ws"].data_ptr(), st["ws"].numel(), C.addressof(need))
+                   self.weight_u8.data_ptr(), self.weight_scales.data_ptr(), alpha.data_ptr(), y.data_ptr(),
+                   m, n, k, ws.data_ptr(), ws.numel(), C.addressof(need))
 
 
 class Bf16Linear:

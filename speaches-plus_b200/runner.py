@@ -12,6 +12,7 @@ from __future__ import annotations
 import ctypes as C
 import enum
 import os
+import threading
 
 import torch
 
@@ -109,6 +110,91 @@ def ensure_workspace_for_stream() -> torch.Tensor:
 
 def release_stream_workspace(device_index: int, cu_stream: int) -> None:
     _WORKSPACES.pop((device_index, cu_stream), None)
+
+
+# ---- stream epochs and per-stream activation staging (rust/crates/nv-quant/src/lib.rs:9-51,
+# rust/crates/nv-layers/src/linear.rs:317-323,1620-1660) -------------------------------------------------
+# Buffers cached per stream must not outlive the stream: whoever retires a stream bumps its epoch, and
+# every cache entry remembers the epoch it was made under and is dropped when the two differ.
+_STREAM_EPOCHS: dict = {}
+_EPOCH_LOCK = threading.Lock()
+
+
+def stream_epoch(stream_key: int) -> int:
+    with _EPOCH_LOCK:
+        return _STREAM_EPOCHS.get(stream_key, 0)
+
+
+def bump_stream_epoch(stream_key: int) -> None:
+    with _EPOCH_LOCK:
+        _STREAM_EPOCHS[stream_key] = _STREAM_EPOCHS.get(stream_key, 0) + 1
+
+
+def stream_cache_key() -> int:
+    """The current stream as a cache key (rust/crates/nv-quant/src/lib.rs:16-30): its handle, except that
+    the per-thread default stream (handle 2) is a different stream in every thread and gets the thread's
+    identity folded in."""
+    raw = int(torch.cuda.current_stream().cuda_stream) if torch.cuda.is_available() else 0
+    if raw != 0x2:
+        return raw
+    return 0x2 | (threading.get_ident() << 8)
+
+
+def release_stream_resources(stream_key: int) -> None:
+    """A stream is going away: drop its GEMM workspaces (on every device) and invalidate what linears
+    staged for it."""
+    for key in [k for k in _WORKSPACES if k[1] == stream_key]:
+        _WORKSPACES.pop(key, None)
+    bump_stream_epoch(stream_key)
+
+
+class StagedActivations:
+    """One (stream, padded row count) staging entry of a quantized linear: packed activations and their
+    swizzled scales, zero beyond the rows last written."""
+    __slots__ = ("epoch", "hwm_rows", "packed", "scales", "extra")
+
+    def __init__(self, epoch: int, packed, scales):
+        self.epoch, self.hwm_rows, self.packed, self.scales, self.extra = epoch, 0, packed, scales, {}
+
+
+class StagingCache:
+    """The reference's `a_staging` map.  Entries are created with zeroed buffers, outside graph capture
+    only; rows-only quantizers then write the live rows and rely on the rest being zero, so a call with
+    fewer rows than the one before first zeroes the buffers (`hwm_rows` is that high-water mark).  During
+    a capture that finds no entry the caller must use buffers of its own and a quantizer that writes the
+    pad rows too: `acquire` returns None."""
+
+    def __init__(self):
+        self._map: dict = {}
+        self._lock = threading.Lock()
+
+    def acquire(self, stream_key: int, m_padded: int, m_logical: int, capturing: bool, alloc_zeros, zero):
+        """alloc_zeros() -> (packed, scales) zero-filled; zero(buffer) clears one in stream order."""
+        key = (stream_key, m_padded)
+        with self._lock:
+            if not capturing:
+                for k in [k for k, v in self._map.items() if v.epoch != stream_epoch(k[0])]:
+                    del self._map[k]
+                if key not in self._map:
+                    packed, scales = alloc_zeros()
+                    self._map[key] = StagedActivations(stream_epoch(stream_key), packed, scales)
+            entry = self._map.get(key)
+            if entry is None:
+                return None
+            if m_logical < entry.hwm_rows:
+                zero(entry.packed)
+                zero(entry.scales)
+            entry.hwm_rows = m_logical
+            return entry
+
+    def diag(self, stream_key: int, m_padded: int):
+        """(epoch, high-water mark) of an entry, or None (linear.rs:1802-1808)."""
+        with self._lock:
+            e = self._map.get((stream_key, m_padded))
+            return None if e is None else (e.epoch, e.hwm_rows)
+
+    def __len__(self):
+        return len(self._map)
 
 
 # ---- the runner -------------------------------------------------------------------------------------------

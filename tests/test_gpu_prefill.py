@@ -148,6 +148,45 @@ def test_runner_with_the_library_backend_pads_and_trims():
     assert U.rel_err_floor(a, b.astype(np.float64)) < 1e-2
 
 
+def test_staging_lifecycle_on_the_device():
+    """rust/crates/nv-layers/tests/nvfp4_staging_lifecycle.rs: the linear's staging entry for the current
+    stream tracks the live rows, a shrinking call resets the mark, releasing the stream's resources rebuilds
+    the entry under a new epoch, and none of it changes the values."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    from speaches_plus_b200 import runner as R
+    rng = np.random.default_rng(9)
+    n, k = 128, 256
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    lin = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+    key = R.stream_cache_key()
+    y = torch.empty((200, n), dtype=torch.bfloat16, device="cuda")
+    x200 = U.dev(U.gauss_bf16(rng, (200, k))).view(torch.bfloat16)
+    x70 = x200[:70].contiguous()
+    lin.forward_prefill_into(x200, y)
+    assert lin.nvfp4_staging_diag(key, 256) == (R.stream_epoch(key), 200)
+    lin.forward_prefill_into(x200[:130].contiguous(), y[:130])
+    assert lin.nvfp4_staging_diag(key, 256)[1] == 130           # the shrink path ran and reset the mark
+    lin.forward_prefill_into(x70, y[:70])
+    a = U.host_u16(y[:70]).copy()
+    assert lin.nvfp4_staging_diag(key, 128)[1] == 70
+    epoch_before = lin.nvfp4_staging_diag(key, 128)[0]
+    R.release_stream_resources(key)
+    lin.forward_prefill_into(x70, y[:70])
+    torch.cuda.synchronize()
+    assert lin.nvfp4_staging_diag(key, 128)[0] > epoch_before   # rebuilt under the new epoch
+    assert lin.nvfp4_staging_diag(key, 256) is None             # ... and the stale entry is gone
+    assert np.array_equal(U.host_u16(y[:70]), a)                # eviction is value-preserving
+    # rows left over from the 200-row call must not leak into a 130-row call's pad rows: same bits as fresh
+    fresh = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+    y2 = torch.empty((130, n), dtype=torch.bfloat16, device="cuda")
+    lin.forward_prefill_into(x200, y)
+    lin.forward_prefill_into(x200[:130].contiguous(), y[:130])
+    fresh.forward_prefill_into(x200[:130].contiguous(), y2)
+    torch.cuda.synchronize()
+    assert np.array_equal(U.host_u16(y[:130]), U.host_u16(y2))
+
+
 def test_true_m_equals_padded_m_bitwise():
     """rust/crates/nv-quant/tests/nvfp4_true_m.rs: a GEMM told the true row count gives the same bits
     for those rows as one told the 128-padded count (pad rows are zeros and are not part of the result)."""

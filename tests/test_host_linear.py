@@ -238,3 +238,48 @@ def test_backend_registry_knows_one_backend():
     assert B.library_for(B.KernelId.GEMM_NVFP4) == "libnvk_b200_prefill.so"
     assert B.library_for(B.KernelId.GEMV_NVFP4) == "libnvk_b200.so"
     assert str(B.BackendKind.CUDA) == "cuda"
+
+
+# ---- stream epochs and activation staging (rust/crates/nv-layers/tests/nvfp4_staging_lifecycle.rs) ----
+def test_stream_epoch_registry_bumps_and_reads():
+    from speaches_plus_b200 import runner as R
+    key = 0xDEADBEEF
+    e0 = R.stream_epoch(key)
+    R.bump_stream_epoch(key)
+    R.bump_stream_epoch(key)
+    assert R.stream_epoch(key) == e0 + 2
+    assert R.stream_epoch(key ^ 1) == 0
+
+
+def test_staging_evicts_on_epoch_bump_and_zeros_on_shrink():
+    """The cache's rules, with numpy buffers standing in for device memory: the high-water mark tracks
+    the live rows; fewer rows than last time zero the entry first; a released stream's entries are
+    rebuilt under the new epoch; a capture that finds no entry gets None and creates nothing."""
+    import numpy as np
+    from speaches_plus_b200 import runner as R
+    cache, key, allocs, zeroed = R.StagingCache(), 0x51A6E, [], []
+
+    def alloc():
+        allocs.append(1)
+        return np.zeros(64, np.uint8), np.zeros(16, np.uint8)
+
+    def zero(buf):
+        zeroed.append(id(buf))
+        buf[:] = 0
+
+    e = cache.acquire(key, 128, 5, False, alloc, zero)
+    e.packed[:] = 7                       # the quantizer wrote rows
+    assert cache.diag(key, 128) == (R.stream_epoch(key), 5) and len(allocs) == 1 and not zeroed
+    e2 = cache.acquire(key, 128, 9, False, alloc, zero)
+    assert e2 is e and cache.diag(key, 128)[1] == 9 and not zeroed       # growing: nothing to clear
+    e3 = cache.acquire(key, 128, 2, False, alloc, zero)
+    assert e3 is e and cache.diag(key, 128)[1] == 2 and len(zeroed) == 2 and not e.packed.any()
+    assert cache.acquire(key, 256, 130, True, alloc, zero) is None and len(allocs) == 1   # capturing, no entry
+    assert cache.acquire(key, 128, 2, True, alloc, zero) is e                             # capturing, entry exists
+    other = cache.acquire(key + 1, 128, 3, False, alloc, zero)
+    epoch_before = cache.diag(key, 128)[0]
+    R.release_stream_resources(key)
+    e4 = cache.acquire(key, 128, 2, False, alloc, zero)
+    assert e4 is not e and cache.diag(key, 128)[0] > epoch_before and len(allocs) == 3
+    assert cache.acquire(key + 1, 128, 3, False, alloc, zero) is other    # another stream's entry survives
+    assert cache.diag(key, 512) is None
