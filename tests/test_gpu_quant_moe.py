@@ -62,6 +62,27 @@ def test_quantizer_ties_and_pad_rows():
     assert U.ffi.call("nv_kernels_quantize_nvfp4_bf16", U.stream(), 0, 0, 0, 1.0, 0, 0, 64) == 0
 
 
+def test_device_scale_byte_at_power_of_two_neighbours():
+    """rust/crates/nv-kernels/tests/ue4m3_log2f_boundary.rs: a block whose maximum is 6 makes the block
+    scale equal the global, so the device encoder can be probed with chosen scales -- every power of two
+    from 2^-9 to 2^8 and its f32 neighbours, where an encoder that takes log2 in floating point picks the
+    wrong exponent.  The byte must equal the host encoder's (itself pinned to the exact-floor form)."""
+    U.require_gpu()
+    f32 = np.float32
+    x = np.zeros((1, 16), np.uint16)
+    x[0, 0] = ref.f32_to_bf16(np.array([6.0], f32))[0]
+    probes = []
+    for e in range(-9, 9):
+        p = f32(2.0) ** f32(e)
+        probes += [np.nextafter(p, f32(0)), p, np.nextafter(p, f32(1e9))]
+    probes += [f32(448.0), np.nextafter(f32(448.0), f32(0)), f32(1e9), f32(447.9), f32(1.0 / 1024.0)]
+    for stored in probes:
+        _, s = gpu_quantize(x, float(stored))
+        want = int(ref.encode_ue4m3(float(stored)))
+        assert int(s[0]) == want, f"scale {float(stored)!r}: device {int(s[0]):#x}, host {want:#x}"
+        assert int(s[0]) != 0x7F
+
+
 def test_weight_quantizer_matches_oracle_and_feeds_the_gemv():
     """Linear::from_bf16_quantized_nvfp4_dev rule end to end on the GPU: global 448*6/amax,
     alpha = 1/global; bytes equal the oracle's, so the GEMV sees identical operands."""
