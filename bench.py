@@ -248,6 +248,15 @@ def run_b200(args) -> dict:
 
     # ---- time of each GEMV inside a graph replay, from GPU timestamps between the launches ----
     stamped = stamped_graph_leg(dev, stream, layers, xs) if world == 1 else None
+    # ... and the same with every launch kept at one CTA per 128-row tile (no dealing of 16-row units over a
+    # full-GPU grid): the pair shows what the dealt launch is worth on the shapes where it is chosen
+    stamped_per_tile = None
+    if world == 1:
+        sp.ffi.check("nvk_b200_set_row_balance", 2)
+        try:
+            stamped_per_tile = stamped_graph_leg(dev, stream, layers, xs)
+        finally:
+            sp.ffi.check("nvk_b200_set_row_balance", 0)
 
     # ---- per-shape breakdown (each shape's copies timed as their own region) ----
     per_shape = {}
@@ -355,6 +364,7 @@ def run_b200(args) -> dict:
                          "us_per_launch_avg": round(ms_per_step * 1e3 / launches_per_step, 3)},
             "per_shape": per_shape,
             "per_shape_in_graph": stamped,
+            "per_shape_in_graph_one_cta_per_tile": stamped_per_tile,
             "clocks": clocks,
         }
         if args.cpu_baseline:
