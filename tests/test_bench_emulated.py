@@ -37,7 +37,7 @@ def test_b200_arm_runs_on_the_emulator_and_prints_the_contract():
     j = json.loads(lines[0])
     for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
                 "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "roofline", "cpu_baseline", "clocks",
-                "step", "step_ms", "per_shape", "per_shape_in_graph", "decode_stack", "moe_decode", "persistent_step"):
+                "step", "step_ms", "per_shape", "per_shape_in_graph", "per_shape_in_graph_one_cta_per_tile", "decode_stack", "moe_decode", "persistent_step"):
         assert key in j, key
     assert j["steps"] == 3 and j["warmup"] >= 3 and j["n_gpus"] == 1 and j["value"] > 0
     assert set(j["roofline"]) >= {"bound", "achieved", "peak", "unit", "frac", "traffic"}
