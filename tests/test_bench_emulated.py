@@ -72,3 +72,52 @@ def test_clock_sampler_keeps_only_samples_inside_the_timed_region():
     assert got["samples_in_region"] == 2 and got["samples_total"] == 4
     assert got["sm_mhz"] == 1850.0 and got["sm_max_mhz"] == 1965.0 and got["reasons"] == ["sw_power_cap"]
     assert got["power_w_max"] == 950.5
+
+
+_SCRIPT_TWO_RANKS = r"""
+import sys, argparse, datetime
+sys.path.insert(0, {root!r})
+from tests.emu import torch_shim
+torch_shim.install()
+import torch.distributed as dist
+import bench
+from speaches_plus_b200 import tp as tpmod
+tpmod.init_process_group_for_node = lambda device, timeout_s=90: dist.init_process_group(
+    "gloo", timeout=datetime.timedelta(seconds=timeout_s))
+bench.SHAPES_KN = [(256, 512), (256, 256), (512, 256)]
+bench.ROW_PARALLEL = {{(256, 256), (512, 256)}}
+bench.COPIES = 2
+bench.STEP_TARGET_S = 1e-4
+bench.STACK_DIMS = {{"H": 256, "QO": 256, "KV": 128, "F": 512, "V": 1000, "layers": 2}}
+bench.MOE_DIMS = {{"E": 16, "H": 256, "F": 128, "TOPK": 4, "layers": 2}}
+args = argparse.Namespace(gpus=2, steps=3, warmup=3, impl="b200", cpu_baseline=False, extras=True, collective="nccl",
+                          profile_case=None, copies=2, persistent=False)
+bench.run_b200(args)
+"""
+
+
+def test_two_ranks_run_the_b200_arm_and_rank_0_prints_the_line():
+    """The N > 1 control flow of the bench -- sharded weight sets, the all-reduce after row-parallel linears,
+    max-over-ranks timing, the tensor-parallel decode stack and the expert-parallel MoE leg, the orderly
+    shutdown -- with two emulated ranks over gloo."""
+    import os
+    import socket
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, "-c", _SCRIPT_TWO_RANKS.format(root=str(ROOT))], env=env, cwd=ROOT,
+                                      stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=900) for p in procs]
+    for p, (so, se) in zip(procs, outs):
+        assert p.returncode == 0, (so + se)[-4000:]
+    lines0 = [ln for ln in outs[0][0].splitlines() if ln.startswith("{")]
+    lines1 = [ln for ln in outs[1][0].splitlines() if ln.startswith("{")]
+    assert len(lines0) == 1 and not lines1            # rank 0 alone prints
+    j = json.loads(lines0[0])
+    assert j["n_gpus"] == 2 and j["scaling"] == "strong" and j["config"]["parallelism"] == "tp2" and j["value"] > 0
+    assert j["per_shape_in_graph"] is None            # the stamped legs are single-GPU
+    assert [d["batch"] for d in j["decode_stack"]] == [1, 16] and [d["batch"] for d in j["moe_decode"]] == [1, 16, 64]
