@@ -94,6 +94,16 @@ int nvk_b200_linear_nvfp4_w4a16_ws(void* stream, const uint8_t* wq_a, const uint
                                    uint16_t* y_b, float alpha_a, float alpha_b, int M, int N, int K,
                                    void* workspace, size_t workspace_bytes);
 
+/* No counterpart in the reference (its residual epilogues take int8 activations only): the W4A16 linear
+ * as a residual update, y[m, n] = bf16(fma(sum_k W[n, k] a[m, k], alpha, residual[m, n])), one rounding,
+ * with a = x or, when x2 is given, a = bf16(SiLU(x) * x2) -- a decoder MLP's tail or an attention output
+ * projection in one launch.  y may alias residual.  1 <= M <= 64.  0 for an empty problem (N or K <= 0);
+ * -1 for M outside [1, 64] or K % 32 != 0; -2 for a null operand (x2 excepted) or one not 16-byte
+ * aligned; -9 when N needs more than 65535 row tiles. */
+int nvk_b200_linear_nvfp4_w4a16_residual(void* stream, const uint8_t* wq, const uint8_t* sc, const uint16_t* x,
+                                         const uint16_t* x2, const uint16_t* residual, uint16_t* y, float alpha, int M,
+                                         int N, int K);
+
 /* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
  * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 16, 32,
  * 64, 128} fixes the rows one CTA owns (M <= 16 only). */

@@ -219,6 +219,23 @@ class Nvfp4Linear:
             mm = min(MAX_DECODE_M, m - r0)
             linear_w4a16(self, None, x2[r0:], None, y[r0:], None, mm)
 
+    def forward_residual_into(self, x2: torch.Tensor, residual: torch.Tensor, y: torch.Tensor,
+                              up: torch.Tensor | None = None) -> None:
+        """y [M, out] = bf16(residual + (a W^T) * alpha) with one rounding, a = x2 or -- when `up` is given --
+        bf16(SiLU(x2) * up); rows in chunks of up to 64.  `y` may be `residual` itself (an in-place update
+        of the hidden state).  The decode-sized W4A16 route only."""
+        assert x2.is_cuda and x2.dtype == torch.bfloat16 and x2.is_contiguous()
+        assert residual.dtype == torch.bfloat16 and residual.is_contiguous() and y.is_contiguous()
+        assert residual.shape == (x2.shape[0], self.out_features) and y.shape == residual.shape
+        assert up is None or (up.shape == x2.shape and up.is_contiguous() and up.dtype == torch.bfloat16)
+        s = _stream()
+        for r0 in range(0, x2.shape[0], MAX_DECODE_M):
+            mm = min(MAX_DECODE_M, x2.shape[0] - r0)
+            _ffi.check("nvk_b200_linear_nvfp4_w4a16_residual", s, self.weight_u8.data_ptr(),
+                       self.weight_scales.data_ptr(), x2[r0:].data_ptr(), up[r0:].data_ptr() if up is not None else None,
+                       residual[r0:].data_ptr(), y[r0:].data_ptr(), self.alpha_w4a16, mm, self.out_features,
+                       self.in_features)
+
     def route_for(self, m: int, allow_prefill: bool = True) -> str:
         """Which kernels M rows take: "gemv" (M = 1), "decode" (row chunks of up to 64 on the W4A16
         kernel) or "prefill" (the FP4 x FP4 GEMM of the prefill library).  The last is chosen only in
@@ -464,6 +481,23 @@ class Nvfp4Mlp:
             mm = min(MAX_DECODE_M, m - r0)
             linear_w4a16(self.gate, self.up, x2[r0:], None, g[r0:], u[r0:], mm)
             linear_w4a16(self.down, None, g[r0:], u[r0:], y[r0:], None, mm)
+        return y.reshape(*x.shape[:-1], hidden)
+
+    def forward_residual(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """residual + MLP(x), the sum rounded once: gate/up as in `forward`, then the down projection with
+        the SiLU prologue and the residual epilogue in one launch.  Returns a new tensor."""
+        x2 = x.reshape(-1, self.gate.in_features).contiguous()
+        m = x2.shape[0]
+        inter, hidden = self.gate.out_features, self.down.out_features
+        r2 = residual.reshape(m, hidden).contiguous()
+        if self._gu is None or self._gu.shape[1] != m or self._gu.device != x.device:
+            self._gu = torch.empty((2, m, inter), dtype=torch.bfloat16, device=x.device)
+        g, u = self._gu[0], self._gu[1]
+        y = torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device)
+        for r0 in range(0, m, MAX_DECODE_M):
+            mm = min(MAX_DECODE_M, m - r0)
+            linear_w4a16(self.gate, self.up, x2[r0:], None, g[r0:], u[r0:], mm)
+        self.down.forward_residual_into(g, r2, y, up=u)
         return y.reshape(*x.shape[:-1], hidden)
 
     __call__ = forward

@@ -179,3 +179,13 @@ def test_library_route_refusals():
     assert g(P + 8, P, P, P, P, 128, 128, 128, 1.0, P, 1024) == -2  # misaligned activations
     assert g(P, P, P, P, P, 128, 128, 128, 1.0, 0, 1024) == -2      # workspace size without a workspace
     assert sp.ffi.prefill_lib().nvk_b200_cublaslt_fp4_workspace_bytes() == 64 << 20
+
+
+def test_residual_linear_refusals():
+    g = lambda *a: f("nvk_b200_linear_nvfp4_w4a16_residual", S, *a)
+    assert g(0, 0, 0, None, 0, 0, 1.0, 4, 0, 128) == 0                   # empty problem
+    assert g(P, P, P, None, P, P, 1.0, 0, 128, 128) == -1 and g(P, P, P, None, P, P, 1.0, 65, 128, 128) == -1
+    assert g(P, P, P, None, P, P, 1.0, 4, 128, 144) == -1                # K % 32
+    assert g(P, P, P, None, 0, P, 1.0, 4, 128, 128) == -2                # no residual
+    assert g(P, P, P + 2, None, P, P, 1.0, 4, 128, 128) == -2            # misaligned x
+    assert g(P, P, P, P + 4, P, P, 1.0, 4, 128, 128) == -2               # misaligned x2

@@ -209,6 +209,72 @@ def test_row_balance_is_chosen_for_a_one_and_a_half_wave_launch():
     check_against_oracle(auto, packed, sw, x, alpha, n, k, cpu_backend=False)
 
 
+def run_residual(packed, sw, x_bits, resid_bits, alpha, m, n, k, up_bits=None, in_place=False):
+    d = [U.dev(packed), U.dev(sw), U.dev(x_bits)]
+    du = U.dev(up_bits) if up_bits is not None else None
+    y = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    if in_place:
+        y[:m * n] = U.dev(resid_bits).view(torch.int16).reshape(-1)
+        r_ptr = y.data_ptr()
+    else:
+        dr = U.dev(resid_bits)
+        r_ptr = dr.data_ptr()
+    rc = U.ffi.call("nvk_b200_linear_nvfp4_w4a16_residual", U.stream(), d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(),
+                    du.data_ptr() if du is not None else None, r_ptr, y.data_ptr(), float(alpha), m, n, k)
+    assert rc == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[m * n:] == 0x7FC0)
+    return out[:m * n].reshape(m, n)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("n,k", [(384, 768), (200, 2304), (2048, 256)])
+def test_residual_epilogue_matches_the_oracle(m, n, k):
+    """y = bf16(residual + alpha * x W^T), one rounding: against the f64 statement of the product plus
+    the residual, with the linear's bound (the floor of the denominator is the rms of the expected
+    output); updating the residual in place gives the same bits as writing elsewhere."""
+    U.require_gpu()
+    rng = np.random.default_rng(m + n + k)
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    resid = U.gauss_bf16(rng, (m, n), 2.0)
+    got = run_residual(packed, sw, x, resid, alpha, m, n, k)
+    want = ref.linear_w4a16_f64(packed, sw, x, alpha, n, k) + ref.bf16_to_f32(resid).astype(np.float64)
+    assert U.rel_err_floor(ref.bf16_to_f32(got), want) < TOL_F64
+    assert np.array_equal(run_residual(packed, sw, x, resid, alpha, m, n, k, in_place=True), got)
+    # a zero residual leaves the plain linear, bit for bit (fma(v, alpha, 0) == v * alpha)
+    zero = np.zeros((m, n), np.uint16)
+    assert np.array_equal(run_residual(packed, sw, x, zero, alpha, m, n, k), run_linear(packed, sw, x, alpha, m, n, k))
+
+
+@pytest.mark.parametrize("m", [1, 5, 20])
+def test_mlp_tail_in_one_launch(m):
+    """SiLU(gate) * up prologue + down projection + residual: equals the prologue linear followed by an
+    addition in f64 within the bound, and Nvfp4Mlp.forward_residual uses it."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(40 + m)
+    hidden, inter = 256, 640
+    wts = [U.make_weight(rng, n, k)[:3] for (n, k) in ((inter, hidden), (inter, hidden), (hidden, inter))]
+    lins = [sp.Nvfp4Linear.new_nvfp4(U.dev(p), U.dev(s_), a, k, n)
+            for (p, s_, a), (n, k) in zip(wts, ((inter, hidden), (inter, hidden), (hidden, inter)))]
+    mlp = sp.Nvfp4Mlp(*lins)
+    x = U.gauss_bf16(rng, (m, hidden))
+    resid = U.gauss_bf16(rng, (m, hidden), 1.5)
+    xt, rt = U.dev(x).view(torch.bfloat16), U.dev(resid).view(torch.bfloat16)
+    y_plain = U.host_u16(mlp(xt))
+    y_res = U.host_u16(mlp.forward_residual(xt, rt))
+    want = ref.bf16_to_f32(y_plain).astype(np.float64) + ref.bf16_to_f32(resid).astype(np.float64)
+    # y_plain is itself rounded to bf16: allow that rounding on top of the fused result's own
+    assert U.rel_err_floor(ref.bf16_to_f32(y_res), want) < 1.2e-2
+    gate, up = U.gauss_bf16(rng, (m, inter)), U.gauss_bf16(rng, (m, inter))
+    got = run_residual(wts[2][0], wts[2][1], gate, resid, wts[2][2], m, hidden, inter, up_bits=up)
+    act = ref.f32_to_bf16(ref.silu_mul(gate, up, round_bf16=True))
+    want2 = ref.linear_w4a16_f64(wts[2][0], wts[2][1], act, wts[2][2], hidden, inter) + ref.bf16_to_f32(resid).astype(np.float64)
+    assert U.rel_err_floor(ref.bf16_to_f32(got), want2) < 2e-2
+
+
 def test_multi_phase_activation_staging():
     """K large enough at M=64 that the activations are staged in several phases, with magnitudes
     that change by 2^40 along K so the per-phase power-of-two rescale is exercised."""
