@@ -104,6 +104,29 @@ int nvk_b200_linear_nvfp4_w4a16_residual(void* stream, const uint8_t* wq, const 
                                          const uint16_t* x2, const uint16_t* residual, uint16_t* y, float alpha, int M,
                                          int N, int K);
 
+/* The same for one row (M = 1), also leaving 1/rms of the new row for the RMSNorm that follows:
+ * rstd_pack[0] = rsqrt(mean(y^2) + eps) over the N rounded outputs.  rstd_pack: three floats in device
+ * memory {rstd, running sum of squares, arrival count}; the last two zero before the first launch, and
+ * returned to zero by every launch.  Partial sums meet through float atomics in arrival order: the last
+ * bits of rstd may differ from run to run, as in the reference's int8 form
+ * (rust/crates/nv-kernels/include/nv_kernels.h:652-678).  -2 for a null rstd_pack. */
+int nvk_b200_linear_nvfp4_w4a16_residual_rstd_emit(void* stream, const uint8_t* wq, const uint8_t* sc,
+                                                   const uint16_t* x, const uint16_t* x2, const uint16_t* residual,
+                                                   uint16_t* y, float alpha, float* rstd_pack, float eps, int N, int K);
+
+/* No counterpart in the reference with this signature (its fused norms feed the quantizing routes): the
+ * W4A16 linear with an RMSNorm in front, y = bf16(alpha * sum_k W[n, k] a[m, k]) with
+ * a[m, k] = bf16(x[m, k] * rstd[m] * norm_weight[k]), rstd[m] = rsqrt(mean_k x[m, k]^2 + eps), for one or
+ * two matrices sharing x (wq_b, sc_b, y_b all null: one).  Bit-identical to nv_kernels_rmsnorm_bf16
+ * followed by the plain linear.  rstd null: every CTA sums its rows' squares itself, M <= 8; rstd given
+ * (one f32 per row, e.g. the first float of a rstd_pack): M <= 64.  0 for an empty problem; -1 for M
+ * outside that range, K % 32 != 0 or a half-given second matrix; -2 for a null or not 16-byte aligned
+ * operand. */
+int nvk_b200_linear_nvfp4_w4a16_normed(void* stream, const uint8_t* wq_a, const uint8_t* sc_a, const uint8_t* wq_b,
+                                       const uint8_t* sc_b, const uint16_t* x, const uint16_t* norm_weight,
+                                       const float* rstd, float eps, uint16_t* y_a, uint16_t* y_b, float alpha_a,
+                                       float alpha_b, int M, int N, int K);
+
 /* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
  * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 16, 32,
  * 64, 128} fixes the rows one CTA owns (M <= 16 only). */

@@ -29,6 +29,8 @@ SIGNATURES = {
     "nvk_b200_stack_build": [_vp, _i, _i, _vp, C.c_size_t, _vp],
     "nvk_b200_stack_run": [_vp, _vp, _i, _i, _i, _i, _vp],
     "nvk_b200_linear_nvfp4_w4a16_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i],
+    "nvk_b200_linear_nvfp4_w4a16_residual_rstd_emit": [_vp] * 7 + [_f, _vp, _f, _i, _i],
+    "nvk_b200_linear_nvfp4_w4a16_normed": [_vp] * 8 + [_f, _vp, _vp, _f, _f, _i, _i, _i],
     "nvk_b200_set_tuning": [_i, _i],
     "nvk_b200_set_row_balance": [_i],
     "nvk_b200_row_balance_grid": [_i, C.c_size_t, _i],

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const QuantParams
             const uint16_t b = p.x[(size_t)row * p.K + i];
             row_s[i] = b;
             const float f = nvk::bf16_bits_to_f32(b);
-            ss += f * f;
+            ss = fmaf(f, f, ss);   // an explicit fma: every copy of this sum rounds alike
         }
     }
     ss = nvk::warp_sum(ss);
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bf16_kernel(const uint16_t* __res
     float ss = 0.f;
     for (size_t i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float f = nvk::bf16_bits_to_f32(xr[i]);
-        ss += f * f;
+        ss = fmaf(f, f, ss);   // an explicit fma: every copy of this sum rounds alike
     }
     ss = nvk::warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;

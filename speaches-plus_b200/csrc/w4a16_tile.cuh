@@ -89,8 +89,8 @@ __device__ __forceinline__ void silu_mul_bf16x8(uint32_t (&ws)[4], const uint4 u
 struct TileView {
     const uint8_t* wq;
     const uint8_t* sc;
-    const uint16_t* x;       // activation rows (gate when PRO == 1; packed e2m1 rows when PRO >= 2)
-    const uint16_t* x2;      // up rows when PRO == 1; the activation's ue4m3 scales when PRO >= 2
+    const uint16_t* x;       // activation rows (gate when PRO == 1; packed e2m1 rows when PRO is 2 or 3)
+    const uint16_t* x2;      // up rows when PRO == 1; the activation's ue4m3 scales when PRO is 2 or 3
     const int32_t* xrows;    // optional gather: token m reads row xrows[xrow0 + m]; else row xrow0 + m
     int x_rows;              // rows of x a gathered index may name (others read as zeros and are reported)
     int* status;             // optional word, bit 1 set when a gathered row index was out of range
@@ -117,6 +117,10 @@ struct TileView {
     // Used only when PRO == 5 (the int8 scale is derived here from partial maxima):
     const float* absmax_partials;
     int n_partials;
+    // Used only when PRO == 6 (an RMSNorm is applied while the activations are staged):
+    const uint16_t* norm_w;     // [K] bf16
+    const float* rstd_in;       // [rows] 1/rms per activation row, or null: computed here from the row
+    float norm_eps;
 };
 
 // The last CTA of a launch to arrive turns the launch's sum of squared outputs into the next
@@ -147,7 +151,9 @@ struct LaunchHooks {
 // PRO: 0 = bf16 activations; 1 = bf16(SiLU(x) * x2); 2 = an NVFP4 activation row whose scales are row 0
 // of a 128x4 swizzled tile; 3 = an NVFP4 activation row with a flat [K/16] scale array; 4 = int8
 // activation rows (their dequant scales are applied in the epilogue through row_scale); 5 = one bf16
-// activation row quantized to int8 here, scale = max(absmax_partials) / 127.
+// activation row quantized to int8 here, scale = max(absmax_partials) / 127; 6 = bf16 rows through an
+// RMSNorm, a = bf16(x * rstd * norm_w) with rstd = rsqrt(mean(x^2) + eps) summed in the order of the
+// stand-alone norm kernel (256 threads striding the row, lanes, then warps) or taken from rstd_in.
 // EPI: 0 = y = bf16(alpha * sum); 1 = y = bf16(fma(sum, alpha * row_scale, residual)), optionally
 // followed by emit_rstd over the launch's outputs.
 // XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
@@ -166,6 +172,8 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     __shared__ float s_rescale[MT];   // 2^(pw_old - pw_new) at a phase boundary
     __shared__ float s_q8[2];         // PRO == 5: the int8 row's dequant scale and its reciprocal
     __shared__ float s_ssq[32];       // EPI == 1: per-warp sums of squared outputs
+    __shared__ float s_rstd[MT];      // PRO == 6: 1/rms of each activation row
+    __shared__ float s_red8[8];       // PRO == 6: per-warp sums of squares
 
     cg::cluster_group cluster = cg::this_cluster();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -340,6 +348,33 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
         __syncthreads();
     }
 
+    if (PRO == 6) {
+        static_assert(PRO != 6 || THREADS == 256, "the row sum follows the 256-thread norm kernel");
+        for (int m = 0; m < M; ++m) {
+            float rs;
+            if (t.rstd_in != nullptr) {
+                rs = t.rstd_in[t.xrow0 + m];
+            } else {
+                const uint16_t* xr = t.x + (size_t)(t.xrow0 + m) * K;
+                float ss = 0.f;
+                for (int i = threadIdx.x; i < K; i += THREADS) {
+                    const float f = nvk::bf16_bits_to_f32(xr[i]);
+                    ss = fmaf(f, f, ss);   // an explicit fma: every copy of this sum rounds alike
+                }
+                ss = nvk::warp_sum(ss);
+                if (lane == 0) s_red8[warp] = ss;
+                __syncthreads();
+                float tot = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) tot += s_red8[i];
+                rs = rsqrtf(tot / (float)K + t.norm_eps);
+                __syncthreads();   // s_red8 is rewritten for the next row
+            }
+            if (threadIdx.x == 0) s_rstd[m] = rs;
+        }
+        __syncthreads();
+    }
+
     for (int p0 = sc_begin; p0 < sc_end; p0 += p.ph) {
         const int pend = min(sc_end, p0 + p.ph);
         const int nsp = pend - p0;
@@ -393,7 +428,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
                 }
                 return true;
             }
-            if (PRO >= 2) {
+            if (PRO == 2 || PRO == 3) {
                 // NVFP4 activation row: eight e2m1 values times their block's ue4m3 scale.  The product
                 // has at most six significand bits, so it is exact as bf16 and the W4A4 contraction
                 // sum (w*ws)*(a*as) is this tile's ordinary W4A16 sum over an exactly dequantized row.
@@ -415,6 +450,17 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             const size_t xr0 = (size_t)xrow * K + k;
             const uint4 v = HK::load_x(t.x + xr0);
             ws[0] = v.x; ws[1] = v.y; ws[2] = v.z; ws[3] = v.w;
+            if (PRO == 6) {
+                const uint4 nw = *reinterpret_cast<const uint4*>(t.norm_w + k);
+                const uint32_t nws[4] = {nw.x, nw.y, nw.z, nw.w};
+                const float rs = s_rstd[m];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float lo = nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu) * rs * nvk::bf16_bits_to_f32(nws[i] & 0xFFFFu);
+                    const float hi = nvk::bf16_bits_to_f32(ws[i] >> 16) * rs * nvk::bf16_bits_to_f32(nws[i] >> 16);
+                    ws[i] = (uint32_t)nvk::f32_to_bf16_bits(lo) | ((uint32_t)nvk::f32_to_bf16_bits(hi) << 16);
+                }
+            }
             if (PRO == 1) silu_mul_bf16x8(ws, HK::load_x(t.x2 + xr0));
             return true;
         };

@@ -293,11 +293,18 @@ class Nvfp4Linear:
         if x2.shape[0] > MAX_DECODE_M:
             raise ValueError(f"forward_prenorm_decode: {x2.shape[0]} rows; the decode route takes up to {MAX_DECODE_M}")
         assert x2.is_cuda and x2.dtype == torch.bfloat16 and norm_weight.dtype == torch.bfloat16
-        xn = torch.empty_like(x2)
-        _ffi.check("nv_kernels_rmsnorm_bf16", _stream(), x2.data_ptr(), norm_weight.data_ptr(), xn.data_ptr(),
-                   x2.shape[0], self.in_features, float(eps))
         y = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x2.device)
-        self.forward_into(xn, y)
+        if x2.shape[0] <= 8 and self.in_features % 32 == 0:
+            # a few rows: the norm is applied while the linear stages its activations (same bits, one launch)
+            _ffi.check("nvk_b200_linear_nvfp4_w4a16_normed", _stream(), self.weight_u8.data_ptr(),
+                       self.weight_scales.data_ptr(), None, None, x2.data_ptr(), norm_weight.data_ptr(), None,
+                       float(eps), y.data_ptr(), None, self.alpha_w4a16, 0.0, x2.shape[0], self.out_features,
+                       self.in_features)
+        else:
+            xn = torch.empty_like(x2)
+            _ffi.check("nv_kernels_rmsnorm_bf16", _stream(), x2.data_ptr(), norm_weight.data_ptr(), xn.data_ptr(),
+                       x2.shape[0], self.in_features, float(eps))
+            self.forward_into(xn, y)
         if self.bias is not None:
             y += self.bias
         return y.reshape(*lead, self.out_features)

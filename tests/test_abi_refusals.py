@@ -189,3 +189,18 @@ def test_residual_linear_refusals():
     assert g(P, P, P, None, 0, P, 1.0, 4, 128, 128) == -2                # no residual
     assert g(P, P, P + 2, None, P, P, 1.0, 4, 128, 128) == -2            # misaligned x
     assert g(P, P, P, P + 4, P, P, 1.0, 4, 128, 128) == -2               # misaligned x2
+
+
+def test_normed_linear_and_rstd_emit_refusals():
+    g = lambda *a: f("nvk_b200_linear_nvfp4_w4a16_normed", S, *a)
+    assert g(0, 0, None, None, 0, 0, None, 1e-6, 0, None, 1.0, 0.0, 1, 0, 128) == 0
+    assert g(P, P, None, None, P, P, None, 1e-6, P, None, 1.0, 0.0, 9, 128, 128) == -1     # no rstd: M <= 8
+    assert g(P, P, None, None, P, P, P, 1e-6, P, None, 1.0, 0.0, 65, 128, 128) == -1       # with rstd: M <= 64
+    assert g(P, P, None, None, P, P, None, 1e-6, P, None, 1.0, 0.0, 1, 128, 144) == -1     # K % 32
+    assert g(P, P, P, None, P, P, None, 1e-6, P, None, 1.0, 0.0, 1, 128, 128) == -1        # half-given second matrix
+    assert g(P, P, None, None, P, 0, None, 1e-6, P, None, 1.0, 0.0, 1, 128, 128) == -2     # no norm weight
+    assert g(P, P, None, None, P, P + 2, None, 1e-6, P, None, 1.0, 0.0, 1, 128, 128) == -2
+    e = lambda *a: f("nvk_b200_linear_nvfp4_w4a16_residual_rstd_emit", S, *a)
+    assert e(P, P, P, None, P, P, 1.0, 0, 1e-6, 128, 128) == -2                             # no pack
+    assert e(P, P, P, None, P, P, 1.0, P, 1e-6, 0, 128) == 0
+    assert e(P, P, P, None, 0, P, 1.0, P, 1e-6, 128, 128) == -2

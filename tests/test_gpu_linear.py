@@ -275,6 +275,111 @@ def test_mlp_tail_in_one_launch(m):
     assert U.rel_err_floor(ref.bf16_to_f32(got), want2) < 2e-2
 
 
+def run_normed(wa, x_bits, norm_bits, eps, m, n, k, wb=None, rstd=None):
+    d = [U.dev(wa[0]), U.dev(wa[1]), U.dev(x_bits), U.dev(norm_bits)]
+    db = [U.dev(wb[0]), U.dev(wb[1])] if wb is not None else None
+    dr = U.dev(np.asarray(rstd, np.float32)) if rstd is not None else None
+    y = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    yb = torch.full((m * n + 64,), 0x7FC0, dtype=torch.int16, device="cuda") if db else None
+    rc = U.ffi.call("nvk_b200_linear_nvfp4_w4a16_normed", U.stream(), d[0].data_ptr(), d[1].data_ptr(),
+                    db[0].data_ptr() if db else None, db[1].data_ptr() if db else None, d[2].data_ptr(), d[3].data_ptr(),
+                    dr.data_ptr() if dr is not None else None, float(eps), y.data_ptr(), yb.data_ptr() if db else None,
+                    float(wa[2]), float(wb[2]) if wb is not None else 0.0, m, n, k)
+    assert rc == 0
+    torch.cuda.synchronize()
+    out = U.host_u16(y)
+    assert np.all(out[m * n:] == 0x7FC0)
+    if db:
+        outb = U.host_u16(yb)
+        assert np.all(outb[m * n:] == 0x7FC0)
+        return out[:m * n].reshape(m, n), outb[:m * n].reshape(m, n)
+    return out[:m * n].reshape(m, n)
+
+
+def device_rmsnorm(x_bits, norm_bits, eps):
+    m, k = x_bits.shape
+    dx, dw = U.dev(x_bits), U.dev(norm_bits)
+    out = torch.zeros((m, k), dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_rmsnorm_bf16", U.stream(), dx.data_ptr(), dw.data_ptr(), out.data_ptr(), m, k,
+                      float(eps)) == 0
+    torch.cuda.synchronize()
+    return U.host_u16(out)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("n,k,dual", [(384, 1024, False), (256, 2560, True), (130, 4352, False)])
+def test_norm_in_the_prologue_equals_norm_then_linear_bitwise(m, n, k, dual):
+    """RMSNorm applied while the activations are staged == nv_kernels_rmsnorm_bf16 followed by the plain
+    linear, bit for bit (one and two matrices, K split over a cluster at the small N), and both give the
+    oracle's answer for the normed rows."""
+    U.require_gpu()
+    rng = np.random.default_rng(m + n + k)
+    wa = U.make_weight(rng, n, k)[:3]
+    wb = U.make_weight(rng, n, k)[:3] if dual else None
+    x = U.gauss_bf16(rng, (m, k), 3.0)
+    nw = U.gauss_bf16(rng, (k,), 1.0)
+    eps = 1e-6
+    normed = device_rmsnorm(x, nw, eps)
+    if dual:
+        fa, fb = run_normed(wa, x, nw, eps, m, n, k, wb)
+        pa, pb = run_linear(wa[0], wa[1], normed, wa[2], m, n, k, wb[0], wb[1], wb[2])
+        assert np.array_equal(fa, pa) and np.array_equal(fb, pb)
+    else:
+        fa = run_normed(wa, x, nw, eps, m, n, k)
+        assert np.array_equal(fa, run_linear(wa[0], wa[1], normed, wa[2], m, n, k))
+    xf = ref.bf16_to_f32(x)
+    rstd = (1.0 / np.sqrt((xf.astype(np.float64) ** 2).mean(1) + eps)).astype(np.float32)
+    want_rows = ref.f32_to_bf16((xf * rstd[:, None]) * ref.bf16_to_f32(nw)[None, :])
+    want = ref.linear_w4a16_f64(wa[0], wa[1], want_rows, wa[2], n, k)
+    assert U.rel_err_floor(ref.bf16_to_f32(fa), want) < 2e-2     # a normed value may round to a neighbouring bf16
+
+
+def test_norm_with_rstd_handed_in_and_the_emit_consume_chain():
+    """(i) rstd given per row, 20 rows: the oracle's answer.  (ii) One row through a layer boundary: the
+    residual-update launch leaves rstd of the new hidden row, the normed linear of the next layer takes
+    it; the result equals norm + linear on that row up to the last bits of rstd."""
+    U.require_gpu()
+    rng = np.random.default_rng(91)
+    n, k, eps = 256, 768, 1e-5
+    wa = U.make_weight(rng, n, k)[:3]
+    nw = U.gauss_bf16(rng, (k,), 1.0)
+    x = U.gauss_bf16(rng, (20, k), 2.0)
+    xf = ref.bf16_to_f32(x)
+    rstd = (1.0 / np.sqrt((xf.astype(np.float64) ** 2).mean(1) + eps)).astype(np.float32)
+    got = run_normed(wa, x, nw, eps, 20, n, k, rstd=rstd)
+    rows = ref.f32_to_bf16((xf * rstd[:, None]) * ref.bf16_to_f32(nw)[None, :])
+    assert U.rel_err_floor(ref.bf16_to_f32(got), ref.linear_w4a16_f64(wa[0], wa[1], rows, wa[2], n, k)) < 2e-2
+
+    # (ii) hidden = k: down projection [k, inter] with residual + rstd emit, then the normed linear [n, k]
+    inter = 512
+    wd = U.make_weight(rng, k, inter)[:3]
+    act = U.gauss_bf16(rng, (1, inter))
+    resid = U.gauss_bf16(rng, (1, k), 1.5)
+    d = [U.dev(wd[0]), U.dev(wd[1]), U.dev(act), U.dev(resid)]
+    h = torch.full((k + 64,), 0x7FC0, dtype=torch.int16, device="cuda")
+    pack = torch.zeros(3, dtype=torch.float32, device="cuda")
+    for _ in range(2):   # the second launch finds the pack's sum and count back at zero
+        assert U.ffi.call("nvk_b200_linear_nvfp4_w4a16_residual_rstd_emit", U.stream(), d[0].data_ptr(), d[1].data_ptr(),
+                          d[2].data_ptr(), None, d[3].data_ptr(), h.data_ptr(), float(wd[2]), pack.data_ptr(), eps,
+                          k, inter) == 0
+    torch.cuda.synchronize()
+    hb = U.host_u16(h)
+    assert np.all(hb[k:] == 0x7FC0)
+    hidden = hb[:k].reshape(1, k)
+    pk = pack.cpu().numpy()
+    hf = ref.bf16_to_f32(hidden).astype(np.float64)
+    assert abs(float(pk[0]) - 1.0 / np.sqrt((hf ** 2).mean() + eps)) < 1e-5 * float(pk[0])
+    assert pk[1] == 0.0 and pack.view(torch.int32).cpu().numpy()[2] == 0
+    dn = [U.dev(wa[0]), U.dev(wa[1]), U.dev(hidden), U.dev(nw)]
+    y = torch.zeros(n, dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nvk_b200_linear_nvfp4_w4a16_normed", U.stream(), dn[0].data_ptr(), dn[1].data_ptr(), None, None,
+                      dn[2].data_ptr(), dn[3].data_ptr(), pack.data_ptr(), eps, y.data_ptr(), None, float(wa[2]), 0.0,
+                      1, n, k) == 0
+    torch.cuda.synchronize()
+    two_step = run_linear(wa[0], wa[1], device_rmsnorm(hidden, nw, eps), wa[2], 1, n, k)
+    assert U.rel_err_floor(ref.bf16_to_f32(U.host_u16(y)).reshape(1, n), ref.bf16_to_f32(two_step).astype(np.float64)) < 1e-2
+
+
 def test_multi_phase_activation_staging():
     """K large enough at M=64 that the activations are staged in several phases, with magnitudes
     that change by 2^40 along K so the per-phase power-of-two rescale is exercised."""
