@@ -605,6 +605,57 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, p
            "tok_s": round(batch / (ms * 1e-3), 1), "bytes_per_step_per_gpu": bytes_rank,
            "gbs_per_gpu": round(bytes_rank / (ms * 1e-3) / 1e9, 1),
            "launches_per_step": layers * 4 + 1, "collectives_per_step": (2 * layers + 1) if world > 1 else 0}
+
+    if world == 1 and batch == 1:
+        # The same stack with both RMSNorms and both residual adds of every layer inside its four launches:
+        # normed QKV -> o_proj + residual (+ 1/rms for the next norm) -> normed gate/up -> SiLU*up + down +
+        # residual (+ 1/rms).  Same weights, same launch count, a little more arithmetic per launch.
+        s_ = lambda: torch.cuda.current_stream().cuda_stream
+        hid = x0.clone()
+        pack = torch.zeros(3, dtype=torch.float32, device=dev)
+        nw = torch.ones((2 * layers, H), **bf)
+        eps = 1e-6
+
+        def normed(lin_a, lin_b, x, w_row, rstd, y_a, y_b):
+            ffi.check("nvk_b200_linear_nvfp4_w4a16_normed", s_(), lin_a.weight_u8.data_ptr(),
+                      lin_a.weight_scales.data_ptr(), lin_b.weight_u8.data_ptr() if lin_b else None,
+                      lin_b.weight_scales.data_ptr() if lin_b else None, x.data_ptr(), w_row.data_ptr(),
+                      rstd.data_ptr() if rstd is not None else None, eps, y_a.data_ptr(),
+                      y_b.data_ptr() if y_b is not None else None, lin_a.alpha_w4a16,
+                      lin_b.alpha_w4a16 if lin_b else 0.0, 1, lin_a.out_features, lin_a.in_features)
+
+        def residual_emit(lin, x, x2):
+            ffi.check("nvk_b200_linear_nvfp4_w4a16_residual_rstd_emit", s_(), lin.weight_u8.data_ptr(),
+                      lin.weight_scales.data_ptr(), x.data_ptr(), x2.data_ptr() if x2 is not None else None,
+                      hid.data_ptr(), hid.data_ptr(), lin.alpha_w4a16, pack.data_ptr(), eps, lin.out_features,
+                      lin.in_features)
+
+        def fused_step():
+            for li, (w_qkv, w_o, w_g, w_u, w_d) in enumerate(stack):
+                normed(w_qkv, None, hid, nw[2 * li], pack if li > 0 else None, qkv, None)
+                residual_emit(w_o, qkv[:, :q_l], None)
+                normed(w_g, w_u, hid, nw[2 * li + 1], pack, gate, up)
+                residual_emit(w_d, gate, up)
+            lm_head.forward_into(hid, logits_l)
+
+        with torch.cuda.stream(stream):
+            fused_step()
+            stream.synchronize()
+            fgraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(fgraph, stream=stream):
+                fused_step()
+            for _ in range(2):
+                fgraph.replay()
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(replays):
+                fgraph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            fms = e0.elapsed_time(e1) / replays
+            del fgraph
+        out["with_norms_and_residuals_fused"] = {"ms_per_step": round(fms, 4), "tok_s": round(1.0 / (fms * 1e-3), 1),
+                                                 "launches_per_step": layers * 4 + 1}
     del graph, stack, lm_head
     torch.cuda.synchronize()
     torch.cuda.empty_cache()

@@ -47,6 +47,8 @@ def test_b200_arm_runs_on_the_emulator_and_prints_the_contract():
     assert j["gpu_launches"] == 3 * rps * 2 * 3        # steps x passes x copies x shapes
     assert "workload" in j["config"] and "model" not in j["config"]
     assert [d["batch"] for d in j["decode_stack"]] == [1, 16] and [d["batch"] for d in j["moe_decode"]] == [1, 16, 64]
+    fused = j["decode_stack"][0]["with_norms_and_residuals_fused"]
+    assert fused["launches_per_step"] == j["decode_stack"][0]["launches_per_step"] and fused["ms_per_step"] > 0
 
 
 def test_both_arms_print_the_same_config_block():
