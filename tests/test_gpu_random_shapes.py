@@ -252,3 +252,36 @@ def test_random_w4a4_gemv_shapes(n, k, seed):
     ulp = U.bf16_ulp_diff(out[:n], want)
     absd = np.abs(ref.bf16_to_f32(out[:n]) - ref.bf16_to_f32(want))
     assert np.all((ulp <= 2) | (absd <= 1e-3))
+
+
+def _fused_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.choice([1, 2, 5, 8, 13, 40, 64])), int(rng.integers(1, 600)), 32 * int(rng.integers(1, 70)),
+             int(rng.integers(0, 2)), seed * 1000 + i) for i in range(count)]
+
+
+@pytest.mark.parametrize("m,n,k,silu,seed", _fused_cases(18, 14))
+def test_random_residual_and_normed_shapes(m, n, k, silu, seed):
+    """The residual-update linear (with and without the SiLU prologue) on drawn shapes against the f64
+    oracle, and -- for up to 8 rows -- the norm-in-prologue linear against norm kernel + plain linear,
+    bit for bit."""
+    U.require_gpu()
+    from tests.test_gpu_linear import TOL_F64, device_rmsnorm, run_normed, run_residual
+    rng = np.random.default_rng(seed)
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    resid = U.gauss_bf16(rng, (m, n), 2.0)
+    if silu:
+        up = U.gauss_bf16(rng, (m, k))
+        got = run_residual(packed, sw, x, resid, alpha, m, n, k, up_bits=up)
+        act = ref.f32_to_bf16(ref.silu_mul(x, up, round_bf16=True))
+        want = ref.linear_w4a16_f64(packed, sw, act, alpha, n, k) + ref.bf16_to_f32(resid).astype(np.float64)
+        assert U.rel_err_floor(ref.bf16_to_f32(got), want) < 2e-2
+    else:
+        got = run_residual(packed, sw, x, resid, alpha, m, n, k)
+        want = ref.linear_w4a16_f64(packed, sw, x, alpha, n, k) + ref.bf16_to_f32(resid).astype(np.float64)
+        assert U.rel_err_floor(ref.bf16_to_f32(got), want) < TOL_F64
+    if m <= 8:
+        nw = U.gauss_bf16(rng, (k,), 1.0)
+        fused = run_normed((packed, sw, alpha), x, nw, 1e-6, m, n, k)
+        assert np.array_equal(fused, run_linear(packed, sw, device_rmsnorm(x, nw, 1e-6), alpha, m, n, k))
