@@ -236,6 +236,22 @@ class Nvfp4Linear:
                        residual[r0:].data_ptr(), y[r0:].data_ptr(), self.alpha_w4a16, mm, self.out_features,
                        self.in_features)
 
+    def forward_nvfp4_gemv_m1(self, x: torch.Tensor) -> torch.Tensor:
+        """One row through the M = 1 GEMV whatever else is configured (no bias, no adapter): what a
+        draft-only lm_head asks for (linear.rs:1420-1442)."""
+        lead = 1
+        for d in x.shape[:-1]:
+            lead *= d
+        if lead != 1:
+            raise ValueError(f"forward_nvfp4_gemv_m1: draft lm_head serves one row per step, got leading {lead}")
+        if x.shape[-1] != self.in_features:
+            raise ValueError(f"forward_nvfp4_gemv_m1: input last dim {x.shape[-1]} != in_features {self.in_features}")
+        x2 = x.reshape(1, self.in_features).contiguous()
+        y = torch.empty((1, self.out_features), dtype=torch.bfloat16, device=x.device)
+        _ffi.check("nv_kernels_nvfp4_gemv_bf16act", _stream(), self.weight_u8.data_ptr(), self.weight_scales.data_ptr(),
+                   x2.data_ptr(), y.data_ptr(), self.alpha_w4a16, self.out_features, self.in_features)
+        return y.reshape(*x.shape[:-1], self.out_features)
+
     def route_for(self, m: int, allow_prefill: bool = True) -> str:
         """Which kernels M rows take: "gemv" (M = 1), "decode" (row chunks of up to 64 on the W4A16
         kernel) or "prefill" (the FP4 x FP4 GEMM of the prefill library).  The last is chosen only in
@@ -448,18 +464,33 @@ class Bf16Linear:
         self.forward_into(x2, y)
         return y.reshape(*x.shape[:-1], self.out_features)
 
-    def forward_into(self, x2: torch.Tensor, y: torch.Tensor) -> None:
-        """x2 [M, in] bf16 contiguous -> y [M, out] (contiguous), allocating nothing."""
+    def forward_into(self, x2: torch.Tensor, y: torch.Tensor, row_off: int = 0, rows: int | None = None) -> None:
+        """x2 [M, in] bf16 contiguous -> y [M, rows] (contiguous), allocating nothing; `rows` weight rows
+        from `row_off` (default: all of them)."""
         s = _stream()
         m = x2.shape[0]
+        rows = self.out_features if rows is None else rows
+        w = self.weight.data_ptr() + 2 * row_off * self.in_features
         if m == 1:
-            _ffi.check("nv_kernels_gemv_bf16", s, self.weight.data_ptr(), x2.data_ptr(), y.data_ptr(), self.out_features,
-                       self.in_features)
+            _ffi.check("nv_kernels_gemv_bf16", s, w, x2.data_ptr(), y.data_ptr(), rows, self.in_features)
             return
         for r0 in range(0, m, MAX_DECODE_M):
             mm = min(MAX_DECODE_M, m - r0)
-            _ffi.check("nvk_b200_linear_bf16", s, self.weight.data_ptr(), x2[r0:].data_ptr(), y[r0:].data_ptr(), mm,
-                       self.out_features, self.in_features)
+            _ffi.check("nvk_b200_linear_bf16", s, w, x2[r0:].data_ptr(), y[r0:].data_ptr(), mm, rows, self.in_features)
+
+    def forward_rows(self, x: torch.Tensor, row_off: int, rows: int) -> torch.Tensor:
+        """The product with weight rows [row_off, row_off + rows) only -- a slice of a vocabulary, say
+        (rust/crates/nv-layers/src/linear.rs:883-913)."""
+        if row_off < 0 or rows < 0 or row_off + rows > self.out_features:
+            raise ValueError(f"forward_rows: rows {row_off}..{row_off + rows} out of range (out_features "
+                             f"{self.out_features})")
+        if x.shape[-1] != self.in_features:
+            raise ValueError(f"forward_rows: input last dim {x.shape[-1]} != in_features {self.in_features}")
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        y = torch.empty((x2.shape[0], rows), dtype=torch.bfloat16, device=x.device)
+        if rows:
+            self.forward_into(x2, y, row_off, rows)
+        return y.reshape(*x.shape[:-1], rows)
 
     __call__ = forward
 

@@ -380,6 +380,32 @@ def test_norm_with_rstd_handed_in_and_the_emit_consume_chain():
     assert U.rel_err_floor(ref.bf16_to_f32(U.host_u16(y)).reshape(1, n), ref.bf16_to_f32(two_step).astype(np.float64)) < 1e-2
 
 
+@pytest.mark.parametrize("m", [1, 5])
+def test_bf16_forward_rows_and_the_unconditional_m1_gemv(m):
+    """rust/crates/nv-layers/src/linear.rs:883-913,1420-1442: a slice of the weight's rows gives exactly the
+    corresponding columns of the full product; the M = 1 NVFP4 entry refuses more than one row."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(60 + m)
+    n, k = 1000, 512
+    w = U.gauss_bf16(rng, (n, k), 0.05)
+    lin = sp.Bf16Linear(U.dev(w).view(torch.bfloat16))
+    xt = U.dev(U.gauss_bf16(rng, (m, k))).view(torch.bfloat16)
+    full = U.host_u16(lin(xt))
+    part = U.host_u16(lin.forward_rows(xt, 128, 300))
+    assert part.shape == (m, 300) and np.array_equal(part, full[:, 128:428])
+    assert lin.forward_rows(xt, 990, 0).shape == (m, 0)
+    with pytest.raises(ValueError, match="out of range"):
+        lin.forward_rows(xt, 900, 101)
+    packed, sw, alpha, _ = U.make_weight(rng, 256, k)
+    q = sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, 256)
+    if m == 1:
+        assert np.array_equal(U.host_u16(q.forward_nvfp4_gemv_m1(xt)), U.host_u16(q(xt)))
+    else:
+        with pytest.raises(ValueError, match="one row per step"):
+            q.forward_nvfp4_gemv_m1(xt)
+
+
 def test_multi_phase_activation_staging():
     """K large enough at M=64 that the activations are staged in several phases, with magnitudes
     that change by 2^40 along K so the per-phase power-of-two rescale is exercised."""
