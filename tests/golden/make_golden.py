@@ -55,6 +55,31 @@ def build() -> dict:
     logits[5, 10] = logits[5, 70] = logits[5].max() + 1  # a tie at the top: the lower index wins
     ids, wts = ref.moe_route_topk(logits, 8)
     out.update(router_logits=logits, router_ids=ids, router_weights=wts)
+    # sigmoid router with a selection bias and a routed scaling (mode 1), top-4 of 40
+    lg1 = rng.standard_normal((5, 40)).astype(np.float32)
+    bias1 = (rng.standard_normal(40) * 0.1).astype(np.float32)
+    ids1, wts1 = ref.moe_route_topk(lg1, 4, bias=bias1, mode=1, norm_topk=True, routed_scaling=2.5)
+    out.update(router1_logits=lg1, router1_bias=bias1, router1_ids=ids1, router1_weights=wts1)
+    # stable slot sort of the first router's ids: offsets, sorted slot -> token, slot -> sorted position
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    inv = np.empty(flat.size, np.int32)
+    inv[order] = np.arange(flat.size, dtype=np.int32)
+    out.update(sort_offsets=np.concatenate([[0], np.cumsum(np.bincount(flat, minlength=128))]).astype(np.int32),
+               sort_perm_token=(order // ids.shape[1]).astype(np.int32), sort_inv_perm=inv)
+    # int8 activation rows (W4A8 route): exact integers and scales, the product with and without a residual
+    x8 = (rng.standard_normal((3, k)) * np.array([[0.3], [1.0], [4.0]])).astype(np.float32)
+    q8, s8 = ref.rowquant_i8(x8)
+    resid = ref.f32_to_bf16(rng.standard_normal((3, n)).astype(np.float32))
+    out.update(x8_f32=x8, x8_q=q8, x8_scales=s8, w4a8_residual_bf16=resid,
+               y_w4a8_f64=ref.linear_w4a8_f64(packed, sw, q8, s8, float(alpha), n, k),
+               y_w4a8_residual_f64=ref.linear_w4a8_f64(packed, sw, q8, s8, float(alpha), n, k, resid))
+    # residual RMSNorm: new residual (exact bits) and the normed row
+    hx = ref.f32_to_bf16(rng.standard_normal((2, 256)).astype(np.float32))
+    hres = ref.f32_to_bf16(rng.standard_normal((2, 256)).astype(np.float32) * 2)
+    hw = ref.f32_to_bf16((1.0 + 0.1 * rng.standard_normal(256)).astype(np.float32))
+    res_out, normed = ref.rmsnorm_residual(hx, hres, hw, 1e-6)
+    out.update(norm_x_bf16=hx, norm_res_bf16=hres, norm_w_bf16=hw, norm_res_out_bf16=res_out, norm_out_bf16=normed)
     return out
 
 

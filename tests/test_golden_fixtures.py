@@ -81,3 +81,56 @@ def test_cuda_path_matches_the_fixture(g):
     torch.cuda.synchronize()
     assert np.array_equal(ids.cpu().numpy(), g["router_ids"])
     assert np.allclose(wts.cpu().numpy(), g["router_weights"], rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_cuda_path_matches_the_fixture_routers_sort_w4a8_and_norm(g):
+    """The second half of the fixture: the sigmoid router, the stable slot sort, the W4A8 product on the
+    fixture's int8 rows (with and without a residual), and the residual RMSNorm."""
+    from tests import _util as U
+    from tests.test_gpu_w4a8 import TOL as W4A8_TOL, rel_quarter, w4a8
+    U.require_gpu()
+    n, k = g["w_packed"].shape[0], g["w_packed"].shape[1] * 2
+    # sigmoid router with bias and routed scaling
+    lg, bias = U.dev(g["router1_logits"]), U.dev(g["router1_bias"])
+    rows, E = g["router1_logits"].shape
+    top_k = g["router1_ids"].shape[1]
+    ids = torch.zeros((rows, top_k), dtype=torch.int32, device="cuda")
+    wts = torch.zeros((rows, top_k), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_route_topk", U.stream(), lg.data_ptr(), bias.data_ptr(), ids.data_ptr(),
+                      wts.data_ptr(), rows, E, top_k, 1, 0.0, 1, 2.5) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(ids.cpu().numpy(), g["router1_ids"])
+    assert np.allclose(wts.cpu().numpy(), g["router1_weights"], rtol=2e-6, atol=1e-7)
+    # stable slot sort of the first router's ids
+    r_ids = U.dev(g["router_ids"])
+    n_tok, kk = g["router_ids"].shape
+    perm = torch.zeros(n_tok * kk, dtype=torch.int32, device="cuda")
+    offs = torch.zeros(129, dtype=torch.int32, device="cuda")
+    inv = torch.zeros(n_tok * kk, dtype=torch.int32, device="cuda")
+    scr = torch.zeros(128, dtype=torch.int32, device="cuda")
+    assert U.ffi.call("nv_kernels_moe_permute", U.stream(), r_ids.data_ptr(), perm.data_ptr(), offs.data_ptr(),
+                      inv.data_ptr(), scr.data_ptr(), n_tok, kk, 128) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(offs.cpu().numpy(), g["sort_offsets"])
+    assert np.array_equal(perm.cpu().numpy(), g["sort_perm_token"])
+    assert np.array_equal(inv.cpu().numpy(), g["sort_inv_perm"])
+    # W4A8: the oracle's row quantizer reproduces the stored integers; the product on them
+    q, sc = ref.rowquant_i8(g["x8_f32"])
+    assert np.array_equal(q, g["x8_q"]) and np.array_equal(sc, g["x8_scales"])
+    wts_ = (g["w_packed"], g["w_scales_swizzled"], float(g["alpha"][0]))
+    y = w4a8("nv_kernels_gemv_nvfp4_w4a8_down_residual_mk", wts_, g["x8_q"], g["x8_scales"], 3, n, k)
+    assert rel_quarter(y, g["y_w4a8_f64"]) < W4A8_TOL
+    yr = w4a8("nv_kernels_gemv_nvfp4_w4a8_down_residual_mk", wts_, g["x8_q"], g["x8_scales"], 3, n, k,
+              residual=g["w4a8_residual_bf16"])
+    assert rel_quarter(yr, g["y_w4a8_residual_f64"]) < W4A8_TOL
+    # residual RMSNorm: the new residual is exact, the normed row within a bf16 step of the oracle's
+    hx, hres, hw = U.dev(g["norm_x_bf16"]), U.dev(g["norm_res_bf16"]), U.dev(g["norm_w_bf16"])
+    b, hidden = g["norm_x_bf16"].shape
+    res_out = torch.zeros((b, hidden), dtype=torch.int16, device="cuda")
+    v = torch.zeros((b, hidden), dtype=torch.int16, device="cuda")
+    assert U.ffi.call("nv_kernels_rmsnorm_residual_writeout_bf16", U.stream(), hx.data_ptr(), hres.data_ptr(),
+                      hw.data_ptr(), res_out.data_ptr(), v.data_ptr(), b, hidden, 1e-6) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(U.host_u16(res_out), g["norm_res_out_bf16"])
+    assert np.max(U.bf16_ulp_diff(U.host_u16(v), g["norm_out_bf16"])) <= 1
