@@ -38,15 +38,15 @@ __global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kerne
     }
     TileView t = {};
     t.unit_p1 = unit_p1;
-    t.wq = p.wq[arm];
-    t.sc = p.sc[arm];
+    t.wq = arm_pick(p.wq, arm);
+    t.sc = arm_pick(p.sc, arm);
     t.x = p.x;
     t.x2 = p.x2;
     t.xrows = nullptr;
     t.x_rows = 0;
     t.status = nullptr;
-    t.y = p.y[arm];
-    t.alpha = p.alpha[arm];
+    t.y = arm_pick(p.y, arm);
+    t.alpha = arm_pick(p.alpha, arm);
     t.xrow0 = 0;
     t.M = p.M;
     t.sub = tile - arm * p.tiles_per_arm;
@@ -60,15 +60,15 @@ __global__ void __launch_bounds__(256, NT >= 4 ? 1 : 2) w4a16_mma_ws_kernel(cons
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     TileView t = {};
-    t.wq = p.wq[arm];
-    t.sc = p.sc[arm];
+    t.wq = arm_pick(p.wq, arm);
+    t.sc = arm_pick(p.sc, arm);
     t.x = nullptr;
     t.x2 = nullptr;
     t.xrows = nullptr;
     t.x_rows = 0;
     t.status = nullptr;
-    t.y = p.y[arm];
-    t.alpha = p.alpha[arm];
+    t.y = arm_pick(p.y, arm);
+    t.alpha = arm_pick(p.alpha, arm);
     t.xrow0 = 0;
     t.M = p.M;
     t.sub = tile - arm * p.tiles_per_arm;
@@ -176,21 +176,21 @@ __global__ void __launch_bounds__(256, 3) w4a16_grouped_kernel(const GemmParams 
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     TileView t = {};
-    t.wq = p.wq[arm] + (size_t)e * g.w_stride;
-    t.sc = p.sc[arm] + (size_t)e * g.sc_stride;
+    t.wq = arm_pick(p.wq, arm) + (size_t)e * g.w_stride;
+    t.sc = arm_pick(p.sc, arm) + (size_t)e * g.sc_stride;
     t.x = p.x;
     t.x2 = p.x2;
     t.xrows = g.xrows;
     t.x_rows = g.x_rows;
     t.status = g.status;
-    t.alpha = g.alphas[arm][e];
+    t.alpha = arm_pick(g.alphas, arm)[e];
     t.sub = tile - arm * p.tiles_per_arm;
     t.pdl = false;
     t.ws = nullptr;
     for (int c0 = begin; c0 < end; c0 += 8) {
         t.xrow0 = c0;
         t.M = min(8, end - c0);
-        t.y = p.y[arm] + (size_t)c0 * p.N;
+        t.y = arm_pick(p.y, arm) + (size_t)c0 * p.N;
         if (c0 > begin) __syncthreads();  // the previous chunk's shared-memory reads are done
         w4a16_tile<1, PRO, 8, 1>(p, t);
     }
@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
     const int arm = row >= p.N ? 1 : 0;
     const int r = row - arm * p.N;
     const int kb_total = p.K >> 4;
-    const uint8_t* wrow = p.wq[arm] + (size_t)r * (p.K >> 1);
-    const uint8_t* sc = p.sc[arm];
+    const uint8_t* wrow = arm_pick(p.wq, arm) + (size_t)r * (p.K >> 1);
+    const uint8_t* sc = arm_pick(p.sc, arm);
     for (int m = 0; m < p.M; ++m) {
         const uint16_t* xr = p.x + (size_t)m * p.K;
         const uint16_t* ur = PRO == 1 ? p.x2 + (size_t)m * p.K : nullptr;
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(256) w4a16_rowwarp_kernel(const GemmParams p) 
             acc = fmaf(s, bd, acc);
         }
         acc = nvk::warp_sum(acc);
-        if (lane == 0) p.y[arm][(size_t)m * p.N + r] = nvk::f32_to_bf16_bits(acc * p.alpha[arm]);
+        if (lane == 0) arm_pick(p.y, arm)[(size_t)m * p.N + r] = nvk::f32_to_bf16_bits(acc * arm_pick(p.alpha, arm));
     }
 }
 

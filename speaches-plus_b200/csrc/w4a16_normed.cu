@@ -24,11 +24,11 @@ __global__ void __launch_bounds__(256, NT >= 4 ? 2 : 3) w4a16_normed_kernel(cons
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     TileView t = {};
-    t.wq = p.wq[arm];
-    t.sc = p.sc[arm];
+    t.wq = arm_pick(p.wq, arm);
+    t.sc = arm_pick(p.sc, arm);
     t.x = p.x;
-    t.y = p.y[arm];
-    t.alpha = p.alpha[arm];
+    t.y = arm_pick(p.y, arm);
+    t.alpha = arm_pick(p.alpha, arm);
     t.M = p.M;
     t.sub = tile - arm * p.tiles_per_arm;
     t.pdl = true;

@@ -30,6 +30,13 @@ struct GemmParams {
     int ring_off;       // byte offset of the weight ring in dynamic shared memory
 };
 
+// One of a pair of per-arm parameters.  A select, not an indexed load: indexing a kernel parameter array
+// with a run-time value makes the compiler copy the parameter block to local memory.
+template <class T>
+__device__ __forceinline__ T arm_pick(const T (&pair)[2], int arm) {
+    return arm ? pair[1] : pair[0];
+}
+
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
     nvk::ptx::mma_m16n8k16_f16(d, a0, a1, a2, a3, b0, b1);
