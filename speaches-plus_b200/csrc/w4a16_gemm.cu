@@ -22,7 +22,7 @@
 namespace {
 
 template <int NT, bool DUAL, int PRO, int UG, int KW>
-__global__ void __launch_bounds__(32 * UG * KW, NT >= 4 ? 2 : 3) w4a16_mma_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(32 * UG * KW, kTileCtasPerSm<NT>) w4a16_mma_kernel(const GemmParams p) {
     const int tile = blockIdx.y;
     int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     int unit_p1 = 0;
@@ -312,7 +312,7 @@ int launch_mma(cudaStream_t stream, GemmParams& p) {
     if (ctas > 65535) return NVK_ERR_GRID_AXIS;
     p.bal_ctas = 0;
     if (UG == 8 && KW == 1 && ksplit == 1) {
-        p.bal_ctas = balanced_grid((long)ctas, smem, NT >= 4 ? 2 : 3, g_balance);
+        p.bal_ctas = balanced_grid((long)ctas, smem, kTileCtasPerSm<NT>, g_balance);
         if (p.bal_ctas > 0) ctas = (size_t)p.bal_ctas;
     }
 

@@ -20,7 +20,7 @@ struct NormArgs {
 };
 
 template <int NT, bool DUAL>
-__global__ void __launch_bounds__(256, NT >= 4 ? 2 : 3) w4a16_normed_kernel(const GemmParams p, const NormArgs a) {
+__global__ void __launch_bounds__(256, kTileCtasPerSm<NT>) w4a16_normed_kernel(const GemmParams p, const NormArgs a) {
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     TileView t = {};

@@ -17,7 +17,7 @@ struct ResidualArgs {
 };
 
 template <int NT, int PRO>
-__global__ void __launch_bounds__(256, NT >= 4 ? 2 : 3) w4a16_residual_kernel(const GemmParams p, const ResidualArgs r) {
+__global__ void __launch_bounds__(256, kTileCtasPerSm<NT>) w4a16_residual_kernel(const GemmParams p, const ResidualArgs r) {
     TileView t = {};
     t.wq = p.wq[0];
     t.sc = p.sc[0];

@@ -25,7 +25,7 @@ struct EpiArgs {
 };
 
 template <int NT, bool DUAL, int PRO>
-__global__ void __launch_bounds__(256, NT >= 4 ? 2 : 3) w4a8_kernel(const GemmParams p, const EpiArgs e) {
+__global__ void __launch_bounds__(256, kTileCtasPerSm<NT>) w4a8_kernel(const GemmParams p, const EpiArgs e) {
     const int tile = blockIdx.y;
     const int arm = DUAL ? (tile >= p.tiles_per_arm ? 1 : 0) : 0;
     TileView t = {};
