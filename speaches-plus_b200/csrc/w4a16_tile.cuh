@@ -42,12 +42,13 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
     nvk::ptx::mma_m16n8k16_f16(d, a0, a1, a2, a3, b0, b1);
 }
 
-// CTAs per SM the tile kernels are compiled for (the register cap of __launch_bounds__): three for up
-// to 16 token columns, two for 32; at 64 the staged activations and the weight ring together exceed half
-// an SM's shared memory for all but the shortest K, so one CTA per SM runs whatever the registers, and
-// none are given up for a second.
+// CTAs per SM the tile kernels are compiled for (the register cap of __launch_bounds__).  The weight ring
+// alone is 80 KB per CTA, so shared memory never admits a third CTA.  Up to 8 token columns: three, the
+// setting the measured M = 1 kernel was built with (80 registers, no spills).  16 and 32 columns: two.
+// 64: the staged activations and the ring together exceed half an SM's shared memory for all but the
+// shortest K, so one CTA per SM runs whatever the registers, and none are given up for a second.
 template <int NT>
-constexpr int kTileCtasPerSm = NT >= 8 ? 1 : NT >= 4 ? 2 : 3;
+constexpr int kTileCtasPerSm = NT >= 8 ? 1 : NT >= 2 ? 2 : 3;
 
 constexpr int kDepth = 4;           // cp.async groups in flight per thread
 constexpr int kSlotBytes = 2560;    // one warp, one iteration: 4 x 512 B of weights + 2 x 256 B of scales
