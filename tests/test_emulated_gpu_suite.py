@@ -37,6 +37,8 @@ def test_gpu_linear_tests_also_pass_with_copies_landing_at_once():
     # ... and the earliest: a slot overwritten while another thread still reads it would show here
     import os
     env = dict(os.environ, NVK_EMU_CP_ASYNC_EARLY="1")
+    # (the bf16 linears copy nothing asynchronously, and the two largest GEMV shapes add only time)
     r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_linear.py", "-m", "gpu", "--emu", "-x", "-q",
-                        "-p", "no:cacheprovider"], cwd=ROOT, capture_output=True, text=True, timeout=1500, env=env)
+                        "-p", "no:cacheprovider", "-k", "not bf16 and not 5376-5376 and not config0"], cwd=ROOT,
+                       capture_output=True, text=True, timeout=1500, env=env)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
