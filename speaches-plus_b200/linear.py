@@ -538,4 +538,27 @@ class Nvfp4Mlp:
         self.down.forward_residual_into(g, r2, y, up=u)
         return y.reshape(*x.shape[:-1], hidden)
 
+    def forward_block(self, h: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """A decoder layer's MLP block, h + MLP(RMSNorm(h)): for up to 8 rows two launches -- gate and up with
+        the norm in their prologue, then down with the SiLU prologue and the residual epilogue; more rows
+        run the norm kernel first.  Returns a new tensor."""
+        hidden, inter = self.gate.in_features, self.gate.out_features
+        h2 = h.reshape(-1, hidden).contiguous()
+        m = h2.shape[0]
+        if m > 8 or hidden % 32 != 0:
+            xn = torch.empty_like(h2)
+            _ffi.check("nv_kernels_rmsnorm_bf16", _stream(), h2.data_ptr(), norm_weight.data_ptr(), xn.data_ptr(), m,
+                       hidden, float(eps))
+            return self.forward_residual(xn, h2).reshape(h.shape)
+        if self._gu is None or self._gu.shape[1] != m or self._gu.device != h.device:
+            self._gu = torch.empty((2, m, inter), dtype=torch.bfloat16, device=h.device)
+        g, u = self._gu[0], self._gu[1]
+        _ffi.check("nvk_b200_linear_nvfp4_w4a16_normed", _stream(), self.gate.weight_u8.data_ptr(),
+                   self.gate.weight_scales.data_ptr(), self.up.weight_u8.data_ptr(), self.up.weight_scales.data_ptr(),
+                   h2.data_ptr(), norm_weight.data_ptr(), None, float(eps), g.data_ptr(), u.data_ptr(),
+                   self.gate.alpha_w4a16, self.up.alpha_w4a16, m, inter, hidden)
+        y = torch.empty_like(h2)
+        self.down.forward_residual_into(g, h2, y, up=u)
+        return y.reshape(h.shape)
+
     __call__ = forward

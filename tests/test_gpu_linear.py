@@ -406,6 +406,31 @@ def test_bf16_forward_rows_and_the_unconditional_m1_gemv(m):
             q.forward_nvfp4_gemv_m1(xt)
 
 
+@pytest.mark.parametrize("m", [1, 4, 12])
+def test_mlp_block_with_norm_and_residual(m):
+    """Nvfp4Mlp.forward_block: h + MLP(RMSNorm(h)) in two launches for a few rows; the same bits as the norm
+    kernel followed by forward_residual, and the many-row route agrees with the few-row one row by row."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(70 + m)
+    hidden, inter, eps = 256, 384, 1e-6
+    shapes = ((inter, hidden), (inter, hidden), (hidden, inter))
+    lins = []
+    for (n, k) in shapes:
+        p_, s_, a_, _ = U.make_weight(rng, n, k)
+        lins.append(sp.Nvfp4Linear.new_nvfp4(U.dev(p_), U.dev(s_), a_, k, n))
+    mlp = sp.Nvfp4Mlp(*lins)
+    h = U.gauss_bf16(rng, (m, hidden), 2.0)
+    nw = U.gauss_bf16(rng, (hidden,), 1.0)
+    ht, nwt = U.dev(h).view(torch.bfloat16), U.dev(nw).view(torch.bfloat16)
+    got = U.host_u16(mlp.forward_block(ht, nwt, eps))
+    normed = U.dev(device_rmsnorm(h, nw, eps)).view(torch.bfloat16)
+    want = U.host_u16(mlp.forward_residual(normed, ht))
+    assert np.array_equal(got, want)
+    one = U.host_u16(mlp.forward_block(ht[:1].contiguous(), nwt, eps))
+    assert np.array_equal(one[0], got[0])
+
+
 def test_multi_phase_activation_staging():
     """K large enough at M=64 that the activations are staged in several phases, with magnitudes
     that change by 2^40 along K so the per-phase power-of-two rescale is exercised."""
