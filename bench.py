@@ -152,6 +152,15 @@ def run_b200(args) -> dict:
             args.collective = f"nccl ({e})"
             mark(str(e))
 
+    peer_fused = None
+    if world > 1 and args.collective == "fused":
+        try:
+            peer_fused = tpmod.PeerFusedLinear(None, dev)
+            mark("fused linear + all-reduce ready")
+        except RuntimeError as e:
+            args.collective = f"nccl ({e})"
+            mark(str(e))
+
     # ---- synthetic weights: seeded, identical on every rank, then sharded ----
     copies = COPIES
     layers = []  # (K, N, [TpLinear per copy])
@@ -163,6 +172,7 @@ def run_b200(args) -> dict:
             w = (torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
             lin = tpmod.TpNvfp4Linear.from_bf16(w, mode, rank, world)
             lin.peer_ar = peer_ar
+            lin.peer_fused = peer_fused
             per_copy.append(lin)
             del w
         layers.append((k, n, per_copy))
@@ -283,6 +293,8 @@ def run_b200(args) -> dict:
     mark("per-shape done")
     if peer_ar is not None:
         peer_ar.check()
+    if peer_fused is not None:
+        peer_fused.check()
     # ---- end to end through the public API with host buffers ----
     pin_x = {k: torch.randn((1, k), dtype=torch.float32).to(torch.bfloat16).pin_memory() for k in xs}
     pin_y = {(k, n): torch.empty((1, n), dtype=torch.bfloat16).pin_memory() for k, n in SHAPES_KN}
@@ -377,7 +389,7 @@ def run_b200(args) -> dict:
         layers.clear()
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
-        stack = [decode_stack_leg(dev, rank, world, b, peer_ar=peer_ar) for b in (1, 16)]
+        stack = [decode_stack_leg(dev, rank, world, b, peer_ar=peer_ar, peer_fused=peer_fused) for b in (1, 16)]
         moe = [moe_decode_leg(dev, b, rank=rank, world=world) for b in (1, 16, 64)]
         pre = None
         if world == 1:
@@ -399,6 +411,8 @@ def run_b200(args) -> dict:
         graph = None
         if peer_ar is not None:
             peer_ar.close()
+        if peer_fused is not None:
+            peer_fused.close()
         clean = tpmod.shutdown_process_group()
         mark(f"process group destroyed: {clean}")
         sys.stdout.flush()
@@ -505,7 +519,7 @@ def persistent_step_leg(dev, layers, xs, replays: int) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
-def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, peer_ar=None) -> dict:
+def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, peer_ar=None, peer_fused=None) -> dict:
     """Dense 64-layer decoder linear stack (hidden 5120, 64 q / 8 kv heads of 128, SwiGLU
     25600, bf16 lm_head 151936), random-init NVFP4 weights, one decode step of `batch` tokens through
     every linear.  Attention itself is outside the path: o_proj is fed the q slice of the QKV output.
@@ -564,13 +578,16 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, p
             else:
                 q_in.copy_(qkv[:, :q_l])
                 q_view = q_in
-            lin_call(w_o, None, q_view, None, o_out, None)
-            if world > 1:
-                reduce_(o_out)
+            # row-parallel linears: the partials meet inside the linear's launch when that fits (<= 8 rows)
+            if not (peer_fused is not None and peer_fused.linear_(w_o, q_view, o_out)):
+                lin_call(w_o, None, q_view, None, o_out, None)
+                if world > 1:
+                    reduce_(o_out)
             lin_call(w_g, w_u, o_out, None, gate, up)
-            lin_call(w_d, None, gate, up, d_out, None)
-            if world > 1:
-                reduce_(d_out)
+            if not (peer_fused is not None and peer_fused.linear_(w_d, gate, d_out, up=up)):
+                lin_call(w_d, None, gate, up, d_out, None)
+                if world > 1:
+                    reduce_(d_out)
         lm_head.forward_into(d_out, logits_l)   # M = 1: the GEMV; M > 1: one pass over the matrix for all rows
         if world > 1:
             dist.all_gather_into_tensor(logits, logits_l)
@@ -933,9 +950,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="skip the decode-stack, MoE and prefill legs")
-    ap.add_argument("--collective", default="nccl", choices=["peer", "nccl"],
-                    help="row-parallel sum at --gpus > 1: NCCL (default; in-switch multicast off), or this "
-                         "library's one-shot all-reduce over CUDA-IPC peer memory")
+    ap.add_argument("--collective", default="nccl", choices=["peer", "nccl", "fused"],
+                    help="row-parallel sum at --gpus > 1: NCCL (default; in-switch multicast off), this library's "
+                         "one-shot all-reduce over CUDA-IPC peer memory, or the exchange fused into the linear's "
+                         "own launch (peer stores from the GEMV's epilogue)")
     ap.add_argument("--profile-case", default=None, metavar="K,N,M",
                     help="run a few eager launches of one case and exit (for profiler captures)")
     ap.add_argument("--copies", type=int, default=4)

@@ -127,6 +127,24 @@ int nvk_b200_linear_nvfp4_w4a16_normed(void* stream, const uint8_t* wq_a, const 
                                        const float* rstd, float eps, uint16_t* y_a, uint16_t* y_b, float alpha_a,
                                        float alpha_b, int M, int N, int K);
 
+/* No counterpart in the reference (it has no multi-GPU path): a row-parallel (K-sharded) W4A16 linear and
+ * its all-reduce in one launch per GPU.  y [M, N] = bf16(sum over ranks of bf16(alpha * x_r W_r^T) (+ residual)),
+ * the same bits on every rank and the same bits as the linear followed by nvk_b200_tp_allreduce_bf16.
+ * Each CTA stores its partials into its own region of every GPU's inbox (plain peer stores), raises one
+ * flag per GPU, waits -- bounded, nvk_b200_set_wait_limit -- for the CTA of the same index on every other
+ * GPU and writes the sum in rank order.  wq / sc / x / x2: this rank's K slice (K = its length);
+ * peer_bufs: `world` device pointers to the ranks' exchange buffers as mapped here, each
+ * nvk_b200_tp_fused_buffer_bytes(world, max_ctas) bytes of plain device memory, zero before the first
+ * call; epoch: max_ctas uint32 of local device memory, zero before the first call; err: one int that
+ * becomes 1 + r if rank r never arrived.  All ranks make the same sequence of calls.  1 <= M <= 8.
+ * 0 for an empty problem; -1 for M outside [1, 8] or K % 32 != 0; -2 for null / misaligned operands or a
+ * rank outside the world; -3 when the launch needs more than max_ctas CTAs. */
+int nvk_b200_tp_linear_nvfp4_w4a16_allreduce(void* stream, const void* const* peer_bufs, int rank, int world,
+                                             const uint8_t* wq, const uint8_t* sc, const uint16_t* x, const uint16_t* x2,
+                                             const uint16_t* residual, uint16_t* y, float alpha, int M, int N, int K,
+                                             int max_ctas, uint32_t* epoch, int* err);
+size_t nvk_b200_tp_fused_buffer_bytes(int world, int max_ctas);
+
 /* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
  * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 16, 32,
  * 64, 128} fixes the rows one CTA owns (M <= 16 only). */

@@ -132,11 +132,34 @@ struct TileView {
     // Used only when PRO == 5 (the int8 scale is derived here from partial maxima):
     const float* absmax_partials;
     int n_partials;
+    // Used only when EPI == 2 (the outputs are partial sums of a K-sharded linear that meet the other GPUs'
+    // partials inside this launch; see exchange_* below):
+    uint8_t* xch_peer[8];       // every rank's exchange buffer as mapped here; xch_peer[xch_rank] is our own
+    uint32_t* xch_epoch;        // [xch_max_ctas] call counters of this rank, local memory
+    int* xch_err;               // becomes 1 + the rank that never arrived if a wait gives up
+    int xch_rank, xch_world;
+    int xch_cta, xch_max_ctas;  // this CTA's index in the launch (cluster ranks included); CTAs the buffers hold
+    unsigned xch_wait_limit;
     // Used only when PRO == 6 (an RMSNorm is applied while the activations are staged):
     const uint16_t* norm_w;     // [K] bf16
     const float* rstd_in;       // [rows] 1/rms per activation row, or null: computed here from the row
     float norm_eps;
 };
+
+// Exchange buffer of the fused linear + all-reduce (one per rank, the same layout everywhere):
+//   [0, max_ctas * 32)   flags: uint32 flag[cta][8 ranks], written by the peers, carry the call number
+//   then                  inbox: 2 parities x world x max_ctas x kXchCtaElems bf16
+// A CTA owns the same region of every inbox in every call (regions of different CTAs never overlap,
+// whatever the matrix), so the two parities suffice: a rank can be at most one call ahead of a peer.
+constexpr int kXchCtaElems = 1024;   // 128 rows x up to 8 tokens
+__host__ __device__ inline size_t exchange_flag_bytes(int max_ctas) { return (size_t)max_ctas * 8 * sizeof(uint32_t); }
+__host__ __device__ inline size_t exchange_buffer_bytes(int world, int max_ctas) {
+    return exchange_flag_bytes(max_ctas) + (size_t)2 * world * max_ctas * kXchCtaElems * sizeof(uint16_t);
+}
+// element offset of (parity, source rank, cta) in an inbox
+__device__ __forceinline__ size_t exchange_slot(uint32_t parity, int src_rank, int cta, int world, int max_ctas) {
+    return (((size_t)parity * world + src_rank) * max_ctas + cta) * kXchCtaElems;
+}
 
 // The last CTA of a launch to arrive turns the launch's sum of squared outputs into the next
 // RMSNorm's 1/rms: pack[0] = rsqrt(pack[1] / n + eps), then pack[1] and the arrival count return to
@@ -170,7 +193,11 @@ struct LaunchHooks {
 // RMSNorm, a = bf16(x * rstd * norm_w) with rstd = rsqrt(mean(x^2) + eps) summed in the order of the
 // stand-alone norm kernel (256 threads striding the row, lanes, then warps) or taken from rstd_in.
 // EPI: 0 = y = bf16(alpha * sum); 1 = y = bf16(fma(sum, alpha * row_scale, residual)), optionally
-// followed by emit_rstd over the launch's outputs.
+// followed by emit_rstd over the launch's outputs; 2 = the launch is one GPU's share of a K-sharded
+// linear: bf16(alpha * sum) is a partial that is stored into every GPU's inbox (peer stores), the
+// CTA raises its flag on every GPU, waits (bounded) for the same CTA of every other GPU and writes
+// y = bf16(sum of the partials in rank order (+ residual)) -- the all-reduce happens tile by tile
+// inside the linear's own launch.  M <= 8.
 // XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
 // in a caller-supplied workspace; the CTA streams them through a shared ring next to the weights
 // instead of converting its whole K range itself.  Needs KW == 1 (all warps walk K together).
@@ -187,6 +214,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     __shared__ float s_rescale[MT];   // 2^(pw_old - pw_new) at a phase boundary
     __shared__ float s_q8[2];         // PRO == 5: the int8 row's dequant scale and its reciprocal
     __shared__ float s_ssq[32];       // EPI == 1: per-warp sums of squared outputs
+    __shared__ int s_xch_ok;          // EPI == 2: every peer's partial arrived
     __shared__ float s_rstd[MT];      // PRO == 6: 1/rms of each activation row
     __shared__ float s_red8[8];       // PRO == 6: per-warp sums of squares
 
@@ -576,8 +604,21 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
 
     // y for (token m, row r) from the finished sum v (the activation power of two already undone)
     float ssq = 0.f;   // EPI == 1 with rstd_pack: this thread's sum of squared (rounded) outputs
+    uint32_t xch_call = 0u;   // EPI == 2: this call's number for this CTA
+    if (EPI == 2) xch_call = t.xch_epoch[t.xch_cta] + 1u;
     auto finish = [&](float v, int m, int r, uint16_t* __restrict__ y, float alpha) {
         uint16_t out;
+        if (EPI == 2) {
+            // the partial goes to slot [our rank] of this CTA's region in every GPU's inbox, ours included
+            out = nvk::f32_to_bf16_bits(v * alpha);
+            const size_t at = exchange_slot(xch_call & 1u, t.xch_rank, t.xch_cta, t.xch_world, t.xch_max_ctas) +
+                              (size_t)(m * kRowsPerCta + (r - mt * kRowsPerCta));
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+                if (g < t.xch_world)
+                    reinterpret_cast<uint16_t*>(t.xch_peer[g] + exchange_flag_bytes(t.xch_max_ctas))[at] = out;
+            return;
+        }
         if (EPI == 0) {
             out = nvk::f32_to_bf16_bits(v * alpha);
         } else {
@@ -660,6 +701,64 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
         if (n_out < N) finish(v, m, n_out, y, alpha);
     }
     if (nranks > 1) cluster.sync();  // peers may still be reading this CTA's partial
+    }
+
+    if (EPI == 2) {
+        static_assert(EPI != 2 || NT == 1, "a CTA's exchange region holds 128 rows x 8 tokens");
+        // every partial of this CTA is on its way: make them visible system-wide, then one flag per GPU
+        if (threadIdx.x == 0) s_xch_ok = 1;
+        __threadfence_system();
+        __syncthreads();
+        uint8_t* own = nullptr;
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+            if (g == t.xch_rank) own = t.xch_peer[g];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (g < t.xch_world && (int)threadIdx.x == g) {
+                nvk::ptx::st_release_sys(reinterpret_cast<uint32_t*>(t.xch_peer[g]) + t.xch_cta * 8 + t.xch_rank, xch_call);
+                const uint32_t* mine = reinterpret_cast<const uint32_t*>(own) + t.xch_cta * 8 + g;
+                if (!nvk::bounded_wait_ge(mine, xch_call, t.xch_wait_limit)) {
+                    atomicExch(t.xch_err, 1 + g);
+                    s_xch_ok = 0;
+                }
+            }
+        }
+        __syncthreads();
+        if (s_xch_ok) {
+            const uint16_t* inbox = reinterpret_cast<const uint16_t*>(own + exchange_flag_bytes(t.xch_max_ctas));
+            auto collect = [&](int m, int r) {
+                const size_t local = (size_t)(m * kRowsPerCta + (r - mt * kRowsPerCta));
+                float acc = 0.f;
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    if (g < t.xch_world)
+                        acc += nvk::bf16_bits_to_f32(
+                            inbox[exchange_slot(xch_call & 1u, g, t.xch_cta, t.xch_world, t.xch_max_ctas) + local]);
+                if (t.residual != nullptr) acc += nvk::bf16_bits_to_f32(t.residual[(size_t)m * N + r]);
+                t.y[(size_t)m * N + r] = nvk::f32_to_bf16_bits(acc);
+            };
+            // the elements this thread pushed, in the same enumeration as above
+            if (KW == 1 && nranks == 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int m = 2 * tg + (j & 1);
+                    const int r = row0 + 32 * (j >> 1);
+                    if (m < M && r < N) collect(m, r);
+                }
+            } else {
+                const int rows_per_rank = ROWS / nranks;
+                for (int i = threadIdx.x; i < M * rows_per_rank; i += THREADS) {
+                    const int m = i / rows_per_rank;
+                    const int rl = crank * rows_per_rank + (i - m * rows_per_rank);
+                    const int uu = (sub % SUB) * UG + (rl >> 4);
+                    const int n_out = mt * kRowsPerCta + 32 * (2 * (uu & 1) + ((rl >> 3) & 1)) + 8 * (uu >> 1) + (rl & 7);
+                    if (n_out < N) collect(m, n_out);
+                }
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) t.xch_epoch[t.xch_cta] = xch_call;   // also after a failed wait: the ranks stay in step
     }
 
     if (EPI == 1 && t.rstd_pack != nullptr) {

@@ -85,7 +85,7 @@ class PeerAllReduce:
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.max_elems = (max_elems + 7) // 8 * 8
-        nbytes = int(_ffi.lib().nvk_b200_tp_allreduce_buffer_bytes(self.world, self.max_elems))
+        nbytes = self._buffer_bytes()
         own = C.c_void_p(0)
         _ffi.check("nvk_b200_tp_buffer_alloc", nbytes, C.addressof(own))   # zero-filled
         self._own = own.value
@@ -116,10 +116,16 @@ class PeerAllReduce:
             self.close()
             raise RuntimeError("peer all-reduce unavailable: " + (failure or "a peer could not map the buffers"))
         self._ptr_array = (C.c_void_p * self.world)(*ptrs)
-        self.epoch = torch.zeros(32, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(self._epoch_words(), dtype=torch.int32, device=device)
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(self.group)  # every inbox exists and is zeroed before anyone pushes
+
+    def _buffer_bytes(self) -> int:
+        return int(self._ffi.lib().nvk_b200_tp_allreduce_buffer_bytes(self.world, self.max_elems))
+
+    def _epoch_words(self) -> int:
+        return 32
 
     def all_reduce_(self, y: torch.Tensor) -> torch.Tensor:
         """In-place sum of a contiguous bf16 tensor across the group."""
@@ -149,6 +155,47 @@ class PeerAllReduce:
         dist.barrier(self.group)
         self._ffi.call("nvk_b200_tp_buffer_free", self._own)
         self._own = None
+
+
+class PeerFusedLinear(PeerAllReduce):
+    """Exchange buffers of the fused row-parallel linear + all-reduce
+    (nvk_b200_tp_linear_nvfp4_w4a16_allreduce): the same plain-device-memory / CUDA IPC set-up as
+    PeerAllReduce, sized for launches of up to `max_ctas` CTAs.  One object serves every row-parallel
+    linear of a step (calls on one stream are ordered); every rank makes the same sequence of calls."""
+
+    MAX_ROWS = 8
+
+    def __init__(self, group, device, max_ctas: int = 512):
+        self.max_ctas = int(max_ctas)
+        super().__init__(group, 8, device)
+
+    def _buffer_bytes(self) -> int:
+        return int(self._ffi.lib().nvk_b200_tp_fused_buffer_bytes(self.world, self.max_ctas))
+
+    def _epoch_words(self) -> int:
+        return self.max_ctas
+
+    def all_reduce_(self, y):
+        raise TypeError("PeerFusedLinear exchanges inside the linear's launch: use linear_()")
+
+    def linear_(self, lin: "L.Nvfp4Linear", xs: torch.Tensor, y: torch.Tensor, up: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None) -> bool:
+        """y [m, N] = sum over ranks of this rank's partial (+ residual), m <= 8; `lin` holds this rank's K
+        slice, xs [m, K_local] (row stride = its own).  False when the launch does not fit (more rows, or
+        more CTAs than the buffers hold): the caller then runs the linear and the all-reduce separately."""
+        m = xs.shape[0]
+        if m > self.MAX_ROWS or lin.in_features % 32 != 0 or (m > 1 and not xs.is_contiguous()):
+            return False
+        rc = self._ffi.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", torch.cuda.current_stream().cuda_stream,
+                            self._C.addressof(self._ptr_array), self.rank, self.world, lin.weight_u8.data_ptr(),
+                            lin.weight_scales.data_ptr(), xs.data_ptr(), up.data_ptr() if up is not None else None,
+                            residual.data_ptr() if residual is not None else None, y.data_ptr(), lin.alpha_w4a16, m,
+                            lin.out_features, lin.in_features, self.max_ctas, self.epoch.data_ptr(), self.err.data_ptr())
+        if rc == -3:
+            return False      # more CTAs than the buffers hold
+        if rc != 0:
+            raise self._ffi.NvkError("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", rc)
+        return True
 
 
 def init_process_group_for_node(device, timeout_s: int = 90):
@@ -262,6 +309,9 @@ class TpNvfp4Linear:
         if m > 1:
             xs = xs.contiguous()
         y = self._buf("yr", (m, self.n), x.device)
+        fused = getattr(self, "peer_fused", None)
+        if fused is not None and fused.linear_(self.local, xs, y):
+            return y          # the partials met inside the linear's own launch
         self.local.forward_into(xs, y, allow_prefill=False)
         if self.peer_ar is not None and y.numel() % 8 == 0 and y.numel() <= self.peer_ar.max_elems:
             self.peer_ar.all_reduce_(y)

@@ -852,6 +852,61 @@ def test_a_wait_on_a_peer_that_never_arrives_runs_out_and_reports():
     assert int(err.cpu().numpy()[0]) == 0 and np.array_equal(U.host_u16(y), U.host_u16(x))
 
 
+def test_fused_linear_allreduce_on_one_device():
+    """nvk_b200_tp_linear_nvfp4_w4a16_allreduce on one GPU: (i) a world of one gives the plain linear's bits
+    (with a residual: the residual-update form's semantics on bf16 partials); (ii) with a second rank that
+    never arrives the bounded wait runs out, err names it, y stays untouched, the call returns, and the
+    next call works.  Nothing faults, traps or hangs."""
+    U.require_gpu()
+    import ctypes as C
+    rng = np.random.default_rng(88)
+    m, n, k, max_ctas = 3, 384, 512, 64
+    packed, sw, alpha, _ = U.make_weight(rng, n, k)
+    x = U.gauss_bf16(rng, (m, k))
+    d = [U.dev(packed), U.dev(sw), U.dev(x)]
+    nbytes = U.ffi.lib().nvk_b200_tp_fused_buffer_bytes(2, max_ctas)
+    assert nbytes > 0 and U.ffi.lib().nvk_b200_tp_fused_buffer_bytes(9, max_ctas) == 0
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    epoch = torch.zeros(max_ctas, dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.full((m * n,), 0x7FC0, dtype=torch.int16, device="cuda")
+
+    def call(world, ptrs, residual=None):
+        return U.ffi.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", U.stream(), C.addressof(ptrs), 0, world,
+                          d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), None,
+                          residual.data_ptr() if residual is not None else None, y.data_ptr(), float(alpha), m, n, k,
+                          max_ctas, epoch.data_ptr(), err.data_ptr())
+
+    one = (C.c_void_p * 1)(bufs[0].data_ptr())
+    assert call(1, one) == 0
+    torch.cuda.synchronize()
+    plain = run_linear(packed, sw, x, alpha, m, n, k)
+    assert int(err.cpu().numpy()[0]) == 0 and np.array_equal(U.host_u16(y).reshape(m, n), plain)
+    resid = U.gauss_bf16(rng, (m, n), 2.0)
+    assert call(1, one, U.dev(resid)) == 0
+    torch.cuda.synchronize()
+    want = ref.f32_to_bf16(ref.bf16_to_f32(plain) + ref.bf16_to_f32(resid))
+    assert np.array_equal(U.host_u16(y).reshape(m, n), want)
+    # a peer that never arrives
+    y.fill_(0x7FC0)
+    two = (C.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    assert U.ffi.call("nvk_b200_set_wait_limit", 1000) == 0
+    try:
+        assert call(2, two) == 0
+        torch.cuda.synchronize()
+        assert int(err.cpu().numpy()[0]) == 2 and np.all(U.host_u16(y) == 0x7FC0)
+    finally:
+        assert U.ffi.call("nvk_b200_set_wait_limit", 0) == 0
+    err.zero_()
+    assert call(1, one) == 0
+    torch.cuda.synchronize()
+    assert int(err.cpu().numpy()[0]) == 0 and np.array_equal(U.host_u16(y).reshape(m, n), plain)
+    assert call(1, one) == 0 and U.ffi.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", U.stream(), C.addressof(one), 0, 1,
+                                            d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), None, None, y.data_ptr(),
+                                            float(alpha), 9, n, k, max_ctas, epoch.data_ptr(), err.data_ptr()) == -1
+    torch.cuda.synchronize()
+
+
 def test_two_ranks_of_the_peer_all_reduce_on_one_device_buffer_pair():
     """Both ranks' kernels of one exchange, run one after the other on ONE GPU with a short wait limit,
     is NOT how the kernel is meant to run (ranks are processes on different GPUs and wait for each other);
