@@ -20,17 +20,9 @@ namespace {
 
 constexpr int kMaxRanks = 8;
 
-struct XchArgs {
-    uint8_t* peer[kMaxRanks];
-    uint32_t* epoch;
-    int* err;
-    const uint16_t* residual;
-    int rank, world, max_ctas;
-    uint32_t wait_limit;
-};
-
 template <int PRO>
-__global__ void __launch_bounds__(256, kTileCtasPerSm<1>) tp_linear_kernel(const GemmParams p, const XchArgs a) {
+__global__ void __launch_bounds__(256, kTileCtasPerSm<1>)
+    tp_linear_kernel(const GemmParams p, const __grid_constant__ ExchangeArgs a) {
     TileView t = {};
     t.wq = p.wq[0];
     t.sc = p.sc[0];
@@ -41,21 +33,13 @@ __global__ void __launch_bounds__(256, kTileCtasPerSm<1>) tp_linear_kernel(const
     t.M = p.M;
     t.sub = blockIdx.y;
     t.pdl = true;
-    t.residual = a.residual;
-#pragma unroll
-    for (int g = 0; g < kMaxRanks; ++g) t.xch_peer[g] = a.peer[g];
-    t.xch_epoch = a.epoch;
-    t.xch_err = a.err;
-    t.xch_rank = a.rank;
-    t.xch_world = a.world;
+    t.xch = &a;   // a grid-constant parameter: its address is usable as it stands, nothing is copied
     t.xch_cta = (int)(blockIdx.y * gridDim.x + blockIdx.x);
-    t.xch_max_ctas = a.max_ctas;
-    t.xch_wait_limit = a.wait_limit;
     w4a16_tile<1, PRO, 8, 1, false, LaunchHooks, 2>(p, t);
 }
 
 template <int PRO>
-int launch_tp_linear(cudaStream_t stream, GemmParams& p, const XchArgs& a) {
+int launch_tp_linear(cudaStream_t stream, GemmParams& p, const ExchangeArgs& a) {
     p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta);
     const int ksplit = tile_ksplit(p.tiles_per_arm, p.nsc);
     if ((long)p.tiles_per_arm * ksplit > a.max_ctas) return NVK_ERR_RESOURCE;
@@ -105,7 +89,7 @@ int nvk_b200_tp_linear_nvfp4_w4a16_allreduce(void* stream, const void* const* pe
         return NVK_ERR_ARG;
     if (!peer_bufs || nvk::any_null(wq, sc, x, y, epoch, err)) return NVK_ERR_ARG;
     if (!aligned16(wq) || !aligned16(sc) || !aligned16(x) || (x2 != nullptr && !aligned16(x2))) return NVK_ERR_ARG;
-    XchArgs a = {};
+    ExchangeArgs a = {};
     for (int r = 0; r < world; ++r) {
         if (!peer_bufs[r]) return NVK_ERR_ARG;
         a.peer[r] = static_cast<uint8_t*>(const_cast<void*>(peer_bufs[r]));

@@ -100,6 +100,16 @@ __device__ __forceinline__ void silu_mul_bf16x8(uint32_t (&ws)[4], const uint4 u
 // A warp iteration covers 256 K values ("super-chunk"): lane (g, tg) takes, for each of its two
 // rows, the two 16-byte pieces at K offsets 32*tg and 128 + 32*tg, so that one cp.async instruction
 // moves whole 64-byte runs per row.  NT: number of 8-token column tiles.
+// EPI == 2: how the GPUs of a K-sharded linear reach each other (see exchange_* below).
+struct ExchangeArgs {
+    uint8_t* peer[8];      // every rank's exchange buffer as mapped here; peer[rank] is our own
+    uint32_t* epoch;       // [max_ctas] call counters of this rank, local memory
+    int* err;              // becomes 1 + the rank that never arrived if a wait gives up
+    const uint16_t* residual;
+    int rank, world, max_ctas;
+    unsigned wait_limit;
+};
+
 // What one CTA works on: one arm's matrix, a set of token rows and where their outputs go.
 struct TileView {
     const uint8_t* wq;
@@ -134,12 +144,8 @@ struct TileView {
     int n_partials;
     // Used only when EPI == 2 (the outputs are partial sums of a K-sharded linear that meet the other GPUs'
     // partials inside this launch; see exchange_* below):
-    uint8_t* xch_peer[8];       // every rank's exchange buffer as mapped here; xch_peer[xch_rank] is our own
-    uint32_t* xch_epoch;        // [xch_max_ctas] call counters of this rank, local memory
-    int* xch_err;               // becomes 1 + the rank that never arrived if a wait gives up
-    int xch_rank, xch_world;
-    int xch_cta, xch_max_ctas;  // this CTA's index in the launch (cluster ranks included); CTAs the buffers hold
-    unsigned xch_wait_limit;
+    const ExchangeArgs* xch;    // the launch's exchange description (a __grid_constant__ kernel parameter)
+    int xch_cta;                // this CTA's index in the launch (cluster ranks included)
     // Used only when PRO == 6 (an RMSNorm is applied while the activations are staged):
     const uint16_t* norm_w;     // [K] bf16
     const float* rstd_in;       // [rows] 1/rms per activation row, or null: computed here from the row
@@ -605,18 +611,17 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     // y for (token m, row r) from the finished sum v (the activation power of two already undone)
     float ssq = 0.f;   // EPI == 1 with rstd_pack: this thread's sum of squared (rounded) outputs
     uint32_t xch_call = 0u;   // EPI == 2: this call's number for this CTA
-    if (EPI == 2) xch_call = t.xch_epoch[t.xch_cta] + 1u;
+    if (EPI == 2) xch_call = t.xch->epoch[t.xch_cta] + 1u;
     auto finish = [&](float v, int m, int r, uint16_t* __restrict__ y, float alpha) {
         uint16_t out;
         if (EPI == 2) {
             // the partial goes to slot [our rank] of this CTA's region in every GPU's inbox, ours included
             out = nvk::f32_to_bf16_bits(v * alpha);
-            const size_t at = exchange_slot(xch_call & 1u, t.xch_rank, t.xch_cta, t.xch_world, t.xch_max_ctas) +
+            const ExchangeArgs& xa = *t.xch;
+            const size_t at = exchange_slot(xch_call & 1u, xa.rank, t.xch_cta, xa.world, xa.max_ctas) +
                               (size_t)(m * kRowsPerCta + (r - mt * kRowsPerCta));
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-                if (g < t.xch_world)
-                    reinterpret_cast<uint16_t*>(t.xch_peer[g] + exchange_flag_bytes(t.xch_max_ctas))[at] = out;
+            for (int g = 0; g < xa.world; ++g)
+                reinterpret_cast<uint16_t*>(xa.peer[g] + exchange_flag_bytes(xa.max_ctas))[at] = out;
             return;
         }
         if (EPI == 0) {
@@ -705,37 +710,30 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
 
     if (EPI == 2) {
         static_assert(EPI != 2 || NT == 1, "a CTA's exchange region holds 128 rows x 8 tokens");
+        const ExchangeArgs& xa = *t.xch;
         // every partial of this CTA is on its way: make them visible system-wide, then one flag per GPU
         if (threadIdx.x == 0) s_xch_ok = 1;
         __threadfence_system();
         __syncthreads();
-        uint8_t* own = nullptr;
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-            if (g == t.xch_rank) own = t.xch_peer[g];
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            if (g < t.xch_world && (int)threadIdx.x == g) {
-                nvk::ptx::st_release_sys(reinterpret_cast<uint32_t*>(t.xch_peer[g]) + t.xch_cta * 8 + t.xch_rank, xch_call);
-                const uint32_t* mine = reinterpret_cast<const uint32_t*>(own) + t.xch_cta * 8 + g;
-                if (!nvk::bounded_wait_ge(mine, xch_call, t.xch_wait_limit)) {
-                    atomicExch(t.xch_err, 1 + g);
-                    s_xch_ok = 0;
-                }
+        uint8_t* own = xa.peer[xa.rank];
+        if ((int)threadIdx.x < xa.world) {
+            const int g = (int)threadIdx.x;
+            nvk::ptx::st_release_sys(reinterpret_cast<uint32_t*>(xa.peer[g]) + t.xch_cta * 8 + xa.rank, xch_call);
+            const uint32_t* mine = reinterpret_cast<const uint32_t*>(own) + t.xch_cta * 8 + g;
+            if (!nvk::bounded_wait_ge(mine, xch_call, xa.wait_limit)) {
+                atomicExch(xa.err, 1 + g);
+                s_xch_ok = 0;
             }
         }
         __syncthreads();
         if (s_xch_ok) {
-            const uint16_t* inbox = reinterpret_cast<const uint16_t*>(own + exchange_flag_bytes(t.xch_max_ctas));
+            const uint16_t* inbox = reinterpret_cast<const uint16_t*>(own + exchange_flag_bytes(xa.max_ctas));
             auto collect = [&](int m, int r) {
                 const size_t local = (size_t)(m * kRowsPerCta + (r - mt * kRowsPerCta));
                 float acc = 0.f;
-#pragma unroll
-                for (int g = 0; g < 8; ++g)
-                    if (g < t.xch_world)
-                        acc += nvk::bf16_bits_to_f32(
-                            inbox[exchange_slot(xch_call & 1u, g, t.xch_cta, t.xch_world, t.xch_max_ctas) + local]);
-                if (t.residual != nullptr) acc += nvk::bf16_bits_to_f32(t.residual[(size_t)m * N + r]);
+                for (int g = 0; g < xa.world; ++g)
+                    acc += nvk::bf16_bits_to_f32(inbox[exchange_slot(xch_call & 1u, g, t.xch_cta, xa.world, xa.max_ctas) + local]);
+                if (xa.residual != nullptr) acc += nvk::bf16_bits_to_f32(xa.residual[(size_t)m * N + r]);
                 t.y[(size_t)m * N + r] = nvk::f32_to_bf16_bits(acc);
             };
             // the elements this thread pushed, in the same enumeration as above
@@ -758,7 +756,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             }
         }
         __syncthreads();
-        if (threadIdx.x == 0) t.xch_epoch[t.xch_cta] = xch_call;   // also after a failed wait: the ranks stay in step
+        if (threadIdx.x == 0) xa.epoch[t.xch_cta] = xch_call;   // also after a failed wait: the ranks stay in step
     }
 
     if (EPI == 1 && t.rstd_pack != nullptr) {

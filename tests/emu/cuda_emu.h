@@ -33,6 +33,7 @@
 #define __noinline__ __attribute__((noinline))
 #define __restrict__ __restrict
 #define __launch_bounds__(...)
+#define __grid_constant__
 #define __align__(n) __attribute__((aligned(n)))
 #define __shared__ static thread_local   // one OS thread runs one block at a time
 #define __constant__ static
