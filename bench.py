@@ -390,7 +390,16 @@ def run_b200(args) -> dict:
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
         stack = [decode_stack_leg(dev, rank, world, b, peer_ar=peer_ar, peer_fused=peer_fused) for b in (1, 16)]
-        moe = [moe_decode_leg(dev, b, rank=rank, world=world) for b in (1, 16, 64)]
+        peer_combine = None
+        if world > 1 and args.collective == "fused":
+            try:
+                peer_combine = tpmod.PeerMoeCombine(None, dev)
+            except RuntimeError as e:
+                mark(str(e))
+        moe = [moe_decode_leg(dev, b, rank=rank, world=world, peer_combine=peer_combine) for b in (1, 16, 64)]
+        if peer_combine is not None:
+            peer_combine.check()
+            peer_combine.close()
         pre = None
         if world == 1:
             pre = (prefill_leg(dev) if sp.ffi.prefill_available()
@@ -679,7 +688,7 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, p
     return out
 
 
-def moe_decode_leg(dev, batch: int, replays: int = 5, rank: int = 0, world: int = 1) -> dict:
+def moe_decode_leg(dev, batch: int, replays: int = 5, rank: int = 0, world: int = 1, peer_combine=None) -> dict:
     """MoE expert decode: 48 layers x 128 experts (hidden 2048, SwiGLU 768), top-8 with
     softmax over the winners, router logits ~ N(0,1); one decode step of `batch` tokens through
     route -> sort -> grouped gate+up -> grouped down (SiLU prologue) -> combine in every layer.
@@ -728,7 +737,7 @@ def moe_decode_leg(dev, batch: int, replays: int = 5, rank: int = 0, world: int 
 
     def step():
         for w, logits in mods:
-            sp.forward_grouped_decode(w, ctx, x, logits)
+            sp.forward_grouped_decode(w, ctx, x, logits, peer_combine=peer_combine)
 
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):

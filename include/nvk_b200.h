@@ -145,6 +145,22 @@ int nvk_b200_tp_linear_nvfp4_w4a16_allreduce(void* stream, const void* const* pe
                                              int max_ctas, uint32_t* epoch, int* err);
 size_t nvk_b200_tp_fused_buffer_bytes(int world, int max_ctas);
 
+/* No counterpart in the reference (it has no multi-GPU path): the expert-parallel MoE combine and the sum
+ * over GPUs in one launch.  Every rank passes the rows of ITS experts' slots (inv_perm < 0, or zero rows,
+ * for the others); y_acc [n_tokens, hidden] f32 receives the sum over ranks of the ranks' weighted
+ * combines, added in rank order -- the same bits on every rank.  Each CTA stores its partials into its
+ * own region of every GPU's inbox (plain peer stores), raises one flag per GPU and waits, bounded, for
+ * the CTA of the same index on the other GPUs.  hidden % 8 == 0, rows 16-byte aligned.  peer_bufs:
+ * `world` pointers to the ranks' exchange buffers (nvk_b200_moe_combine_buffer_bytes(world, max_ctas)
+ * bytes of plain device memory each, zero before the first call); epoch: max_ctas uint32, zero before
+ * the first call; err: becomes 1 + r if rank r never arrived.  -2 for bad arguments; -3 when
+ * ceil(hidden / 1024) * n_tokens exceeds max_ctas. */
+int nvk_b200_moe_combine_allreduce(void* stream, const void* const* peer_bufs, int rank, int world,
+                                   const uint16_t* y_sorted_bf16, const float* topk_weights, const int32_t* inv_perm,
+                                   float* y_acc_f32, int n_tokens, int k, int hidden, int y_sorted_row_stride,
+                                   int sorted_rows, int* status, int max_ctas, uint32_t* epoch, int* err);
+size_t nvk_b200_moe_combine_buffer_bytes(int world, int max_ctas);
+
 /* No counterpart in the reference: tuning/test hook.  force_ksplit in {0 (auto), 1, 2, 4, 8} fixes
  * how many CTAs of a cluster share one row tile's K range; force_rows_per_cta in {0 (auto), 16, 32,
  * 64, 128} fixes the rows one CTA owns (M <= 16 only). */

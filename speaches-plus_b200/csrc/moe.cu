@@ -481,6 +481,94 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineArgs a) {
     }
 }
 
+// ---- expert-parallel combine: the weighted sum and the sum over GPUs in one launch --------------------
+// Every GPU ran the slots of its own experts (the other slots' rows are zeros or skipped), so its combine
+// yields a partial y_acc.  Each CTA stores its 128 x 8 f32 partials into its own region of every GPU's
+// inbox (plain peer stores), raises one flag per GPU, waits -- bounded -- for the CTA of the same index
+// on every other GPU and writes the sum in rank order: the same bits on every GPU.  Buffer layout (one
+// per rank): [flags: max_ctas x 8 uint32][inbox: 2 parities x world x max_ctas x 1024 f32].
+struct CombineXchArgs {
+    uint8_t* peer[8];
+    uint32_t* epoch;
+    int* err;
+    int rank, world, max_ctas;
+    unsigned wait_limit;
+};
+constexpr int kCombineCtaElems = 1024;
+__host__ __device__ inline size_t combine_xch_flag_bytes(int max_ctas) { return (size_t)max_ctas * 8 * sizeof(uint32_t); }
+
+__global__ void __launch_bounds__(128) combine_allreduce_kernel(const CombineArgs a, const __grid_constant__ CombineXchArgs x) {
+    __shared__ int s_ok;
+    nvk::ptx::pdl_wait();
+    nvk::ptx::pdl_launch_dependents();
+    const int n = blockIdx.y;
+    const int h0 = (blockIdx.x * 128 + threadIdx.x) * 8;
+    const int cta = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+    const uint32_t call = x.epoch[cta] + 1u;
+    const bool live = h0 < a.hidden;          // hidden % 8 == 0: a thread's eight values are all in or all out
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        for (int s = 0; s < a.k; ++s) {
+            const int slot = n * a.k + s;
+            const int row = a.inv_perm[slot];
+            if (row < 0) continue;
+            if (row >= a.sorted_rows) {
+                if (a.status != nullptr && threadIdx.x == 0 && blockIdx.x == 0) atomicOr(a.status, 4);
+                continue;
+            }
+            const float w = a.weights[slot];
+            const uint4 v = *reinterpret_cast<const uint4*>(a.y_sorted + (size_t)row * a.row_stride + h0);
+            const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] = fmaf(w, nvk::bf16_bits_to_f32(ws[i] & 0xFFFFu), acc[2 * i]);
+                acc[2 * i + 1] = fmaf(w, nvk::bf16_bits_to_f32(ws[i] >> 16), acc[2 * i + 1]);
+            }
+        }
+    }
+    const size_t region = (size_t)x.world * x.max_ctas * kCombineCtaElems;    // f32 per parity
+    auto slot_of = [&](int src_rank) {
+        return (size_t)(call & 1u) * region + ((size_t)src_rank * x.max_ctas + cta) * kCombineCtaElems + threadIdx.x * 8;
+    };
+    if (live) {
+        const float4 lo = make_float4(acc[0], acc[1], acc[2], acc[3]), hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        for (int g = 0; g < x.world; ++g) {
+            float* inbox = reinterpret_cast<float*>(x.peer[g] + combine_xch_flag_bytes(x.max_ctas));
+            float4* dst = reinterpret_cast<float4*>(inbox + slot_of(x.rank));
+            dst[0] = lo;
+            dst[1] = hi;
+        }
+    }
+    if (threadIdx.x == 0) s_ok = 1;
+    __threadfence_system();
+    __syncthreads();
+    uint8_t* own = x.peer[x.rank];
+    if ((int)threadIdx.x < x.world) {
+        const int g = (int)threadIdx.x;
+        nvk::ptx::st_release_sys(reinterpret_cast<uint32_t*>(x.peer[g]) + cta * 8 + x.rank, call);
+        if (!nvk::bounded_wait_ge(reinterpret_cast<const uint32_t*>(own) + cta * 8 + g, call, x.wait_limit)) {
+            atomicExch(x.err, 1 + g);
+            s_ok = 0;
+        }
+    }
+    __syncthreads();
+    if (s_ok && live) {
+        const float* inbox = reinterpret_cast<const float*>(own + combine_xch_flag_bytes(x.max_ctas));
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int g = 0; g < x.world; ++g) {
+            const float4* src = reinterpret_cast<const float4*>(inbox + slot_of(g));
+            const float4 lo = src[0], hi = src[1];
+            sum[0] += lo.x; sum[1] += lo.y; sum[2] += lo.z; sum[3] += lo.w;
+            sum[4] += hi.x; sum[5] += hi.y; sum[6] += hi.z; sum[7] += hi.w;
+        }
+        float4* out = reinterpret_cast<float4*>(a.y_acc + (size_t)n * a.hidden + h0);
+        out[0] = make_float4(sum[0], sum[1], sum[2], sum[3]);
+        out[1] = make_float4(sum[4], sum[5], sum[6], sum[7]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) x.epoch[cta] = call;   // also after a failed wait: the ranks stay in step
+}
+
 template <bool TAIL>
 int launch_combine(cudaStream_t stream, const CombineArgs& a) {
     const bool vec = (a.hidden & 7) == 0 && (a.row_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(a.y_sorted) & 15u) == 0;
@@ -727,6 +815,51 @@ int nvk_b200_moe_combine(void* stream, const uint16_t* y_sorted_bf16, const floa
     if (nvk::any_null(y_sorted_bf16, topk_weights, inv_perm, y_acc_f32)) return NVK_ERR_ARG;
     return combine(stream, y_sorted_bf16, topk_weights, inv_perm, y_acc_f32, nullptr, nullptr, nullptr, n_tokens, k,
                    hidden, y_sorted_row_stride, sorted_rows, status, false);
+}
+
+// Bytes of the exchange buffer every rank provides (zero before the first call) for
+// nvk_b200_moe_combine_allreduce launches of up to max_ctas CTAs; 0 for arguments out of range.
+size_t nvk_b200_moe_combine_buffer_bytes(int world, int max_ctas) {
+    if (world <= 0 || world > 8 || max_ctas <= 0 || max_ctas > 4096) return 0;
+    return combine_xch_flag_bytes(max_ctas) + (size_t)2 * world * max_ctas * kCombineCtaElems * sizeof(float);
+}
+
+// Expert-parallel combine (no counterpart in the reference, which has no multi-GPU path): every rank
+// passes the rows of ITS experts' slots (inv_perm < 0 or zero rows for the others); y_acc [n_tokens,
+// hidden] receives the sum over ranks of the ranks' weighted combines, added in rank order -- the same
+// bits on every rank -- without a separate all-reduce.  hidden % 8 == 0, the sorted rows 16-byte
+// aligned.  peer_bufs / epoch (max_ctas uint32, zero before the first call) / err as for
+// nvk_b200_tp_linear_nvfp4_w4a16_allreduce; all ranks make the same sequence of calls.  -2 for bad
+// arguments, -3 when ceil(hidden / 1024) * n_tokens exceeds max_ctas.
+int nvk_b200_moe_combine_allreduce(void* stream, const void* const* peer_bufs, int rank, int world,
+                                   const uint16_t* y_sorted_bf16, const float* topk_weights, const int32_t* inv_perm,
+                                   float* y_acc_f32, int n_tokens, int k, int hidden, int y_sorted_row_stride,
+                                   int sorted_rows, int* status, int max_ctas, uint32_t* epoch, int* err) {
+    if (n_tokens <= 0 || k <= 0 || hidden <= 0) return 0;
+    if (y_sorted_row_stride < hidden || sorted_rows < 0 || (hidden & 7) != 0 || (y_sorted_row_stride & 7) != 0)
+        return NVK_ERR_ARG;
+    if (world <= 0 || world > 8 || rank < 0 || rank >= world || max_ctas <= 0 || max_ctas > 4096) return NVK_ERR_ARG;
+    if (!peer_bufs || nvk::any_null(y_sorted_bf16, topk_weights, inv_perm, y_acc_f32, epoch, err)) return NVK_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(y_sorted_bf16) | reinterpret_cast<uintptr_t>(y_acc_f32)) & 15u) return NVK_ERR_ARG;
+    const long ctas = (long)nvk::ceil_div(hidden, 1024) * n_tokens;
+    if (ctas > max_ctas || n_tokens > 65535) return NVK_ERR_RESOURCE;
+    CombineArgs a = {};
+    a.y_sorted = y_sorted_bf16; a.weights = topk_weights; a.inv_perm = inv_perm; a.y_acc = y_acc_f32;
+    a.n_tokens = n_tokens; a.k = k; a.hidden = hidden; a.row_stride = y_sorted_row_stride;
+    a.sorted_rows = sorted_rows; a.status = status;
+    CombineXchArgs x = {};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_bufs[r]) return NVK_ERR_ARG;
+        x.peer[r] = static_cast<uint8_t*>(const_cast<void*>(peer_bufs[r]));
+    }
+    x.epoch = epoch; x.err = err; x.rank = rank; x.world = world; x.max_ctas = max_ctas;
+    x.wait_limit = nvk::wait_limit_setting();
+    nvk::Launch l;
+    l.grid = dim3((unsigned)nvk::ceil_div(hidden, 1024), (unsigned)n_tokens, 1);
+    l.block = dim3(128, 1, 1);
+    l.stream = (cudaStream_t)stream;
+    l.pdl = true;
+    return nvk::launch(l, combine_allreduce_kernel, a, x);
 }
 
 int nv_kernels_moe_permute(void* stream, const int32_t* topk_ids, int32_t* permuted_token_idx,

@@ -129,13 +129,15 @@ class GroupedDecodeContext:
 
 def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: torch.Tensor,
                            router_logits: torch.Tensor, bias=None, mode: int = 0, softcap: float = 0.0,
-                           norm_topk: bool = True, routed_scaling: float = 1.0, group=None) -> torch.Tensor:
+                           norm_topk: bool = True, routed_scaling: float = 1.0, group=None,
+                           peer_combine=None) -> torch.Tensor:
     """x [n, hidden] bf16, router_logits [n, E] f32 -> y_acc [n, hidden] f32 (the view of ctx.y_acc).
 
     Expert parallelism: when `w` holds only a block of the layer's experts (`shard_experts`), every
     rank routes all tokens over all E experts (the router is replicated), runs the slots that landed
     on ITS experts, leaves zeros in the other slots' rows, combines, and the ranks' f32 partial
-    outputs are summed with one all-reduce over `group`."""
+    outputs are summed with one all-reduce over `group` -- or, with a `tp.PeerMoeCombine`, inside the
+    combine's own launch (peer stores from the combine kernel, no separate collective)."""
     n, k, E = x.shape[0], ctx.top_k, w.total_experts
     assert n <= ctx.max_tokens and x.dtype == torch.bfloat16 and x.is_contiguous()
     assert router_logits.dtype == torch.float32 and router_logits.is_contiguous()
@@ -171,6 +173,9 @@ def forward_grouped_decode(w: MoeGroupedWeights, ctx: GroupedDecodeContext, x: t
     _ffi.check("nvk_b200_moe_grouped_w4a16", s, d[0].data_ptr(), d[1].data_ptr(), None, None, d[2].data_ptr(), None,
                ctx.gate_out.data_ptr(), ctx.up_out.data_ptr(), None, offsets, act, n_act, ctx.down_out.data_ptr(),
                None, w.num_experts, w.hidden, w.inter, slots, slots, ctx.status.data_ptr())
+    if w.sharded and peer_combine is not None and peer_combine.combine_(
+            ctx.down_out, ctx.topk_weights, ctx.inv_perm, ctx.y_acc, n, k, w.hidden, slots, ctx.status):
+        return ctx.y_acc[:n]      # combined and summed over the ranks in one launch
     _ffi.check("nvk_b200_moe_combine", s, ctx.down_out.data_ptr(), ctx.topk_weights.data_ptr(),
                ctx.inv_perm.data_ptr(), ctx.y_acc.data_ptr(), n, k, w.hidden, w.hidden, slots, ctx.status.data_ptr())
     if w.sharded:

@@ -198,6 +198,39 @@ class PeerFusedLinear(PeerAllReduce):
         return True
 
 
+class PeerMoeCombine(PeerAllReduce):
+    """Exchange buffers of the expert-parallel combine that sums over the GPUs inside its own launch
+    (nvk_b200_moe_combine_allreduce); set up like PeerAllReduce."""
+
+    def __init__(self, group, device, max_ctas: int = 512):
+        self.max_ctas = int(max_ctas)
+        super().__init__(group, 8, device)
+
+    def _buffer_bytes(self) -> int:
+        return int(self._ffi.lib().nvk_b200_moe_combine_buffer_bytes(self.world, self.max_ctas))
+
+    def _epoch_words(self) -> int:
+        return self.max_ctas
+
+    def all_reduce_(self, y):
+        raise TypeError("PeerMoeCombine sums inside the combine's launch: use combine_()")
+
+    def combine_(self, down_out: torch.Tensor, topk_weights: torch.Tensor, inv_perm: torch.Tensor, y_acc: torch.Tensor,
+                 n: int, k: int, hidden: int, slots: int, status: torch.Tensor) -> bool:
+        """False when the launch does not fit the buffers (the caller then combines and all-reduces)."""
+        if hidden % 8 != 0:
+            return False
+        rc = self._ffi.call("nvk_b200_moe_combine_allreduce", torch.cuda.current_stream().cuda_stream,
+                            self._C.addressof(self._ptr_array), self.rank, self.world, down_out.data_ptr(),
+                            topk_weights.data_ptr(), inv_perm.data_ptr(), y_acc.data_ptr(), n, k, hidden, hidden, slots,
+                            status.data_ptr(), self.max_ctas, self.epoch.data_ptr(), self.err.data_ptr())
+        if rc == -3:
+            return False
+        if rc != 0:
+            raise self._ffi.NvkError("nvk_b200_moe_combine_allreduce", rc)
+        return True
+
+
 def init_process_group_for_node(device, timeout_s: int = 90):
     """NCCL process group for the GPUs of one node with in-switch multicast (NVLS) turned off: on
     shared machines a rank that goes away while its memory is bound to an NVLink multicast object

@@ -217,3 +217,14 @@ def test_fused_linear_allreduce_refusals():
     assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 0, P) == -2              # no call counters
     assert g(P, 0, 2, P, P, P + 4, None, None, P, 1.0, 1, 128, 128, 64, P, P) == -2          # misaligned x
     assert f("nvk_b200_tp_fused_buffer_bytes", 0, 64) == 0 and f("nvk_b200_tp_fused_buffer_bytes", 2, 5000) == 0
+
+
+def test_combine_allreduce_refusals():
+    g = lambda *a: f("nvk_b200_moe_combine_allreduce", S, *a)
+    assert g(P, 0, 2, P, P, P, P, 0, 2, 256, 256, 8, None, 64, P, P) == 0                    # no tokens
+    assert g(P, 0, 2, P, P, P, P, 1, 2, 252, 256, 8, None, 64, P, P) == -2                   # hidden % 8
+    assert g(P, 0, 2, P, P, P, P, 1, 2, 256, 128, 8, None, 64, P, P) == -2                   # row stride < hidden
+    assert g(P, 3, 2, P, P, P, P, 1, 2, 256, 256, 8, None, 64, P, P) == -2                   # rank outside the world
+    assert g(P, 0, 2, P, P, P, P, 65, 2, 2048, 2048, 8, None, 64, P, P) == -3                # 130 CTAs > 64
+    assert g(P, 0, 2, P, P, P, P, 1, 2, 256, 256, 8, None, 64, 0, P) == -2                   # no call counters
+    assert f("nvk_b200_moe_combine_buffer_bytes", 2, 64) == 64 * 32 + 2 * 2 * 64 * 4096

@@ -114,3 +114,49 @@ def test_a_rank_that_never_arrives_is_reported_and_the_next_call_works():
     assert _run_ranks(fused, world) == [0, 0]
     assert int(errs[0].read()[0]) == 0 and int(errs[1].read()[0]) == 0
     assert np.array_equal(ys[0].read(), ys[1].read())
+
+
+@pytest.mark.parametrize("world,n_tok,top_k,hidden", [(2, 1, 4, 256), (4, 5, 2, 2048), (8, 3, 8, 1032)])
+def test_expert_parallel_combine_sums_over_ranks_in_one_launch(world, n_tok, top_k, hidden):
+    """nvk_b200_moe_combine_allreduce with all ranks at once: each rank holds the rows of the slots routed to
+    its own experts (the other slots have inv_perm = -1 there); every rank ends with the same bits, equal to
+    the ranks' own combines (nvk_b200_moe_combine) added in rank order in fp32."""
+    rng = np.random.default_rng(world * 7 + n_tok)
+    slots = n_tok * top_k
+    nbytes = H.lib().nvk_b200_moe_combine_buffer_bytes(world, MAX_CTAS)
+    bufs = [H.Buf(np.zeros(nbytes, np.uint8)) for _ in range(world)]
+    ptrs = (C.c_void_p * world)(*[b.ptr for b in bufs])
+    epochs = [H.Buf(np.zeros(MAX_CTAS, np.uint32)) for _ in range(world)]
+    errs = [H.Buf(np.zeros(1, np.int32)) for _ in range(world)]
+    for call in range(3):
+        owner = rng.integers(0, world, size=slots)              # which rank's expert each slot went to
+        weights = rng.random(slots).astype(np.float32)
+        rows = U.gauss_bf16(rng, (slots, hidden))
+        perm = rng.permutation(slots).astype(np.int32)          # slot -> row of the sorted buffer
+        dw = H.Buf(weights)
+        per_rank = []
+        for r in range(world):
+            inv = np.where(owner == r, perm, -1).astype(np.int32)
+            sorted_rows = np.zeros((slots, hidden), np.uint16)
+            sorted_rows[perm[owner == r]] = rows[owner == r]
+            per_rank.append((H.Buf(sorted_rows), H.Buf(inv)))
+        ys = [H.Buf(np.full((n_tok, hidden), np.nan, np.float32)) for _ in range(world)]
+        status = [H.Buf(np.zeros(1, np.int32)) for _ in range(world)]
+
+        def fused(r):
+            return H.call("nvk_b200_moe_combine_allreduce", None, C.addressof(ptrs), r, world, per_rank[r][0], dw,
+                          per_rank[r][1], ys[r], n_tok, top_k, hidden, hidden, slots, status[r], MAX_CTAS, epochs[r], errs[r])
+
+        assert _run_ranks(fused, world) == [0] * world
+        acc = np.zeros((n_tok, hidden), np.float32)
+        for r in range(world):
+            own = H.Buf(np.zeros((n_tok, hidden), np.float32))
+            assert H.call("nvk_b200_moe_combine", None, per_rank[r][0], dw, per_rank[r][1], own, n_tok, top_k, hidden, hidden,
+                          slots, None) == 0
+            acc = acc + own.read()
+        for r in range(world):
+            assert int(errs[r].read()[0]) == 0 and int(status[r].read()[0]) == 0
+            assert np.array_equal(ys[r].read(), acc), (call, r)
+        # and it is the mixture: sum_s w_s * row_s per token
+        want = (weights[:, None].astype(np.float64) * ref.bf16_to_f32(rows).astype(np.float64)).reshape(n_tok, top_k, hidden).sum(1)
+        assert np.allclose(acc, want, rtol=1e-5, atol=1e-5)

@@ -746,6 +746,51 @@ def test_slot_sort_and_combine_skip_ids_outside_the_expert_range():
     np.testing.assert_allclose(acc.cpu().numpy(), want2, rtol=1e-6, atol=1e-7)
 
 
+def test_combine_allreduce_on_one_device():
+    """nvk_b200_moe_combine_allreduce on one GPU: a world of one equals nvk_b200_moe_combine bit for bit; with
+    a second rank that never arrives the bounded wait runs out, err names it, y_acc stays untouched and the
+    next call works."""
+    U.require_gpu()
+    import ctypes as C
+    rng = np.random.default_rng(31)
+    n_tok, k, hidden, max_ctas = 3, 4, 1032, 64
+    slots = n_tok * k
+    rows = U.dev(U.gauss_bf16(rng, (slots, hidden)))
+    wts = U.dev(rng.random(slots).astype(np.float32))
+    inv = U.dev(rng.permutation(slots).astype(np.int32))
+    want = torch.zeros((n_tok, hidden), dtype=torch.float32, device="cuda")
+    assert U.ffi.call("nvk_b200_moe_combine", U.stream(), rows.data_ptr(), wts.data_ptr(), inv.data_ptr(), want.data_ptr(),
+                      n_tok, k, hidden, hidden, slots, None) == 0
+    nbytes = U.ffi.lib().nvk_b200_moe_combine_buffer_bytes(2, max_ctas)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    epoch = torch.zeros(max_ctas, dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.full((n_tok, hidden), -7.0, dtype=torch.float32, device="cuda")
+
+    def call(world, ptrs):
+        return U.ffi.call("nvk_b200_moe_combine_allreduce", U.stream(), C.addressof(ptrs), 0, world, rows.data_ptr(),
+                          wts.data_ptr(), inv.data_ptr(), y.data_ptr(), n_tok, k, hidden, hidden, slots, None, max_ctas,
+                          epoch.data_ptr(), err.data_ptr())
+
+    one = (C.c_void_p * 1)(bufs[0].data_ptr())
+    assert call(1, one) == 0
+    torch.cuda.synchronize()
+    assert int(err.cpu().numpy()[0]) == 0 and torch.equal(y, want)
+    y.fill_(-7.0)
+    two = (C.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    assert U.ffi.call("nvk_b200_set_wait_limit", 1000) == 0
+    try:
+        assert call(2, two) == 0
+        torch.cuda.synchronize()
+        assert int(err.cpu().numpy()[0]) == 2 and bool((y == -7.0).all())
+    finally:
+        assert U.ffi.call("nvk_b200_set_wait_limit", 0) == 0
+    err.zero_()
+    assert call(1, one) == 0
+    torch.cuda.synchronize()
+    assert int(err.cpu().numpy()[0]) == 0 and torch.equal(y, want)
+
+
 def test_grouped_linear_does_not_follow_offsets_or_rows_outside_its_buffers():
     U.require_gpu()
     rng = np.random.default_rng(12)
