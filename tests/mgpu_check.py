@@ -1,6 +1,7 @@
 """Multi-GPU checks, run as `torchrun --nproc-per-node N tests/mgpu_check.py` (one rank per GPU):
 the peer-memory all-reduce equals the fp32 rank-order sum bit for bit (eagerly and replayed from a
-CUDA graph); tensor-parallel NVFP4 linears (column and row) and the expert-parallel MoE step are
+CUDA graph); tensor-parallel NVFP4 linears (column and row, the row form also with its all-reduce
+fused into the linear's launch) and the expert-parallel MoE step (also with the fused combine) are
 checked against the CPU oracle (f64 statement of the contraction, the tolerance form of the GEMV
 tests), not against the unsharded GPU result."""
 import os
@@ -90,6 +91,28 @@ def main():
             assert err < 1e-4 + 1e-2, f"{mode}-parallel vs the f64 oracle: {err} (rank {rank}, m={m})"
     ar.check()
 
+    # the same row-parallel linear with the exchange inside its own launch: bit-equal to linear + all-reduce
+    fused = tp.PeerFusedLinear(None, dev)
+    n, k = 512, 4096
+    w = ref.f32_to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    packed, sw, alpha = ref.quantize_weight_bf16(w)
+    shard = tp.TpNvfp4Linear.from_parts(torch.from_numpy(packed), torch.from_numpy(sw), alpha, n, k, "row", rank, world,
+                                        device=dev)
+    shard.peer_ar = ar
+    for m in (1, 5):
+        x = ref.f32_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+        xt = torch.from_numpy(x.view(np.int16)).to(dev).view(torch.bfloat16)
+        two_kernels = bits(shard.forward(xt)).copy()
+        shard.peer_fused = fused
+        one_kernel = bits(shard.forward(xt)).copy()
+        shard.peer_fused = None
+        torch.cuda.synchronize()
+        assert np.array_equal(one_kernel, two_kernels), f"fused row-parallel linear differs (rank {rank}, m={m})"
+        err = rel_err_floor(ref.bf16_to_f32(one_kernel).reshape(m, n), ref.linear_w4a16_f64(packed, sw, x, alpha, n, k))
+        assert err < 1e-4 + 1e-2, f"fused row-parallel linear vs the f64 oracle: {err}"
+    fused.check()
+    fused.close()
+
     # expert parallelism against the per-(token, expert) oracle
     E, top_k, hidden, inter, n_tok = 16, 4, 256, 384, 7
     experts, host = [], []
@@ -123,6 +146,14 @@ def main():
             want[t] += np.float64(wts[t, j]) * ref.bf16_to_f32(down)[0].astype(np.float64)
     err = rel_err_floor(got, want)
     assert err < 1e-2, f"expert-parallel MoE step vs the per-pair oracle: {err} (rank {rank})"
+    # ... and with the sum over the ranks inside the combine's own launch
+    pc = tp.PeerMoeCombine(None, dev)
+    got2 = sp.forward_grouped_decode(mine, ctx, xt, torch.from_numpy(logits).to(dev), peer_combine=pc).cpu().numpy()
+    torch.cuda.synchronize()
+    ctx.check_status()
+    pc.check()
+    assert rel_err_floor(got2, want) < 1e-2, f"fused expert-parallel combine vs the per-pair oracle (rank {rank})"
+    pc.close()
 
     if rank == 0:
         print("mgpu_check ok", flush=True)
