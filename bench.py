@@ -631,6 +631,10 @@ def decode_stack_leg(dev, rank: int, world: int, batch: int, replays: int = 5, p
            "tok_s": round(batch / (ms * 1e-3), 1), "bytes_per_step_per_gpu": bytes_rank,
            "gbs_per_gpu": round(bytes_rank / (ms * 1e-3) / 1e9, 1),
            "launches_per_step": layers * 4 + 1, "collectives_per_step": (2 * layers + 1) if world > 1 else 0}
+    if world > 1 and peer_fused is not None and batch <= peer_fused.MAX_ROWS:
+        # the row-parallel sums happen inside the linears' own launches; only the lm_head's gather is left
+        out["collectives_per_step"] = 1
+        out["row_parallel_sum"] = "inside the linear's launch"
 
     if world == 1 and batch == 1:
         # The same stack with both RMSNorms and both residual adds of every layer inside its four launches:
