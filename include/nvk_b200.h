@@ -134,16 +134,17 @@ int nvk_b200_linear_nvfp4_w4a16_normed(void* stream, const uint8_t* wq_a, const 
  * flag per GPU, waits -- bounded, nvk_b200_set_wait_limit -- for the CTA of the same index on every other
  * GPU and writes the sum in rank order.  wq / sc / x / x2: this rank's K slice (K = its length);
  * peer_bufs: `world` device pointers to the ranks' exchange buffers as mapped here, each
- * nvk_b200_tp_fused_buffer_bytes(world, max_ctas) bytes of plain device memory, zero before the first
- * call; epoch: max_ctas uint32 of local device memory, zero before the first call; err: one int that
- * becomes 1 + r if rank r never arrived.  All ranks make the same sequence of calls.  1 <= M <= 8.
- * 0 for an empty problem; -1 for M outside [1, 8] or K % 32 != 0; -2 for null / misaligned operands or a
- * rank outside the world; -3 when the launch needs more than max_ctas CTAs. */
+ * nvk_b200_tp_fused_buffer_bytes(world, max_ctas, max_rows) bytes of plain device memory, zero before the
+ * first call; epoch: max_ctas uint32 of local device memory, zero before the first call; err: one int
+ * that becomes 1 + r if rank r never arrived.  All ranks make the same sequence of calls.
+ * 1 <= M <= max_rows <= 64.  0 for an empty problem; -1 for M outside that range or K % 32 != 0; -2 for
+ * null / misaligned operands, a rank outside the world or a row capacity outside [1, 64]; -3 when the
+ * launch needs more than max_ctas CTAs. */
 int nvk_b200_tp_linear_nvfp4_w4a16_allreduce(void* stream, const void* const* peer_bufs, int rank, int world,
                                              const uint8_t* wq, const uint8_t* sc, const uint16_t* x, const uint16_t* x2,
                                              const uint16_t* residual, uint16_t* y, float alpha, int M, int N, int K,
-                                             int max_ctas, uint32_t* epoch, int* err);
-size_t nvk_b200_tp_fused_buffer_bytes(int world, int max_ctas);
+                                             int max_ctas, int max_rows, uint32_t* epoch, int* err);
+size_t nvk_b200_tp_fused_buffer_bytes(int world, int max_ctas, int max_rows);
 
 /* No counterpart in the reference (it has no multi-GPU path): the expert-parallel MoE combine and the sum
  * over GPUs in one launch.  Every rank passes the rows of ITS experts' slots (inv_perm < 0, or zero rows,

@@ -31,8 +31,8 @@ SIGNATURES = {
     "nvk_b200_linear_nvfp4_w4a16_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i],
     "nvk_b200_linear_nvfp4_w4a16_residual_rstd_emit": [_vp] * 7 + [_f, _vp, _f, _i, _i],
     "nvk_b200_linear_nvfp4_w4a16_normed": [_vp] * 8 + [_f, _vp, _vp, _f, _f, _i, _i, _i],
-    "nvk_b200_tp_linear_nvfp4_w4a16_allreduce": [_vp, _vp, _i, _i] + [_vp] * 6 + [_f, _i, _i, _i, _i, _vp, _vp],
-    "nvk_b200_tp_fused_buffer_bytes": [_i, _i],
+    "nvk_b200_tp_linear_nvfp4_w4a16_allreduce": [_vp, _vp, _i, _i] + [_vp] * 6 + [_f, _i, _i, _i, _i, _i, _vp, _vp],
+    "nvk_b200_tp_fused_buffer_bytes": [_i, _i, _i],
     "nvk_b200_moe_combine_allreduce": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp],
     "nvk_b200_moe_combine_buffer_bytes": [_i, _i],
     "nvk_b200_set_tuning": [_i, _i],

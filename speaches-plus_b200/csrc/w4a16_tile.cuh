@@ -107,6 +107,7 @@ struct ExchangeArgs {
     int* err;              // becomes 1 + the rank that never arrived if a wait gives up
     const uint16_t* residual;
     int rank, world, max_ctas;
+    int cta_elems;         // bf16 values of one CTA's inbox region: 128 rows x the row capacity of the buffers
     unsigned wait_limit;
 };
 
@@ -154,17 +155,16 @@ struct TileView {
 
 // Exchange buffer of the fused linear + all-reduce (one per rank, the same layout everywhere):
 //   [0, max_ctas * 32)   flags: uint32 flag[cta][8 ranks], written by the peers, carry the call number
-//   then                  inbox: 2 parities x world x max_ctas x kXchCtaElems bf16
+//   then                  inbox: 2 parities x world x max_ctas x (128 * max_rows) bf16
 // A CTA owns the same region of every inbox in every call (regions of different CTAs never overlap,
 // whatever the matrix), so the two parities suffice: a rank can be at most one call ahead of a peer.
-constexpr int kXchCtaElems = 1024;   // 128 rows x up to 8 tokens
 __host__ __device__ inline size_t exchange_flag_bytes(int max_ctas) { return (size_t)max_ctas * 8 * sizeof(uint32_t); }
-__host__ __device__ inline size_t exchange_buffer_bytes(int world, int max_ctas) {
-    return exchange_flag_bytes(max_ctas) + (size_t)2 * world * max_ctas * kXchCtaElems * sizeof(uint16_t);
+__host__ __device__ inline size_t exchange_buffer_bytes(int world, int max_ctas, int max_rows) {
+    return exchange_flag_bytes(max_ctas) + (size_t)2 * world * max_ctas * (128 * max_rows) * sizeof(uint16_t);
 }
 // element offset of (parity, source rank, cta) in an inbox
-__device__ __forceinline__ size_t exchange_slot(uint32_t parity, int src_rank, int cta, int world, int max_ctas) {
-    return (((size_t)parity * world + src_rank) * max_ctas + cta) * kXchCtaElems;
+__device__ __forceinline__ size_t exchange_slot(const ExchangeArgs& xa, uint32_t parity, int src_rank, int cta) {
+    return (((size_t)parity * xa.world + src_rank) * xa.max_ctas + cta) * (size_t)xa.cta_elems;
 }
 
 // The last CTA of a launch to arrive turns the launch's sum of squared outputs into the next
@@ -203,7 +203,7 @@ struct LaunchHooks {
 // linear: bf16(alpha * sum) is a partial that is stored into every GPU's inbox (peer stores), the
 // CTA raises its flag on every GPU, waits (bounded) for the same CTA of every other GPU and writes
 // y = bf16(sum of the partials in rank order (+ residual)) -- the all-reduce happens tile by tile
-// inside the linear's own launch.  M <= 8.
+// inside the linear's own launch.
 // XWS: the activations were converted beforehand (x_prepare_kernel) into per-super-chunk f16 stages
 // in a caller-supplied workspace; the CTA streams them through a shared ring next to the weights
 // instead of converting its whole K range itself.  Needs KW == 1 (all warps walk K together).
@@ -618,7 +618,7 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
             // the partial goes to slot [our rank] of this CTA's region in every GPU's inbox, ours included
             out = nvk::f32_to_bf16_bits(v * alpha);
             const ExchangeArgs& xa = *t.xch;
-            const size_t at = exchange_slot(xch_call & 1u, xa.rank, t.xch_cta, xa.world, xa.max_ctas) +
+            const size_t at = exchange_slot(xa, xch_call & 1u, xa.rank, t.xch_cta) +
                               (size_t)(m * kRowsPerCta + (r - mt * kRowsPerCta));
             for (int g = 0; g < xa.world; ++g)
                 reinterpret_cast<uint16_t*>(xa.peer[g] + exchange_flag_bytes(xa.max_ctas))[at] = out;
@@ -709,7 +709,6 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
     }
 
     if (EPI == 2) {
-        static_assert(EPI != 2 || NT == 1, "a CTA's exchange region holds 128 rows x 8 tokens");
         const ExchangeArgs& xa = *t.xch;
         // every partial of this CTA is on its way: make them visible system-wide, then one flag per GPU
         if (threadIdx.x == 0) s_xch_ok = 1;
@@ -732,18 +731,20 @@ __device__ __forceinline__ void w4a16_tile(const GemmParams& p, const TileView& 
                 const size_t local = (size_t)(m * kRowsPerCta + (r - mt * kRowsPerCta));
                 float acc = 0.f;
                 for (int g = 0; g < xa.world; ++g)
-                    acc += nvk::bf16_bits_to_f32(inbox[exchange_slot(xch_call & 1u, g, t.xch_cta, xa.world, xa.max_ctas) + local]);
+                    acc += nvk::bf16_bits_to_f32(inbox[exchange_slot(xa, xch_call & 1u, g, t.xch_cta) + local]);
                 if (xa.residual != nullptr) acc += nvk::bf16_bits_to_f32(xa.residual[(size_t)m * N + r]);
                 t.y[(size_t)m * N + r] = nvk::f32_to_bf16_bits(acc);
             };
             // the elements this thread pushed, in the same enumeration as above
             if (KW == 1 && nranks == 1) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int m = 2 * tg + (j & 1);
-                    const int r = row0 + 32 * (j >> 1);
-                    if (m < M && r < N) collect(m, r);
-                }
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int m = 8 * n + 2 * tg + (j & 1);
+                        const int r = row0 + 32 * (j >> 1);
+                        if (m < M && r < N) collect(m, r);
+                    }
             } else {
                 const int rows_per_rank = ROWS / nranks;
                 for (int i = threadIdx.x; i < M * rows_per_rank; i += THREADS) {

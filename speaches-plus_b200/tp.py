@@ -163,14 +163,12 @@ class PeerFusedLinear(PeerAllReduce):
     PeerAllReduce, sized for launches of up to `max_ctas` CTAs.  One object serves every row-parallel
     linear of a step (calls on one stream are ordered); every rank makes the same sequence of calls."""
 
-    MAX_ROWS = 8
-
-    def __init__(self, group, device, max_ctas: int = 512):
-        self.max_ctas = int(max_ctas)
+    def __init__(self, group, device, max_ctas: int = 512, max_rows: int = 16):
+        self.max_ctas, self.MAX_ROWS = int(max_ctas), int(max_rows)
         super().__init__(group, 8, device)
 
     def _buffer_bytes(self) -> int:
-        return int(self._ffi.lib().nvk_b200_tp_fused_buffer_bytes(self.world, self.max_ctas))
+        return int(self._ffi.lib().nvk_b200_tp_fused_buffer_bytes(self.world, self.max_ctas, self.MAX_ROWS))
 
     def _epoch_words(self) -> int:
         return self.max_ctas
@@ -180,7 +178,7 @@ class PeerFusedLinear(PeerAllReduce):
 
     def linear_(self, lin: "L.Nvfp4Linear", xs: torch.Tensor, y: torch.Tensor, up: torch.Tensor | None = None,
                 residual: torch.Tensor | None = None) -> bool:
-        """y [m, N] = sum over ranks of this rank's partial (+ residual), m <= 8; `lin` holds this rank's K
+        """y [m, N] = sum over ranks of this rank's partial (+ residual), m <= max_rows; `lin` holds this rank's K
         slice, xs [m, K_local] (row stride = its own).  False when the launch does not fit (more rows, or
         more CTAs than the buffers hold): the caller then runs the linear and the all-reduce separately."""
         m = xs.shape[0]
@@ -190,7 +188,8 @@ class PeerFusedLinear(PeerAllReduce):
                             self._C.addressof(self._ptr_array), self.rank, self.world, lin.weight_u8.data_ptr(),
                             lin.weight_scales.data_ptr(), xs.data_ptr(), up.data_ptr() if up is not None else None,
                             residual.data_ptr() if residual is not None else None, y.data_ptr(), lin.alpha_w4a16, m,
-                            lin.out_features, lin.in_features, self.max_ctas, self.epoch.data_ptr(), self.err.data_ptr())
+                            lin.out_features, lin.in_features, self.max_ctas, self.MAX_ROWS, self.epoch.data_ptr(),
+                            self.err.data_ptr())
         if rc == -3:
             return False      # more CTAs than the buffers hold
         if rc != 0:

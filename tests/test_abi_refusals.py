@@ -208,15 +208,17 @@ def test_normed_linear_and_rstd_emit_refusals():
 
 def test_fused_linear_allreduce_refusals():
     g = lambda *a: f("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", S, *a)
-    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 0, 128, 64, P, P) == 0                 # empty problem
-    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 9, 128, 128, 64, P, P) == -1              # more than 8 rows
-    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 144, 64, P, P) == -1              # K % 32
-    assert g(P, 2, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, P, P) == -2              # rank outside the world
-    assert g(P, 0, 9, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, P, P) == -2              # more than 8 ranks
-    assert g(0, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, P, P) == -2              # no buffers
-    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 0, P) == -2              # no call counters
-    assert g(P, 0, 2, P, P, P + 4, None, None, P, 1.0, 1, 128, 128, 64, P, P) == -2          # misaligned x
-    assert f("nvk_b200_tp_fused_buffer_bytes", 0, 64) == 0 and f("nvk_b200_tp_fused_buffer_bytes", 2, 5000) == 0
+    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 0, 128, 64, 8, P, P) == 0                 # empty problem
+    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 9, 128, 128, 64, 8, P, P) == -1              # more rows than the buffers hold
+    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 65, P, P) == -2             # row capacity > 64
+    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 144, 64, 8, P, P) == -1              # K % 32
+    assert g(P, 2, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 8, P, P) == -2              # rank outside the world
+    assert g(P, 0, 9, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 8, P, P) == -2              # more than 8 ranks
+    assert g(0, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 8, P, P) == -2              # no buffers
+    assert g(P, 0, 2, P, P, P, None, None, P, 1.0, 1, 128, 128, 64, 8, 0, P) == -2              # no call counters
+    assert g(P, 0, 2, P, P, P + 4, None, None, P, 1.0, 1, 128, 128, 64, 8, P, P) == -2          # misaligned x
+    assert f("nvk_b200_tp_fused_buffer_bytes", 0, 64, 8) == 0 and f("nvk_b200_tp_fused_buffer_bytes", 2, 5000, 8) == 0
+    assert f("nvk_b200_tp_fused_buffer_bytes", 2, 64, 16) == 64 * 32 + 2 * 2 * 64 * 128 * 16 * 2
 
 
 def test_combine_allreduce_refusals():

@@ -14,6 +14,7 @@ from tests import _util as U
 from tests.emu import harness as H
 
 MAX_CTAS = 512
+MAX_ROWS = 24
 
 
 def _run_ranks(fn, world):
@@ -38,10 +39,11 @@ def _run_ranks(fn, world):
 
 
 @pytest.mark.parametrize("world,m,n,k_rank,silu,resid", [(2, 1, 384, 512, False, False), (4, 3, 200, 1024, True, True),
-                                                         (8, 8, 640, 256, False, True), (2, 5, 19200, 256, False, False)])
+                                                         (8, 8, 640, 256, False, True), (2, 5, 19200, 256, False, False),
+                                                         (2, 13, 256, 512, False, True), (4, 24, 384, 256, True, False)])
 def test_fused_linear_allreduce_equals_the_two_kernel_form(world, m, n, k_rank, silu, resid):
     rng = np.random.default_rng(world * 100 + m + n)
-    nbytes = H.lib().nvk_b200_tp_fused_buffer_bytes(world, MAX_CTAS)
+    nbytes = H.lib().nvk_b200_tp_fused_buffer_bytes(world, MAX_CTAS, MAX_ROWS)
     bufs = [H.Buf(np.zeros(nbytes, np.uint8)) for _ in range(world)]
     ptrs = (C.c_void_p * world)(*[b.ptr for b in bufs])
     epochs = [H.Buf(np.zeros(MAX_CTAS, np.uint32)) for _ in range(world)]
@@ -59,7 +61,7 @@ def test_fused_linear_allreduce_equals_the_two_kernel_form(world, m, n, k_rank, 
 
         def fused(r):
             return H.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", None, C.addressof(ptrs), r, world, dw[r][0], dw[r][1],
-                          dx[r], du[r], dr[r], ys[r], float(shards[r][2]), m, n, k_rank, MAX_CTAS, epochs[r], errs[r])
+                          dx[r], du[r], dr[r], ys[r], float(shards[r][2]), m, n, k_rank, MAX_CTAS, MAX_ROWS, epochs[r], errs[r])
 
         assert _run_ranks(fused, world) == [0] * world
         # the two-kernel form: every rank's plain linear, then the fp32 sum in rank order, one rounding
@@ -87,7 +89,7 @@ def test_a_rank_that_never_arrives_is_reported_and_the_next_call_works():
     word names the peer, the call returns normally; then both ranks run and agree."""
     world, m, n, k = 2, 2, 256, 256
     rng = np.random.default_rng(5)
-    nbytes = H.lib().nvk_b200_tp_fused_buffer_bytes(world, MAX_CTAS)
+    nbytes = H.lib().nvk_b200_tp_fused_buffer_bytes(world, MAX_CTAS, MAX_ROWS)
     bufs = [H.Buf(np.zeros(nbytes, np.uint8)) for _ in range(world)]
     ptrs = (C.c_void_p * world)(*[b.ptr for b in bufs])
     epochs = [H.Buf(np.zeros(MAX_CTAS, np.uint32)) for _ in range(world)]
@@ -99,7 +101,7 @@ def test_a_rank_that_never_arrives_is_reported_and_the_next_call_works():
 
     def fused(r):
         return H.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", None, C.addressof(ptrs), r, world, dw[r][0], dw[r][1],
-                      dx[r], None, None, ys[r], float(shards[r][2]), m, n, k, MAX_CTAS, epochs[r], errs[r])
+                      dx[r], None, None, ys[r], float(shards[r][2]), m, n, k, MAX_CTAS, MAX_ROWS, epochs[r], errs[r])
 
     assert H.call("nvk_b200_set_wait_limit", 2000) == 0
     try:

@@ -864,8 +864,8 @@ def test_fused_linear_allreduce_on_one_device():
     packed, sw, alpha, _ = U.make_weight(rng, n, k)
     x = U.gauss_bf16(rng, (m, k))
     d = [U.dev(packed), U.dev(sw), U.dev(x)]
-    nbytes = U.ffi.lib().nvk_b200_tp_fused_buffer_bytes(2, max_ctas)
-    assert nbytes > 0 and U.ffi.lib().nvk_b200_tp_fused_buffer_bytes(9, max_ctas) == 0
+    nbytes = U.ffi.lib().nvk_b200_tp_fused_buffer_bytes(2, max_ctas, 8)
+    assert nbytes > 0 and U.ffi.lib().nvk_b200_tp_fused_buffer_bytes(9, max_ctas, 8) == 0
     bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
     epoch = torch.zeros(max_ctas, dtype=torch.int32, device="cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -875,7 +875,7 @@ def test_fused_linear_allreduce_on_one_device():
         return U.ffi.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", U.stream(), C.addressof(ptrs), 0, world,
                           d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), None,
                           residual.data_ptr() if residual is not None else None, y.data_ptr(), float(alpha), m, n, k,
-                          max_ctas, epoch.data_ptr(), err.data_ptr())
+                          max_ctas, 8, epoch.data_ptr(), err.data_ptr())
 
     one = (C.c_void_p * 1)(bufs[0].data_ptr())
     assert call(1, one) == 0
@@ -903,7 +903,7 @@ def test_fused_linear_allreduce_on_one_device():
     assert int(err.cpu().numpy()[0]) == 0 and np.array_equal(U.host_u16(y).reshape(m, n), plain)
     assert call(1, one) == 0 and U.ffi.call("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", U.stream(), C.addressof(one), 0, 1,
                                             d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), None, None, y.data_ptr(),
-                                            float(alpha), 9, n, k, max_ctas, epoch.data_ptr(), err.data_ptr()) == -1
+                                            float(alpha), 9, n, k, max_ctas, 8, epoch.data_ptr(), err.data_ptr()) == -1
     torch.cuda.synchronize()
 
 
