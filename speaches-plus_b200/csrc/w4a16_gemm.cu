@@ -392,28 +392,26 @@ int launch_prepare(cudaStream_t stream, const uint16_t* x, const uint16_t* x2, u
 
 template <bool DUAL, int PRO>
 int launch_grouped(cudaStream_t stream, GemmParams& p, const GroupedParams& g, int E) {
-    constexpr int MT = 8, RS = 128 + 4, KW = 1;
     p.M = 8;
     p.tiles_per_arm = nvk::ceil_div(p.N, kRowsPerCta);
-    p.spc = p.nsc;
-    p.ph = min(max(1, (48 * 1024) / (8 * 512)), p.nsc);
-    p.x_stride = p.ph * 512 + 64;
-    const size_t smem_x = (size_t)8 * p.x_stride;
-    const size_t smem_red = (size_t)(KW + 1) * MT * RS * sizeof(float);
-    p.ring_off = (int)((max(smem_x, smem_red) + 127) / 128 * 128);
-    const size_t smem = (size_t)p.ring_off + (size_t)8 * kDepth * kSlotBytes;
+    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
+    if (ctas > 65535 || E > 65535) return NVK_ERR_GRID_AXIS;
+    // K split over a cluster by the rule of the dense launches, applied to ONE expert's row tiles: a
+    // decode step may route to a single expert, and a rule that looked at the number of routed experts
+    // or tokens would make a slot's bits depend on the rest of the batch.
+    int ksplit = g_force_ksplit > 0 ? g_force_ksplit : tile_ksplit((int)ctas, p.nsc);
+    const size_t smem = tile_layout_rows128(p, 8, 8, ksplit);
     static nvk::SmemOptin optin;
     auto* kern = w4a16_grouped_kernel<DUAL, PRO>;
     if (int rc = optin.ensure((const void*)kern, smem)) return rc;
-    const size_t ctas = (size_t)(DUAL ? 2 : 1) * p.tiles_per_arm;
-    if (ctas > 65535 || E > 65535) return NVK_ERR_GRID_AXIS;
     nvk::Launch l;
     // with a list of active experts the grid covers only as many experts as there are slots
     const int grid_z = g.active != nullptr ? max(1, min(E, g.n_slots)) : E;
-    l.grid = dim3(1, (unsigned)ctas, (unsigned)grid_z);
+    l.grid = dim3((unsigned)ksplit, (unsigned)ctas, (unsigned)grid_z);
     l.block = dim3(256, 1, 1);
     l.smem = smem;
     l.stream = stream;
+    l.cluster_x = (unsigned)ksplit;
     l.pdl = true;
     return nvk::launch(l, kern, p, g);
 }

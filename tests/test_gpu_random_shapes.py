@@ -156,7 +156,9 @@ def _moe_cases(seed, count):
     return out
 
 
-@pytest.mark.parametrize("n_tok,E,top_k,hidden,inter,seed", _moe_cases(15, 8))
+# the last two: K long enough that an expert's row tiles split K over a cluster (gate/up, and down too)
+@pytest.mark.parametrize("n_tok,E,top_k,hidden,inter,seed", _moe_cases(15, 8) + [(3, 4, 2, 1024, 512, 15100),
+                                                                                  (11, 6, 3, 1536, 1280, 15101)])
 def test_random_moe_decode_shapes(n_tok, E, top_k, hidden, inter, seed):
     """The grouped decode step (router + slot sort + active list, gate/up, SiLU prologue + down, f32
     combine) on drawn (tokens, experts, winners, hidden, expert width), against the per-(token, expert)
@@ -194,6 +196,13 @@ def test_random_moe_decode_shapes(n_tok, E, top_k, hidden, inter, seed):
             down = ref.f32_to_bf16(ref.linear_w4a16_f64(pd, sd, act, ad, hidden, inter).astype(np.float32))
             want[t] += np.float64(wts[t, j]) * ref.bf16_to_f32(down)[0].astype(np.float64)
     assert U.rel_err_floor(got, want) < 1e-2
+    if seed == 15100:
+        # a token's bits do not depend on what else is in the batch, split K or not
+        got = got.copy()
+        xt = U.dev(x).view(torch.bfloat16)
+        for t in range(n_tok):
+            y1 = sp.forward_grouped_decode(w, ctx, xt[t:t + 1].contiguous(), U.dev(logits[t:t + 1])).cpu().numpy()
+            assert np.array_equal(y1[0], got[t])
 
 
 def _w4a8_cases(seed, count):
