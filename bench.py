@@ -766,9 +766,35 @@ def moe_decode_leg(dev, batch: int, replays: int = 5, rank: int = 0, world: int 
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    # the same step with every expert's K range kept in one CTA per row tile (no cluster split of K): the pair
+    # shows, per batch size, what the split is worth -- its rule looks at one expert's tiles only, so that a
+    # slot's bits never depend on the batch, and is therefore the same at every batch size
+    ms_unsplit = None
+    if world == 1:
+        sp.ffi.check("nvk_b200_set_tuning", 1, 0)
+        try:
+            with torch.cuda.stream(stream):
+                step()
+                stream.synchronize()
+                graph1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph1, stream=stream):
+                    step()
+                for _ in range(2):
+                    graph1.replay()
+                stream.synchronize()
+                e0.record(stream)
+                for _ in range(replays):
+                    graph1.replay()
+                e1.record(stream)
+                stream.synchronize()
+                ms_unsplit = e0.elapsed_time(e1) / replays
+                del graph1
+        finally:
+            sp.ffi.check("nvk_b200_set_tuning", 0, 0)
     per_expert = mods[0][0].per_expert_bytes()
     nbytes = distinct * per_expert
     out = {"batch": batch, "layers": layers, "experts": E, "top_k": TOPK, "ep": world, "ms_per_step": round(ms, 4),
+           "ms_per_step_no_k_split": round(ms_unsplit, 4) if ms_unsplit is not None else None,
            "tok_s": round(batch / (ms * 1e-3), 1), "distinct_experts_per_layer": round(distinct / layers, 2),
            "bytes_per_step": nbytes, "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
            "launches_per_step": layers * (4 if world == 1 else 5), "collectives_per_step": layers if world > 1 else 0}
