@@ -237,5 +237,45 @@ inline void forward_grouped_decode(void* stream, const MoeGroupedWeights& w, con
                                                        n, k, w.hidden, w.hidden, slots, ctx.status));
 }
 
+// ---- tensor / expert parallelism over peer memory ---------------------------------------------------
+// The exchange buffers of a group of GPUs as one rank sees them: `bufs[r]` is rank r's buffer mapped in
+// this process (nvk_b200_tp_buffer_alloc / _ipc_export / _ipc_open, handles exchanged by the host),
+// `epoch` max_ctas zeroed uint32 of local device memory, `err` one zeroed int.  One such object per kind
+// of exchange (they differ in buffer size: nvk_b200_tp_fused_buffer_bytes, nvk_b200_moe_combine_buffer_bytes).
+struct PeerExchange {
+    const void* const* bufs;
+    int rank, world;
+    int max_ctas, max_rows;
+    uint32_t* epoch;
+    int* err;
+};
+
+// Row-parallel linear (this rank's K slice in `shard`, this rank's activation slice in x) with the sum
+// over the ranks inside the linear's own launch; y [m, out] is complete and identical on every rank.
+// False when the launch does not fit the buffers: run shard.forward_into and an all-reduce instead.
+inline bool tp_linear_allreduce(void* stream, const PeerExchange& px, const Nvfp4Linear& shard, const uint16_t* x,
+                                const uint16_t* up, const uint16_t* residual, uint16_t* y, int m) {
+    if (m > px.max_rows) return false;
+    const int rc = nvk_b200_tp_linear_nvfp4_w4a16_allreduce(
+        stream, px.bufs, px.rank, px.world, shard.weight_u8(), shard.weight_scales(), x, up, residual, y,
+        shard.alpha_w4a16(), m, shard.out_features(), shard.in_features(), px.max_ctas, px.max_rows, px.epoch, px.err);
+    if (rc == -3) return false;
+    check("nvk_b200_tp_linear_nvfp4_w4a16_allreduce", rc);
+    return true;
+}
+
+// Expert-parallel tail of forward_grouped_decode: the weighted combine of this rank's experts' slots and
+// the sum over the ranks in one launch.  False when it does not fit the buffers.
+inline bool moe_combine_allreduce(void* stream, const PeerExchange& px, const MoeGroupedWeights& w,
+                                  const GroupedDecodeContext& ctx, int n) {
+    const int slots = n * ctx.top_k;
+    const int rc = nvk_b200_moe_combine_allreduce(stream, px.bufs, px.rank, px.world, ctx.down_out, ctx.topk_weights,
+                                                  ctx.inv_perm, ctx.y_acc, n, ctx.top_k, w.hidden, w.hidden, slots,
+                                                  ctx.status, px.max_ctas, px.epoch, px.err);
+    if (rc == -3) return false;
+    check("nvk_b200_moe_combine_allreduce", rc);
+    return true;
+}
+
 }  // namespace host
 }  // namespace nvk

@@ -135,6 +135,19 @@ int main(int argc, char** argv) {
             download("out_moe_ids.bin", c.topk_ids, slots);
             download("out_moe_status.bin", c.status, 1);
         }
+        // ---- the fused row-parallel linear with a world of one: the plain linear's bits ----
+        {
+            const int m = (int)meta["lin_m"] > 8 ? 8 : (int)meta["lin_m"], n = (int)meta["lin_n"], k = (int)meta["lin_k"];
+            Nvfp4Linear lin(upload<uint8_t>("lin_packed.bin"), upload<uint8_t>("lin_scales.bin"), (float)meta["lin_alpha"], k, n);
+            const int max_ctas = 64, max_rows = 8;
+            void* buf = device_zeros<uint8_t>(nvk_b200_tp_fused_buffer_bytes(1, max_ctas, max_rows));
+            const void* bufs[1] = {buf};
+            PeerExchange px = {bufs, 0, 1, max_ctas, max_rows, device_zeros<uint32_t>(max_ctas), device_zeros<int>(1)};
+            uint16_t* y = device_zeros<uint16_t>((size_t)m * n);
+            const bool ran = tp_linear_allreduce(stream, px, lin, upload<uint16_t>("lin_x.bin"), nullptr, nullptr, y, m);
+            std::printf("tp fused: %d err %d\n", ran ? 1 : 0, *px.err);
+            download("out_lin_tp1.bin", y, (size_t)m * n);
+        }
         // ---- a refusal arrives as an exception that names the entry point ----
         {
             Nvfp4Linear lin(reinterpret_cast<const uint8_t*>(0x1000), reinterpret_cast<const uint8_t*>(0x1000), 1.f, 144, 128);

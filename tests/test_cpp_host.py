@@ -83,6 +83,8 @@ def test_cpp_host_layer_matches_the_oracle(tmp_path):
     y = out("out_lin.bin", np.uint16, (m, n))
     assert U.rel_err_floor(ref.bf16_to_f32(y), want) < 1e-4 + 1e-2
     assert np.array_equal(out("out_lin_m1.bin", np.uint16, (n,)), y[0])            # a row's bits do not depend on M
+    assert "tp fused: 1 err 0" in r.stdout
+    assert np.array_equal(out("out_lin_tp1.bin", np.uint16, (8, n)), y[:8])        # a world of one: the plain linear
     yr = out("out_lin_residual.bin", np.uint16, (m, n))
     assert U.rel_err_floor(ref.bf16_to_f32(yr), want + ref.bf16_to_f32(resid).astype(np.float64)) < 1e-4 + 1e-2
     xf = ref.bf16_to_f32(x)
