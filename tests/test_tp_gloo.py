@@ -370,3 +370,33 @@ def test_single_process_still_routes_large_m_to_the_prefill_gemm():
     assert sp.ffi.distributed_world() == 1
     assert [lin.route_for(m) for m in (1, 2, 64, 65)] == ["gemv", "decode", "decode", "prefill"]
     assert lin.route_for(65, allow_prefill=False) == "decode"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_random_shards_reconstruct_the_whole_product(world):
+    """shard_nvfp4 on random shapes, no process group needed: the column shards' oracle products are the
+    column blocks of the whole product bit for bit (same rows, same K order), and the row shards'
+    products -- each over its own K slice, scales re-laid for the slice -- add up to the whole in f64."""
+    import numpy as np
+    import torch
+    from oracle import ref
+    from speaches_plus_b200 import tp
+    rng = np.random.default_rng(world)
+    for _ in range(3):
+        n = 128 * world * int(rng.integers(1, 4))
+        k = 64 * world * int(rng.integers(1, 5))
+        w = ref.f32_to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        packed, sw, alpha = ref.quantize_weight_bf16(w)
+        x = ref.f32_to_bf16(rng.standard_normal((3, k)).astype(np.float32))
+        whole = ref.linear_w4a16_f64(packed, sw, x, alpha, n, k)
+        tp_, ts_ = torch.from_numpy(packed), torch.from_numpy(sw)
+        cols, acc = [], np.zeros_like(whole)
+        for r in range(world):
+            p_c, s_c, n_l, k_l, _ = tp.shard_nvfp4(tp_, ts_, n, k, "column", r, world)
+            assert (n_l, k_l) == (n // world, k)
+            cols.append(ref.linear_w4a16_f64(p_c.numpy(), s_c.numpy(), x, alpha, n_l, k))
+            p_r, s_r, n_l, k_l, off = tp.shard_nvfp4(tp_, ts_, n, k, "row", r, world)
+            assert (n_l, k_l) == (n, k // world) and off == r * (k // world)
+            acc += ref.linear_w4a16_f64(p_r.numpy(), s_r.numpy(), np.ascontiguousarray(x[:, off:off + k_l]), alpha, n, k_l)
+        assert np.array_equal(np.concatenate(cols, axis=1), whole)
+        assert np.allclose(acc, whole, rtol=1e-12, atol=1e-12)
