@@ -579,6 +579,8 @@ int nvk_b200_stack_run(void* stream, void* plan_dev, int n_ops, int M, int grid,
  *            indices outside them are never followed: such slots are skipped (offset) or read as
  *            zeros (row) and bit 0 / bit 1 of *status (one device int the caller zeroes; may be
  *            NULL) is set.
+ *   order:   a slot's result does not depend on the other slots or on how many experts are active:
+ *            whether K is split over a cluster is decided from one expert's N and K alone.
  * K % 32 == 0 (-1 otherwise), 16-byte aligned pointers (-2 otherwise). */
 int nvk_b200_moe_grouped_w4a16(void* stream, const uint8_t* wq_bank_a, const uint8_t* sc_bank_a,
                                const uint8_t* wq_bank_b, const uint8_t* sc_bank_b, const float* alphas_a,
