@@ -109,6 +109,7 @@ const uint32_t (*warp_publish(const uint32_t* words, int n_words))[8];
 
 // cp.async, completed at the matching wait_group (or at once when option cp_async_early is set)
 void cp_async(uint32_t dst_shared, const void* src, int bytes, int src_bytes);
+void note_fetch(const void* src, int bytes);   // weight-stream accounting, see emu_rt.cpp
 void cp_async_commit();
 void cp_async_wait(int allowed_pending);
 uint32_t shared_addr(const void* p);        // generic -> shared window address

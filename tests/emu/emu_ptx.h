@@ -127,7 +127,10 @@ inline int dp4a_s8(uint32_t a, uint32_t b, int c) {
     return c;
 }
 
-inline uint4 ldg_stream_v4(const void* p) { return *static_cast<const uint4*>(p); }
+inline uint4 ldg_stream_v4(const void* p) {
+    emu::note_fetch(p, 16);
+    return *static_cast<const uint4*>(p);
+}
 inline void st_release_sys(uint32_t* p, uint32_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
 inline uint32_t ld_acquire_sys(const uint32_t* p) {
     const uint32_t v = __atomic_load_n(p, __ATOMIC_ACQUIRE);

@@ -11,6 +11,7 @@
 #include <map>
 #include <mutex>
 #include <thread>
+#include <unordered_set>
 
 #include "cuda_emu.h"
 
@@ -105,6 +106,8 @@ struct Block {
     char sync_block[2] = {0, 0};
     char sync_start = 0, sync_end = 0;   // scheduler -> threads at block start, threads -> scheduler at its end
     char* sync_worker = nullptr;         // orders successive blocks on one arena (its shared memory, its stacks)
+    // 32-byte sectors of global memory this block fetched with cp.async or streaming loads (see note_fetch)
+    std::unordered_set<uintptr_t> fetched;
 };
 
 thread_local Block* g_block = nullptr;
@@ -128,6 +131,11 @@ namespace {
 // launch boundaries: what ran before a launch -> its threads (begin); its threads -> what comes next (end).
 // Two addresses, so that the blocks of ONE launch are not ordered with each other through them.
 char g_launch_begin = 0, g_launch_end = 0;
+
+// weight-stream accounting (note_fetch below)
+std::atomic<unsigned long long> g_fetch_sectors{0};
+std::atomic<int> g_fetch_on{0};
+
 
 inline void yield() {
     TSAN_SWITCH(g_block->tsan_sched);
@@ -266,6 +274,10 @@ void run_block(Block& b, Arena* arena) {
             idle_passes = 0;
         }
     }
+    if (!b.fetched.empty()) {
+        g_fetch_sectors.fetch_add(b.fetched.size(), std::memory_order_relaxed);
+        b.fetched.clear();
+    }
     TSAN_ACQUIRE(&b.sync_end);     // the threads are done: the worker may reuse or free what they used
     TSAN_RELEASE(b.sync_worker);
 #ifdef NVK_EMU_TSAN
@@ -389,7 +401,19 @@ static void do_copy(const Copy& c) {
     if (c.src_bytes < c.bytes) memset(d + c.src_bytes, 0, (size_t)(c.bytes - c.src_bytes));
 }
 
+// Weight-stream accounting: every global address range a block fetches with cp.async or a streaming load
+// is recorded as 32-byte sectors, once per block (a second fetch of a sector by the same block is what a
+// warp's coalescer or L1 would absorb); the sum over the blocks of a launch is the traffic its SMs ask
+// of L2 for those streams.  Equal to the algorithmic bytes when every byte is fetched by exactly one block.
+
+void note_fetch(const void* src, int bytes) {
+    if (!g_fetch_on.load(std::memory_order_relaxed) || bytes <= 0 || g_block == nullptr) return;
+    const uintptr_t a0 = (uintptr_t)src >> 5, a1 = ((uintptr_t)src + (uintptr_t)bytes - 1) >> 5;
+    for (uintptr_t a = a0; a <= a1; ++a) g_block->fetched.insert(a);
+}
+
 void cp_async(uint32_t dst, const void* src, int bytes, int src_bytes) {
+    note_fetch(src, src_bytes);
     if (src_bytes < 0 || src_bytes > bytes) die("cp.async: src-size larger than the copy");
     if ((dst & (uint32_t)(bytes - 1)) != 0) die("cp.async: misaligned shared destination");
     if (src_bytes > 0 && ((uintptr_t)src & (uintptr_t)(bytes - 1)) != 0) die("cp.async: misaligned global source");
@@ -617,6 +641,13 @@ void emu_free(void* p) { (void)cudaFree(p); }
 
 // Options: "cp_async_early" (0: copies land at the matching wait_group, the latest the ISA allows;
 // 1: at once), "sms" (what cudaDevAttrMultiProcessorCount reports), "threads" (host threads per launch).
+// Start (on != 0: counter to zero) or stop the weight-stream accounting; read the sectors counted so far.
+void emu_fetch_accounting(int on) {
+    if (on) emu::g_fetch_sectors.store(0);
+    emu::g_fetch_on.store(on ? 1 : 0);
+}
+unsigned long long emu_fetched_bytes(void) { return emu::g_fetch_sectors.load() * 32ull; }
+
 int emu_set_option(const char* name, int value) {
     if (!strcmp(name, "cp_async_early")) emu::g_opt.cp_async_early = value;
     else if (!strcmp(name, "sms")) emu::g_opt.sms = value;
