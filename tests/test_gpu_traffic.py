@@ -145,3 +145,30 @@ def test_fused_collective_epilogue_adds_no_weight_traffic():
                           epoch.data_ptr(), err.data_ptr()) == 0
         torch.cuda.synchronize()
     assert c.bytes == nvfp4_bytes(n, k) and int(err.cpu().numpy()[0]) == 0
+
+
+def test_w4a8_and_fp4_gemv_fetch_every_weight_byte_once():
+    U.require_gpu()
+    from tests.test_gpu_w4a8 import w4a8
+    rng = np.random.default_rng(8)
+    n, k, m = 384, 1024, 6
+    wa, wb = U.make_weight(rng, n, k)[:3], U.make_weight(rng, n, k)[:3]
+    q, sc = ref.rowquant_i8((rng.standard_normal((m, k)) * 1.5).astype(np.float32))
+    with counted() as c:
+        w4a8("nv_kernels_gemv_nvfp4_w4a8_dual_mk", wa, q, sc, m, n, k, second=wb)
+    assert c.bytes == 2 * nvfp4_bytes(n, k)
+    with counted() as c:
+        w4a8("nv_kernels_gemv_nvfp4_w4a8_down_residual_mk", wa, q, sc, m, n, k, residual=U.gauss_bf16(rng, (m, n)))
+    assert c.bytes == nvfp4_bytes(n, k)
+    # the M = 1 FP4 x FP4 GEMV: weights once; the activation row's 4-bit codes are not part of this count
+    x = U.dev(U.gauss_bf16(rng, (1, k)))
+    xp = torch.zeros(k // 2, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(k // 16, dtype=torch.uint8, device="cuda")
+    assert U.ffi.call("nv_kernels_nvfp4_quantize_row_bf16", U.stream(), x.data_ptr(), xp.data_ptr(), xs.data_ptr(), 1.0, k) == 0
+    y = torch.zeros(n, dtype=torch.int16, device="cuda")
+    dw, ds = U.dev(wa[0]), U.dev(wa[1])
+    with counted() as c:
+        assert U.ffi.call("nv_kernels_nvfp4_gemv_bf16", U.stream(), dw.data_ptr(), ds.data_ptr(), xp.data_ptr(), xs.data_ptr(),
+                          y.data_ptr(), float(wa[2]), n, k) == 0
+        torch.cuda.synchronize()
+    assert c.bytes == nvfp4_bytes(n, k)
