@@ -172,3 +172,41 @@ def test_w4a8_and_fp4_gemv_fetch_every_weight_byte_once():
                           y.data_ptr(), float(wa[2]), n, k) == 0
         torch.cuda.synchronize()
     assert c.bytes == nvfp4_bytes(n, k)
+
+
+@pytest.mark.parametrize("rows", [16, 128])
+def test_persistent_step_fetches_every_weight_byte_once(rows):
+    """A two-layer SwiGLU step as ONE persistent launch: the work items (128-row or 16-row slabs drawn from
+    per-operation counters) partition every matrix, so each weight byte still crosses once; with 16-row
+    items the two units of a scale-sector pair can sit in different CTAs, which asks for scale sectors up
+    to twice (an upper bound here: items are drawn dynamically)."""
+    U.require_gpu()
+    import speaches_plus_b200 as sp
+    rng = np.random.default_rng(33)
+    m, hidden, inter = 2, 512, 1024
+
+    def make(n, k):
+        packed, sw, alpha, _ = U.make_weight(rng, n, k, 0.05)
+        return sp.Nvfp4Linear.new_nvfp4(U.dev(packed), U.dev(sw), alpha, k, n)
+
+    layers = [(make(inter, hidden), make(inter, hidden), make(hidden, inter)) for _ in range(2)]
+    bf = dict(dtype=torch.bfloat16, device="cuda")
+    x = U.dev(U.gauss_bf16(rng, (m, hidden))).view(torch.bfloat16)
+    step = sp.DecodeStep(m, "cuda")
+    dep = -1
+    for (g, u, d) in layers:
+        yg, yu, yd = torch.zeros((m, inter), **bf), torch.zeros((m, inter), **bf), torch.zeros((m, hidden), **bf)
+        gu = step.add(g, x, yg, lin_b=u, y_b=yu, dep=dep, rows_per_item=rows)
+        dep = step.add(d, yg, yd, x2=yu, dep=gu, rows_per_item=rows)
+        x = yd
+    step.build()
+    with counted() as c:
+        step.run()
+        torch.cuda.synchronize()
+    step.check()
+    weights = 2 * (2 * inter * hidden // 2 + hidden * inter // 2)
+    scales = 2 * (2 * inter * hidden // 16 + hidden * inter // 16)
+    if rows == 128:
+        assert c.bytes == weights + scales
+    else:
+        assert weights + scales <= c.bytes <= weights + 2 * scales
