@@ -614,7 +614,7 @@ def test_row_chunk_invariance_is_bitwise():
     batch, whatever the batch size (1..64), and wherever it sits."""
     U.require_gpu()
     rng = np.random.default_rng(77)
-    n, k, m = (384, 1536, 64) if U.ffi.EMULATED else (1024, 5376, 64)   # the host emulation is given less to do
+    n, k, m = (384, 1536, 64) if getattr(U.ffi, "EMULATED", False) else (1024, 5376, 64)   # the host emulation is given less to do
     packed, sw, alpha, _ = U.make_weight(rng, n, k)
     x = U.gauss_bf16(rng, (m, k))
     full = run_linear(packed, sw, x, alpha, m, n, k)
