@@ -112,6 +112,7 @@ class NvkStackOp(C.Structure):
 
 
 _lib = None
+EMULATED = False   # set by the test harness when it points this binding at the host emulation
 _prefill_lib = None
 
 
