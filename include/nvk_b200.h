@@ -136,7 +136,8 @@ int nvk_b200_linear_nvfp4_w4a16_normed(void* stream, const uint8_t* wq_a, const 
  * peer_bufs: `world` device pointers to the ranks' exchange buffers as mapped here, each
  * nvk_b200_tp_fused_buffer_bytes(world, max_ctas, max_rows) bytes of plain device memory, zero before the
  * first call; epoch: max_ctas uint32 of local device memory, zero before the first call; err: one int
- * that becomes 1 + r if rank r never arrived.  All ranks make the same sequence of calls.
+ * that becomes 1 + r if rank r never arrived.  All ranks make the same sequence of calls with the same
+ * M, N and K (the K slices have equal length): CTAs are paired across the ranks by their index.
  * 1 <= M <= max_rows <= 64.  0 for an empty problem; -1 for M outside that range or K % 32 != 0; -2 for
  * null / misaligned operands, a rank outside the world or a row capacity outside [1, 64]; -3 when the
  * launch needs more than max_ctas CTAs. */

@@ -161,7 +161,9 @@ class PeerFusedLinear(PeerAllReduce):
     """Exchange buffers of the fused row-parallel linear + all-reduce
     (nvk_b200_tp_linear_nvfp4_w4a16_allreduce): the same plain-device-memory / CUDA IPC set-up as
     PeerAllReduce, sized for launches of up to `max_ctas` CTAs.  One object serves every row-parallel
-    linear of a step (calls on one stream are ordered); every rank makes the same sequence of calls."""
+    linear of a step (calls on one stream are ordered); every rank makes the same sequence of calls, with
+    K slices of equal length (the launch geometry, and with it the pairing of CTAs across the ranks, follows
+    from N and the slice's K)."""
 
     def __init__(self, group, device, max_ctas: int = 512, max_rows: int = 16):
         self.max_ctas, self.MAX_ROWS = int(max_ctas), int(max_rows)
@@ -342,7 +344,8 @@ class TpNvfp4Linear:
             xs = xs.contiguous()
         y = self._buf("yr", (m, self.n), x.device)
         fused = getattr(self, "peer_fused", None)
-        if fused is not None and fused.linear_(self.local, xs, y):
+        # the fused form needs the same launch geometry on every rank: equal K slices
+        if fused is not None and self.k % (64 * self.world) == 0 and fused.linear_(self.local, xs, y):
             return y          # the partials met inside the linear's own launch
         self.local.forward_into(xs, y, allow_prefill=False)
         if self.peer_ar is not None and y.numel() % 8 == 0 and y.numel() <= self.peer_ar.max_elems:
